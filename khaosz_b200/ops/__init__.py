@@ -1,0 +1,24 @@
+"""Hand-written sm_100a kernels and their PyTorch-facing wrappers."""
+
+from ._lib import KernelError, available, launch_count, raise_on_device_error
+from .functional import (
+    add_rms_norm,
+    cross_entropy,
+    cross_entropy_rows,
+    embedding,
+    gemm,
+    linear,
+    multi_linear,
+    rms_norm,
+    rope,
+    rope_table,
+    sdpa_reference,
+    swiglu,
+    token_logprobs,
+)
+
+__all__ = [
+    "KernelError", "available", "launch_count", "raise_on_device_error", "add_rms_norm", "cross_entropy",
+    "cross_entropy_rows", "embedding", "gemm", "linear", "multi_linear", "rms_norm", "rope", "rope_table",
+    "sdpa_reference", "swiglu", "token_logprobs",
+]

@@ -1,0 +1,326 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   C[M,N] = op(A) * op(B)^T (+ R)          bf16 in, fp32 accumulate in TMEM, bf16 out
+//
+// A is either K-major ([M,K] row-major) or MN-major ([K,M] row-major); likewise B
+// ([N,K] or [K,N]).  That covers the three products of a linear layer without any
+// transposed copy: forward (K,K), input gradient (K,MN) and weight gradient (MN,MN).
+//
+// Structure: persistent kernel, one CTA per SM, 128x256 output tile, BK=64.
+//   warp 0      TMA producer: 4-stage ring of 128B-swizzled A/B tiles (cp.async.bulk.tensor,
+//               no cluster multicast), completion on "full" mbarriers
+//   warp 1      allocates 512 TMEM columns (two 128x256 fp32 accumulators) and issues
+//               tcgen05.mma from one thread; tcgen05.commit releases stages / publishes
+//               the accumulator
+//   warps 2-5   epilogue: tcgen05.ld -> (+residual) -> bf16 -> swizzled staging tile ->
+//               TMA store, overlapped with the next tile's main loop through the second
+//               accumulator
+// All waits are bounded (see common.cuh).
+#include "common.cuh"
+#include "kb_api.h"
+
+namespace kb {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int ATOM_BYTES = BK * 128;        // one 64-wide MN atom of an MN-major tile
+constexpr int EPI_COLS = 64;
+constexpr int EPI_BUF_BYTES = BM * EPI_COLS * 2;  // 16 KiB
+constexpr int NUM_EPI_BUFS = 2;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES =
+    STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + NUM_EPI_BUFS * EPI_BUF_BYTES + 256 + 1024;
+
+struct Params {
+  const __nv_bfloat16* R;  // optional addend [M,N]
+  long ldr;
+  int M, N, K;
+  int a_mn, b_mn;
+  int epi;  // 0: none, 1: += R
+  int* err;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+  const int group_size = GROUP_M * num_n;
+  const int g = t / group_size;
+  const int first_m = g * GROUP_M;
+  const int gm = min(num_m - first_m, GROUP_M);
+  const int r = t - g * group_size;
+  m_blk = first_m + r % gm;
+  n_blk = r / gm;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_c, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint8_t* sEpi = sB + STAGES * B_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + NUM_EPI_BUFS * EPI_BUF_BYTES);
+  uint64_t* full = bars;                  // [STAGES]
+  uint64_t* empty = bars + STAGES;        // [STAGES]
+  uint64_t* tfull = bars + 2 * STAGES;    // [2]
+  uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_k = (p.K + BK - 1) / BK;
+  const int total = num_m * num_n;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_c);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        const int m0 = m_blk * BM, n0 = n_blk * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[s], A_STAGE_BYTES + B_STAGE_BYTES);
+          uint8_t* a_dst = sA + s * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + s * B_STAGE_BYTES;
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_2d(a_dst, &tmap_a, &full[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int a = 0; a < BM / 64; ++a)
+              tma_load_2d(a_dst + a * ATOM_BYTES, &tmap_a, &full[s], m0 + a * 64, k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(b_dst, &tmap_b, &full[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int a = 0; a < BN / 64; ++a)
+              tma_load_2d(b_dst + a * ATOM_BYTES, &tmap_b, &full[s], n0 + a * 64, k0);
+          }
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(BM, BN, p.a_mn != 0, p.b_mn != 0);
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t aph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], aph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(&full[s], ph, abort_flag, p.err, KB_ERR_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j) {
+            const uint64_t a_desc = p.a_mn ? umma_desc_mnmajor(a_addr, j * UMMA_K, ATOM_BYTES)
+                                           : umma_desc_kmajor(a_addr, j * UMMA_K * 2);
+            const uint64_t b_desc = p.b_mn ? umma_desc_mnmajor(b_addr, j * UMMA_K, ATOM_BYTES)
+                                           : umma_desc_kmajor(b_addr, j * UMMA_K * 2);
+            umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          aph ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue -------------------------------
+    const int q = warp & 3;               // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;  // 0..127
+    int acc = 0;
+    uint32_t aph = 0;
+    int buf = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      const int m0 = m_blk * BM, n0 = n_blk * BN;
+      if (!mbar_wait(&tfull[acc], aph, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const int grow = m0 + row_in_tile;
+#pragma unroll 1
+      for (int c = 0; c < BN / EPI_COLS; ++c) {
+        const int col0 = n0 + c * EPI_COLS;
+        if (col0 >= p.N) break;  // uniform across the CTA
+        uint32_t v[EPI_COLS];
+        tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
+        tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
+        tmem_ld_wait();
+        // staging buffer `buf` must have been drained by the TMA store issued 2 chunks ago
+        if (epi_tid == 0) tma_store_wait_read<NUM_EPI_BUFS - 1>();
+        named_barrier_sync(1, 128);
+        uint8_t* stage = sEpi + buf * EPI_BUF_BYTES;
+        const bool row_ok = grow < p.M;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[ch * 8 + e]);
+          if (p.epi == 1 && row_ok && (col0 + ch * 8) < p.N) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(p.R + (size_t)grow * p.ldr + col0 + ch * 8);
+            const float2 r0 = unpack_bf16x2(rv.x), r1 = unpack_bf16x2(rv.y),
+                         r2 = unpack_bf16x2(rv.z), r3 = unpack_bf16x2(rv.w);
+            f[0] += r0.x; f[1] += r0.y; f[2] += r1.x; f[3] += r1.y;
+            f[4] += r2.x; f[5] += r2.y; f[6] += r3.x; f[7] += r3.y;
+          }
+          uint4 o;
+          o.x = pack_bf16x2(f[0], f[1]);
+          o.y = pack_bf16x2(f[2], f[3]);
+          o.z = pack_bf16x2(f[4], f[5]);
+          o.w = pack_bf16x2(f[6], f[7]);
+          *reinterpret_cast<uint4*>(stage + sw128_offset(row_in_tile, ch)) = o;
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(1, 128);
+        if (epi_tid == 0) {
+          tma_store_2d(&tmap_c, stage, col0, m0);
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+      // accumulator fully read: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        aph ^= 1u;
+      }
+    }
+    if (epi_tid == 0) tma_store_wait_all<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace gemm
+}  // namespace kb
+
+extern "C" int kb_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N,
+                            int K, long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn,
+                            int epi, void* stream) {
+  using namespace kb::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return KB_STATUS_BAD_ARG;
+  auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+  if (misaligned(A) || misaligned(B) || misaligned(C) || (lda & 7) || (ldb & 7) || (ldc & 7))
+    return KB_STATUS_BAD_ARG;
+  if (epi == 1 && (R == nullptr || misaligned(R) || (ldr & 7) || (N & 7))) return KB_STATUS_BAD_ARG;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return KB_STATUS_CUDA_ERROR;
+    attr_set = true;
+  }
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static int sm_count[64] = {0};
+  if (sm_count[dev] == 0) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+
+  CUtensorMap ta, tb, tc;
+  int rc;
+  if (!a_mn) rc = kb::make_tmap_2d(&ta, A, 2, M, K, lda * 2, BM, BK, true);
+  else       rc = kb::make_tmap_2d(&ta, A, 2, K, M, lda * 2, BK, 64, true);
+  if (rc) return KB_STATUS_TMAP_ERROR;
+  if (!b_mn) rc = kb::make_tmap_2d(&tb, B, 2, N, K, ldb * 2, BN, BK, true);
+  else       rc = kb::make_tmap_2d(&tb, B, 2, K, N, ldb * 2, BK, 64, true);
+  if (rc) return KB_STATUS_TMAP_ERROR;
+  rc = kb::make_tmap_2d(&tc, C, 2, M, N, ldc * 2, BM, EPI_COLS, true);
+  if (rc) return KB_STATUS_TMAP_ERROR;
+
+  Params p;
+  p.R = static_cast<const __nv_bfloat16*>(R);
+  p.ldr = ldr;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.epi = epi;
+  p.err = kb::error_word(dev);
+
+  const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
+  const int total = num_m * num_n;
+  const int grid = total < sm_count[dev] ? total : sm_count[dev];
+  gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ta, tb, tc, p);
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}

@@ -1,0 +1,101 @@
+// C ABI of the khaosz_b200 kernel library (libkhaosz_b200_kernels.so).
+// Every entry point takes raw device pointers and a CUDA stream handle, launches
+// asynchronously on that stream and returns a KB_STATUS_* code.  Unless a comment says
+// otherwise no entry point allocates device memory after the first call on a device
+// (the first call sets up a 64-byte error word).
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  KB_STATUS_OK = 0,
+  KB_STATUS_BAD_ARG = 1,
+  KB_STATUS_CUDA_ERROR = 2,
+  KB_STATUS_TMAP_ERROR = 3,
+  KB_STATUS_TOO_LARGE = 4,
+};
+
+// ---- runtime ------------------------------------------------------------------------
+int kb_last_error(void);  // device-side status of bounded waits since the last call (0 = ok)
+int kb_sm_count(void);
+int kb_last_tmap_error(void);  // CUresult of the last failed tensor-map encode
+const char* kb_version(void);
+
+// ---- GEMM ---------------------------------------------------------------------------
+// C[M,N] = op(A) op(B)^T (+R).  a_mn=0: A is [M,K] row-major (pitch lda); a_mn=1: A is stored
+// [K,M] row-major.  b_mn=0: B is [N,K]; b_mn=1: B is stored [K,N].  epi: 0 none, 1 add R.
+int kb_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                 long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn, int epi, void* stream);
+
+// ---- normalisation ------------------------------------------------------------------
+// y = rmsnorm(x (+ res)) * w ; when res != NULL the sum x+res is also written to sum_out.
+int kb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out,
+                   float* rstd, int rows, int dim, float eps, void* stream);
+// dx = d rmsnorm (+ dres_in); dw_partial is scratch [n_partial_rows, dim] fp32 provided by the
+// caller (n_partial_rows = kb_rmsnorm_bwd_partials(rows)); dw (fp32 [dim]) is overwritten.
+int kb_rmsnorm_bwd_partials(int rows);
+int kb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                   const void* dres_in, void* dx, float* dw, float* dw_partial, int rows, int dim,
+                   void* stream);
+
+// ---- rotary embedding ---------------------------------------------------------------
+// In-place capable. x: [tokens, row_stride] bf16, rotates heads [0, n_heads) of width head_dim
+// as interleaved (even, odd) pairs. cs: [max_pos, head_dim/2, 2] fp32 (cos, sin).
+// pos: int32 [tokens] or NULL (position = token index % seq_len). inverse=1 applies the
+// transpose rotation (backward pass).
+int kb_rope(const void* x, void* y, const float* cs, const int* pos, int tokens, int seq_len,
+            int n_heads, int head_dim, long row_stride, int inverse, void* stream);
+
+// ---- SwiGLU -------------------------------------------------------------------------
+// gu: [rows, 2*F] (gate = [:, :F], up = [:, F:]); h = up * silu(gate)
+int kb_swiglu_fwd(const void* gu, void* h, int rows, int F, void* stream);
+int kb_swiglu_bwd(const void* gu, const void* dh, void* dgu, int rows, int F, void* stream);
+
+// ---- cross entropy ------------------------------------------------------------------
+// logits [rows, V] bf16 (pitch ld), targets int64. Per-row outputs: loss (label-smoothed NLL,
+// 0 for ignored rows), lse, and logp (log-prob of the target, 0 for ignored rows).
+int kb_ce_fwd(const void* logits, const long long* targets, float* loss, float* lse, float* logp,
+              int rows, int V, long ld, float smoothing, long long ignore_index, void* stream);
+// dlogits = gscale[row-independent scalar on device] * dloss_row * d loss / d logits, written
+// to `dlogits` (may alias logits). row_grad: fp32 [rows] upstream gradient per row.
+// mode 0: gradient of the label-smoothed loss; mode 1: gradient of logp.
+int kb_ce_bwd(const void* logits, const long long* targets, const float* lse,
+              const float* row_grad, void* dlogits, int rows, int V, long ld, float smoothing,
+              long long ignore_index, int mode, void* stream);
+
+// ---- embedding ----------------------------------------------------------------------
+int kb_embedding_fwd(const void* table, const long long* ids, void* out, int tokens, int dim,
+                     int vocab, void* stream);
+// dtable (fp32 [vocab, dim]) += scatter of dy; caller zero-fills.
+int kb_embedding_bwd(const void* dy, const long long* ids, float* dtable, int tokens, int dim,
+                     int vocab, void* stream);
+
+// ---- optimiser ----------------------------------------------------------------------
+// sum of squares of a bf16 buffer, accumulated into *out (fp32, caller zero-fills)
+int kb_sumsq_bf16(const void* g, long long n, float* out, void* stream);
+// AdamW over a flat bf16 parameter / gradient buffer with fp32 moments.
+// grad_scale multiplies gradients first; if gnorm_sq != NULL and max_norm > 0 the clip factor
+// min(1, max_norm / (sqrt(*gnorm_sq) * grad_scale + 1e-6)) is applied too (no host sync).
+// lr and step are read from device memory (lr_step[0] = lr, lr_step[1] = bias-correction step).
+int kb_adamw_bf16(void* p, const void* g, float* m, float* v, long long n, const float* lr_step,
+                  float beta1, float beta2, float eps, float weight_decay, float grad_scale,
+                  const float* gnorm_sq, float max_norm, void* stream);
+
+// ---- attention ----------------------------------------------------------------------
+// Causal / full flash attention, q [B,S,H,D], k/v [B,S,Hkv,D] given as row pitches (elements)
+// inside packed buffers; D must be 128. lse: fp32 [B,H,S].
+int kb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S,
+                 int H, int Hkv, int D, long q_pitch, long k_pitch, long v_pitch, long o_pitch,
+                 float scale, int causal, void* stream);
+int kb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                 const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int H,
+                 int Hkv, int D, long q_pitch, long k_pitch, long v_pitch, long o_pitch,
+                 long do_pitch, long dq_pitch, long dk_pitch, long dv_pitch, float scale,
+                 int causal, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

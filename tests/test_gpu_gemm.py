@@ -1,0 +1,99 @@
+"""tcgen05 GEMM vs an fp32 PyTorch product, all operand layouts and ragged shapes."""
+import pytest
+import torch
+
+from khaosz_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn, res=None):
+    am = a.float().t() if a_mn else a.float()
+    bm = b.float() if b_mn else b.float().t()
+    out = am @ bm
+    if res is not None:
+        out = out + res.float()
+    return out
+
+
+def _check(M, N, K, a_mn, b_mn, with_res=False):
+    dev = "cuda"
+    a = torch.randn((K, M) if a_mn else (M, K), device=dev, dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=dev, dtype=torch.bfloat16)
+    res = torch.randn((M, N), device=dev, dtype=torch.bfloat16) if with_res else None
+    out = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, residual=res)
+    torch.cuda.synchronize()
+    ops.raise_on_device_error()
+    ref = _ref(a, b, a_mn, b_mn, res)
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 2e-2 * scale + 1e-2, f"max err {err} (scale {scale}) for {(M, N, K, a_mn, b_mn)}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (1024, 2048, 512)])
+def test_gemm_layouts(shape, a_mn, b_mn):
+    _check(*shape, a_mn, b_mn)
+
+
+@pytest.mark.parametrize("shape", [(200, 264, 72), (8, 2048, 2048), (136, 32000, 128), (4096, 96, 520)])
+def test_gemm_ragged(shape):
+    _check(*shape, False, False)
+    _check(*shape, False, True)
+    _check(*shape, True, True)
+
+
+def test_gemm_residual_and_accumulate():
+    _check(512, 1024, 256, False, False, with_res=True)
+    a = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(256, 384, device="cuda", dtype=torch.bfloat16)
+    acc = torch.randn(512, 384, device="cuda", dtype=torch.bfloat16)
+    ref = a.float().t() @ b.float() + acc.float()
+    ops.gemm(a, b, a_mn=True, b_mn=True, out=acc, residual=acc)
+    assert (acc.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+def test_gemm_many_tiles_persistent():
+    # more tiles than SMs: exercises the stage/accumulator phase wrap-around
+    _check(2048, 4096, 320, False, False)
+
+
+def test_linear_autograd_matches_fp32():
+    x = torch.randn(4, 96, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = ops.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf = x.detach().float().requires_grad_()
+    wf = w.detach().float().requires_grad_()
+    yf = torch.nn.functional.linear(xf, wf)
+    yf.backward(g.float())
+    for got, ref in ((y, yf), (x.grad, xf.grad), (w.grad, wf.grad)):
+        assert (got.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+def test_gemm_throughput_report():
+    """Not an assertion on speed: prints achieved TFLOP/s for the 1B-model shapes."""
+    shapes = [(8192, 3072, 2048), (8192, 2048, 2048), (8192, 11264, 2048), (8192, 2048, 5632), (8192, 32000, 2048)]
+    for (M, N, K) in shapes:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for _ in range(3):
+            ops.gemm(a, b, out=out)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            ops.gemm(a, b, out=out)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 10
+        e0.record()
+        for _ in range(10):
+            torch.matmul(a, b.t(), out=out)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_ref = e0.elapsed_time(e1) / 10
+        print(f"GEMM {M}x{N}x{K}: {2 * M * N * K / ms / 1e9:.0f} TFLOP/s (cuBLAS {2 * M * N * K / ms_ref / 1e9:.0f})")
+    ops.raise_on_device_error()

@@ -1,0 +1,126 @@
+"""Bandwidth-bound kernels vs plain fp32 PyTorch references."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from khaosz_b200 import ops
+from khaosz_b200.ops import functional as KF
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(got, ref, rtol=2e-2, atol=2e-2):
+    err = (got.float() - ref.float()).abs().max().item()
+    lim = rtol * ref.float().abs().max().item() + atol
+    assert err <= lim, f"max err {err} > {lim}"
+
+
+@pytest.mark.parametrize("rows,dim", [(64, 2048), (1000, 512), (7, 128), (33, 4096)])
+def test_rmsnorm_fwd_bwd(rows, dim):
+    x = torch.randn(rows, dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(dim, device="cuda")).to(torch.bfloat16).requires_grad_()
+    y = ops.rms_norm(x, w, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yf = F.rms_norm(xf, (dim,), wf, 1e-5)
+    yf.backward(g.float())
+    _close(y, yf)
+    _close(x.grad, xf.grad)
+    _close(w.grad, wf.grad, rtol=3e-2, atol=0.3)
+
+
+def test_add_rmsnorm_fwd_bwd():
+    rows, dim = 300, 2048
+    x = torch.randn(rows, dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(rows, dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.ones(dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y, s = ops.add_rms_norm(x, r, w, 1e-5)
+    g1, g2 = torch.randn_like(y), torch.randn_like(s)
+    (y * g1 + s * g2).sum().backward()
+    xf, rf, wf = (t.detach().float().requires_grad_() for t in (x, r, w))
+    sf = xf + rf
+    yf = F.rms_norm(sf, (dim,), wf, 1e-5)
+    (yf * g1.float() + sf * g2.float()).sum().backward()
+    _close(y, yf)
+    _close(s, sf)
+    _close(x.grad, xf.grad, atol=5e-2)
+    _close(r.grad, rf.grad, atol=5e-2)
+
+
+def test_rope_matches_complex_rotation():
+    B, S, H, D = 2, 64, 6, 128
+    x = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    cs = ops.rope_table(D, 256, 10000.0, device="cuda")
+    y = ops.rope(x, cs)
+    freqs = torch.view_as_complex(cs[:S].contiguous())  # cos + i sin
+    xc = torch.view_as_complex(x.detach().float().reshape(B, S, H, D // 2, 2))
+    ref = torch.view_as_real(xc * freqs[None, :, None, :]).reshape(B, S, H, D)
+    _close(y, ref)
+    g = torch.randn_like(y)
+    y.backward(g)
+    gc = torch.view_as_complex(g.float().reshape(B, S, H, D // 2, 2))
+    gref = torch.view_as_real(gc * freqs.conj()[None, :, None, :]).reshape(B, S, H, D)
+    _close(x.grad, gref)
+    # explicit positions and partial-head rotation
+    pos = torch.randint(0, 256, (B, S), device="cuda")
+    y2 = ops.rope(x.detach(), cs, pos, n_heads=4)
+    ref2 = KF._rope_torch(x.detach().float()[:, :, :4], cs, pos)
+    _close(y2[:, :, :4], ref2)
+    assert torch.equal(y2[:, :, 4:], x.detach()[:, :, 4:])
+
+
+def test_swiglu_fwd_bwd():
+    gu = torch.randn(257, 2 * 1408, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    h = ops.swiglu(gu)
+    g = torch.randn_like(h)
+    h.backward(g)
+    guf = gu.detach().float().requires_grad_()
+    hf = guf[:, 1408:] * F.silu(guf[:, :1408])
+    hf.backward(g.float())
+    _close(h, hf)
+    _close(gu.grad, guf.grad)
+
+
+@pytest.mark.parametrize("V,smoothing", [(32000, 0.0), (32000, 0.1), (1000, 0.05), (1003, 0.0)])
+def test_cross_entropy_fwd_bwd(V, smoothing):
+    rows = 96
+    ld = (V + 7) // 8 * 8
+    buf = torch.randn(rows, ld, device="cuda", dtype=torch.bfloat16) * 3
+    logits = buf[:, :V].detach().requires_grad_()
+    t = torch.randint(0, V, (rows,), device="cuda")
+    t[::7] = -100
+    ref_in = logits.detach().float().requires_grad_()
+    ref = F.cross_entropy(ref_in, t, label_smoothing=smoothing, ignore_index=-100)
+    ref.backward()
+    loss = ops.cross_entropy(logits, t, smoothing, -100)
+    loss.backward()
+    assert abs(loss.item() - ref.item()) <= 2e-3 * abs(ref.item()) + 1e-3
+    _close(logits.grad, ref_in.grad, rtol=2e-2, atol=1e-5)
+
+
+def test_token_logprobs_fwd_bwd():
+    B, S, V = 3, 17, 4096
+    logits = (torch.randn(B, S, V, device="cuda", dtype=torch.bfloat16) * 2).requires_grad_()
+    t = torch.randint(0, V, (B, S), device="cuda")
+    ref_in = logits.detach().float().requires_grad_()
+    ref = torch.log_softmax(ref_in, -1).gather(-1, t[..., None]).squeeze(-1)
+    w = torch.randn(B, S, device="cuda")
+    (ref * w).sum().backward()
+    lp = ops.token_logprobs(logits, t)
+    (lp * w).sum().backward()
+    _close(lp, ref, rtol=1e-3, atol=2e-3)
+    _close(logits.grad, ref_in.grad, rtol=2e-2, atol=1e-4)
+
+
+def test_embedding_fwd_bwd():
+    V, D = 1000, 256
+    table = torch.randn(V, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, V, (4, 64), device="cuda")
+    out = ops.embedding(ids, table)
+    assert torch.equal(out, table.detach()[ids])
+    g = torch.randn_like(out)
+    out.backward(g)
+    tf = table.detach().float().requires_grad_()
+    F.embedding(ids, tf).backward(g.float())
+    _close(table.grad, tf.grad)
