@@ -1,0 +1,141 @@
+"""Attention ops.
+
+* :func:`rope_attention_packed` — training / prefill path: RoPE applied in place on the packed
+  ``[B,S,H+2Hkv,D]`` projection buffer, then causal flash attention (tcgen05 kernels for
+  ``D == 128``) reading q/k/v straight out of that buffer; the backward writes one packed
+  gradient buffer and un-rotates it in place.
+* :func:`attention` — generic path for every other configuration (fp32, CPU, masks, other
+  head sizes): fp32 softmax attention with GQA broadcast, also the oracle of the tests.
+
+Replaces ``repeat_kv`` + permutes + ``F.scaled_dot_product_attention`` of the reference
+(``astrai/model/components/attention.py:95-103``).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from ._lib import check, lib, ptr, stream
+from .functional import _rope_kernel, _rope_torch, sdpa_reference
+
+FLASH_HEAD_DIM = 128
+
+
+def flash_available() -> bool:
+    return _lib.available() and _lib.has("kb_flash_fwd")
+
+
+def fused_ok(qkv: torch.Tensor, head_dim: int) -> bool:
+    return qkv.is_cuda and qkv.dtype == torch.bfloat16 and head_dim == FLASH_HEAD_DIM and qkv.is_contiguous()
+
+
+def _flash_fwd(q, k, v, causal, scale):
+    """q [B,S,H,D], k/v [B,S,Hkv,D] views with unit inner stride and a common row pitch."""
+    B, S, H, D = q.shape
+    Hkv = k.shape[2]
+    o = torch.empty((B, S, H, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    check(lib().kb_flash_fwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), B, S, H, Hkv, D, q.stride(1), k.stride(1),
+                             v.stride(1), o.stride(1), float(scale), int(causal), stream()), "flash_fwd")
+    return o, lse
+
+
+def _flash_bwd(q, k, v, o, do, lse, dq, dk, dv, causal, scale):
+    B, S, H, D = q.shape
+    Hkv = k.shape[2]
+    delta = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    check(lib().kb_flash_bwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(do), ptr(lse), ptr(delta), ptr(dq), ptr(dk), ptr(dv),
+                             B, S, H, Hkv, D, q.stride(1), k.stride(1), v.stride(1), o.stride(1), do.stride(1),
+                             dq.stride(1), dk.stride(1), dv.stride(1), float(scale), int(causal), stream()),
+          "flash_bwd")
+    _lib.add_launches(2)
+
+
+class _RopeAttnPackedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cs, pos, H, Hkv, causal):
+        B, S, _, D = qkv.shape
+        scale = 1.0 / math.sqrt(D)
+        _rope_kernel(qkv, cs, pos, H + Hkv, False)  # in place: qkv is a fresh GEMM output
+        ctx.mark_dirty(qkv)
+        q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+        o, lse = _flash_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(qkv, o, lse)
+        ctx.meta = (cs, pos, H, Hkv, causal, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, o, lse = ctx.saved_tensors
+        cs, pos, H, Hkv, causal, scale = ctx.meta
+        do = do.contiguous()
+        dqkv = torch.empty_like(qkv)
+        q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+        dq, dk, dv = dqkv[:, :, :H], dqkv[:, :, H:H + Hkv], dqkv[:, :, H + Hkv:]
+        _flash_bwd(q, k, v, o, do, lse, dq, dk, dv, causal, scale)
+        _rope_kernel(dqkv, cs, pos, H + Hkv, True)
+        return dqkv, None, None, None, None, None
+
+
+def rope_attention_packed(qkv: torch.Tensor, cs: torch.Tensor, pos: Optional[torch.Tensor], H: int, Hkv: int,
+                          causal: bool = True) -> torch.Tensor:
+    """RoPE + attention on a packed projection buffer ``[B,S,H+2Hkv,D]`` -> ``[B,S,H,D]``."""
+    if flash_available():
+        return _RopeAttnPackedFn.apply(qkv, cs, pos, H, Hkv, causal)
+    from .functional import rope
+
+    qk = rope(qkv[:, :, :H + Hkv], cs, pos)
+    return attention(qk[:, :, :H], qk[:, :, H:], qkv[:, :, H + Hkv:], causal=causal)
+
+
+class _FlashFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = _flash_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.meta = (causal, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        causal, scale = ctx.meta
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _flash_bwd(q, k, v, o, do.contiguous(), lse, dq, dk, dv, causal, scale)
+        return dq, dk, dv, None, None
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True,
+              mask: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
+    """Softmax attention on ``[B,S,H,D]`` / ``[B,T,Hkv,D]`` tensors.
+
+    ``mask`` is an additive ``[B,1,S,T]`` (or broadcastable) tensor; with a mask ``causal`` is
+    ignored exactly like the reference does.
+    """
+    B, S, H, D = q.shape
+    T, Hkv = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if (mask is None and S == T and q.is_cuda and q.dtype == torch.bfloat16 and D == FLASH_HEAD_DIM
+            and v.shape[-1] == D and flash_available()):
+        return _FlashFn.apply(q, k, v, bool(causal), scale)
+    qh, kh, vh = q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3)
+    if Hkv != H and kh.shape[1] != 1:
+        rep = H // Hkv
+        kh, vh = kh.repeat_interleave(rep, dim=1), vh.repeat_interleave(rep, dim=1)
+    if mask is not None:
+        out = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask.to(qh.dtype), scale=scale)
+    elif causal and S != T:
+        cm = torch.ones(S, T, dtype=torch.bool, device=q.device).tril(T - S)
+        out = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=cm, scale=scale)
+    else:
+        out = F.scaled_dot_product_attention(qh, kh, vh, is_causal=bool(causal), scale=scale)
+    return out.permute(0, 2, 1, 3)
+
+
+__all__ = ["attention", "rope_attention_packed", "fused_ok", "flash_available", "sdpa_reference", "_rope_torch"]

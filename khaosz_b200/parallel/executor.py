@@ -1,0 +1,350 @@
+"""Execution strategies behind the trainer: ``none``, ``ddp``, ``fsdp`` and ``tp``.
+
+The contract is the reference's (``astrai/parallel/executor.py:82-137``)::
+
+    model, optimizer, dataloader, scheduler = executor.prepare(model, optimizer, dataloader, scheduler)
+    with executor.accumulate(model):
+        loss = ...; executor.backward(loss / executor.grad_accum_steps)
+        if executor.sync_gradients: optimizer.step(); optimizer.zero_grad(); scheduler.step()
+    full_state_dict = executor.unwrap_model(model)
+
+but the machinery is rebuilt: instead of wrapping the model in torch DDP / FSDP, an executor
+owns *flat* parameter and gradient buffers (``khaosz_b200.utils.FlatParameters``).  Weight
+gradients are accumulated into the flat gradient buffer by the GEMM epilogues, the gradient
+collective runs once per optimizer step over that buffer (hand-written NVLink kernels on
+CUDA, ``torch.distributed`` on CPU/gloo), and a ``FusedAdamW`` optimizer updates the whole
+model in one launch.  ``ddp`` replicates parameters; ``fsdp`` shards gradients, optimizer
+state and the update (each rank owns a contiguous slice, updated parameters are
+all-gathered); ``tp`` is described in ``khaosz_b200.parallel.tensor_parallel``.
+"""
+
+from __future__ import annotations
+
+import contextlib
+import logging
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..factory import BaseFactory
+from ..utils.flat_params import FlatParameters
+from .setup import get_rank, get_world_size
+
+log = logging.getLogger(__name__)
+
+
+class GradientState:
+    """Counts micro-steps globally; gradients are synchronised every ``num_steps``-th one."""
+
+    def __init__(self, grad_accum_steps: int = 1):
+        self.num_steps = max(int(grad_accum_steps), 1)
+        self._step = 0
+        self._sync_gradients = True
+
+    @property
+    def sync_gradients(self) -> bool:
+        return self._sync_gradients
+
+    def _do_sync(self) -> None:
+        self._step += 1
+        self._sync_gradients = self._step % self.num_steps == 0
+
+
+class AccumOptimizer:
+    """Optimizer facade that only acts on synchronisation steps.  ``zero_grad`` keeps
+    ``param.grad`` aliased to the flat gradient buffer when the executor owns one."""
+
+    def __init__(self, optimizer, gradient_state: GradientState, flat: Optional[FlatParameters] = None,
+                 after_step=None):
+        self.optimizer = optimizer
+        self.gradient_state = gradient_state
+        self.flat = flat
+        self._after_step = after_step
+
+    def step(self, closure=None):
+        if self.gradient_state.sync_gradients:
+            self.optimizer.step(closure) if closure is not None else self.optimizer.step()
+            if self._after_step is not None:
+                self._after_step()
+
+    def zero_grad(self, *args, **kwargs):
+        if not self.gradient_state.sync_gradients:
+            return
+        if self.flat is not None and self.flat.grad is not None:
+            self.flat.zero_grad()
+        else:
+            self.optimizer.zero_grad(*args, **kwargs)
+
+    @property
+    def param_groups(self):
+        return self.optimizer.param_groups
+
+    def state_dict(self):
+        return self.optimizer.state_dict()
+
+    def load_state_dict(self, state):
+        self.optimizer.load_state_dict(state)
+
+    def __getattr__(self, name):  # fused_clip, flat hooks, ...
+        return getattr(self.optimizer, name)
+
+
+class AccumScheduler:
+    def __init__(self, scheduler, gradient_state: GradientState):
+        self.scheduler = scheduler
+        self.gradient_state = gradient_state
+
+    def step(self):
+        if self.gradient_state.sync_gradients:
+            self.scheduler.step()
+
+    def state_dict(self):
+        return self.scheduler.state_dict()
+
+    def load_state_dict(self, state):
+        self.scheduler.load_state_dict(state)
+
+    def get_last_lr(self):
+        return self.scheduler.get_last_lr()
+
+
+def _wants_flat(model: nn.Module) -> bool:
+    params = list(model.parameters())
+    return bool(params) and all(p.is_cuda and p.dtype == torch.bfloat16 for p in params)
+
+
+class BaseExecutor:
+    flatten_on_cuda = True
+
+    def __init__(self, grad_accum_steps: int = 1):
+        self.gradient_state = GradientState(grad_accum_steps)
+        self.flat: Optional[FlatParameters] = None
+
+    # -- preparation ------------------------------------------------------------------------
+    def prepare(self, model: nn.Module, optimizer=None, dataloader=None, scheduler=None) -> Tuple[Any, Any, Any, Any]:
+        model = self._prepare_model(model)
+        if optimizer is not None:
+            if self.flat is not None and hasattr(optimizer, "attach_flat"):
+                optimizer.attach_flat(self.flat)
+            optimizer = AccumOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step)
+        if scheduler is not None:
+            scheduler = AccumScheduler(scheduler, self.gradient_state)
+        return model, optimizer, dataloader, scheduler
+
+    def _prepare_model(self, model: nn.Module) -> nn.Module:
+        if self.flatten_on_cuda and _wants_flat(model):
+            self.flat = FlatParameters(model, with_grad=True)
+        return model
+
+    def _after_optimizer_step(self) -> None:
+        """Hook for sharded executors (parameter all-gather)."""
+
+    # -- the loop ---------------------------------------------------------------------------
+    def _no_sync(self, model: nn.Module):
+        return contextlib.nullcontext()
+
+    @contextlib.contextmanager
+    def accumulate(self, model: nn.Module):
+        self.gradient_state._do_sync()
+        ctx = contextlib.nullcontext() if self.gradient_state.sync_gradients else self._no_sync(model)
+        with ctx:
+            yield
+
+    def backward(self, loss: torch.Tensor) -> None:
+        loss.backward()
+        if self.gradient_state.sync_gradients:
+            self._sync_gradients()
+
+    def _sync_gradients(self) -> None:
+        """Cross-rank gradient reduction on synchronisation steps."""
+
+    def unwrap_model(self, model: nn.Module) -> Dict[str, torch.Tensor]:
+        return model.state_dict()
+
+    def grad_norm_sq_extra(self) -> Optional[torch.Tensor]:
+        """Sharded executors return a device scalar with the *global* squared gradient norm."""
+        return None
+
+    @property
+    def use_distributed(self) -> bool:
+        return get_world_size() > 1
+
+    @property
+    def sync_gradients(self) -> bool:
+        return self.gradient_state.sync_gradients
+
+    @property
+    def grad_accum_steps(self) -> int:
+        return self.gradient_state.num_steps
+
+
+class ExecutorFactory(BaseFactory[BaseExecutor]):
+    pass
+
+
+@ExecutorFactory.register("none")
+class NoneExecutor(BaseExecutor):
+    """Single process."""
+
+
+def _broadcast_parameters(model: nn.Module, flat: Optional[FlatParameters]) -> None:
+    if get_world_size() <= 1:
+        return
+    if flat is not None:
+        dist.broadcast(flat.data, src=0)
+        return
+    for t in list(model.parameters()) + list(model.buffers()):
+        dist.broadcast(t.data, src=0)
+
+
+@ExecutorFactory.register("ddp")
+class DDPExecutor(BaseExecutor):
+    """Data parallel with replicated parameters.
+
+    Works on CPU/gloo as well as CUDA/NCCL (the reference's wrapper cannot wrap a CPU model,
+    ``astrai/parallel/executor.py:181-193``).  The torch-DDP keyword arguments of the
+    reference are accepted for compatibility; ``bucket_cap_mb`` sizes the chunks of the
+    NVLink all-reduce kernel.
+    """
+
+    def __init__(self, grad_accum_steps: int = 1, find_unused_parameters: bool = False, bucket_cap_mb: int = 25,
+                 gradient_as_bucket_view: bool = True, broadcast_buffers: bool = False, static_graph: bool = False,
+                 init_sync: bool = True, comm: str = "auto", **_ignored):
+        super().__init__(grad_accum_steps)
+        self.bucket_cap_mb = bucket_cap_mb
+        self.init_sync = init_sync
+        self.comm = comm  # "auto" | "nccl" | "kernel"
+        self._reducer = None
+
+    def _prepare_model(self, model: nn.Module) -> nn.Module:
+        params = list(model.parameters())
+        same = len({(p.dtype, p.device) for p in params}) == 1
+        if same:
+            self.flat = FlatParameters(model, with_grad=True)
+        if self.init_sync:
+            _broadcast_parameters(model, self.flat)
+        self._model = model
+        if self.flat is not None and self.flat.data.is_cuda and get_world_size() > 1 and self.comm != "nccl":
+            from .comm import GradReducer
+
+            self._reducer = GradReducer.create(self.flat, mode="allreduce")
+        return model
+
+    def _sync_gradients(self) -> None:
+        ws = get_world_size()
+        if ws <= 1:
+            return
+        if self._reducer is not None:
+            self._reducer.reduce()
+            return
+        if self.flat is not None:
+            dist.all_reduce(self.flat.grad)
+            self.flat.grad.div_(ws)
+            return
+        for p in self._model.parameters():
+            if p.grad is not None:
+                dist.all_reduce(p.grad)
+                p.grad.div_(ws)
+
+    def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):
+        out = super().prepare(model, optimizer, dataloader, scheduler)
+        if self._reducer is not None and optimizer is not None and hasattr(optimizer, "attach_reducer"):
+            optimizer.attach_reducer(self._reducer)
+        return out
+
+
+@ExecutorFactory.register("fsdp")
+class FSDPExecutor(BaseExecutor):
+    """Fully sharded data parallel over flat buffers.
+
+    Every rank owns the contiguous slice ``[rank * n / ws, (rank + 1) * n / ws)`` of the flat
+    parameter vector: gradients are reduce-scattered to their owner, optimizer state exists
+    for the owned slice only and the owner updates it; updated parameters are all-gathered
+    before the next forward.  ``unwrap_model`` returns the full (unsharded) state dict on every
+    rank, as the reference's ``FULL_STATE_DICT`` gather does (``astrai/parallel/executor.py:263-272``).
+    """
+
+    def __init__(self, grad_accum_steps: int = 1, comm: str = "auto", **_ignored):
+        super().__init__(grad_accum_steps)
+        self.comm = comm
+        self.shard: Optional[Tuple[int, int]] = None
+        self._reducer = None
+
+    def _prepare_model(self, model: nn.Module) -> nn.Module:
+        ws = get_world_size()
+        self.flat = FlatParameters(model, with_grad=True, pad_to=8 * max(ws, 1))
+        _broadcast_parameters(model, self.flat)
+        n = self.flat.numel // max(ws, 1)
+        self.shard = (get_rank() * n, n)
+        self._model = model
+        if self.flat.data.is_cuda and ws > 1 and self.comm != "nccl":
+            from .comm import GradReducer
+
+            self._reducer = GradReducer.create(self.flat, mode="reducescatter")
+        return model
+
+    def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):
+        model = self._prepare_model(model)
+        if optimizer is not None:
+            if hasattr(optimizer, "attach_flat"):
+                optimizer.attach_flat(self.flat, shard=self.shard if get_world_size() > 1 else None)
+                if self._reducer is not None and hasattr(optimizer, "attach_reducer"):
+                    optimizer.attach_reducer(self._reducer)
+            elif get_world_size() > 1:
+                log.warning("fsdp: optimizer %s cannot shard its state; gradients are all-reduced and every "
+                            "rank updates the full model", type(optimizer).__name__)
+                self.shard = None
+            optimizer = AccumOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step)
+        if scheduler is not None:
+            scheduler = AccumScheduler(scheduler, self.gradient_state)
+        return model, optimizer, dataloader, scheduler
+
+    def _sync_gradients(self) -> None:
+        ws = get_world_size()
+        if ws <= 1:
+            return
+        if self._reducer is not None:
+            self._reducer.reduce()
+            return
+        g = self.flat.grad
+        if self.shard is None:
+            dist.all_reduce(g)
+            g.div_(ws)
+            return
+        off, n = self.shard
+        mine = g[off:off + n]
+        if dist.get_backend() == "gloo":  # gloo has no reduce_scatter_tensor
+            dist.all_reduce(g)
+        else:
+            dist.reduce_scatter_tensor(mine, g[: n * ws])
+        mine.div_(ws)
+
+    def _after_optimizer_step(self) -> None:
+        ws = get_world_size()
+        if ws <= 1 or self.shard is None:
+            return
+        if self._reducer is not None and self._reducer.gathers_params:
+            return  # the fused kernel already published the updated slice to every rank
+        off, n = self.shard
+        data = self.flat.data
+        if dist.get_backend() == "gloo":
+            pieces = [torch.empty(n, dtype=data.dtype, device=data.device) for _ in range(ws)]
+            dist.all_gather(pieces, data[off:off + n].clone())
+            for r, piece in enumerate(pieces):
+                data[r * n:(r + 1) * n].copy_(piece)
+        else:
+            dist.all_gather_into_tensor(data[: n * ws], data[off:off + n].clone())
+
+    def unwrap_model(self, model: nn.Module) -> Dict[str, torch.Tensor]:
+        # parameters are kept whole between steps, so the local state dict is the full one
+        return {k: v.detach().clone() for k, v in model.state_dict().items()}
+
+    def grad_norm_sq_extra(self) -> Optional[torch.Tensor]:
+        if get_world_size() <= 1 or self.shard is None:
+            return None
+        off, n = self.shard
+        sq = self.flat.grad[off:off + n].float().pow(2).sum()
+        dist.all_reduce(sq)
+        return sq
