@@ -1,0 +1,423 @@
+#!/usr/bin/env python
+"""Headline benchmark: pre-training throughput (tokens/s) of the 1B-class decoder.
+
+Model: 24 layers, d_model 2048, 16 query / 4 KV heads (head_dim 128), SwiGLU ffn 5632, vocab
+32000, tied embeddings, bf16.  Step = one optimizer step = 8 micro-batches of 4 x 2048
+tokens per GPU (weak scaling: per-GPU work is fixed), AdamW(lr 3e-4, betas (0.9, 0.95),
+wd 0.01), label smoothing 0.05, gradient clip 1.0.  Synthetic uniform random token ids and
+random-init N(0, 0.02) weights.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 5 --warmup 3
+    python bench.py --impl reference ...   # the unmodified reference from baseline/_ref
+
+Two numbers come out of the own arm: ``value`` — K steps timed on the device with CUDA
+events, inputs already resident; and ``e2e`` — the same K steps through the public
+``Trainer`` API, where every micro-batch is copied from pinned host memory and every
+micro-batch loss is read back to the host.  Rank 0 prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+METRIC = "train_tokens_per_s_1B"
+MODEL = dict(vocab_size=32000, dim=2048, n_layers=24, norm_eps=1e-5, dim_ffn=5632, tie_weight=True, max_len=2048,
+             rope_theta=10000.0, n_heads=16, n_kv_heads=4)
+SEQ, BPD, ACCUM = 2048, 4, 8
+LR, BETAS, WD, SMOOTH, CLIP = 3e-4, (0.9, 0.95), 0.01, 0.05, 1.0
+SEED = 3407
+
+
+# ----------------------------------------------------------------------------------------
+# helpers shared by both arms
+# ----------------------------------------------------------------------------------------
+def env_rank():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.device_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def max_over_ranks(ms: float, device) -> float:
+    if dist.is_initialized():
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return ms
+
+
+def barrier_sync():
+    if dist.is_initialized():
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+class SyntheticTokens(torch.utils.data.Dataset):
+    """Uniform random token ids, generated once on the host (pinned by the DataLoader)."""
+
+    def __init__(self, n_samples: int, seq: int, vocab: int, seed: int):
+        g = torch.Generator().manual_seed(seed)
+        self.data = torch.randint(0, vocab, (n_samples, seq + 1), generator=g, dtype=torch.long)
+
+    def __len__(self):
+        return self.data.shape[0]
+
+    def __getitem__(self, i):
+        row = self.data[i]
+        return {"input_ids": row[:-1], "target_ids": row[1:]}
+
+
+class StepTimer:
+    """Trainer callback (both arms): times exactly ``steps`` optimizer steps after ``warmup``
+    ones with CUDA events bracketed by barrier + synchronize."""
+
+    def __init__(self, warmup: int, steps: int, accum: int, device_index: int, count_launches=None):
+        self.first = warmup * accum
+        self.last = (warmup + steps) * accum
+        self.seen = 0
+        self.ms = None
+        self.launches = None
+        self.clocks = None
+        self._count = count_launches
+        self._sampler = ClockSampler(device_index)
+
+    def on_batch_begin(self, context):
+        if self.seen == self.first:
+            barrier_sync()
+            self._sampler.start()
+            self._l0 = self._count() if self._count else 0
+            self._e0 = torch.cuda.Event(enable_timing=True)
+            self._e1 = torch.cuda.Event(enable_timing=True)
+            self._e0.record()
+        self.seen += 1
+
+    def on_train_end(self, context):
+        self._finish()
+
+    def on_epoch_end(self, context):
+        self._finish()
+
+    def _finish(self):
+        if self.ms is not None or self.seen < self.last:
+            return
+        self._e1.record()
+        barrier_sync()
+        self.ms = self._e0.elapsed_time(self._e1)
+        if dist.is_initialized():  # max over ranks while the trainer's process group is alive
+            t = torch.tensor([self.ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            self.ms = float(t.item())
+        self.launches = (self._count() - self._l0) if self._count else None
+        self.clocks = self._sampler.stop()
+
+
+def emit(payload: dict):
+    if env_rank()[0] == 0:
+        print(json.dumps(payload), flush=True)
+
+
+def base_payload(args, ws: int, impl: str) -> dict:
+    return {"metric": METRIC, "unit": "tokens/s", "n_gpus": ws, "steps": args.steps, "warmup": args.warmup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": impl,
+            "config": {"model": "1B decoder (24L, d2048, 16q/4kv heads, ffn5632, vocab32000, tied)",
+                       "global_batch": BPD * ACCUM * ws, "micro_batch_per_gpu": BPD, "grad_accum": ACCUM,
+                       "seq_len": SEQ, "parallelism": f"dp{ws}" if ws > 1 else "single",
+                       "optimizer": "AdamW lr3e-4 betas(0.9,0.95) wd0.01 clip1.0 label_smoothing0.05",
+                       "l2": "no flush: weights (2.3 GB) + activations exceed the 126 MB L2 every step"}}
+
+
+# ----------------------------------------------------------------------------------------
+# own arm
+# ----------------------------------------------------------------------------------------
+def run_own(args):
+    rank, local_rank, ws = env_rank()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if ws > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=device)
+    sys.path.insert(0, ROOT)
+    from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig, TrainConfig
+    from khaosz_b200.models.components.layers import Linear
+    from khaosz_b200.ops import _lib, raise_on_device_error
+    from khaosz_b200.parallel import ExecutorFactory
+    from khaosz_b200.trainer import FusedAdamW, SchedulerFactory, StrategyFactory, Trainer
+
+    cfg = AutoRegressiveLMConfig(**MODEL)
+    mode = "ddp" if ws > 1 else "none"
+    steps_total = args.warmup + args.steps
+
+    def model_fn():
+        torch.manual_seed(SEED)
+        model = AutoRegressiveLM(cfg)
+        for m in model.modules():
+            if isinstance(m, Linear):
+                torch.nn.init.normal_(m.weight, mean=0.0, std=0.02)
+        return model.to(dtype=torch.bfloat16)
+
+    def optimizer_fn(model):
+        return FusedAdamW(model.parameters(), lr=LR, betas=BETAS, weight_decay=WD)
+
+    def scheduler_fn(opt):
+        return SchedulerFactory.create(opt, "cosine", warmup_steps=1, lr_decay_steps=10_000)
+
+    # ---- device-timed steps (inputs resident on the device) ----
+    model = model_fn().to(device)
+    executor = ExecutorFactory.create(mode, grad_accum_steps=ACCUM)
+    opt = optimizer_fn(model)
+    model, opt, _, sched = executor.prepare(model, opt, None, scheduler_fn(opt))
+    strategy = StrategyFactory.create("seq", model, device, label_smoothing=SMOOTH)
+    g = torch.Generator(device="cpu").manual_seed(SEED + rank)
+    pool = torch.randint(0, MODEL["vocab_size"], (ACCUM, BPD, SEQ + 1), generator=g).to(device)
+    model.train()
+
+    def one_step():
+        for mb in range(ACCUM):
+            batch = {"input_ids": pool[mb, :, :-1], "target_ids": pool[mb, :, 1:]}
+            with executor.accumulate(model):
+                loss = strategy(batch)
+                executor.backward(loss / ACCUM)
+                if executor.sync_gradients:
+                    opt.fused_clip(CLIP)
+                    opt.step()
+                    opt.zero_grad()
+                    sched.step()
+        return loss
+
+    for _ in range(args.warmup):
+        one_step()
+    barrier_sync()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = one_step()
+    e1.record()
+    barrier_sync()
+    ms = max_over_ranks(e0.elapsed_time(e1), device)
+    launches = _lib.launch_count() - l0
+    clocks = sampler.stop()
+    final_loss = float(loss)
+    raise_on_device_error()
+    tokens = args.steps * ACCUM * BPD * SEQ * ws
+    value = tokens / (ms / 1e3)
+    del model, opt, sched, strategy, executor, pool
+    torch.cuda.empty_cache()
+
+    # ---- end to end through the public Trainer API ----
+    e2e = None
+    if not args.no_e2e:
+        n_samples = steps_total * ACCUM * BPD * ws
+        dataset = SyntheticTokens(n_samples, SEQ, MODEL["vocab_size"], SEED)
+        timer = StepTimer(args.warmup, args.steps, ACCUM, local_rank, _lib.launch_count)
+        tmp = tempfile.mkdtemp(prefix="kb200_bench_")
+        tc = TrainConfig(model_fn=model_fn, strategy="seq", dataset=dataset, optimizer_fn=optimizer_fn,
+                         scheduler_fn=scheduler_fn, n_epoch=1, batch_per_device=BPD, grad_accum_steps=ACCUM,
+                         max_grad_norm=CLIP, ckpt_dir=tmp, ckpt_interval=10 ** 9, log_dir=os.path.join(tmp, "logs"),
+                         log_interval=ACCUM, random_seed=SEED, num_workers=0, pin_memory=True, nprocs=ws,
+                         backend="nccl", parallel_mode=mode, device_type="cuda",
+                         extra_kwargs={"label_smoothing": SMOOTH})
+
+        trainer = Trainer(tc, callbacks=[timer])
+        # the end-of-run checkpoint and the progress bar are not part of a training step
+        trainer.callbacks = [cb for cb in trainer.callbacks
+                             if type(cb).__name__ not in ("CheckpointCallback", "ProgressBarCallback")]
+        trainer.train()
+        ms_e2e = timer.ms  # already the max over ranks
+        e2e = {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+               "h2d_bytes_per_step": ACCUM * 2 * BPD * SEQ * 8, "d2h_bytes_per_step": ACCUM * 4,
+               "api": "khaosz_b200.trainer.Trainer.train (DataLoader pin_memory -> H2D per micro-batch, "
+                      "loss read back per micro-batch)"}
+
+    payload = base_payload(args, ws, "khaosz_b200")
+    payload.update({"value": value, "ms_per_step": ms / args.steps, "clocks": clocks, "gpu_launches": launches,
+                    "final_loss": final_loss})
+    if e2e is not None:
+        payload["e2e"] = e2e
+    emit(payload)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------
+# reference arm: the unmodified reference package installed under baseline/_ref
+# ----------------------------------------------------------------------------------------
+def _install_h5py_stub():
+    """The reference imports h5py at module import; the wheel is not available offline.  The
+    bench never touches HDF5, so an empty stand-in module satisfies the import."""
+    try:
+        import h5py  # noqa: F401
+    except ImportError:
+        import types
+
+        stub = types.ModuleType("h5py")
+
+        class _Missing:
+            def __init__(self, *a, **k):
+                raise ImportError("h5py is not installed (bench stub)")
+
+        stub.File = _Missing
+        sys.modules["h5py"] = stub
+
+
+def run_reference(args):
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "astrai")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/astrai is not installed"}), flush=True)
+        return
+    rank, local_rank, ws = env_rank()
+    try:
+        _install_h5py_stub()
+        sys.path.insert(0, ref_root)
+        import astrai  # noqa: F401
+        from astrai.config import AutoRegressiveLMConfig, TrainConfig
+        from astrai.model import AutoRegressiveLM
+        from astrai.model.components.linear import Linear
+        from astrai.trainer import SchedulerFactory, Trainer
+    except Exception as exc:  # pragma: no cover
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": f"import failed: {type(exc).__name__}: {exc}"[:300]}),
+                  flush=True)
+        return
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    cfg = AutoRegressiveLMConfig(**MODEL)
+    steps_total = args.warmup + args.steps
+
+    def model_fn():
+        torch.manual_seed(SEED)
+        model = AutoRegressiveLM(cfg)
+        for m in model.modules():
+            if isinstance(m, Linear):
+                torch.nn.init.normal_(m.weight, mean=0.0, std=0.02)
+        return model.to(dtype=torch.bfloat16)
+
+    def optimizer_fn(model):
+        return torch.optim.AdamW(model.parameters(), fused=True, lr=LR, betas=BETAS, weight_decay=WD)
+
+    def scheduler_fn(opt):
+        return SchedulerFactory.create(opt, schedule_type="cosine", warmup_steps=1, lr_decay_steps=10_000)
+
+    dataset = SyntheticTokens(steps_total * ACCUM * BPD * ws, SEQ, MODEL["vocab_size"], SEED)
+    timer = StepTimer(args.warmup, args.steps, ACCUM, local_rank)
+    tmp = tempfile.mkdtemp(prefix="ref_bench_")
+    tc = TrainConfig(model_fn=model_fn, strategy="seq", dataset=dataset, optimizer_fn=optimizer_fn,
+                     scheduler_fn=scheduler_fn, n_epoch=1, batch_per_device=BPD, grad_accum_steps=ACCUM,
+                     max_grad_norm=CLIP, ckpt_dir=tmp, ckpt_interval=10 ** 9, log_dir=os.path.join(tmp, "logs"),
+                     log_interval=ACCUM, random_seed=SEED, num_workers=0, pin_memory=True, nprocs=ws, backend="nccl",
+                     parallel_mode="ddp" if ws > 1 else "none", device_type="cuda",
+                     executor_kwargs={"gradient_as_bucket_view": True, "broadcast_buffers": False} if ws > 1 else {},
+                     extra_kwargs={"label_smoothing": SMOOTH})
+    trainer = Trainer(tc, callbacks=[timer])
+    # the final full checkpoint (2.3 GB safetensors) is outside the timed steps; skip writing it
+    trainer.callbacks = [cb for cb in trainer.callbacks if type(cb).__name__ != "CheckpointCallback"]
+    try:
+        trainer.train()
+    except Exception as exc:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": f"run failed: {type(exc).__name__}: {exc}"[:300]}),
+                  flush=True)
+        return
+    ms = timer.ms  # already the max over ranks
+    tokens = args.steps * ACCUM * BPD * SEQ * ws
+    payload = base_payload(args, ws, "reference")
+    val = tokens / (ms / 1e3)
+    payload.update({"value": val, "ms_per_step": ms / args.steps, "clocks": timer.clocks, "gpu_launches": None,
+                    "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": ACCUM * 2 * BPD * SEQ * 8,
+                            "d2h_bytes_per_step": ACCUM * 4,
+                            "api": "astrai.trainer.Trainer.train (the reference's only training path: H2D per "
+                                   "micro-batch and loss.item() per micro-batch are inside it)"}})
+    emit(payload)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="khaosz_b200", choices=["khaosz_b200", "own", "reference"])
+    ap.add_argument("--no-e2e", dest="no_e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    ws = env_rank()[2]
+    if args.gpus > 1 and ws == 1:
+        # convenience: re-launch under torchrun when called directly with --gpus N
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29533"),
+               os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device visible"}), flush=True)
+        return
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_own(args)
+
+
+if __name__ == "__main__":
+    main()
