@@ -638,3 +638,67 @@ int kb_adamw_bf16(void* p, const void* g, float* m, float* v, long long n, const
 }
 
 }  // extern "C"
+
+// =======================================================================================
+// Allocation-free RMSNorm backward (see kb_noalloc.h).  The per-CTA weight-gradient partials
+// go to a file-scope device array instead of a caller-provided buffer.
+// =======================================================================================
+#include <stdio.h>
+
+#include "kb_noalloc.h"
+
+namespace {
+// Scratch for the weight-gradient partial rows: [KB_STATIC_RMS_MAX_PARTIALS][dim] floats.
+static __device__ __align__(256) float g_rms_static_scratch[KB_STATIC_RMS_MAX_PARTIALS * KB_STATIC_RMS_MAX_DIM];
+
+// In host code the array's name is only a handle; the device address is looked up once per
+// device and cached here.
+constexpr int kStaticMaxDevices = 64;
+float* g_rms_static_ptr[kStaticMaxDevices] = {nullptr};
+thread_local char g_rms_static_msg[192] = "";
+
+int rms_static_fail(int status, const char* fmt, long a, long b) {
+  snprintf(g_rms_static_msg, sizeof(g_rms_static_msg), fmt, a, b);
+  return status;
+}
+}  // namespace
+
+extern "C" const char* kb_rmsnorm_bwd_static_error(void) { return g_rms_static_msg; }
+
+extern "C" int kb_rmsnorm_bwd_static(const void* dy, const void* x, const void* w, const float* rstd,
+                                     const void* dres_in, void* dx, float* dw, int rows, int dim,
+                                     void* stream) {
+  g_rms_static_msg[0] = '\0';
+  if (rows <= 0) return KB_STATUS_OK;
+  if (dim <= 0 || (dim & 7))
+    return rms_static_fail(KB_STATUS_BAD_ARG, "kb_rmsnorm_bwd_static: dim %ld must be a positive multiple of 8", dim, 0);
+  if (dim > KB_STATIC_RMS_MAX_DIM)
+    return rms_static_fail(KB_STATUS_TOO_LARGE,
+                           "kb_rmsnorm_bwd_static: dim %ld exceeds the built-in scratch (max %ld); use "
+                           "kb_rmsnorm_bwd with a caller-provided buffer", dim, KB_STATIC_RMS_MAX_DIM);
+  if (mis16(dy) || mis16(x) || mis16(w) || mis16(dx) || (dres_in && mis16(dres_in)) || !rstd || !dw)
+    return rms_static_fail(KB_STATUS_BAD_ARG, "kb_rmsnorm_bwd_static: null or misaligned (16 B) pointer", 0, 0);
+
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices)
+    return rms_static_fail(KB_STATUS_CUDA_ERROR, "kb_rmsnorm_bwd_static: cannot query the current device", 0, 0);
+  if (g_rms_static_ptr[dev] == nullptr) {
+    // once per device, with that device current
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rms_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return rms_static_fail(KB_STATUS_CUDA_ERROR, "kb_rmsnorm_bwd_static: cudaGetSymbolAddress failed (%ld)",
+                             (long)e, 0);
+    g_rms_static_ptr[dev] = p;
+  }
+  float* scratch = g_rms_static_ptr[dev];
+
+  int blocks = (rows + RMS_BWD_ROWS - 1) / RMS_BWD_ROWS;
+  if (blocks > KB_STATIC_RMS_MAX_PARTIALS) blocks = KB_STATIC_RMS_MAX_PARTIALS;  // the kernel strides over rows
+  rmsnorm_bwd_kernel<<<blocks, RMS_BWD_THREADS, 0, (cudaStream_t)stream>>>(
+      (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres_in, (bf16*)dx, scratch, rows, dim);
+  colsum_kernel<<<(dim + 127) / 128, 128, 0, (cudaStream_t)stream>>>(scratch, dw, blocks, dim);
+  if (cudaGetLastError() != cudaSuccess)
+    return rms_static_fail(KB_STATUS_CUDA_ERROR, "kb_rmsnorm_bwd_static: kernel launch failed", 0, 0);
+  return KB_STATUS_OK;
+}
