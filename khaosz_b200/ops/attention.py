@@ -61,8 +61,9 @@ class _RopeAttnPackedFn(torch.autograd.Function):
     def forward(ctx, qkv, cs, pos, H, Hkv, causal):
         B, S, _, D = qkv.shape
         scale = 1.0 / math.sqrt(D)
-        _rope_kernel(qkv, cs, pos, H + Hkv, False)  # in place: qkv is a fresh GEMM output
-        ctx.mark_dirty(qkv)
+        # in place through the raw pointer: qkv is a fresh GEMM output that nothing else reads,
+        # and the projection's backward does not need its own output
+        _rope_kernel(qkv, cs, pos, H + Hkv, False)
         q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
         o, lse = _flash_fwd(q, k, v, causal, scale)
         ctx.save_for_backward(qkv, o, lse)

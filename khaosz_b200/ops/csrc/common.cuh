@@ -154,6 +154,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* s
                "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int32_t x,
+                                             int32_t y, int32_t z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* smem_src, int32_t x,
                                              int32_t y, int32_t z, int32_t w) {
   asm volatile(
@@ -286,6 +293,14 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
       "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -358,6 +373,9 @@ __device__ __forceinline__ float warp_max(float v) {
 // box = [box_rows, box_cols]; 128B swizzle when `swizzle128`.
 int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
                  uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, bool swizzle128);
+// 3-D tensor [d2, d1, d0(innermost)], strides in bytes for d1 and d2; box innermost first.
+int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, const uint64_t dims[3],
+                 const uint64_t strides_bytes[2], const uint32_t box[3], bool swizzle128);
 // 4-D tensor, dims/strides innermost first (strides in bytes for dims 1..3).
 int make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, const uint64_t dims[4],
                  const uint64_t strides_bytes[3], const uint32_t box[4], bool swizzle128);

@@ -82,6 +82,22 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t ro
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, const uint64_t dims_in[3],
+                 const uint64_t strides_bytes[2], const uint32_t box_in[3], bool swizzle128) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  cuuint64_t dims[3] = {dims_in[0], dims_in[1], dims_in[2]};
+  cuuint64_t strides[2] = {strides_bytes[0], strides_bytes[1]};
+  cuuint32_t box[3] = {box_in[0], box_in[1], box_in[2]};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, dtype_of(elem_bytes), 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) g_last_tmap_error = (int)r;
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 int make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, const uint64_t dims_in[4],
                  const uint64_t strides_bytes[3], const uint32_t box_in[4], bool swizzle128) {
   EncodeTiledFn enc = get_encode();
