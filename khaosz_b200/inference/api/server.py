@@ -1,0 +1,132 @@
+"""FastAPI application: ``/health``, ``/stats``, ``/v1/chat/completions`` (OpenAI) and
+``/v1/messages`` (Anthropic) on top of one ``InferenceEngine``
+(reference: ``astrai/inference/api/server.py:30-169``).  ``/stats`` additionally reports
+decode throughput and TTFT / latency percentiles."""
+
+from __future__ import annotations
+
+import logging
+from contextlib import asynccontextmanager
+from pathlib import Path
+from typing import Any, Dict, List, Optional, Union
+
+import torch
+import uvicorn
+from fastapi import FastAPI, HTTPException
+from pydantic import BaseModel, Field
+
+from ...models import AutoModel
+from ...tokenize import AutoTokenizer
+from ..engine import InferenceEngine
+from .anthropic import AnthropicResponseBuilder
+from .openai import OpenAIResponseBuilder
+from .protocol import ProtocolHandler
+
+log = logging.getLogger(__name__)
+DEFAULT_PARAM_DIR = Path(__file__).resolve().parents[3] / "params"
+
+
+class ChatMessage(BaseModel):
+    role: str
+    content: str
+
+
+class ChatCompletionRequest(BaseModel):
+    model: str = "astrai"
+    messages: List[ChatMessage]
+    temperature: Optional[float] = Field(default=1.0, ge=0.0, le=2.0)
+    top_p: Optional[float] = Field(default=1.0, ge=0.0, le=1.0)
+    top_k: Optional[int] = Field(default=50, ge=1)
+    stream: Optional[bool] = False
+    stop: Optional[Union[str, List[str]]] = None
+    max_tokens: Optional[int] = Field(default=2048, ge=1)
+    n: Optional[int] = Field(default=1, ge=1)
+    presence_penalty: Optional[float] = Field(default=0.0, ge=-2.0, le=2.0)
+    frequency_penalty: Optional[float] = Field(default=0.0, ge=-2.0, le=2.0)
+    logit_bias: Optional[Dict[int, float]] = None
+    user: Optional[str] = None
+
+
+class AnthropicMessage(BaseModel):
+    role: str
+    content: Union[str, List[Dict[str, Any]]]
+
+
+class MessagesRequest(BaseModel):
+    model: str = "astrai"
+    max_tokens: int = Field(default=1024, ge=1)
+    messages: List[AnthropicMessage]
+    system: Optional[str] = None
+    temperature: Optional[float] = Field(default=1.0, ge=0.0, le=2.0)
+    top_p: Optional[float] = Field(default=1.0, ge=0.0, le=1.0)
+    top_k: Optional[int] = Field(default=50, ge=1)
+    stream: Optional[bool] = False
+    stop_sequences: Optional[List[str]] = None
+
+
+def _create_engine(param_path: Optional[Path] = None, device: str = "cuda", dtype: torch.dtype = torch.bfloat16,
+                   max_batch_size: int = 16, page_size: int = 16, max_seq_len: Optional[int] = None) -> InferenceEngine:
+    root = Path(param_path) if param_path is not None else DEFAULT_PARAM_DIR
+    if not root.exists():
+        raise FileNotFoundError(f"Parameter directory not found: {root}")
+    tokenizer = AutoTokenizer.from_pretrained(root)
+    model = AutoModel.from_pretrained(root).to(device=device, dtype=dtype).eval()
+    if next(model.parameters()).is_cuda and hasattr(model, "pack_parameters"):
+        model.pack_parameters(with_grad=False)  # adjacent q/k/v and gate/up weights -> single GEMMs
+    log.info("Model loaded on %s with dtype %s", device, dtype)
+    return InferenceEngine(model=model, tokenizer=tokenizer, max_batch_size=max_batch_size, page_size=page_size,
+                           max_seq_len=max_seq_len)
+
+
+@asynccontextmanager
+async def lifespan(app: FastAPI):
+    config = getattr(app.state, "server_config", None) or {}
+    if not config.get("_test", False):
+        kwargs = {k: v for k, v in config.items() if not k.startswith("_")}
+        app.state.engine = _create_engine(**kwargs)
+    elif not hasattr(app.state, "engine"):
+        app.state.engine = None
+    yield
+    if getattr(app.state, "engine", None):
+        app.state.engine.shutdown()
+        log.info("Inference engine shutdown complete")
+
+
+app = FastAPI(title="khaosz_b200 inference server", version="0.1.0", lifespan=lifespan)
+app.state.engine = None
+app.state.server_config = {}
+
+
+def _get_engine() -> InferenceEngine:
+    engine = getattr(app.state, "engine", None)
+    if engine is None:
+        raise HTTPException(status_code=503, detail="Engine not initialized")
+    return engine
+
+
+@app.get("/health")
+async def health():
+    return {"status": "ok", "model_loaded": getattr(app.state, "engine", None) is not None}
+
+
+@app.get("/stats")
+async def get_stats():
+    return _get_engine().get_stats()
+
+
+@app.post("/v1/chat/completions")
+async def chat_completion(request: ChatCompletionRequest):
+    return await ProtocolHandler(request, _get_engine(), OpenAIResponseBuilder()).handle()
+
+
+@app.post("/v1/messages")
+async def create_message(request: MessagesRequest):
+    return await ProtocolHandler(request, _get_engine(), AnthropicResponseBuilder()).handle()
+
+
+def run_server(host: str = "0.0.0.0", port: int = 8000, reload: bool = False, device: str = "cuda",
+               dtype: torch.dtype = torch.bfloat16, param_path: Optional[Path] = None, max_batch_size: int = 16,
+               page_size: int = 16, max_seq_len: Optional[int] = None) -> None:
+    app.state.server_config = {"device": device, "dtype": dtype, "param_path": param_path,
+                               "max_batch_size": max_batch_size, "page_size": page_size, "max_seq_len": max_seq_len}
+    uvicorn.run(app, host=host, port=port, reload=reload)

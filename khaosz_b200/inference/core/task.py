@@ -1,0 +1,159 @@
+"""Generation tasks and the thread-safe queues the scheduler pulls from
+(reference: ``astrai/inference/core/task.py:13-209``).  Tasks additionally record
+time-to-first-token and finish time so the engine can report latency statistics."""
+
+from __future__ import annotations
+
+import threading
+import time
+import uuid
+from collections import deque
+from enum import Enum
+from typing import Any, Callable, Deque, Dict, List, Optional
+
+STOP = object()  # sentinel pushed through stream callbacks when a task ends
+
+
+class TaskStatus(Enum):
+    PENDING = "pending"
+    RUNNING = "running"
+    FINISHED = "finished"
+    ABORTED = "aborted"
+
+
+class Task:
+    def __init__(self, task_id: str, prompt_ids: List[int], max_tokens: Optional[int] = None, temperature: float = 1.0,
+                 top_p: float = 1.0, top_k: int = 50, stream_callback: Optional[Callable] = None):
+        self.task_id, self.prompt_ids, self.max_tokens = task_id, prompt_ids, max_tokens
+        self.temperature, self.top_p, self.top_k = temperature, top_p, top_k
+        self.status = TaskStatus.PENDING
+        self.output_ids: List[int] = []
+        self.input_tokens = 0
+        self.output_tokens = 0
+        self.arrival_time = time.time()
+        self.first_token_time: Optional[float] = None
+        self.finish_time: Optional[float] = None
+        self.stream_callback = stream_callback
+
+    @property
+    def next_pos(self) -> int:
+        return self.input_tokens + len(self.output_ids)
+
+    def is_finished(self, stop_ids: List[int]) -> bool:
+        if self.max_tokens is not None and self.output_tokens >= self.max_tokens:
+            return True
+        return bool(self.output_ids) and self.output_ids[-1] in stop_ids
+
+
+class TaskManager:
+    def __init__(self, tokenizer, max_batch_size: int = 16, max_seq_len: int = 8192, max_prompt_len: int = 512):
+        self.tokenizer = tokenizer
+        self.max_batch_size, self.max_seq_len, self.max_prompt_len = max_batch_size, max_seq_len, max_prompt_len
+        self.waiting_queue: Deque[Task] = deque()
+        self.active_tasks: List[Task] = []
+        self._task_event = threading.Event()
+        self._lock = threading.Lock()
+        self._total_tasks = 0
+        self._total_tokens = 0
+        self._ttft: List[float] = []
+        self._latency: List[float] = []
+
+    def add_task(self, prompt, max_tokens: Optional[int] = None, temperature: float = 1.0, top_p: float = 1.0,
+                 top_k: int = 50, stream_callback: Optional[Callable] = None) -> str:
+        """``prompt`` is text, or a list of token ids (used by load generators)."""
+        task_id = f"task_{int(time.time())}_{uuid.uuid4().hex[:8]}"
+        ids = list(prompt) if isinstance(prompt, (list, tuple)) else self.tokenizer.encode(prompt)
+        if len(ids) > self.max_prompt_len:
+            ids = ids[-self.max_prompt_len:]
+        room = self.max_seq_len - len(ids)
+        if room <= 0:
+            if stream_callback:
+                stream_callback(STOP)
+            return task_id
+        task = Task(task_id, ids, room if max_tokens is None else min(max_tokens, room), temperature, top_p, top_k,
+                    stream_callback)
+        with self._lock:
+            self.waiting_queue.append(task)
+            self._total_tasks += 1
+        self._task_event.set()
+        return task_id
+
+    def remove_task(self, task_id: str) -> List[Task]:
+        with self._lock:
+            removed = [t for t in self.active_tasks if t.task_id == task_id]
+            self.waiting_queue = deque(t for t in self.waiting_queue if t.task_id != task_id)
+            self.active_tasks = [t for t in self.active_tasks if t.task_id != task_id]
+        return removed
+
+    def get_stats(self) -> Dict[str, Any]:
+        return {"total_tasks": self._total_tasks, "total_tokens": self._total_tokens,
+                "active_tasks": len(self.active_tasks), "waiting_queue": len(self.waiting_queue)}
+
+    def latency_stats(self) -> Dict[str, Any]:
+        def pct(xs, q):
+            if not xs:
+                return None
+            ys = sorted(xs)
+            return ys[min(len(ys) - 1, int(q * len(ys)))]
+
+        with self._lock:
+            return {"ttft_p50_s": pct(self._ttft, 0.5), "ttft_p99_s": pct(self._ttft, 0.99),
+                    "latency_p50_s": pct(self._latency, 0.5), "finished": len(self._latency)}
+
+    def remove_finished_tasks(self, stop_ids: List[int]) -> List[Task]:
+        now = time.time()
+        with self._lock:
+            done: List[Task] = []
+            for t in self.active_tasks:
+                if t.status == TaskStatus.ABORTED:
+                    t.finish_time = now
+                    done.append(t)
+                elif t.is_finished(stop_ids):
+                    t.status, t.finish_time = TaskStatus.FINISHED, now
+                    self._total_tokens += t.output_tokens
+                    self._latency.append(now - t.arrival_time)
+                    if t.first_token_time is not None:
+                        self._ttft.append(t.first_token_time - t.arrival_time)
+                    done.append(t)
+            self.active_tasks = [t for t in self.active_tasks
+                                 if t.status not in (TaskStatus.FINISHED, TaskStatus.ABORTED)]
+            return done
+
+    def pull_candidates(self, n: int) -> List[Task]:
+        with self._lock:
+            return [self.waiting_queue.popleft() for _ in range(min(max(n, 0), len(self.waiting_queue)))]
+
+    def activate(self, task: Task) -> None:
+        task.status = TaskStatus.RUNNING
+        with self._lock:
+            self.active_tasks.append(task)
+
+    def return_to_waiting(self, tasks: List[Task]) -> None:
+        with self._lock:
+            self.waiting_queue.extendleft(reversed(tasks))
+
+    def has_work(self) -> bool:
+        return bool(self.active_tasks or self.waiting_queue)
+
+    def wait_for_tasks(self, timeout: float = 1.0) -> None:
+        with self._lock:
+            if self.waiting_queue or self.active_tasks:
+                return
+            self._task_event.clear()
+        self._task_event.wait(timeout=timeout)
+
+    def get_active_tasks(self) -> List[Task]:
+        with self._lock:
+            return list(self.active_tasks)
+
+    def get_waiting_tasks(self) -> List[Task]:
+        with self._lock:
+            return list(self.waiting_queue)
+
+    def clear_queues(self) -> None:
+        with self._lock:
+            self.waiting_queue.clear()
+            self.active_tasks.clear()
+
+    def wake(self) -> None:
+        self._task_event.set()

@@ -55,8 +55,8 @@ def _declare(lib):
         "kb_adamw_bf16": ([P, P, P, P, LL, P, F, F, F, F, F, P, F, P], I),
         "kb_flash_fwd": ([P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P], I),
         "kb_flash_bwd": ([P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, L, L, F, I, P], I),
-        "kb_paged_decode": ([P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, L, L, L, F, I, P], I),
-        "kb_paged_kv_write": ([P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, P], I),
+        "kb_paged_decode_attn": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, L, F, P], I),
+        "kb_paged_kv_write": ([P, P, P, P, P, I, I, L, L, P], I),
         "kb_sample": ([P, P, P, P, P, P, I, I, L, LL, P], I),
         "kb_gemv_bf16": ([P, P, P, P, I, I, I, L, L, L, L, P], I),
         "kb_gemv_w8": ([P, P, P, P, P, I, I, I, L, L, L, L, P], I),

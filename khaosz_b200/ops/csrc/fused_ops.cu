@@ -187,13 +187,21 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// out[col] = sum over rows of partial[row][col]; block = 32 columns x 32 row lanes.
 __global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int nrows,
                               int dim) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= dim) return;
+  __shared__ float tile[32][33];
+  const int col = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int r = 0; r < nrows; ++r) s += partial[(size_t)r * dim + col];
-  out[col] = s;
+  if (col < dim)
+    for (int r = threadIdx.y; r < nrows; r += 32) s += partial[(size_t)r * dim + col];
+  tile[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  // transpose so that a warp reduces one column
+  float v = tile[threadIdx.x][threadIdx.y];
+  v = warp_sum(v);
+  const int ocol = blockIdx.x * 32 + threadIdx.y;
+  if (threadIdx.x == 0 && ocol < dim) out[ocol] = v;
 }
 
 // =======================================================================================
@@ -551,7 +559,7 @@ int kb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rs
   rmsnorm_bwd_kernel<<<blocks, RMS_BWD_THREADS, 0, (cudaStream_t)stream>>>(
       (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres_in, (bf16*)dx,
       dw_partial, rows, dim);
-  colsum_kernel<<<(dim + 127) / 128, 128, 0, (cudaStream_t)stream>>>(dw_partial, dw, blocks, dim);
+  colsum_kernel<<<(dim + 31) / 32, dim3(32, 32), 0, (cudaStream_t)stream>>>(dw_partial, dw, blocks, dim);
   return launch_status();
 }
 
@@ -697,7 +705,7 @@ extern "C" int kb_rmsnorm_bwd_static(const void* dy, const void* x, const void* 
   if (blocks > KB_STATIC_RMS_MAX_PARTIALS) blocks = KB_STATIC_RMS_MAX_PARTIALS;  // the kernel strides over rows
   rmsnorm_bwd_kernel<<<blocks, RMS_BWD_THREADS, 0, (cudaStream_t)stream>>>(
       (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres_in, (bf16*)dx, scratch, rows, dim);
-  colsum_kernel<<<(dim + 127) / 128, 128, 0, (cudaStream_t)stream>>>(scratch, dw, blocks, dim);
+  colsum_kernel<<<(dim + 31) / 32, dim3(32, 32), 0, (cudaStream_t)stream>>>(scratch, dw, blocks, dim);
   if (cudaGetLastError() != cudaSuccess)
     return rms_static_fail(KB_STATUS_CUDA_ERROR, "kb_rmsnorm_bwd_static: kernel launch failed", 0, 0);
   return KB_STATUS_OK;
