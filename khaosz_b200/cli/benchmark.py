@@ -1,0 +1,170 @@
+"""Inference micro-benchmarks with CUDA-event timing.
+
+``prefill`` / ``decode`` follow the recipe of the reference's ``scripts/tools/benchmark.py``
+(random-init model, B x prompt tokens, 3 warm-ups, N timed trials); ``serve`` replays a
+Poisson arrival trace of random-token prompts through ``InferenceEngine`` and reports decode
+tokens/s and the median time to first token.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import random
+import threading
+import time
+
+import torch
+
+from ..config import AutoRegressiveLMConfig
+from ..inference import InferenceEngine
+from ..inference.core.cache import KVCache
+from ..models import AutoRegressiveLM
+
+PRESETS = {
+    "reference": dict(vocab_size=10000, dim=1536, n_heads=24, n_kv_heads=4, dim_ffn=6912, max_len=2048, n_layers=24,
+                      norm_eps=1e-5),
+    "1b": dict(vocab_size=32000, dim=2048, n_heads=16, n_kv_heads=4, dim_ffn=5632, max_len=4096, n_layers=24,
+               norm_eps=1e-5, tie_weight=True),
+}
+
+
+class _IdTokenizer:
+    """Token-id pass-through for synthetic load (prompts are lists of ids)."""
+
+    stop_ids: list = []
+
+    def encode(self, text, **_):
+        return list(text) if not isinstance(text, str) else [ord(c) % 1000 for c in text]
+
+    def decode(self, ids, **_):
+        return " ".join(map(str, ids))
+
+
+def build_model(preset: str, device: str, dtype):
+    cfg = AutoRegressiveLMConfig(**PRESETS[preset])
+    model = AutoRegressiveLM(cfg).to(device=device, dtype=dtype).eval()
+    if device.startswith("cuda") and dtype == torch.bfloat16:
+        model.pack_parameters(with_grad=False)
+    return cfg, model
+
+
+def _timed(fn, trials: int):
+    total = 0.0
+    for _ in range(trials):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1) / 1e3
+    return total
+
+
+@torch.inference_mode()
+def bench_prefill(model, cfg, batch: int, prompt: int, trials: int, device):
+    ids = lambda: torch.randint(0, cfg.vocab_size, (batch, prompt), device=device)
+    for _ in range(3):
+        model(ids())
+    torch.cuda.synchronize()
+    seconds = _timed(lambda: model(ids()), trials)
+    return {"benchmark": "prefill", "batch": batch, "prompt": prompt, "tokens_per_s": batch * prompt * trials / seconds}
+
+
+@torch.inference_mode()
+def bench_decode(model, cfg, batch: int, prompt: int, gen: int, trials: int, page_size: int, device, dtype):
+    n_pages = batch * ((prompt + gen + page_size - 1) // page_size + 1)
+    cache = KVCache(cfg.n_layers, n_pages, page_size, cfg.n_kv_heads, cfg.dim // cfg.n_heads, device, dtype)
+    names = [f"b{i}" for i in range(batch)]
+    for n in names:
+        cache.task_alloc(n, list(range(prompt + gen)))
+    table = cache.make_table_tensor(names, device)
+
+    def run():
+        ids = torch.randint(0, cfg.vocab_size, (batch, prompt), device=device)
+        model(ids, paged_cache=cache.bind(table, total_len=prompt), logits_rows=torch.arange(batch, device=device))
+        tok = torch.randint(0, cfg.vocab_size, (batch, 1), device=device)
+        for step in range(gen):
+            pos = torch.full((batch, 1), prompt + step, device=device, dtype=torch.long)
+            out = model(tok, paged_cache=cache.bind(table, seq_lens=pos.squeeze(1) + 1), position_ids=pos)
+            tok = out["logits"][:, -1].argmax(-1, keepdim=True)
+
+    run()
+    torch.cuda.synchronize()
+    seconds = _timed(run, trials)
+    return {"benchmark": "decode", "batch": batch, "prompt": prompt, "generated": gen,
+            "tokens_per_s": batch * gen * trials / seconds}
+
+
+def bench_serve(model, cfg, requests: int, rate: float, min_prompt: int, max_prompt: int, gen: int, max_batch: int,
+                page_size: int, seed: int):
+    rng = random.Random(seed)
+    engine = InferenceEngine(model, _IdTokenizer(), max_batch_size=max_batch, max_seq_len=max_prompt + gen + 1,
+                             max_prompt_len=max_prompt, page_size=page_size)
+    done = threading.Semaphore(0)
+    t_start = time.time()
+
+    def submit():
+        prompt = [rng.randrange(cfg.vocab_size) for _ in range(rng.randint(min_prompt, max_prompt))]
+
+        def cb(tok):
+            from ..inference.core.task import STOP
+
+            if tok is STOP:
+                done.release()
+
+        engine.scheduler.add_task(prompt, max_tokens=gen, temperature=1.0, top_p=1.0, top_k=1, stream_callback=cb)
+
+    for _ in range(requests):
+        submit()
+        if rate > 0:
+            time.sleep(rng.expovariate(rate))
+    for _ in range(requests):
+        done.acquire()
+    wall = time.time() - t_start
+    stats = engine.get_stats()
+    engine.shutdown()
+    return {"benchmark": "serve", "requests": requests, "arrival_rate_per_s": rate, "generated_per_request": gen,
+            "output_tokens_per_s_wall": requests * gen / wall, "decode_tokens_per_s_busy": stats["decode_tokens_per_s"],
+            "ttft_p50_s": stats["ttft_p50_s"], "ttft_p99_s": stats["ttft_p99_s"], "wall_s": wall}
+
+
+def parse_args(argv=None):
+    p = argparse.ArgumentParser(description="prefill / decode / serving benchmarks")
+    p.add_argument("mode", choices=["prefill", "decode", "serve", "all"], nargs="?", default="all")
+    p.add_argument("--preset", choices=sorted(PRESETS), default="reference")
+    p.add_argument("--batch_size", type=int, default=4)
+    p.add_argument("--prompt_length", type=int, default=512)
+    p.add_argument("--gen_length", type=int, default=128)
+    p.add_argument("--trials", type=int, default=5)
+    p.add_argument("--page_size", type=int, default=128)
+    p.add_argument("--requests", type=int, default=256)
+    p.add_argument("--rate", type=float, default=64.0, help="Poisson arrival rate (requests/s)")
+    p.add_argument("--min_prompt", type=int, default=128)
+    p.add_argument("--max_prompt", type=int, default=2048)
+    p.add_argument("--max_batch_size", type=int, default=256)
+    p.add_argument("--seed", type=int, default=3407)
+    p.add_argument("--device", default="cuda")
+    return p.parse_args(argv)
+
+
+def main(argv=None):
+    a = parse_args(argv)
+    dtype = torch.bfloat16
+    cfg, model = build_model(a.preset, a.device, dtype)
+    out = []
+    if a.mode in ("prefill", "all"):
+        out.append(bench_prefill(model, cfg, a.batch_size, a.prompt_length, a.trials, a.device))
+    if a.mode in ("decode", "all"):
+        out.append(bench_decode(model, cfg, a.batch_size, a.prompt_length, a.gen_length, a.trials, a.page_size,
+                                a.device, dtype))
+    if a.mode == "serve":
+        out.append(bench_serve(model, cfg, a.requests, a.rate, a.min_prompt, a.max_prompt, a.gen_length,
+                               a.max_batch_size, a.page_size if a.page_size != 128 else 16, a.seed))
+    for row in out:
+        print(json.dumps(row))
+    return out
+
+
+if __name__ == "__main__":
+    main()

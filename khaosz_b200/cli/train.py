@@ -1,0 +1,118 @@
+"""Training CLI: ``python -m khaosz_b200.cli.train --train_type seq --param_path ... --data_root_path ...``.
+
+Flag names and defaults are the reference's (``scripts/tools/train.py:15-190``); new here:
+``--parallel_mode tp``, ``--tp_size``, ``--fp8`` and ``--optimizer {adamw,muon}``.  The model
+is created in bf16, the optimizer is the fused flat AdamW and the schedule is warm-up +
+cosine over the number of optimizer steps.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+from functools import partial
+
+import torch
+
+from ..config import AutoRegressiveLMConfig, TrainConfig
+from ..data import DatasetFactory
+from ..models import AutoRegressiveLM
+from ..models.components.block import DecoderBlock
+from ..trainer import FusedAdamW, Muon, SchedulerFactory, Trainer
+
+
+def parse_args(argv=None) -> argparse.Namespace:
+    p = argparse.ArgumentParser(description="Train a decoder language model")
+    p.add_argument("--train_type", choices=["seq", "sft", "dpo", "grpo"], required=True)
+    p.add_argument("--data_root_path", type=str, required=True, help="Directory of token shards")
+    p.add_argument("--param_path", type=str, required=True, help="Directory with config.json (and weights)")
+    p.add_argument("--n_epoch", type=int, default=1)
+    p.add_argument("--batch_per_device", type=int, default=1)
+    p.add_argument("--grad_accum_steps", type=int, default=1)
+    p.add_argument("--warmup_ratio", type=float, default=0.05)
+    p.add_argument("--max_lr", type=float, default=3e-4)
+    p.add_argument("--max_grad_norm", type=float, default=1.0)
+    p.add_argument("--adamw_beta1", type=float, default=0.9)
+    p.add_argument("--adamw_beta2", type=float, default=0.95)
+    p.add_argument("--adamw_weight_decay", type=float, default=0.01)
+    p.add_argument("--optimizer", choices=["adamw", "muon"], default="adamw")
+    p.add_argument("--random_seed", type=int, default=3407)
+    p.add_argument("--num_workers", type=int, default=4)
+    p.add_argument("--no_pin_memory", dest="pin_memory", action="store_false", default=True)
+    p.add_argument("--window_size", type=int, default=None, help="Tokens per sample (default: config.max_len)")
+    p.add_argument("--stride", type=int, default=None)
+    p.add_argument("--dpo_beta", type=float, default=0.1)
+    p.add_argument("--group_size", type=int, default=4)
+    p.add_argument("--grpo_clip_eps", type=float, default=0.2)
+    p.add_argument("--grpo_kl_coef", type=float, default=0.01)
+    p.add_argument("--grpo_sync_interval", type=int, default=200)
+    p.add_argument("--label_smoothing", type=float, default=0.05)
+    p.add_argument("--gradient_checkpointing", action="store_true", default=False)
+    p.add_argument("--ckpt_interval", type=int, default=5000)
+    p.add_argument("--ckpt_dir", type=str, default="checkpoint")
+    p.add_argument("--start_epoch", type=int, default=0)
+    p.add_argument("--start_batch", type=int, default=0)
+    p.add_argument("--master_addr", type=str, default="localhost")
+    p.add_argument("--master_port", type=str, default="29500")
+    p.add_argument("--backend", type=str, default="nccl")
+    p.add_argument("--nprocs", type=int, default=1)
+    p.add_argument("--parallel_mode", choices=["none", "ddp", "fsdp", "tp"], default="none")
+    p.add_argument("--tp_size", type=int, default=None)
+    p.add_argument("--fp8", action="store_true", default=False, help="block-scaled fp8 GEMMs (tp mode)")
+    p.add_argument("--device_type", type=str, default="cuda")
+    p.add_argument("--start_method", type=str, default="spawn")
+    return p.parse_args(argv)
+
+
+def create_model(config: AutoRegressiveLMConfig):
+    return AutoRegressiveLM(config).to(dtype=torch.bfloat16)
+
+
+def create_optimizer(model, kind: str = "adamw", **kwargs):
+    if kind == "muon":
+        return Muon(model.parameters(), lr=kwargs["lr"], adamw_betas=kwargs["betas"], adamw_wd=kwargs["weight_decay"])
+    return FusedAdamW(model.parameters(), **kwargs)
+
+
+def compute_total_steps(dataset_len: int, n_epoch: int, batch_per_device: int, nprocs: int, grad_accum_steps: int) -> int:
+    per_rank = -(-dataset_len // nprocs)
+    batches = -(-per_rank // batch_per_device)
+    return (batches // grad_accum_steps) * n_epoch
+
+
+def train(args: argparse.Namespace) -> None:
+    if not os.path.exists(args.param_path):
+        raise FileNotFoundError(args.param_path)
+    if args.nprocs > 1 and args.parallel_mode == "none":
+        raise ValueError("--nprocs > 1 requires --parallel_mode to be 'ddp', 'fsdp' or 'tp'")
+    config = AutoRegressiveLMConfig.from_file(os.path.join(args.param_path, "config.json"))
+    window = args.window_size or config.max_len
+    dataset = DatasetFactory.load(train_type=args.train_type, load_path=args.data_root_path, window_size=window,
+                                  stride=args.stride)
+    total = compute_total_steps(len(dataset), args.n_epoch, args.batch_per_device, args.nprocs, args.grad_accum_steps)
+    warmup = min(int(args.warmup_ratio * total), total)
+    executor_kwargs = {"gradient_as_bucket_view": True, "broadcast_buffers": False}
+    if args.parallel_mode == "tp":
+        executor_kwargs.update(tp_size=args.tp_size or args.nprocs, fp8=args.fp8)
+    cfg = TrainConfig(
+        model_fn=partial(create_model, config), strategy=args.train_type, dataset=dataset,
+        optimizer_fn=partial(create_optimizer, kind=args.optimizer, lr=args.max_lr,
+                             betas=(args.adamw_beta1, args.adamw_beta2), weight_decay=args.adamw_weight_decay),
+        scheduler_fn=partial(SchedulerFactory.create, schedule_type="cosine", warmup_steps=warmup,
+                             lr_decay_steps=max(total - warmup, 1)),
+        ckpt_dir=args.ckpt_dir, n_epoch=args.n_epoch, batch_per_device=args.batch_per_device,
+        start_epoch=args.start_epoch, start_batch=args.start_batch, ckpt_interval=args.ckpt_interval,
+        grad_accum_steps=args.grad_accum_steps, max_grad_norm=args.max_grad_norm, random_seed=args.random_seed,
+        num_workers=args.num_workers, pin_memory=args.pin_memory, nprocs=args.nprocs, backend=args.backend,
+        master_addr=args.master_addr, master_port=args.master_port, parallel_mode=args.parallel_mode,
+        device_type=args.device_type, start_method=args.start_method,
+        gradient_checkpointing_modules=[DecoderBlock] if args.gradient_checkpointing else [],
+        executor_kwargs=executor_kwargs,
+        extra_kwargs={"beta": args.dpo_beta, "label_smoothing": args.label_smoothing, "clip_eps": args.grpo_clip_eps,
+                      "kl_coef": args.grpo_kl_coef, "group_size": args.group_size,
+                      "sync_interval": args.grpo_sync_interval})
+    Trainer(cfg).train(resume_dir=args.param_path)
+
+
+if __name__ == "__main__":
+    train(parse_args())

@@ -63,11 +63,10 @@ def _declare(lib):
         "kb_quant_fp8_1x128": ([P, P, P, I, I, L, P], I),
         "kb_quant_fp8_128x128": ([P, P, P, I, I, L, P], I),
         "kb_gemm_fp8": ([P, P, P, P, P, I, I, I, L, L, L, P], I),
-        "kb_allreduce_adamw": ([P, P, P, P, P, P, I, I, LL, P, F, F, F, F, F, F, P, P, I, P], I),
-        "kb_peer_barrier": ([P, I, I, I, P], I),
-        "kb_allreduce_bf16": ([P, P, P, I, I, LL, F, I, P], I),
-        "kb_allgather_gemm": ([P, P, P, P, P, I, I, I, I, I, I, P], I),
-        "kb_gemm_reducescatter": ([P, P, P, P, P, I, I, I, I, I, I, P], I),
+        "kb_comm_slots": ([], I),
+        "kb_reduce_adamw": ([P, P, P, P, P, P, I, I, LL, LL, P, P, P, F, F, F, F, F, P, ctypes.c_uint, P], I),
+        "kb_allreduce_bf16": ([P, P, P, I, I, LL, F, ctypes.c_uint, P], I),
+        "kb_peer_barrier": ([P, I, I, I, ctypes.c_uint, I, P], I),
         "kb_rmsnorm_bwd_static": ([P, P, P, P, P, P, P, I, I, P], I),
     }
     for name, (argtypes, restype) in sigs.items():

@@ -1,0 +1,313 @@
+// Collectives issued from inside kernels over NVLink peer memory (symmetric buffers: every
+// rank passes the same-sized buffer and knows every peer's pointer to it).
+//
+//   kb_reduce_adamw      gradient reduce-scatter + global-norm clip + sharded AdamW + parameter
+//                        all-gather for the data-parallel executors: rank r owns slice r of the
+//                        flat parameter vector, pulls that slice of every peer's gradient
+//                        (plain peer loads, or one multimem.ld_reduce through the NVSwitch),
+//                        updates it, and pushes the new values into every peer's parameter
+//                        buffer (peer stores or multimem.st).
+//   kb_allreduce_bf16    stand-alone sum all-reduce (reduce own slice, write it everywhere).
+//   kb_peer_barrier      stand-alone barrier (also the unit test of the bounded wait).
+//
+// Synchronisation: a control buffer of epoch counters, one row of `ws` words per CTA slot.
+// A barrier stores the current epoch into row[slot][my rank] of every peer (release, system
+// scope) and waits until its own row holds that epoch from every peer (acquire), for at most
+// KB_WAIT_BUDGET_NS; on expiry the kernel records KB_ERR_TIMEOUT_PEER and skips its work, so a
+// missing peer can never hang the GPU.  No TMA multicast is used anywhere.
+#include "common.cuh"
+#include "kb_api.h"
+
+namespace kb {
+namespace comm {
+
+constexpr int MAX_RANKS = 8;
+constexpr int THREADS = 512;
+
+struct Peers {
+  void* p[MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// All threads of the CTA call this.  Returns false after a timeout (error word set).
+__device__ bool cta_peer_barrier(const Peers& ctrl, int rank, int ws, int slot, uint32_t epoch, int* err,
+                                 unsigned long long budget_ns) {
+  __shared__ int s_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < ws) {
+    const int peer = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(ctrl.p[peer]) + (size_t)slot * MAX_RANKS + rank, epoch);
+    const uint32_t* mine = static_cast<const uint32_t*>(ctrl.p[rank]) + (size_t)slot * MAX_RANKS + peer;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t it = 0;
+    // epochs only grow; "at least this epoch" tolerates a peer that already moved on
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++it & 255u) == 0u && globaltimer_ns() - t0 > budget_ns) {
+        s_ok = 0;
+        if (err) atomicCAS(err, 0, KB_ERR_TIMEOUT_PEER);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__device__ __forceinline__ void acc8(float* acc, uint4 v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = unpack_bf16x2(w[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_bf16x8(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// ---------------------------------------------------------------------------------------
+// Phase 1: reduce my slice of the gradients (mean over ranks), keep it in my own gradient
+// buffer, accumulate its squared norm.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS)
+reduce_slice_kernel(Peers grads, const void* grad_mc, Peers ctrl, int rank, int ws, long long slice_off,
+                    long long slice_n, float scale, float* norm_sq_local, uint32_t epoch, int* err) {
+  __shared__ float red[32];
+  if (!cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch, err, KB_WAIT_BUDGET_NS)) return;
+  __nv_bfloat16* mine = static_cast<__nv_bfloat16*>(grads.p[rank]) + slice_off;
+  const long long nchunks = slice_n >> 3;
+  float sq = 0.f;
+  for (long long c = blockIdx.x * (long long)THREADS + threadIdx.x; c < nchunks; c += (long long)gridDim.x * THREADS) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (grad_mc != nullptr) {
+      acc8(acc, multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(grad_mc) + slice_off + c * 8));
+    } else {
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r) {
+        if (r < ws) {
+          const int peer = (rank + r) % ws;  // spread the traffic: every rank starts with itself
+          acc8(acc, *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[peer]) + slice_off + c * 8));
+        }
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0] * scale, acc[1] * scale);
+    o.y = pack_bf16x2(acc[2] * scale, acc[3] * scale);
+    o.z = pack_bf16x2(acc[4] * scale, acc[5] * scale);
+    o.w = pack_bf16x2(acc[6] * scale, acc[7] * scale);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sq += (acc[e] * scale) * (acc[e] * scale);
+    *reinterpret_cast<uint4*>(mine + c * 8) = o;
+  }
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < THREADS / 32 ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) atomicAdd(norm_sq_local, v);
+  }
+}
+
+// Phase 2 (one CTA): publish my partial squared norm to every peer, barrier, total.
+__global__ void exchange_norm_kernel(Peers norms, Peers ctrl, int rank, int ws, const float* norm_sq_local,
+                                     float* norm_sq_total, int slot, uint32_t epoch, int* err) {
+  if (threadIdx.x < ws)
+    static_cast<float*>(norms.p[threadIdx.x])[rank] = *norm_sq_local;
+  if (!cta_peer_barrier(ctrl, rank, ws, slot, epoch, err, KB_WAIT_BUDGET_NS)) return;
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    const volatile float* mine = static_cast<const volatile float*>(norms.p[rank]);
+    for (int r = 0; r < ws; ++r) t += mine[r];
+    *norm_sq_total = t;
+  }
+}
+
+// Phase 3: AdamW on my slice, new parameters to every rank, closing barrier.
+__global__ void __launch_bounds__(THREADS)
+adamw_allgather_kernel(Peers params, void* param_mc, Peers grads, Peers ctrl, int rank, int ws,
+                       long long slice_off, long long slice_n, float* m, float* v, const float* lr_step, float beta1,
+                       float beta2, float eps, float wd, const float* norm_sq_total, float max_norm, uint32_t epoch,
+                       int* err) {
+  const float lr = lr_step[0], step = lr_step[1];
+  float gs = 1.f;
+  if (max_norm > 0.f) gs = fminf(1.f, max_norm / (sqrtf(*norm_sq_total) + 1e-6f));
+  const float bc1 = 1.f - powf(beta1, step), bc2 = 1.f - powf(beta2, step);
+  const float step_size = lr / bc1, inv_sqrt_bc2 = rsqrtf(bc2), decay = 1.f - lr * wd;
+  __nv_bfloat16* p_mine = static_cast<__nv_bfloat16*>(params.p[rank]) + slice_off;
+  const __nv_bfloat16* g_mine = static_cast<const __nv_bfloat16*>(grads.p[rank]) + slice_off;
+  const long long nchunks = slice_n >> 3;
+  for (long long c = blockIdx.x * (long long)THREADS + threadIdx.x; c < nchunks; c += (long long)gridDim.x * THREADS) {
+    float pf[8] = {0}, gf[8] = {0};
+    acc8(pf, *reinterpret_cast<const uint4*>(p_mine + c * 8));
+    acc8(gf, *reinterpret_cast<const uint4*>(g_mine + c * 8));
+    float4 m0 = *reinterpret_cast<float4*>(m + c * 8), m1 = *reinterpret_cast<float4*>(m + c * 8 + 4);
+    float4 v0 = *reinterpret_cast<float4*>(v + c * 8), v1 = *reinterpret_cast<float4*>(v + c * 8 + 4);
+    float mf[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+    float vf[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float g = gf[e] * gs;
+      mf[e] = beta1 * mf[e] + (1.f - beta1) * g;
+      vf[e] = beta2 * vf[e] + (1.f - beta2) * g * g;
+      pf[e] = pf[e] * decay - step_size * mf[e] / (sqrtf(vf[e]) * inv_sqrt_bc2 + eps);
+    }
+    *reinterpret_cast<float4*>(m + c * 8) = make_float4(mf[0], mf[1], mf[2], mf[3]);
+    *reinterpret_cast<float4*>(m + c * 8 + 4) = make_float4(mf[4], mf[5], mf[6], mf[7]);
+    *reinterpret_cast<float4*>(v + c * 8) = make_float4(vf[0], vf[1], vf[2], vf[3]);
+    *reinterpret_cast<float4*>(v + c * 8 + 4) = make_float4(vf[4], vf[5], vf[6], vf[7]);
+    uint4 o;
+    o.x = pack_bf16x2(pf[0], pf[1]); o.y = pack_bf16x2(pf[2], pf[3]);
+    o.z = pack_bf16x2(pf[4], pf[5]); o.w = pack_bf16x2(pf[6], pf[7]);
+    if (param_mc != nullptr) {
+      multimem_st_bf16x8(static_cast<__nv_bfloat16*>(param_mc) + slice_off + c * 8, o);
+    } else {
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r)
+        if (r < ws) {
+          const int peer = (rank + r) % ws;
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[peer]) + slice_off + c * 8) = o;
+        }
+    }
+  }
+  cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch, err, KB_WAIT_BUDGET_NS);
+}
+
+// Stand-alone all-reduce (sum * scale) of a symmetric bf16 buffer, in place on every rank.
+__global__ void __launch_bounds__(THREADS)
+allreduce_kernel(Peers bufs, void* mc, Peers ctrl, int rank, int ws, long long n, float scale, uint32_t epoch,
+                 int* err) {
+  if (!cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch, err, KB_WAIT_BUDGET_NS)) return;
+  const long long per = (n / ws) & ~7LL;
+  const long long off = per * rank;
+  const long long cnt = (rank == ws - 1) ? (n - off) : per;
+  const long long nchunks = cnt >> 3;
+  for (long long c = blockIdx.x * (long long)THREADS + threadIdx.x; c < nchunks; c += (long long)gridDim.x * THREADS) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (mc != nullptr) {
+      acc8(acc, multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(mc) + off + c * 8));
+    } else {
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r)
+        if (r < ws)
+          acc8(acc, *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(bufs.p[(rank + r) % ws]) + off + c * 8));
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0] * scale, acc[1] * scale); o.y = pack_bf16x2(acc[2] * scale, acc[3] * scale);
+    o.z = pack_bf16x2(acc[4] * scale, acc[5] * scale); o.w = pack_bf16x2(acc[6] * scale, acc[7] * scale);
+    if (mc != nullptr) {
+      multimem_st_bf16x8(static_cast<__nv_bfloat16*>(mc) + off + c * 8, o);
+    } else {
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r)
+        if (r < ws) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bufs.p[(rank + r) % ws]) + off + c * 8) = o;
+    }
+  }
+  cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch + 1, err, KB_WAIT_BUDGET_NS);
+}
+
+__global__ void barrier_kernel(Peers ctrl, int rank, int ws, int slot, uint32_t epoch, int* err,
+                               unsigned long long budget_ns) {
+  cta_peer_barrier(ctrl, rank, ws, slot, epoch, err, budget_ns);
+}
+
+inline int grid_size() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;  // one CTA per SM: every CTA of every rank is resident, so per-CTA barriers are safe
+}
+
+inline Peers load_peers(const void* const* host_ptrs, int ws) {
+  Peers p;
+  for (int i = 0; i < MAX_RANKS; ++i) p.p[i] = i < ws ? const_cast<void*>(host_ptrs[i]) : nullptr;
+  return p;
+}
+
+}  // namespace comm
+}  // namespace kb
+
+extern "C" {
+
+// Number of control rows (CTA slots) the kernels use: kb_comm_slots() rows of 8 uint32 words.
+int kb_comm_slots(void) { return kb::comm::grid_size() + 8; }
+
+// Pointer arrays are host arrays of `ws` device pointers (peer addresses of the symmetric
+// buffers).  slice = [slice_off, slice_off + slice_n) elements, owned by this rank; slice_n and
+// slice_off are multiples of 8.  `epoch` must grow by at least 4 between calls.
+// scratch: 2 floats (local partial norm, total norm), zeroed by this call.
+int kb_reduce_adamw(const void* const* grad_ptrs, const void* const* param_ptrs, const void* const* ctrl_ptrs,
+                    const void* const* norm_ptrs, const void* grad_mc, void* param_mc, int rank, int ws,
+                    long long slice_off, long long slice_n, float* m, float* v, const float* lr_step, float beta1,
+                    float beta2, float eps, float weight_decay, float max_norm, float* scratch,
+                    unsigned int epoch, void* stream) {
+  using namespace kb::comm;
+  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || (slice_off & 7) || (slice_n & 7)) return KB_STATUS_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* err = kb::error_word(dev);
+  const Peers grads = load_peers(grad_ptrs, ws), params = load_peers(param_ptrs, ws);
+  const Peers ctrl = load_peers(ctrl_ptrs, ws), norms = load_peers(norm_ptrs, ws);
+  const int grid = grid_size();
+  cudaMemsetAsync(scratch, 0, 2 * sizeof(float), st);
+  reduce_slice_kernel<<<grid, THREADS, 0, st>>>(grads, grad_mc, ctrl, rank, ws, slice_off, slice_n, 1.f / ws, scratch,
+                                                epoch, err);
+  exchange_norm_kernel<<<1, 32, 0, st>>>(norms, ctrl, rank, ws, scratch, scratch + 1, grid, epoch + 1, err);
+  adamw_allgather_kernel<<<grid, THREADS, 0, st>>>(params, param_mc, grads, ctrl, rank, ws, slice_off, slice_n, m, v,
+                                                   lr_step, beta1, beta2, eps, weight_decay, scratch + 1, max_norm,
+                                                   epoch + 2, err);
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+int kb_allreduce_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, void* mc, int rank, int ws,
+                      long long n, float scale, unsigned int epoch, void* stream) {
+  using namespace kb::comm;
+  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || (n & 7)) return KB_STATUS_BAD_ARG;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  allreduce_kernel<<<grid_size(), THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      load_peers(buf_ptrs, ws), mc, load_peers(ctrl_ptrs, ws), rank, ws, n, scale, epoch, kb::error_word(dev));
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+// budget_ms <= 0 selects the default wait budget.
+int kb_peer_barrier(const void* const* ctrl_ptrs, int rank, int ws, int slot, unsigned int epoch, int budget_ms,
+                    void* stream) {
+  using namespace kb::comm;
+  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws) return KB_STATUS_BAD_ARG;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const unsigned long long budget = budget_ms > 0 ? (unsigned long long)budget_ms * 1000000ull : kb::KB_WAIT_BUDGET_NS;
+  barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(load_peers(ctrl_ptrs, ws), rank, ws, slot, epoch,
+                                                                 kb::error_word(dev), budget);
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+}  // extern "C"

@@ -222,7 +222,7 @@ class DDPExecutor(BaseExecutor):
         params = list(model.parameters())
         same = len({(p.dtype, p.device) for p in params}) == 1
         if same:
-            self.flat = FlatParameters(model, with_grad=True)
+            self.flat = FlatParameters(model, with_grad=True, pad_to=8 * max(get_world_size(), 1))
         if self.init_sync:
             _broadcast_parameters(model, self.flat)
         self._model = model
@@ -237,7 +237,8 @@ class DDPExecutor(BaseExecutor):
         if ws <= 1:
             return
         if self._reducer is not None:
-            self._reducer.reduce()
+            if not getattr(self, "_fused", False):
+                self._reducer.allreduce_grads()  # the optimizer cannot fuse: kernel all-reduce only
             return
         if self.flat is not None:
             dist.all_reduce(self.flat.grad)
@@ -249,10 +250,20 @@ class DDPExecutor(BaseExecutor):
                 p.grad.div_(ws)
 
     def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):
-        out = super().prepare(model, optimizer, dataloader, scheduler)
-        if self._reducer is not None and optimizer is not None and hasattr(optimizer, "attach_reducer"):
-            optimizer.attach_reducer(self._reducer)
-        return out
+        model = self._prepare_model(model)
+        self._fused = False
+        if optimizer is not None:
+            if self._reducer is not None and hasattr(optimizer, "attach_reducer"):
+                optimizer.attach_flat(self.flat, allocate=False)
+                if getattr(optimizer, "_flat", None) is not None:
+                    optimizer.attach_reducer(self._reducer)
+                    self._fused = True
+            elif self.flat is not None and hasattr(optimizer, "attach_flat"):
+                optimizer.attach_flat(self.flat)
+            optimizer = AccumOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step)
+        if scheduler is not None:
+            scheduler = AccumScheduler(scheduler, self.gradient_state)
+        return model, optimizer, dataloader, scheduler
 
 
 @ExecutorFactory.register("fsdp")
@@ -287,11 +298,15 @@ class FSDPExecutor(BaseExecutor):
 
     def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):
         model = self._prepare_model(model)
+        self._fused = False
         if optimizer is not None:
             if hasattr(optimizer, "attach_flat"):
-                optimizer.attach_flat(self.flat, shard=self.shard if get_world_size() > 1 else None)
-                if self._reducer is not None and hasattr(optimizer, "attach_reducer"):
+                use_reducer = self._reducer is not None and hasattr(optimizer, "attach_reducer")
+                optimizer.attach_flat(self.flat, shard=self.shard if get_world_size() > 1 else None,
+                                      allocate=not use_reducer)
+                if use_reducer:
                     optimizer.attach_reducer(self._reducer)
+                    self._fused = True
             elif get_world_size() > 1:
                 log.warning("fsdp: optimizer %s cannot shard its state; gradients are all-reduced and every "
                             "rank updates the full model", type(optimizer).__name__)
@@ -306,7 +321,8 @@ class FSDPExecutor(BaseExecutor):
         if ws <= 1:
             return
         if self._reducer is not None:
-            self._reducer.reduce()
+            if not self._fused:
+                self._reducer.allreduce_grads()
             return
         g = self.flat.grad
         if self.shard is None:
@@ -325,8 +341,8 @@ class FSDPExecutor(BaseExecutor):
         ws = get_world_size()
         if ws <= 1 or self.shard is None:
             return
-        if self._reducer is not None and self._reducer.gathers_params:
-            return  # the fused kernel already published the updated slice to every rank
+        if self._reducer is not None:
+            return  # fused: the kernel already published the updated slice; unfused: full update everywhere
         off, n = self.shard
         data = self.flat.data
         if dist.get_backend() == "gloo":

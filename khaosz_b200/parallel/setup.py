@@ -48,10 +48,15 @@ def _resolve_device(device_type: str, local_rank: int) -> torch.device:
 @contextlib.contextmanager
 def setup_parallel(rank: int, world_size: int, local_rank: int, backend: str = "nccl",
                    master_addr: str = "localhost", master_port: str = "29500", device_type: str = "cuda"):
-    if dist.is_available() and dist.is_initialized():
-        yield dist.group.WORLD  # an outer scope owns the group
-        return
     device = _resolve_device(device_type, local_rank)
+    if dist.is_available() and dist.is_initialized():
+        # an outer scope owns the group; still export this rank's device
+        os.environ["LOCAL_RANK"] = str(local_rank)
+        os.environ["LOCAL_DEVICE"] = str(device)
+        if device.type == "cuda":
+            torch.cuda.set_device(device)
+        yield dist.group.WORLD
+        return
     os.environ["LOCAL_RANK"] = str(local_rank)
     os.environ["WORLD_SIZE"] = str(max(world_size, 1))
     os.environ["LOCAL_DEVICE"] = str(device)

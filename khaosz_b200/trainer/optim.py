@@ -41,7 +41,7 @@ class FusedAdamW(Optimizer):
         self.last_grad_norm: Optional[torch.Tensor] = None
 
     # -- wiring done by the executors -------------------------------------------------------
-    def attach_flat(self, flat, shard: Optional[Tuple[int, int]] = None) -> None:
+    def attach_flat(self, flat, shard: Optional[Tuple[int, int]] = None, allocate: bool = True) -> None:
         """Operate on ``flat.data`` / ``flat.grad`` (optionally only ``[offset, offset+n)``)."""
         mine = {id(p) for g in self.param_groups for p in g["params"]}
         trainable = {id(p) for p in flat.params if p.requires_grad}
@@ -50,16 +50,20 @@ class FusedAdamW(Optimizer):
         self._flat, self._shard = flat, shard
         off, n = shard if shard is not None else (0, flat.numel)
         dev = flat.data.device
-        self._m = torch.zeros(n, dtype=torch.float32, device=dev)
-        self._v = torch.zeros(n, dtype=torch.float32, device=dev)
+        if allocate:
+            self._m = torch.zeros(n, dtype=torch.float32, device=dev)
+            self._v = torch.zeros(n, dtype=torch.float32, device=dev)
         self._gnorm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
         if dev.type == "cuda":
             self._lr_step_host = torch.zeros(2, dtype=torch.float32).pin_memory()
             self._lr_step_dev = torch.zeros(2, dtype=torch.float32, device=dev)
 
     def attach_reducer(self, reducer) -> None:
-        """A gradient reducer that fuses the AdamW update into its collective kernel."""
+        """A gradient reducer that fuses the AdamW update into its collective kernel; the
+        moments live with the reducer and cover this rank's slice only."""
         self._reducer = reducer
+        if self._flat is not None:
+            self._m, self._v, self._shard = reducer.moments()
 
     def fused_clip(self, max_norm: Optional[float]) -> None:
         """Clip to ``max_norm`` (global L2 norm over all ranks' shards) inside the next step."""
@@ -193,14 +197,25 @@ class FusedAdamW(Optimizer):
 
 
 def newton_schulz_orthogonalize(G: torch.Tensor, steps: int = 5) -> torch.Tensor:
-    """Quintic Newton-Schulz iteration pushing the singular values of ``G`` towards 1."""
+    """Quintic Newton-Schulz iteration pushing the singular values of ``G`` towards 1, times
+    ``sqrt(max(1, rows / cols))``.
+
+    The iteration runs on the unit-Frobenius-norm matrix (on its transpose when it is tall, so
+    the Gram matrix is the small one) and the aspect-ratio factor is applied afterwards.  The
+    reference multiplies by that factor *before* iterating (``astrai/trainer/optim.py:5-17``),
+    which pushes low-rank tall matrices such as embedding gradients outside the convergence
+    region of the polynomial and produces NaNs.
+    """
     assert G.ndim == 2
-    X = G / (G.norm() + 1e-7) * math.sqrt(max(1.0, G.size(0) / G.size(1)))
+    tall = G.size(0) > G.size(1)
+    X = G.t() if tall else G
+    X = X / (X.norm() + 1e-7)
     a, b, c = 3.4445, -4.7750, 2.0315
     for _ in range(steps):
         A = X @ X.t()
         X = a * X + (b * A + c * (A @ A)) @ X
-    return X
+    X = X.t() if tall else X
+    return X * math.sqrt(max(1.0, G.size(0) / G.size(1)))
 
 
 class Muon(Optimizer):

@@ -58,6 +58,25 @@ class FlatParameters:
                     p.main_grad = g
                     p.grad = g
 
+    def rebind(self, data: torch.Tensor, grad: Optional[torch.Tensor] = None) -> None:
+        """Move the storage to new buffers of the same layout (e.g. symmetric memory) and
+        re-point every parameter / gradient view."""
+        assert data.numel() >= self.numel and data.dtype == self.data.dtype
+        with torch.no_grad():
+            data[: self.numel].copy_(self.data[: self.numel])
+            self.data = data
+            for p, o in zip(self.params, self.offsets):
+                p.data = data[o:o + p.numel()].view(p.shape)
+            if grad is not None:
+                if self.grad is not None:
+                    grad[: self.numel].copy_(self.grad[: self.numel])
+                self.grad = grad
+                for p, o in zip(self.params, self.offsets):
+                    if p.requires_grad:
+                        g = grad[o:o + p.numel()].view(p.shape)
+                        p.main_grad = g
+                        p.grad = g
+
     def zero_grad(self) -> None:
         if self.grad is not None:
             self.grad.zero_()

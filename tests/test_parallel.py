@@ -1,0 +1,171 @@
+"""Process launch and executor parity on CPU (gloo, world size 2)."""
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from khaosz_b200.parallel import ExecutorFactory, only_on_rank, spawn_parallel_fn
+
+
+def _allreduce(out_dir):
+    t = torch.tensor([float(dist.get_rank() + 1)])
+    dist.all_reduce(t)
+    assert t.item() == 3.0
+
+    @only_on_rank(0)
+    def mark():
+        open(os.path.join(out_dir, f"rank{dist.get_rank()}"), "w").close()
+        return "done"
+
+    assert mark() == ("done" if dist.get_rank() == 0 else None)
+
+
+def test_spawn_gloo_default_device_type(tmp_path):
+    spawn_parallel_fn(_allreduce, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29621",
+                      out_dir=str(tmp_path))
+    assert os.listdir(tmp_path) == ["rank0"]
+
+
+def _fail_on_rank1():
+    if dist.get_rank() == 1:
+        raise RuntimeError("rank 1 dies")
+    dist.barrier()  # never completes: the launcher has to tear this rank down
+
+
+def test_spawn_propagates_child_failure():
+    os.environ["GLOO_SOCKET_TIMEOUT"] = "5"
+    with pytest.raises(Exception):
+        spawn_parallel_fn(_fail_on_rank1, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29622")
+
+
+def test_single_process_runs_inline():
+    seen = []
+    spawn_parallel_fn(lambda: seen.append(os.environ["WORLD_SIZE"]), world_size=1, device_type="cpu")
+    assert seen == ["1"]
+
+
+# ---- BASELINE config 1: tiny decoder, next-token training, 10 steps, DDP/FSDP on gloo == single process ----
+def _tiny_cfg():
+    from khaosz_b200 import AutoRegressiveLMConfig
+
+    return AutoRegressiveLMConfig(vocab_size=1000, dim=128, n_layers=2, norm_eps=1e-5, dim_ffn=384, tie_weight=False,
+                                  max_len=128, rope_theta=1e4, n_heads=4, n_kv_heads=2)
+
+
+def _make_model():
+    from khaosz_b200 import AutoRegressiveLM
+    from khaosz_b200.models.components.layers import Linear
+
+    torch.manual_seed(3407)
+    m = AutoRegressiveLM(_tiny_cfg())
+    for mod in m.modules():
+        if isinstance(mod, Linear):
+            torch.nn.init.normal_(mod.weight, 0.0, 0.02)
+    return m
+
+
+def _run_steps(mode, world, rank, steps=10, accum=1, fused=True):
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    g = torch.Generator().manual_seed(3407)
+    data = torch.randint(0, 1000, (steps * accum, 2 * world, 129), generator=g)  # global batch = 2 per rank
+    model = _make_model()
+    ex = ExecutorFactory.create(mode, grad_accum_steps=accum)
+    if fused:
+        opt = FusedAdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.01)
+    else:
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.01)
+    model, opt, _, _ = ex.prepare(model, opt, None, None)
+    strat = StrategyFactory.create("seq", model, "cpu", label_smoothing=0.05)
+    losses = []
+    for i in range(steps * accum):
+        mine = data[i, 2 * rank:2 * rank + 2]
+        with ex.accumulate(model):
+            loss = strat({"input_ids": mine[:, :-1], "target_ids": mine[:, 1:]})
+            ex.backward(loss / accum)
+            if ex.sync_gradients:
+                if hasattr(opt, "fused_clip"):
+                    opt.fused_clip(1.0)
+                else:
+                    torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+                opt.step()
+                opt.zero_grad()
+        t = loss.detach().clone()
+        if world > 1:
+            dist.all_reduce(t)
+            t /= world
+        losses.append(t.item())
+    return losses, {k: v.detach().clone() for k, v in ex.unwrap_model(model).items()}
+
+
+def _distributed_case(mode, out):
+    losses, sd = _run_steps(mode, dist.get_world_size(), dist.get_rank())
+    if dist.get_rank() == 0:
+        torch.save({"losses": losses, "sd": sd}, out)
+
+
+def _single_reference():
+    """Single process over the *global* batch (4 sequences) == the average of two ranks."""
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    g = torch.Generator().manual_seed(3407)
+    data = torch.randint(0, 1000, (10, 4, 129), generator=g)
+    model = _make_model()
+    opt = FusedAdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.01)
+    strat = StrategyFactory.create("seq", model, "cpu", label_smoothing=0.05)
+    losses = []
+    for i in range(10):
+        loss = strat({"input_ids": data[i, :, :-1], "target_ids": data[i, :, 1:]})
+        loss.backward()
+        opt.fused_clip(1.0)
+        opt.step()
+        opt.zero_grad()
+        losses.append(loss.item())
+    return losses, model.state_dict()
+
+
+@pytest.mark.parametrize("mode,port", [("ddp", "29631"), ("fsdp", "29632")])
+def test_executor_matches_single_process(mode, port, tmp_path):
+    out = str(tmp_path / "r.pt")
+    spawn_parallel_fn(_distributed_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port=port,
+                      mode=mode, out=out)
+    got = torch.load(out)
+    ref_losses, ref_sd = _single_reference()
+    assert got["losses"] == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
+    assert got["losses"][-1] < got["losses"][0]
+    for k, v in ref_sd.items():
+        assert torch.allclose(got["sd"][k], v, rtol=1e-3, atol=2e-5), k
+
+
+def test_fused_adamw_matches_torch_adamw():
+    a, _ = _run_steps("none", 1, 0, steps=4, fused=True)
+    b, _ = _run_steps("none", 1, 0, steps=4, fused=False)
+    assert a == pytest.approx(b, rel=1e-5, abs=1e-6)
+
+
+def test_grad_accumulation_equals_big_batch():
+    # 2 micro-batches of 2 == one batch of 4 (same data order)
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    g = torch.Generator().manual_seed(1)
+    data = torch.randint(0, 1000, (2, 2, 129), generator=g)
+    m1, m2 = _make_model(), _make_model()
+    ex = ExecutorFactory.create("none", grad_accum_steps=2)
+    o1 = FusedAdamW(m1.parameters(), lr=1e-3)
+    m1, o1, _, _ = ex.prepare(m1, o1, None, None)
+    s1 = StrategyFactory.create("seq", m1, "cpu")
+    for i in range(2):
+        with ex.accumulate(m1):
+            ex.backward(s1({"input_ids": data[i, :, :-1], "target_ids": data[i, :, 1:]}) / 2)
+            assert ex.sync_gradients == (i == 1)
+            o1.step()
+            o1.zero_grad()
+    o2 = FusedAdamW(m2.parameters(), lr=1e-3)
+    s2 = StrategyFactory.create("seq", m2, "cpu")
+    big = data.reshape(4, 129)
+    s2({"input_ids": big[:, :-1], "target_ids": big[:, 1:]}).backward()
+    o2.step()
+    for (k, a), b in zip(m1.state_dict().items(), m2.state_dict().values()):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-6), k

@@ -1,0 +1,125 @@
+import json
+
+import pytest
+from fastapi.testclient import TestClient
+
+from khaosz_b200.inference.api import (AnthropicResponseBuilder, OpenAIResponseBuilder, StopChecker, StopInfo, app,
+                                       sse_done, sse_event)
+from khaosz_b200.inference.api.protocol import GenContext
+
+
+class FakeTokenizer:
+    def apply_chat_template(self, messages, tokenize=False, **_):
+        return "".join(f"[{m['role']}]{m['content']}" for m in messages)
+
+    def encode(self, text, **_):
+        return list(range(len(text.split()) + 1))
+
+
+class FakeEngine:
+    def __init__(self, tokens):
+        self.tokens, self.tokenizer, self.calls = tokens, FakeTokenizer(), []
+
+    def generate_async(self, prompt, **kw):
+        self.calls.append((prompt, kw))
+
+        async def gen():
+            for t in self.tokens:
+                yield t
+
+        return gen()
+
+    def get_stats(self):
+        return {"total_tasks": 1, "total_tokens": 3, "active_tasks": 0, "waiting_queue": 0}
+
+    def shutdown(self):
+        pass
+
+
+@pytest.fixture
+def client():
+    app.state.server_config = {"_test": True}
+    app.state.engine = FakeEngine(["Hello", " wor", "ld", "!", " END", " tail"])
+    with TestClient(app) as c:
+        yield c
+    app.state.engine = None
+
+
+def _events(text):
+    out = []
+    for line in text.splitlines():
+        if line.startswith("data: ") and line != "data: [DONE]":
+            out.append(json.loads(line[6:]))
+    return out
+
+
+def test_health_and_stats(client):
+    assert client.get("/health").json() == {"status": "ok", "model_loaded": True}
+    assert client.get("/stats").json()["total_tasks"] == 1
+    app.state.engine = None
+    assert client.get("/health").json()["model_loaded"] is False
+    assert client.get("/stats").status_code == 503
+
+
+def test_openai_non_stream_keeps_stop_sequence(client):
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "stop": "END",
+                                                  "max_tokens": 16, "top_k": 5})
+    body = r.json()
+    assert body["object"] == "chat.completion" and body["choices"][0]["finish_reason"] == "stop"
+    assert body["choices"][0]["message"] == {"role": "assistant", "content": "Hello world! END"}
+    assert body["usage"]["completion_tokens"] == 4 and body["usage"]["total_tokens"] == body["usage"]["prompt_tokens"] + 4
+    prompt, kw = app.state.engine.calls[0]
+    assert prompt == "[user]hi" and kw["max_tokens"] == 16 and kw["top_k"] == 5 and kw["temperature"] == 1.0
+
+
+def test_openai_stream(client):
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "stream": True,
+                                                  "stop": ["END"]})
+    assert r.headers["content-type"].startswith("text/event-stream") and r.text.rstrip().endswith("data: [DONE]")
+    ev = _events(r.text)
+    assert ev[0]["choices"][0]["delta"] == {"role": "assistant"}
+    assert "".join(e["choices"][0]["delta"].get("content", "") for e in ev if "choices" in e) == "Hello world!"
+    assert ev[-2]["choices"][0]["finish_reason"] == "stop" and ev[-1]["completion_tokens"] == 4
+
+
+def test_anthropic_non_stream_trims_stop_sequence(client):
+    r = client.post("/v1/messages", json={"messages": [{"role": "user", "content": [{"type": "text", "text": "hi"}]}],
+                                          "system": "be nice", "stop_sequences": ["END"], "max_tokens": 32})
+    body = r.json()
+    assert body["type"] == "message" and body["content"] == [{"type": "text", "text": "Hello world! "}]
+    assert body["stop_reason"] == "stop_sequence" and body["stop_sequence"] == "END"
+    assert app.state.engine.calls[0][0] == "[system]be nice[user]hi"
+    body = client.post("/v1/messages", json={"messages": [{"role": "user", "content": "hi"}]}).json()
+    assert body["stop_reason"] == "end_turn" and body["content"][0]["text"].endswith(" tail")
+
+
+def test_anthropic_stream_event_order(client):
+    r = client.post("/v1/messages", json={"messages": [{"role": "user", "content": "hi"}], "stream": True,
+                                          "stop_sequences": ["ld"]})
+    names = [l[7:] for l in r.text.splitlines() if l.startswith("event: ")]
+    assert names[:2] == ["message_start", "content_block_start"]
+    assert names[-3:] == ["content_block_stop", "message_delta", "message_stop"]
+    ev = _events(r.text)
+    text = "".join(e["delta"]["text"] for e in ev if e.get("type") == "content_block_delta")
+    assert text == "Hello wor"
+    delta = [e for e in ev if e.get("type") == "message_delta"][0]
+    assert delta["delta"]["stop_reason"] == "stop_sequence" and delta["usage"]["output_tokens"] == 2
+
+
+def test_request_validation(client):
+    assert client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "top_k": 0}).status_code == 422
+    assert client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "temperature": 3}).status_code == 422
+    assert client.post("/v1/messages", json={"messages": [], "max_tokens": 0}).status_code == 422
+
+
+def test_protocol_helpers():
+    assert sse_event({"a": 1}) == 'data: {"a": 1}\n\n' and sse_event({"a": 1}, event="x").startswith("event: x\ndata: ")
+    assert sse_done() == "data: [DONE]\n\n"
+    assert StopChecker(["", "ab"]).check("xxabyy") == "ab" and StopChecker([]).check("anything") is None
+    b = AnthropicResponseBuilder()
+    ctx = GenContext("id", 0, "m", 3, 2)
+    events = b.format_stream_end(ctx, StopInfo(matched="END", body="abc END", yielded="ab"))
+    assert '"text": "c "' in events[0]   # un-streamed text before the stop sequence is flushed
+    o = OpenAIResponseBuilder()
+    o._resp_id, o._model = "r", "m"
+    assert json.loads(o.format_chunk("t")[6:])["created"] == 0
