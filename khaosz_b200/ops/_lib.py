@@ -41,6 +41,7 @@ def _declare(lib):
         "kb_sm_count": ([], I),
         "kb_last_tmap_error": ([], I),
         "kb_gemm_bf16": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, P], I),
+        "kb_gemm_bf16_bn": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P], I),
         "kb_rmsnorm_fwd": ([P, P, P, P, P, P, I, I, F, P], I),
         "kb_rmsnorm_bwd_partials": ([I], I),
         "kb_rmsnorm_bwd": ([P, P, P, P, P, P, P, P, I, I, P], I),

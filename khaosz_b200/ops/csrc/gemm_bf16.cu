@@ -6,7 +6,8 @@
 // ([N,K] or [K,N]).  That covers the three products of a linear layer without any
 // transposed copy: forward (K,K), input gradient (K,MN) and weight gradient (MN,MN).
 //
-// Structure: persistent kernel, one CTA per SM, 128x256 output tile, BK=64.
+// Structure: persistent kernel, one CTA per SM, 128 x BN output tile (BN = 256, 192 or 128,
+// chosen per problem to minimise idle SM-waves), BK=64.
 //   warp 0      TMA producer: 4-stage ring of 128B-swizzled A/B tiles (cp.async.bulk.tensor,
 //               no cluster multicast), completion on "full" mbarriers
 //   warp 1      allocates 512 TMEM columns (two 128x256 fp32 accumulators) and issues
@@ -23,21 +24,26 @@ namespace kb {
 namespace gemm {
 
 constexpr int BM = 128;
-constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int ATOM_BYTES = BK * 128;        // one 64-wide MN atom of an MN-major tile
 constexpr int EPI_COLS = 64;
 constexpr int EPI_BUF_BYTES = BM * EPI_COLS * 2;  // 16 KiB
 constexpr int NUM_EPI_BUFS = 2;
-constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES =
-    STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + NUM_EPI_BUFS * EPI_BUF_BYTES + 256 + 1024;
+
+// The N extent of the tile is a template parameter (256, 192 or 128): the launcher picks the
+// one that wastes the fewest SM-waves for the problem at hand.
+template <int BN>
+struct Cfg {
+  static constexpr int STAGES = BN == 128 ? 6 : 4;
+  static constexpr int B_STAGE_BYTES = BN * BK * 2;
+  static constexpr int TMEM_COLS = BN == 128 ? 256 : 512;
+  static constexpr int SMEM_BYTES =
+      STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + NUM_EPI_BUFS * EPI_BUF_BYTES + 256 + 1024;
+};
 
 struct Params {
   const __nv_bfloat16* R;  // optional addend [M,N]
@@ -58,10 +64,14 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   n_blk = r / gm;
 }
 
+template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, const Params p) {
+  constexpr int STAGES = Cfg<BN>::STAGES;
+  constexpr int B_STAGE_BYTES = Cfg<BN>::B_STAGE_BYTES;
+  constexpr int TMEM_COLS = Cfg<BN>::TMEM_COLS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -277,39 +287,71 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }  // namespace gemm
 }  // namespace kb
 
-extern "C" int kb_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N,
-                            int K, long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn,
-                            int epi, void* stream) {
+namespace kb {
+namespace gemm {
+
+template <int BN>
+static int launch(const void* A, const void* B, void* C, const Params& p, long lda, long ldb, long ldc, int grid_cap,
+                  cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg<BN>::SMEM_BYTES) != cudaSuccess)
+      return KB_STATUS_CUDA_ERROR;
+    attr_set = true;
+  }
+  CUtensorMap ta, tb, tc;
+  int rc;
+  if (!p.a_mn) rc = kb::make_tmap_2d(&ta, A, 2, p.M, p.K, lda * 2, BM, BK, true);
+  else         rc = kb::make_tmap_2d(&ta, A, 2, p.K, p.M, lda * 2, BK, 64, true);
+  if (rc) return KB_STATUS_TMAP_ERROR;
+  if (!p.b_mn) rc = kb::make_tmap_2d(&tb, B, 2, p.N, p.K, ldb * 2, BN, BK, true);
+  else         rc = kb::make_tmap_2d(&tb, B, 2, p.K, p.N, ldb * 2, BK, 64, true);
+  if (rc) return KB_STATUS_TMAP_ERROR;
+  rc = kb::make_tmap_2d(&tc, C, 2, p.M, p.N, ldc * 2, BM, EPI_COLS, true);
+  if (rc) return KB_STATUS_TMAP_ERROR;
+  const int total = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = total < grid_cap ? total : grid_cap;
+  gemm_bf16_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, tc, p);
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+// Estimated relative cost of running the problem with tile width bn: SM-waves times the work of
+// one tile, with a small penalty for the lower operand reuse of narrower tiles.
+static double tile_cost(int M, int N, int bn, int sms) {
+  const long tiles = (long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  const long waves = (tiles + sms - 1) / sms;
+  // measured on B200: narrower tiles are shared-memory-bandwidth bound (A is re-read per tile),
+  // a 192-wide tile runs at ~79 % and a 128-wide one at ~58 % of the 256-wide tile's rate
+  const double per_tile = bn == 256 ? 1.0 : bn == 192 ? 0.95 : 0.88;
+  return waves * per_tile;
+}
+
+}  // namespace gemm
+}  // namespace kb
+
+extern "C" int kb_gemm_bf16_bn(const void* A, const void* B, void* C, const void* R, int M, int N,
+                               int K, long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn,
+                               int epi, int bn, void* stream) {
   using namespace kb::gemm;
   if (M <= 0 || N <= 0 || K <= 0) return KB_STATUS_BAD_ARG;
   auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
   if (misaligned(A) || misaligned(B) || misaligned(C) || (lda & 7) || (ldb & 7) || (ldc & 7))
     return KB_STATUS_BAD_ARG;
   if (epi == 1 && (R == nullptr || misaligned(R) || (ldr & 7) || (N & 7))) return KB_STATUS_BAD_ARG;
-
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return KB_STATUS_CUDA_ERROR;
-    attr_set = true;
-  }
   int dev = 0;
   cudaGetDevice(&dev);
   static int sm_count[64] = {0};
   if (sm_count[dev] == 0) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-
-  CUtensorMap ta, tb, tc;
-  int rc;
-  if (!a_mn) rc = kb::make_tmap_2d(&ta, A, 2, M, K, lda * 2, BM, BK, true);
-  else       rc = kb::make_tmap_2d(&ta, A, 2, K, M, lda * 2, BK, 64, true);
-  if (rc) return KB_STATUS_TMAP_ERROR;
-  if (!b_mn) rc = kb::make_tmap_2d(&tb, B, 2, N, K, ldb * 2, BN, BK, true);
-  else       rc = kb::make_tmap_2d(&tb, B, 2, K, N, ldb * 2, BK, 64, true);
-  if (rc) return KB_STATUS_TMAP_ERROR;
-  rc = kb::make_tmap_2d(&tc, C, 2, M, N, ldc * 2, BM, EPI_COLS, true);
-  if (rc) return KB_STATUS_TMAP_ERROR;
-
+  const int sms = sm_count[dev];
+  if (bn == 0) {
+    bn = 256;
+    double best = tile_cost(M, N, 256, sms);
+    for (int cand : {192, 128}) {
+      const double c = tile_cost(M, N, cand, sms);
+      if (c < best * 0.999) { best = c; bn = cand; }
+    }
+  }
   Params p;
   p.R = static_cast<const __nv_bfloat16*>(R);
   p.ldr = ldr;
@@ -317,10 +359,17 @@ extern "C" int kb_gemm_bf16(const void* A, const void* B, void* C, const void* R
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.epi = epi;
   p.err = kb::error_word(dev);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (bn) {
+    case 256: return launch<256>(A, B, C, p, lda, ldb, ldc, sms, st);
+    case 192: return launch<192>(A, B, C, p, lda, ldb, ldc, sms, st);
+    case 128: return launch<128>(A, B, C, p, lda, ldb, ldc, sms, st);
+    default: return KB_STATUS_BAD_ARG;
+  }
+}
 
-  const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
-  const int total = num_m * num_n;
-  const int grid = total < sm_count[dev] ? total : sm_count[dev];
-  gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ta, tb, tc, p);
-  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+extern "C" int kb_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N,
+                            int K, long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn,
+                            int epi, void* stream) {
+  return kb_gemm_bf16_bn(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, epi, 0, stream);
 }

@@ -30,6 +30,12 @@ const char* kb_version(void);
 int kb_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
                  long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn, int epi, void* stream);
 
+// Same with an explicit tile width bn in {256, 192, 128}; bn = 0 picks the width that wastes the
+// fewest SM-waves.
+int kb_gemm_bf16_bn(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                    long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn, int epi, int bn,
+                    void* stream);
+
 // ---- normalisation ------------------------------------------------------------------
 // y = rmsnorm(x (+ res)) * w ; when res != NULL the sum x+res is also written to sum_out.
 int kb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out,

@@ -97,3 +97,21 @@ def test_gemm_throughput_report():
         ms_ref = e0.elapsed_time(e1) / 10
         print(f"GEMM {M}x{N}x{K}: {2 * M * N * K / ms / 1e9:.0f} TFLOP/s (cuBLAS {2 * M * N * K / ms_ref / 1e9:.0f})")
     ops.raise_on_device_error()
+
+
+@pytest.mark.parametrize("bn", [128, 192, 256])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm_tile_widths(bn, a_mn, b_mn):
+    from khaosz_b200.ops._lib import check, lib, ptr, stream
+
+    M, N, K = 1160, 1992, 712
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+    r = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    check(lib().kb_gemm_bf16_bn(ptr(a), ptr(b), ptr(out), ptr(r), M, N, K, a.stride(0), b.stride(0), N, N, int(a_mn),
+                                int(b_mn), 1, bn, stream()), "gemm_bn")
+    torch.cuda.synchronize()
+    ops.raise_on_device_error()
+    ref = _ref(a, b, a_mn, b_mn, r)
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
