@@ -42,6 +42,7 @@ def _declare(lib):
         "kb_last_tmap_error": ([], I),
         "kb_gemm_bf16": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, P], I),
         "kb_gemm_bf16_bn": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P], I),
+        "kb_gemm_bf16_pair": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, P], I),
         "kb_rmsnorm_fwd": ([P, P, P, P, P, P, I, I, F, P], I),
         "kb_rmsnorm_bwd_partials": ([I], I),
         "kb_rmsnorm_bwd": ([P, P, P, P, P, P, P, P, I, I, P], I),
@@ -59,8 +60,8 @@ def _declare(lib):
         "kb_paged_decode_attn": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, L, F, P], I),
         "kb_paged_kv_write": ([P, P, P, P, P, I, I, L, L, P], I),
         "kb_sample": ([P, P, P, P, P, P, I, I, L, LL, P], I),
-        "kb_gemv_bf16": ([P, P, P, P, I, I, I, L, L, L, L, P], I),
-        "kb_gemv_w8": ([P, P, P, P, P, I, I, I, L, L, L, L, P], I),
+        "kb_gemm_w8": ([P, P, P, P, I, I, I, L, L, L, P], I),
+        "kb_quant_w8": ([P, P, P, I, I, P], I),
         "kb_quant_fp8_1x128": ([P, P, P, I, I, L, P], I),
         "kb_quant_fp8_128x128": ([P, P, P, I, I, L, P], I),
         "kb_gemm_fp8": ([P, P, P, P, P, I, I, I, L, L, L, P], I),

@@ -115,3 +115,64 @@ def test_gemm_tile_widths(bn, a_mn, b_mn):
     ops.raise_on_device_error()
     ref = _ref(a, b, a_mn, b_mn, r)
     assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+def _pair(a, b, out, r, M, N, K, a_mn, b_mn):
+    from khaosz_b200.ops._lib import check, lib, ptr, stream
+
+    check(lib().kb_gemm_bf16_pair(ptr(a), ptr(b), ptr(out), ptr(r), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+                                  r.stride(0) if r is not None else 0, int(a_mn), int(b_mn), 1 if r is not None else 0,
+                                  stream()), "gemm_pair")
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 256), (1160, 1992, 712), (2048, 4096, 320), (136, 520, 2048)])
+def test_gemm_cta_pair(shape, a_mn, b_mn):
+    M, N, K = shape
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+    r = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    _pair(a, b, out, r, M, N, K, a_mn, b_mn)
+    torch.cuda.synchronize()
+    ops.raise_on_device_error()
+    ref = _ref(a, b, a_mn, b_mn, r)
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+def test_gemm_cta_pair_throughput_report():
+    shapes = [(8192, 3072, 2048), (8192, 2048, 2048), (8192, 11264, 2048), (8192, 2048, 5632), (8192, 32000, 2048)]
+    for (M, N, K) in shapes:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for _ in range(3):
+            _pair(a, b, out, None, M, N, K, False, False)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            _pair(a, b, out, None, M, N, K, False, False)
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"pair GEMM {M}x{N}x{K}: {2 * M * N * K / (e0.elapsed_time(e1) / 10) / 1e9:.0f} TFLOP/s")
+    ops.raise_on_device_error()
+
+
+@pytest.mark.parametrize("M,N,K", [(4, 2048, 2048), (256, 5632, 2048), (130, 520, 528), (1024, 2048, 5632)])
+def test_int8_weight_gemm(M, N, K):
+    from khaosz_b200.ops.quant import linear_w8, quantize_w8
+
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    q, scale = quantize_w8(w)
+    q_ref, scale_ref = quantize_w8(w.cpu())
+    assert (q.cpu().int() - q_ref.int()).abs().max().item() <= 1 and torch.allclose(scale.cpu(), scale_ref, rtol=1e-3)
+    out = linear_w8(x, q, scale)
+    torch.cuda.synchronize()
+    ops.raise_on_device_error()
+    ref = x.float() @ (q.float() * scale[:, None]).t()
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+    # and the quantisation error itself stays small against the bf16 weights
+    full = x.float() @ w.float().t()
+    assert (ref - full).abs().max().item() <= 0.05 * full.abs().max().item() + 0.05

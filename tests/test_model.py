@@ -209,3 +209,16 @@ def test_lora_rank_mismatch(tmp_path):
     inject_lora(b, r=2, alpha=8)
     with pytest.raises(RuntimeError, match="size mismatch"):
         load_lora(b, str(tmp_path / "ad"))
+
+
+def test_int8_weight_only_model_close_to_full_precision():
+    from khaosz_b200.ops.quant import Int8Linear, quantize_model_int8
+
+    torch.manual_seed(0)
+    model = AutoRegressiveLM(tiny_config()).eval()
+    ids = torch.randint(0, 300, (2, 12))
+    ref = model(ids)["logits"]
+    n = quantize_model_int8(model)
+    assert n == 2 * 7 and isinstance(model.layers[0].attention.q_proj, Int8Linear)
+    got = model(ids)["logits"]
+    assert (got - ref).abs().max().item() < 0.05 * ref.abs().max().item() + 0.02
