@@ -1,0 +1,371 @@
+// GEMMs fused with their collective over NVLink peer memory (tensor-parallel layers and
+// sharded-weight data parallelism).  One persistent tcgen05 kernel, three fusions:
+//
+//   all-gather -> GEMM    an operand whose rows are sharded over the ranks (sequence-sharded
+//                         activations for column-parallel layers, or row-sharded weights under
+//                         FSDP) is never assembled: the TMA producer reads every tile straight
+//                         from the rank that owns it (plain cp.async.bulk.tensor on a peer
+//                         pointer, no multicast), local tiles first, then the peers in ring order.
+//   GEMM -> reduce-scatter  each finished output tile is TMA-stored into the owner rank's staging
+//                         slot for this source rank while the next tile is being computed;
+//                         after a grid-wide + cross-rank barrier every rank sums the slots of
+//                         the rows it owns (fixed order: deterministic).
+//   GEMM -> all-reduce    same, but the tile goes to every rank's staging buffer and every rank
+//                         sums all rows (decode-time row-parallel layers).
+//
+// Operands may be K-major or MN-major exactly as in gemm_bf16.cu; for an MN-major gathered
+// operand the sharded dimension is the reduction dimension and the source rank changes per
+// k-block instead of per tile.  All waits (mbarriers, peer flags, the grid barrier) are bounded.
+#include "comm.cuh"
+#include "kb_api.h"
+
+namespace kb {
+namespace gcomm {
+
+using comm::MAX_RANKS;
+using comm::Peers;
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int ATOM_BYTES = BK * 128;
+constexpr int EPI_COLS = 64;
+constexpr int EPI_BUF_BYTES = BM * EPI_COLS * 2;
+constexpr int NUM_EPI_BUFS = 2;
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + NUM_EPI_BUFS * EPI_BUF_BYTES + 256 + 1024;
+
+struct Maps {
+  CUtensorMap m[MAX_RANKS];
+};
+
+struct Params {
+  int M, N, K;        // full problem seen by this rank
+  int a_mn, b_mn;
+  int a_gather;       // rows of the stored A are sharded: a_rows rows per rank
+  int b_gather;
+  int a_rows, b_rows;
+  int c_mode;         // 0 local store, 1 reduce-scatter, 2 all-reduce
+  int c_rows;         // output rows owned per rank (c_mode 1) or M (c_mode 2)
+  int c_slot_rows;    // rows between two source ranks' slots in a staging buffer (multiple of 128)
+  int rank, ws;
+  uint32_t epoch;
+  Peers ctrl;
+  const __nv_bfloat16* stage;  // this rank's staging buffer [ws, c_rows, N]
+  __nv_bfloat16* out;          // reduced output [c_rows, N] (c_mode != 0)
+  long ldo;
+  unsigned int* grid_sync;     // two words, zero before the first launch
+  int* err;
+};
+
+// Map index + coordinate inside that rank's shard for a stored row index.
+__device__ __forceinline__ void locate(int row, int rows_per_rank, int gather, int& which, int& local_row) {
+  if (gather) {
+    which = row / rows_per_rank;
+    local_row = row - which * rows_per_rank;
+  } else {
+    which = 0;
+    local_row = row;
+  }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Maps maps_b,
+                 const __grid_constant__ Maps maps_c, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint8_t* sEpi = sB + STAGES * B_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + NUM_EPI_BUFS * EPI_BUF_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN, num_k = (p.K + BK - 1) / BK;
+  const int total = num_m * num_n;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Every rank's inputs are complete (and its staging buffer free) before anyone reads or writes
+  // peer memory.
+  bool peers_ok = true;
+  if (p.ws > 1) peers_ok = comm::cta_peer_barrier(p.ctrl, p.rank, p.ws, blockIdx.x, p.epoch, p.err, KB_WAIT_BUDGET_NS);
+
+  // Tile order: rotate the m-tiles (K-major gathered A) so that this rank starts with its own
+  // shard and the ranks walk the ring in step, spreading the load over the links.
+  const int m_rot = (p.a_gather && !p.a_mn) ? (p.rank * p.a_rows) / BM : 0;
+  auto tile_of = [&](int t, int& m_blk, int& n_blk) {
+    m_blk = (t % num_m + m_rot) % num_m;
+    n_blk = t / num_m;
+  };
+
+  if (warp == 0) {
+    if (lane == 0 && peers_ok) {
+      int s = 0; uint32_t ph = 0; bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_of(t, m_blk, n_blk);
+        const int m0 = m_blk * BM, n0 = n_blk * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(&full[s], A_STAGE_BYTES + B_STAGE_BYTES);
+          uint8_t* a_dst = sA + s * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + s * B_STAGE_BYTES;
+          const int k0 = kb * BK;
+          int which, lr;
+          if (!p.a_mn) {
+            locate(m0, p.a_rows, p.a_gather, which, lr);
+            tma_load_2d(a_dst, &maps_a.m[which], &full[s], k0, lr);
+          } else {
+            locate(k0, p.a_rows, p.a_gather, which, lr);
+#pragma unroll
+            for (int a = 0; a < BM / 64; ++a) tma_load_2d(a_dst + a * ATOM_BYTES, &maps_a.m[which], &full[s], m0 + a * 64, lr);
+          }
+          if (!p.b_mn) {
+            locate(n0, p.b_rows, p.b_gather, which, lr);
+            tma_load_2d(b_dst, &maps_b.m[which], &full[s], k0, lr);
+          } else {
+            locate(k0, p.b_rows, p.b_gather, which, lr);
+#pragma unroll
+            for (int a = 0; a < BN / 64; ++a) tma_load_2d(b_dst + a * ATOM_BYTES, &maps_b.m[which], &full[s], n0 + a * 64, lr);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && peers_ok) {
+      const uint32_t idesc = umma_idesc(BM, BN, p.a_mn != 0, p.b_mn != 0);
+      int s = 0; uint32_t ph = 0; int acc = 0; uint32_t aph = 0; bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], aph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(&full[s], ph, abort_flag, p.err, KB_ERR_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES), b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j) {
+            const uint64_t a_desc = p.a_mn ? umma_desc_mnmajor(a_addr, j * UMMA_K, ATOM_BYTES) : umma_desc_kmajor(a_addr, j * 32);
+            const uint64_t b_desc = p.b_mn ? umma_desc_mnmajor(b_addr, j * UMMA_K, ATOM_BYTES) : umma_desc_kmajor(b_addr, j * 32);
+            umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        if (++acc == 2) { acc = 0; aph ^= 1u; }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;
+    int acc = 0; uint32_t aph = 0; int buf = 0; bool ok = peers_ok;
+    for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      int m_blk, n_blk;
+      tile_of(t, m_blk, n_blk);
+      const int m0 = m_blk * BM, n0 = n_blk * BN;
+      if (!mbar_wait(&tfull[acc], aph, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      // destination(s) of this tile
+      int owner = 0, dst_row = m0;
+      if (p.c_mode == 1) {
+        owner = m0 / p.c_rows;
+        dst_row = p.rank * p.c_slot_rows + (m0 - owner * p.c_rows);
+      } else if (p.c_mode == 2) {
+        dst_row = p.rank * p.c_slot_rows + m0;
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / EPI_COLS; ++c) {
+        const int col0 = n0 + c * EPI_COLS;
+        if (col0 >= p.N) break;
+        uint32_t v[EPI_COLS];
+        tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
+        tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
+        tmem_ld_wait();
+        if (epi_tid == 0) tma_store_wait_read<NUM_EPI_BUFS - 1>();
+        named_barrier_sync(1, 128);
+        uint8_t* stage = sEpi + buf * EPI_BUF_BYTES;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]));
+          o.y = pack_bf16x2(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]));
+          o.z = pack_bf16x2(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]));
+          o.w = pack_bf16x2(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]));
+          *reinterpret_cast<uint4*>(stage + sw128_offset(row_in_tile, ch)) = o;
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(1, 128);
+        if (epi_tid == 0) {
+          if (p.c_mode == 2) {
+            for (int r = 0; r < p.ws; ++r) tma_store_2d(&maps_c.m[(p.rank + r) % p.ws], stage, col0, dst_row);
+          } else {
+            tma_store_2d(&maps_c.m[owner], stage, col0, dst_row);
+          }
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) { acc = 0; aph ^= 1u; }
+    }
+    if (epi_tid == 0) tma_store_wait_all<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+
+  // ---------------- phase 2: cross-rank completion, then the reduction of the staged tiles ----------------
+  if (p.ws > 1) {
+    // grid-wide arrival on this rank (all CTAs are resident: grid <= SM count, one CTA per SM)
+    __shared__ int s_go;
+    if (threadIdx.x == 0) {
+      __threadfence_system();  // this CTA's peer stores are ordered before its arrival
+      s_go = 1;
+      const unsigned int gen = p.epoch;  // generation tag of this launch
+      const unsigned int arrived = atomicAdd(&p.grid_sync[0], 1u) + 1u;
+      if (arrived == gridDim.x) {
+        atomicExch(&p.grid_sync[0], 0u);  // last arriver re-arms the counter for the next launch
+        __threadfence();
+        atomicExch(&p.grid_sync[1], gen);
+      } else {
+        const unsigned long long t0 = globaltimer_ns();
+        while (atomicAdd(&p.grid_sync[1], 0u) != gen) {
+          if (globaltimer_ns() - t0 > KB_WAIT_BUDGET_NS) { s_go = 0; atomicCAS(p.err, 0, KB_ERR_TIMEOUT_MISC); break; }
+        }
+      }
+    }
+    __syncthreads();
+    const bool go = s_go != 0;
+    // every CTA of every rank has issued (and completed) its stores
+    const bool all_ok = go && comm::cta_peer_barrier(p.ctrl, p.rank, p.ws, blockIdx.x, p.epoch + 1, p.err, KB_WAIT_BUDGET_NS);
+    if (p.c_mode != 0 && all_ok && peers_ok) {
+      const int rows = p.c_rows;
+      const int cpr = p.N >> 3;
+      const long total_chunks = (long)rows * cpr;
+      for (long i = blockIdx.x * (long)NUM_THREADS + threadIdx.x; i < total_chunks; i += (long)gridDim.x * NUM_THREADS) {
+        const long r = i / cpr;
+        const int c = (int)(i - r * cpr);
+        float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < p.ws; ++s) {
+          const uint4 v = *reinterpret_cast<const uint4*>(p.stage + ((size_t)s * p.c_slot_rows + r) * p.N + c * 8);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) { const float2 f = unpack_bf16x2(w[k]); acc8[2 * k] += f.x; acc8[2 * k + 1] += f.y; }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc8[0], acc8[1]); o.y = pack_bf16x2(acc8[2], acc8[3]);
+        o.z = pack_bf16x2(acc8[4], acc8[5]); o.w = pack_bf16x2(acc8[6], acc8[7]);
+        *reinterpret_cast<uint4*>(p.out + r * p.ldo + c * 8) = o;
+      }
+    }
+  }
+}
+
+}  // namespace gcomm
+}  // namespace kb
+
+extern "C" {
+
+// a_ptrs / b_ptrs / stage_ptrs / ctrl_ptrs: host arrays of `ws` device pointers (peer addresses of
+// symmetric buffers); for a non-gathered operand only entry [rank] is used.
+//   a_gather: stored A rows are sharded, a_rows per rank (K-major: M = ws * a_rows; MN-major: K = ws * a_rows)
+//   c_mode 0: C_local [M, N] written to c_local (pitch ldc)
+//   c_mode 1: reduce-scatter: out [M / ws, N] on each rank; staging buffers [ws, M / ws, N]
+//   c_mode 2: all-reduce:     out [M, N] on every rank;     staging buffers [ws, roundup(M, 128), N]
+// epoch must grow by at least 2 per call; grid_sync: 2 uints, zero-initialised once.
+int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_local, const void* const* stage_ptrs,
+                 const void* const* ctrl_ptrs, void* out, int M, int N, int K, long lda, long ldb, long ldc, long ldo,
+                 int a_mn, int b_mn, int a_gather, int b_gather, int c_mode, int rank, int ws, unsigned int epoch,
+                 unsigned int* grid_sync, void* stream) {
+  using namespace kb::gcomm;
+  if (M <= 0 || N <= 0 || K <= 0 || ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws) return KB_STATUS_BAD_ARG;
+  if ((lda & 7) || (ldb & 7) || (N & 7)) return KB_STATUS_BAD_ARG;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_comm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return KB_STATUS_CUDA_ERROR;
+    attr_set = true;
+  }
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static int sms = 0;
+  if (sms == 0) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+
+  Params p = {};
+  p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.a_gather = a_gather; p.b_gather = b_gather;
+  p.c_mode = c_mode; p.rank = rank; p.ws = ws; p.epoch = epoch; p.err = kb::error_word(dev);
+  p.grid_sync = grid_sync; p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo;
+  for (int i = 0; i < MAX_RANKS; ++i) p.ctrl.p[i] = (ctrl_ptrs && i < ws) ? const_cast<void*>(ctrl_ptrs[i]) : nullptr;
+
+  // stored-row extents of the operands
+  const int a_stored_rows = a_mn ? K : M, a_stored_cols = a_mn ? M : K;
+  const int b_stored_rows = b_mn ? K : N, b_stored_cols = b_mn ? N : K;
+  p.a_rows = a_gather ? a_stored_rows / ws : a_stored_rows;
+  p.b_rows = b_gather ? b_stored_rows / ws : b_stored_rows;
+  if (a_gather && (a_stored_rows % ws || p.a_rows % (a_mn ? BK : BM))) return KB_STATUS_BAD_ARG;
+  if (b_gather && (b_stored_rows % ws || p.b_rows % (b_mn ? BK : BN))) return KB_STATUS_BAD_ARG;
+  p.c_rows = c_mode == 1 ? M / ws : M;
+  p.c_slot_rows = (p.c_rows + BM - 1) / BM * BM;  // whole tiles per slot: a tile never spills into a neighbour
+  if (c_mode == 1 && (M % ws || p.c_rows % BM)) return KB_STATUS_BAD_ARG;
+  if (c_mode != 0 && (!stage_ptrs || !out || !grid_sync)) return KB_STATUS_BAD_ARG;
+  p.stage = c_mode != 0 ? static_cast<const __nv_bfloat16*>(stage_ptrs[rank]) : nullptr;
+
+  Maps ma, mb, mc;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    const int ia = a_gather ? (i < ws ? i : rank) : rank;
+    const int ib = b_gather ? (i < ws ? i : rank) : rank;
+    const void* ap = a_ptrs[a_gather ? ia : (ws > 0 ? rank : 0)];
+    const void* bp = b_ptrs[b_gather ? ib : (ws > 0 ? rank : 0)];
+    int rc;
+    if (!a_mn) rc = kb::make_tmap_2d(&ma.m[i], ap, 2, p.a_rows, a_stored_cols, lda * 2, BM, BK, true);
+    else       rc = kb::make_tmap_2d(&ma.m[i], ap, 2, p.a_rows, a_stored_cols, lda * 2, BK, 64, true);
+    if (rc) return KB_STATUS_TMAP_ERROR;
+    if (!b_mn) rc = kb::make_tmap_2d(&mb.m[i], bp, 2, p.b_rows, b_stored_cols, ldb * 2, BN, BK, true);
+    else       rc = kb::make_tmap_2d(&mb.m[i], bp, 2, p.b_rows, b_stored_cols, ldb * 2, BK, 64, true);
+    if (rc) return KB_STATUS_TMAP_ERROR;
+    if (c_mode == 0) {
+      rc = kb::make_tmap_2d(&mc.m[i], c_local, 2, M, N, ldc * 2, BM, EPI_COLS, true);
+    } else {
+      const void* sp = stage_ptrs[i < ws ? i : rank];
+      rc = kb::make_tmap_2d(&mc.m[i], sp, 2, (uint64_t)ws * p.c_slot_rows, N, (uint64_t)N * 2, BM, EPI_COLS, true);
+    }
+    if (rc) return KB_STATUS_TMAP_ERROR;
+  }
+  const int total = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int grid = total < sms ? total : sms;
+  if (c_mode != 0 && grid < 1) grid = 1;
+  gemm_comm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ma, mb, mc, p);
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+}  // extern "C"

@@ -72,3 +72,103 @@ def quantize_model_int8(model: nn.Module, skip=("lm_head",)) -> int:
                 setattr(module, child_name, Int8Linear(child.weight))
                 count += 1
     return count
+
+
+# ---------------------------------------------------------------------------------------
+# Block-scaled fp8 (e4m3): 1x128 activation scales, 128x128 weight scales
+# ---------------------------------------------------------------------------------------
+FP8_MAX = 448.0
+
+
+def _fp8_kernels(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and _lib.has("kb_gemm_fp8")
+
+
+def quantize_fp8_1x128(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``x [M, K]`` -> ``(e4m3 bytes [M, K] as uint8, fp32 scale [M, K/128])``; ``K % 128 == 0``."""
+    M, K = x.shape
+    assert K % 128 == 0
+    if _fp8_kernels(x):
+        x = x if x.stride(-1) == 1 else x.contiguous()
+        q = torch.empty((M, K), dtype=torch.uint8, device=x.device)
+        s = torch.empty((M, K // 128), dtype=torch.float32, device=x.device)
+        check(lib().kb_quant_fp8_1x128(ptr(x), ptr(q), ptr(s), M, K, x.stride(0), stream()), "quant_fp8_1x128")
+        return q, s
+    blocks = x.float().reshape(M, K // 128, 128)
+    amax = blocks.abs().amax(dim=-1)
+    s = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    q = (blocks / s[..., None]).reshape(M, K).to(torch.float8_e4m3fn).view(torch.uint8)
+    return q, s
+
+
+def quantize_fp8_128x128(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``w [N, K]`` -> ``(e4m3 bytes [N, K], fp32 scale [ceil(N/128), K/128])``."""
+    N, K = w.shape
+    assert K % 128 == 0
+    nb = (N + 127) // 128
+    if _fp8_kernels(w):
+        w = w if w.stride(-1) == 1 else w.contiguous()
+        q = torch.empty((N, K), dtype=torch.uint8, device=w.device)
+        s = torch.empty((nb, K // 128), dtype=torch.float32, device=w.device)
+        check(lib().kb_quant_fp8_128x128(ptr(w), ptr(q), ptr(s), N, K, w.stride(0), stream()), "quant_fp8_128x128")
+        return q, s
+    wf = torch.zeros((nb * 128, K), dtype=torch.float32, device=w.device)
+    wf[:N] = w.float()
+    blocks = wf.reshape(nb, 128, K // 128, 128)
+    amax = blocks.abs().amax(dim=(1, 3))
+    s = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    q = (blocks / s[:, None, :, None]).reshape(nb * 128, K)[:N].to(torch.float8_e4m3fn).view(torch.uint8)
+    return q, s
+
+
+def dequantize_fp8(q: torch.Tensor, scale: torch.Tensor, weight: bool) -> torch.Tensor:
+    """fp32 reconstruction (the oracle of the GEMM test)."""
+    v = q.view(torch.float8_e4m3fn).float()
+    R, K = v.shape
+    if weight:
+        s = scale.repeat_interleave(128, dim=0)[:R].repeat_interleave(128, dim=1)
+    else:
+        s = scale.repeat_interleave(128, dim=1)
+    return v * s
+
+
+def gemm_fp8(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Tensor) -> torch.Tensor:
+    """``dequant(a8, sa) @ dequant(b8, sb).T`` -> bf16 ``[M, N]``."""
+    M, K = a8.shape
+    N = b8.shape[0]
+    if a8.is_cuda and _lib.has("kb_gemm_fp8") and N % 8 == 0:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a8.device)
+        check(lib().kb_gemm_fp8(ptr(a8), ptr(b8), ptr(sa), ptr(sb), ptr(out), M, N, K, a8.stride(0), b8.stride(0),
+                                out.stride(0), stream()), "gemm_fp8")
+        return out
+    return (dequantize_fp8(a8, sa, False) @ dequantize_fp8(b8, sb, True).t()).to(torch.bfloat16)
+
+
+class _Fp8LinearFn(torch.autograd.Function):
+    """Forward in block-scaled fp8 from bf16 master weights; backward in bf16."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = x.reshape(-1, x.shape[-1])
+        a8, sa = quantize_fp8_1x128(x2)
+        b8, sb = quantize_fp8_128x128(w)
+        ctx.save_for_backward(x2, w)
+        ctx.shape = x.shape
+        return gemm_fp8(a8, sa, b8, sb).view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .functional import gemm
+
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dx = gemm(dy2, w, b_mn=True).view(ctx.shape)
+        dw = gemm(dy2, x2.contiguous(), a_mn=True, b_mn=True)
+        return dx, dw
+
+
+def linear_fp8(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w.T`` with e4m3 operands (1x128 / 128x128 scales) and bf16 master weights."""
+    if x.shape[-1] % 128:
+        return torch.nn.functional.linear(x, w)
+    return _Fp8LinearFn.apply(x, w)

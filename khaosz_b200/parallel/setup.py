@@ -70,11 +70,21 @@ def setup_parallel(rank: int, world_size: int, local_rank: int, backend: str = "
     kwargs = {}
     if backend == "nccl" and device.type == "cuda":
         kwargs["device_id"] = device
+    if os.environ.get("KHAOSZ_B200_PG_TIMEOUT_S"):
+        import datetime
+
+        kwargs["timeout"] = datetime.timedelta(seconds=float(os.environ["KHAOSZ_B200_PG_TIMEOUT_S"]))
     dist.init_process_group(backend=backend, rank=rank, world_size=world_size, **kwargs)
+    failed = False
     try:
         yield dist.group.WORLD
+    except BaseException:
+        failed = True
+        raise
     finally:
-        if dist.is_initialized():
+        # A rank that is unwinding an exception must not wait for its peers in a collective
+        # tear-down: it has to exit so that the launcher sees the failure and stops the others.
+        if not failed and dist.is_initialized():
             dist.destroy_process_group()
 
 

@@ -1,0 +1,280 @@
+"""Tensor parallelism with sequence-sharded activations (Megatron style) on fused kernels.
+
+Between tensor-parallel regions activations are sharded over the token dimension.  A
+column-parallel layer consumes them through **all-gather -> GEMM** (every rank's TMA producer
+reads the peers' token shards directly over NVLink), a row-parallel layer hands its partial
+sums back through **GEMM -> reduce-scatter** (training / prefill) or **GEMM -> all-reduce**
+(decode); both directions of the backward pass run on the same kernel with MN-major operands.
+On CPU (gloo) the same modules fall back to ``torch.distributed`` collectives, which is also the
+numerical reference in the tests.
+
+The reference only ships forward-only ``ColumnParallelLinear`` / ``RowParallelLinear``
+primitives (``astrai/parallel/module.py:18-115``); the class names, weight shapes and the
+``load_state_dict`` slicing of a full weight are kept.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import _lib
+from ..ops._lib import check, lib, ptr, stream
+from .comm import PeerControl, SymmetricBuffer
+
+
+class TPContext:
+    """Per-process state of the fused tensor-parallel kernels: control flags, a pool of
+    symmetric activation / staging buffers and the grid-barrier words."""
+
+    _current: Optional["TPContext"] = None
+
+    def __init__(self, group=None, device=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.ws = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.use_kernels = self.device.type == "cuda" and self.ws > 1 and self.ws <= 8 and _lib.has("kb_gemm_comm")
+        self._pool: Dict[Tuple[str, int], SymmetricBuffer] = {}
+        if self.use_kernels:
+            self.ctrl = PeerControl(self.device, self.group)
+            self.grid_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
+
+    @classmethod
+    def get(cls, group=None) -> "TPContext":
+        if cls._current is None:
+            dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+            cls._current = cls(group, dev)
+        return cls._current
+
+    @classmethod
+    def reset(cls) -> None:
+        cls._current = None
+
+    def buffer(self, tag: str, numel: int) -> SymmetricBuffer:
+        """Symmetric bf16 buffer of at least ``numel`` elements (collective on first use per tag/size)."""
+        key = (tag, numel)
+        buf = self._pool.get(key)
+        if buf is None:
+            buf = SymmetricBuffer(numel, torch.bfloat16, self.device, self.group, zero=True)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+            self._pool[key] = buf
+        return buf
+
+    def stage_in(self, tag: str, t: torch.Tensor) -> SymmetricBuffer:
+        """Copy a local tensor into symmetric memory so that peers can read it."""
+        buf = self.buffer(tag, t.numel())
+        buf.tensor[: t.numel()].view(t.shape).copy_(t)
+        return buf
+
+
+def _ptr_list(values):
+    return (ctypes.c_void_p * len(values))(*values)
+
+
+def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, b_gather=False, c_mode=0,
+               tag="tp") -> torch.Tensor:
+    """``op(A) op(B)^T`` with the fused collective.  ``a`` / ``b`` are local tensors (gathered
+    operands are this rank's shard).  Returns the local result (c_mode 0), this rank's rows of the
+    sum (c_mode 1) or the full sum (c_mode 2)."""
+    ws, rank = ctx.ws, ctx.rank
+    a_rows, a_cols = a.shape
+    b_rows, b_cols = b.shape
+    A_rows = a_rows * ws if a_gather else a_rows
+    B_rows = b_rows * ws if b_gather else b_rows
+    M = a_cols if a_mn else A_rows
+    K = A_rows if a_mn else a_cols
+    N = b_cols if b_mn else B_rows
+    Kb = B_rows if b_mn else b_cols
+    assert K == Kb, (K, Kb)
+    if a_gather:
+        sa = ctx.stage_in(tag + ".a", a)
+        a_ptrs, lda = sa.ptrs, a_cols
+    else:
+        a = a if a.stride(-1) == 1 else a.contiguous()
+        a_ptrs, lda = _ptr_list([a.data_ptr()] * ws), a.stride(0)
+    if b_gather:
+        sb = ctx.stage_in(tag + ".b", b)
+        b_ptrs, ldb = sb.ptrs, b_cols
+    else:
+        b = b if b.stride(-1) == 1 else b.contiguous()
+        b_ptrs, ldb = _ptr_list([b.data_ptr()] * ws), b.stride(0)
+    c_local = out = None
+    stage_ptrs = None
+    if c_mode == 0:
+        c_local = torch.empty((M, N), dtype=a.dtype, device=a.device)
+        ldc, ldo = N, 0
+    else:
+        rows = M // ws if c_mode == 1 else M
+        slot_rows = (rows + 127) // 128 * 128
+        stage = ctx.buffer(tag + ".stage", ws * slot_rows * N)
+        stage_ptrs = stage.ptrs
+        out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
+        ldc, ldo = N, N
+    check(lib().kb_gemm_comm(a_ptrs, b_ptrs, ptr(c_local), stage_ptrs, ctx.ctrl.flags.ptrs, ptr(out), M, N, K, lda, ldb,
+                             ldc, ldo, int(a_mn), int(b_mn), int(a_gather), int(b_gather), c_mode, rank, ws,
+                             ctx.ctrl.next_epoch(), ptr(ctx.grid_sync), stream()), "gemm_comm")
+    return c_local if c_mode == 0 else out
+
+
+# ---- reference collectives (CPU/gloo and the oracle of the GPU tests) -----------------------
+def _all_gather_rows(x: torch.Tensor, group) -> torch.Tensor:
+    parts = [torch.empty_like(x) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    return torch.cat(parts, dim=0)
+
+
+def _reduce_scatter_rows(x: torch.Tensor, group) -> torch.Tensor:
+    ws, rank = dist.get_world_size(group), dist.get_rank(group)
+    x = x.contiguous()
+    dist.all_reduce(x, group=group)
+    n = x.shape[0] // ws
+    return x[rank * n:(rank + 1) * n].clone()
+
+
+def _kernel_ok(ctx: TPContext, *tensors) -> bool:
+    return ctx.use_kernels and all(t.is_cuda and t.dtype == torch.bfloat16 for t in tensors)
+
+
+class _ColumnParallelFn(torch.autograd.Function):
+    """y[M, N_local] = all_gather(x_shard)[M, K] @ W_local[N_local, K]^T"""
+
+    @staticmethod
+    def forward(ctx, x_shard, w, tp):
+        ctx.tp = tp
+        ctx.save_for_backward(x_shard, w)
+        if _kernel_ok(tp, x_shard, w) and x_shard.shape[0] % 128 == 0:
+            return _comm_gemm(tp, x_shard, w, a_gather=True, tag="col.fwd")
+        return _all_gather_rows(x_shard, tp.group) @ w.t()
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_shard, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy = dy.contiguous()
+        if _kernel_ok(tp, dy, w) and x_shard.shape[0] % 128 == 0:
+            dx = _comm_gemm(tp, dy, w, b_mn=True, c_mode=1, tag="col.dx")                   # RS(dy W)
+            dw = _comm_gemm(tp, dy, x_shard, a_mn=True, b_mn=True, b_gather=True, tag="col.dw")  # dy^T AG(x)
+        else:
+            dx = _reduce_scatter_rows(dy @ w, tp.group)
+            dw = dy.t() @ _all_gather_rows(x_shard, tp.group)
+        return dx, dw, None
+
+
+class _RowParallelFn(torch.autograd.Function):
+    """y_shard[M / ws, N] = reduce_scatter(x[M, K_local] @ W_local[N, K_local]^T)"""
+
+    @staticmethod
+    def forward(ctx, x, w, tp, all_reduce):
+        ctx.tp, ctx.all_reduce = tp, all_reduce
+        ctx.save_for_backward(x, w)
+        x = x.contiguous()
+        if _kernel_ok(tp, x, w) and (all_reduce or (x.shape[0] % (128 * tp.ws) == 0)):
+            return _comm_gemm(tp, x, w, c_mode=2 if all_reduce else 1, tag="row.fwd")
+        y = x @ w.t()
+        if all_reduce:
+            dist.all_reduce(y, group=tp.group)
+            return y
+        return _reduce_scatter_rows(y, tp.group)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy = dy.contiguous()
+        if ctx.all_reduce:  # dy is already complete on every rank
+            return dy @ w, dy.t() @ x, None, None
+        if _kernel_ok(tp, dy, w) and dy.shape[0] % 128 == 0:
+            dx = _comm_gemm(tp, dy, w, a_gather=True, b_mn=True, tag="row.dx")                  # AG(dy) W
+            dw = _comm_gemm(tp, dy, x, a_mn=True, b_mn=True, a_gather=True, tag="row.dw")       # AG(dy)^T x
+        else:
+            full = _all_gather_rows(dy, tp.group)
+            dx, dw = full @ w, full.t() @ x
+        return dx, dw, None, None
+
+
+def _shard(full: torch.Tensor, dim: int, rank: int, ws: int) -> torch.Tensor:
+    n = full.shape[dim] // ws
+    return full.narrow(dim, rank * n, n).contiguous()
+
+
+class ColumnParallelLinear(nn.Module):
+    """Weight ``[out / ws, in]``.  Input: this rank's token shard ``[tokens / ws, in]`` (gathered
+    inside the GEMM) or, with ``sequence_parallel=False``, the full replicated input.
+    ``gather_output`` concatenates the output slices of all ranks (reference behaviour)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, gather_output: bool = False,
+                 sequence_parallel: bool = True, group=None):
+        super().__init__()
+        self.group = group
+        self.ws = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        assert out_features % self.ws == 0
+        self.in_features, self.out_features = in_features, out_features
+        self.gather_output, self.sequence_parallel = gather_output, sequence_parallel
+        self.weight = nn.Parameter(torch.empty(out_features // self.ws, in_features))
+        self.bias = nn.Parameter(torch.zeros(out_features // self.ws)) if bias else None
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        if self.ws == 1:
+            y = x2 @ self.weight.t()
+        elif self.sequence_parallel:
+            y = _ColumnParallelFn.apply(x2, self.weight, TPContext.get(self.group))
+        else:
+            y = x2 @ self.weight.t()
+        if self.bias is not None:
+            y = y + self.bias
+        if self.gather_output and self.ws > 1:
+            parts = [torch.empty_like(y) for _ in range(self.ws)]
+            dist.all_gather(parts, y.contiguous(), group=self.group)
+            y = torch.cat(parts, dim=-1)
+        return y
+
+    def load_state_dict(self, state_dict, strict: bool = True, assign: bool = False):
+        sd = dict(state_dict)
+        w = sd.get("weight")
+        if w is not None and w.shape[0] == self.out_features and self.ws > 1:
+            sd["weight"] = _shard(w, 0, self.rank, self.ws)
+            if "bias" in sd and sd["bias"].shape[0] == self.out_features:
+                sd["bias"] = _shard(sd["bias"], 0, self.rank, self.ws)
+        return super().load_state_dict(sd, strict=strict, assign=assign)
+
+
+class RowParallelLinear(nn.Module):
+    """Weight ``[out, in / ws]``.  Output: this rank's token shard of the summed result
+    (``reduce_scatter=True``, sequence parallel) or the full sum on every rank."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, reduce_scatter: bool = True,
+                 group=None):
+        super().__init__()
+        self.group = group
+        self.ws = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        assert in_features % self.ws == 0
+        self.in_features, self.out_features, self.reduce_scatter = in_features, out_features, reduce_scatter
+        self.weight = nn.Parameter(torch.empty(out_features, in_features // self.ws))
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x2 = x.reshape(-1, x.shape[-1])
+        if self.ws == 1:
+            y = x2 @ self.weight.t()
+        else:
+            y = _RowParallelFn.apply(x2, self.weight, TPContext.get(self.group), not self.reduce_scatter)
+        return y if self.bias is None else y + self.bias
+
+    def load_state_dict(self, state_dict, strict: bool = True, assign: bool = False):
+        sd = dict(state_dict)
+        w = sd.get("weight")
+        if w is not None and w.shape[1] == self.in_features and self.ws > 1:
+            sd["weight"] = _shard(w, 1, self.rank, self.ws)
+        return super().load_state_dict(sd, strict=strict, assign=assign)

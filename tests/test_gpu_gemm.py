@@ -176,3 +176,53 @@ def test_int8_weight_gemm(M, N, K):
     # and the quantisation error itself stays small against the bf16 weights
     full = x.float() @ w.float().t()
     assert (ref - full).abs().max().item() <= 0.05 * full.abs().max().item() + 0.05
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (512, 1024, 1024), (300, 520, 2048), (8192, 2048, 2048)])
+def test_fp8_block_scaled_gemm(M, N, K):
+    from khaosz_b200.ops import quant
+
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    a8, sa = quant.quantize_fp8_1x128(x)
+    b8, sb = quant.quantize_fp8_128x128(w)
+    # quantisers agree with the PyTorch formulation
+    a8c, sac = quant.quantize_fp8_1x128(x.cpu())
+    assert torch.allclose(sa.cpu(), sac, rtol=1e-5)
+    assert (quant.dequantize_fp8(a8.cpu(), sa.cpu(), False) - quant.dequantize_fp8(a8c, sac, False)).abs().max() <= 0.13 * x.abs().max().item()
+    b8c, sbc = quant.quantize_fp8_128x128(w.cpu())
+    assert torch.allclose(sb.cpu(), sbc, rtol=1e-5)
+    out = quant.gemm_fp8(a8, sa, b8, sb)
+    torch.cuda.synchronize()
+    ops.raise_on_device_error()
+    ref = quant.dequantize_fp8(a8, sa, False) @ quant.dequantize_fp8(b8, sb, True).t()
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+    full = x.float() @ w.float().t()
+    assert (ref - full).abs().mean().item() <= 0.05 * full.abs().mean().item() + 1e-3
+
+
+def test_fp8_linear_autograd_and_throughput():
+    from khaosz_b200.ops import quant
+
+    x = torch.randn(256, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(768, 1024, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    y = quant.linear_fp8(x, w)
+    y.sum().backward()
+    assert x.grad is not None and w.grad is not None and w.grad.shape == w.shape
+    ref = x.detach().float() @ w.detach().float().t()
+    assert (y.float() - ref).abs().mean().item() <= 0.06 * ref.abs().mean().item() + 1e-3
+    M, N, K = 8192, 11264, 2048
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    a8, sa = quant.quantize_fp8_1x128(a)
+    b8, sb = quant.quantize_fp8_128x128(b)
+    for _ in range(3):
+        quant.gemm_fp8(a8, sa, b8, sb)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        quant.gemm_fp8(a8, sa, b8, sb)
+    e1.record()
+    torch.cuda.synchronize()
+    print(f"fp8 block-scaled GEMM {M}x{N}x{K}: {2 * M * N * K / (e0.elapsed_time(e1) / 10) / 1e9:.0f} TFLOP/s")
+    ops.raise_on_device_error()

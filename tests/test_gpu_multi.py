@@ -18,6 +18,7 @@ from khaosz_b200.parallel import ExecutorFactory, spawn_parallel_fn  # noqa: E40
 def _spawn(fn, port, **kw):
     os.environ["KHAOSZ_B200_NVLS"] = "0"
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["KHAOSZ_B200_PG_TIMEOUT_S"] = "90"  # a failing rank must not keep the others waiting
     spawn_parallel_fn(fn, world_size=2, backend="nccl", master_addr="127.0.0.1", master_port=str(port), **kw)
 
 
@@ -183,3 +184,109 @@ def test_fused_data_parallel_step_matches_single_gpu(mode, port, tmp_path):
     worst = max((got["sd"][k].float() - v.float().cpu()).abs().max().item() for k, v in sd.items())
     assert worst < 2e-2, worst
     assert got["m0"].shape == sd["embed_tokens.weight"].shape
+
+
+def _tp_kernels_case():
+    from khaosz_b200.ops import raise_on_device_error
+    from khaosz_b200.parallel.tensor_parallel import TPContext, _comm_gemm
+
+    rank, ws = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", rank)
+    tp = TPContext.get()
+    assert tp.use_kernels
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    M, K, N = 512, 640, 768  # M = tokens over all ranks
+    x_shard = torch.randn(M // ws, K, device=dev, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+
+    def gather(t):
+        parts = [torch.empty_like(t) for _ in range(ws)]
+        dist.all_gather(parts, t)
+        return torch.cat(parts, 0)
+
+    def close(got, ref):
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item() + 2e-2, err
+
+    x_full = gather(x_shard).float()
+    for _ in range(2):  # twice: buffers, epochs and the grid barrier are reused
+        # all-gather -> GEMM (K-major gathered A)
+        close(_comm_gemm(tp, x_shard, w, a_gather=True, tag="t1"), x_full @ w.float().t())
+        # gathered weights (FSDP style): B rows sharded over ranks
+        w_shard = w[rank * (N // ws):(rank + 1) * (N // ws)].contiguous() if (N // ws) % 256 == 0 else None
+        # GEMM -> reduce-scatter and GEMM -> all-reduce
+        xa = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        total = xa.float() @ w.float().t()
+        dist.all_reduce(total)
+        rs = _comm_gemm(tp, xa, w, c_mode=1, tag="t2")
+        close(rs, total[rank * (M // ws):(rank + 1) * (M // ws)])
+        ar = _comm_gemm(tp, xa[:24].contiguous(), w, c_mode=2, tag="t3")
+        close(ar, total[:24])
+        # MN-major gathered operand: dW = dy^T all_gather(x)   (reduction dimension sharded)
+        dy = torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16)
+        dw = _comm_gemm(tp, dy, x_shard, a_mn=True, b_mn=True, b_gather=True, tag="t4")
+        close(dw, dy.float().t() @ x_full)
+        torch.cuda.synchronize()
+        raise_on_device_error()
+    # weights sharded by rows and gathered inside the GEMM (the FSDP use of the same kernel)
+    N2 = 256 * ws
+    w2 = (torch.randn(N2 // ws, K, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+    y = _comm_gemm(tp, xa, w2, b_gather=True, tag="t5")
+    close(y, xa.float() @ gather(w2).float().t())
+    torch.cuda.synchronize()
+    raise_on_device_error()
+
+
+def test_fused_comm_gemm_kernels():
+    _spawn(_tp_kernels_case, 29705)
+
+
+def _tp_mlp_case(out):
+    """Column-parallel -> SwiGLU -> row-parallel MLP on sequence-sharded tokens, forward and
+    backward through the fused kernels, against the same MLP on one GPU."""
+    from khaosz_b200 import ops
+    from khaosz_b200.parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+
+    rank, ws = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(7)
+    T, D, Fh = 512, 512, 1024
+    x_full = torch.randn(T, D, device=dev).to(torch.bfloat16)
+    wg = (torch.randn(Fh, D, device=dev) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(Fh, D, device=dev) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(D, Fh, device=dev) * 0.05).to(torch.bfloat16)
+    go_full = torch.randn(T, D, device=dev).to(torch.bfloat16)
+    gate_up = ColumnParallelLinear(D, 2 * Fh).to(dev, torch.bfloat16)
+    down = RowParallelLinear(Fh, D).to(dev, torch.bfloat16)
+    n = Fh // ws
+    with torch.no_grad():  # local slices: [gate_r | up_r]
+        gate_up.weight.copy_(torch.cat([wg[rank * n:(rank + 1) * n], wu[rank * n:(rank + 1) * n]], 0))
+    down.load_state_dict({"weight": wd})
+    x = x_full[rank * (T // ws):(rank + 1) * (T // ws)].clone().requires_grad_()
+    y = down(ops.swiglu(gate_up(x)))
+    y.backward(go_full[rank * (T // ws):(rank + 1) * (T // ws)])
+    ops.raise_on_device_error()
+    # single-GPU oracle in fp32
+    xf = x_full.float().requires_grad_()
+    wgf, wuf, wdf = (t.float().requires_grad_() for t in (wg, wu, wd))
+    ref = ((xf @ wuf.t()) * torch.nn.functional.silu(xf @ wgf.t())) @ wdf.t()
+    ref.backward(go_full.float())
+    sl = slice(rank * (T // ws), (rank + 1) * (T // ws))
+
+    def close(got, want, name):
+        err = (got.float() - want).abs().max().item()
+        assert err <= 3e-2 * want.abs().max().item() + 3e-2, (name, err)
+
+    close(y, ref[sl], "y")
+    close(x.grad, xf.grad[sl], "dx")
+    close(gate_up.weight.grad[:n], wgf.grad[rank * n:(rank + 1) * n], "dwg")
+    close(gate_up.weight.grad[n:], wuf.grad[rank * n:(rank + 1) * n], "dwu")
+    close(down.weight.grad, wdf.grad[:, rank * n:(rank + 1) * n], "dwd")
+    if rank == 0:
+        open(out, "w").write("ok")
+
+
+def test_tensor_parallel_mlp_matches_single_gpu(tmp_path):
+    out = str(tmp_path / "tp.txt")
+    _spawn(_tp_mlp_case, 29706, out=out)
+    assert open(out).read() == "ok"
