@@ -104,6 +104,7 @@ constexpr int RMS_BWD_THREADS = 256;
 constexpr int RMS_BWD_MAX_NCH = 4;  // dim <= 8 * 256 * 4 = 8192
 constexpr int RMS_BWD_ROWS = 4;
 
+template <int NCH>
 __global__ void __launch_bounds__(RMS_BWD_THREADS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -112,10 +113,10 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   __shared__ float red[RMS_BWD_ROWS * 32];
   const int nchunks = dim >> 3;
   const int tid = threadIdx.x;
-  float wacc[RMS_BWD_MAX_NCH][8];
-  float wreg[RMS_BWD_MAX_NCH][8];
+  float wacc[NCH][8];
+  float wreg[NCH][8];
 #pragma unroll
-  for (int i = 0; i < RMS_BWD_MAX_NCH; ++i) {
+  for (int i = 0; i < NCH; ++i) {
     const int c = tid + i * RMS_BWD_THREADS;
 #pragma unroll
     for (int e = 0; e < 8; ++e) wacc[i][e] = 0.f;
@@ -132,7 +133,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       const int row = r0 + j;
       if (row < rows) {
 #pragma unroll
-        for (int i = 0; i < RMS_BWD_MAX_NCH; ++i) {
+        for (int i = 0; i < NCH; ++i) {
           const int c = tid + i * RMS_BWD_THREADS;
           if (c < nchunks) {
             float a[8], b[8];
@@ -153,7 +154,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         const float rs = rstd[row];
         const float coef = dot[j] * rs * rs * rs * inv_dim;
 #pragma unroll
-        for (int i = 0; i < RMS_BWD_MAX_NCH; ++i) {
+        for (int i = 0; i < NCH; ++i) {
           const int c = tid + i * RMS_BWD_THREADS;
           if (c < nchunks) {
             float a[8], b[8], o[8];
@@ -177,7 +178,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     }
   }
 #pragma unroll
-  for (int i = 0; i < RMS_BWD_MAX_NCH; ++i) {
+  for (int i = 0; i < NCH; ++i) {
     const int c = tid + i * RMS_BWD_THREADS;
     if (c < nchunks) {
       float* dst = dw_partial + (size_t)blockIdx.x * dim + c * 8;
@@ -185,6 +186,16 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       *reinterpret_cast<float4*>(dst + 4) = make_float4(wacc[i][4], wacc[i][5], wacc[i][6], wacc[i][7]);
     }
   }
+}
+
+// Picks the instantiation with the fewest per-thread column chunks that covers `dim`.
+static void launch_rmsnorm_bwd(int blocks, cudaStream_t st, const __nv_bfloat16* dy, const __nv_bfloat16* x,
+                               const __nv_bfloat16* w, const float* rstd, const __nv_bfloat16* dres,
+                               __nv_bfloat16* dx, float* partial, int rows, int dim) {
+  const int nch = ((dim >> 3) + RMS_BWD_THREADS - 1) / RMS_BWD_THREADS;
+  if (nch <= 1) rmsnorm_bwd_kernel<1><<<blocks, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, partial, rows, dim);
+  else if (nch <= 2) rmsnorm_bwd_kernel<2><<<blocks, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, partial, rows, dim);
+  else rmsnorm_bwd_kernel<4><<<blocks, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, partial, rows, dim);
 }
 
 // out[col] = sum over rows of partial[row][col]; block = 32 columns x 32 row lanes.
@@ -556,9 +567,8 @@ int kb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rs
   if (mis16(dy) || mis16(x) || mis16(w) || mis16(dx) || mis16(dw_partial) || (dres_in && mis16(dres_in)))
     return KB_STATUS_BAD_ARG;
   const int blocks = kb_rmsnorm_bwd_partials(rows);
-  rmsnorm_bwd_kernel<<<blocks, RMS_BWD_THREADS, 0, (cudaStream_t)stream>>>(
-      (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres_in, (bf16*)dx,
-      dw_partial, rows, dim);
+  launch_rmsnorm_bwd(blocks, (cudaStream_t)stream, (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+                     (const bf16*)dres_in, (bf16*)dx, dw_partial, rows, dim);
   colsum_kernel<<<(dim + 31) / 32, dim3(32, 32), 0, (cudaStream_t)stream>>>(dw_partial, dw, blocks, dim);
   return launch_status();
 }
@@ -703,8 +713,8 @@ extern "C" int kb_rmsnorm_bwd_static(const void* dy, const void* x, const void* 
 
   int blocks = (rows + RMS_BWD_ROWS - 1) / RMS_BWD_ROWS;
   if (blocks > KB_STATIC_RMS_MAX_PARTIALS) blocks = KB_STATIC_RMS_MAX_PARTIALS;  // the kernel strides over rows
-  rmsnorm_bwd_kernel<<<blocks, RMS_BWD_THREADS, 0, (cudaStream_t)stream>>>(
-      (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres_in, (bf16*)dx, scratch, rows, dim);
+  launch_rmsnorm_bwd(blocks, (cudaStream_t)stream, (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+                     (const bf16*)dres_in, (bf16*)dx, scratch, rows, dim);
   colsum_kernel<<<(dim + 31) / 32, dim3(32, 32), 0, (cudaStream_t)stream>>>(scratch, dw, blocks, dim);
   if (cudaGetLastError() != cudaSuccess)
     return rms_static_fail(KB_STATUS_CUDA_ERROR, "kb_rmsnorm_bwd_static: kernel launch failed", 0, 0);
