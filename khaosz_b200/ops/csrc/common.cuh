@@ -61,6 +61,10 @@ __device__ __forceinline__ bool elect_one() {
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// Non-blocking arrival on a named barrier whose other participants call named_barrier_sync.
+__device__ __forceinline__ void named_barrier_arrive(uint32_t id, uint32_t nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
 // ---------------------------------------------------------------------------------------
 // mbarrier

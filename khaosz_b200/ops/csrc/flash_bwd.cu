@@ -24,7 +24,8 @@ constexpr int D = 128;
 constexpr int BLK = 128;
 constexpr int CHUNK_BYTES = 128 * 64 * 2;
 constexpr int TILE_BYTES = 2 * CHUNK_BYTES;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 compute warps (two per TMEM lane quarter)
+constexpr int COMPUTE_THREADS = 256;
 constexpr int SMEM_BYTES = 6 * TILE_BYTES + 4 * 128 * 4 + 256 + 1024;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -85,9 +86,11 @@ __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint3
 }
 
 // TMEM accumulator [128 x 128] fp32 -> bf16 (x mul) -> swizzled staging tile (2 chunks)
-__device__ __forceinline__ void acc_to_staging(uint32_t t_addr, uint8_t* stage, int row, float mul) {
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
+// for the 32-column groups [c_begin, c_end)
+__device__ __forceinline__ void acc_to_staging(uint32_t t_addr, uint8_t* stage, int row, float mul, int c_begin,
+                                               int c_end) {
+#pragma unroll 2
+  for (int c = c_begin; c < c_end; ++c) {
     uint32_t o[32];
     tmem_ld_32x32b_x32(t_addr + c * 32, o);
     tmem_ld_wait();
@@ -130,7 +133,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   uint64_t* p_ready = bars + 7;    // [1]
   uint64_t* ds_ready = bars + 8;   // [1]
   uint64_t* acc_full = bars + 9;   // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* s_read = bars + 10;    // [4]  lower-half warp of a lane quarter has loaded its S^T columns
+  uint64_t* dp_read = bars + 14;   // [4]  ... its dP^T columns
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -146,7 +151,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 2); mbar_init(&q_empty[i], 1); }
     mbar_init(st_full, 1); mbar_init(dpt_full, 1);
-    mbar_init(p_ready, 4); mbar_init(ds_ready, 4); mbar_init(acc_full, 1);
+    mbar_init(p_ready, 8); mbar_init(ds_ready, 8); mbar_init(acc_full, 1);
+    for (int i = 0; i < 4; ++i) { mbar_init(&s_read[i], 1); mbar_init(&dp_read[i], 1); }
     mbar_fence_init();
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
     tma_prefetch_desc(&tm_do); tma_prefetch_desc(&tm_dk); tma_prefetch_desc(&tm_dv);
@@ -235,8 +241,13 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       }
     }
   } else {
-    // ------------------------------- compute warps (one thread per key) -------------------------------
+    // ------------- compute warps: one thread per (key, half of the 128 query columns) -------------
+    // Warp w reads TMEM lanes [32 * (w % 4), +32).  Warps 2-5 take query columns 0-63, warps 6-9
+    // columns 64-127.  The packed bf16 result of the upper half lands in fp32 columns 32-63, which
+    // the lower-half warp of the same lane quarter reads: it arrives on an mbarrier once its loads
+    // have completed and the upper-half warp waits on that before storing.
     const int qtr = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = qtr * 32 + lane;
     const int kv = kv0 + row;
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
@@ -244,33 +255,41 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1;
       const int q0 = (i_start + it % per_head) * BLK;
-      const float* lse2 = sLse + s * 128;
-      const float* dlt = sDelta + s * 128;
+      const float* lse2 = sLse + s * 128 + half * 64;
+      const float* dlt = sDelta + s * 128 + half * 64;
       // acquire the producer's lse/delta writes for this stage directly
       if (!mbar_wait(&q_full[s], (it >> 1) & 1, abort_flag, p.err, KB_ERR_TIMEOUT_FULL)) { ok = false; break; }
       if (!mbar_wait(st_full, it & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const bool diag = p.causal && (q0 < kv0 + BLK);
-      uint32_t preg[64];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32];
-        tmem_ld_32x32b_x32(T_ST + lane_off + c * 32, sv);
+      const int qc = q0 + half * 64;  // first query column of this thread
+      uint32_t preg[32];
+      {
+        uint32_t sv[64];
+        tmem_ld_32x32b_x32(T_ST + lane_off + half * 64, sv);
+        tmem_ld_32x32b_x32(T_ST + lane_off + half * 64 + 32, sv + 32);
         tmem_ld_wait();
+        if (half == 0) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_read[qtr]);
+        }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int c0 = c * 32 + 2 * i;
-          float p0 = exp2f(__uint_as_float(sv[2 * i]) * p.scale_log2 - lse2[c0]);
-          float p1 = exp2f(__uint_as_float(sv[2 * i + 1]) * p.scale_log2 - lse2[c0 + 1]);
+        for (int i = 0; i < 32; ++i) {
+          float p0 = exp2f(__uint_as_float(sv[2 * i]) * p.scale_log2 - lse2[2 * i]);
+          float p1 = exp2f(__uint_as_float(sv[2 * i + 1]) * p.scale_log2 - lse2[2 * i + 1]);
           if (diag) {
-            if (kv > q0 + c0) p0 = 0.f;
-            if (kv > q0 + c0 + 1) p1 = 0.f;
+            if (kv > qc + 2 * i) p0 = 0.f;
+            if (kv > qc + 2 * i + 1) p1 = 0.f;
           }
-          preg[c * 16 + i] = pack_bf16x2(p0, p1);
+          preg[i] = pack_bf16x2(p0, p1);
         }
       }
-      tmem_st_32x32b_x32(T_ST + lane_off, preg);
-      tmem_st_32x32b_x32(T_ST + lane_off + 32, preg + 32);
+      if (half == 1) {
+        if (!mbar_wait(&s_read[qtr], it & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+      }
+      tmem_st_32x32b_x32(T_ST + lane_off + half * 32, preg);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -278,41 +297,51 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
       if (!mbar_wait(dpt_full, it & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t dv[32];
-        tmem_ld_32x32b_x32(T_DPT + lane_off + c * 32, dv);
+      uint32_t ds[32];
+      {
+        uint32_t dv[64];
+        tmem_ld_32x32b_x32(T_DPT + lane_off + half * 64, dv);
+        tmem_ld_32x32b_x32(T_DPT + lane_off + half * 64 + 32, dv + 32);
         tmem_ld_wait();
-        uint32_t ds[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int c0 = c * 32 + 2 * i;
-          const float2 pp = unpack_bf16x2(preg[c * 16 + i]);
-          ds[i] = pack_bf16x2(pp.x * (__uint_as_float(dv[2 * i]) - dlt[c0]),
-                              pp.y * (__uint_as_float(dv[2 * i + 1]) - dlt[c0 + 1]));
+        if (half == 0) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&dp_read[qtr]);
         }
-        tmem_st_32x32b_x16(T_DPT + lane_off + c * 16, ds);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float2 pp = unpack_bf16x2(preg[i]);
+          ds[i] = pack_bf16x2(pp.x * (__uint_as_float(dv[2 * i]) - dlt[2 * i]),
+                              pp.y * (__uint_as_float(dv[2 * i + 1]) - dlt[2 * i + 1]));
+        }
       }
+      if (half == 1) {
+        if (!mbar_wait(&dp_read[qtr], it & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+      }
+      tmem_st_32x32b_x32(T_DPT + lane_off + half * 32, ds);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_ready);
     }
-    // ---- epilogue: dV, dK -> bf16 -> staging (the Q/dO stage buffers) -> TMA store ----
-    if (n_it > 0 && ok && mbar_wait(acc_full, 0, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) {
+    // ---- epilogue: dV (lower-half warps), dK (upper-half warps) -> bf16 -> staging -> TMA store ----
+    const bool have = n_it > 0 && ok && mbar_wait(acc_full, 0, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL);
+    if (have) {
       tc_fence_after();
-      acc_to_staging(T_DV + lane_off, sQ, row, 1.f);
-      acc_to_staging(T_DK + lane_off, sQ + TILE_BYTES, row, p.scale);
+      if (half == 0) acc_to_staging(T_DV + lane_off, sQ, row, 1.f, 0, 4);
+      else acc_to_staging(T_DK + lane_off, sQ + TILE_BYTES, row, p.scale, 0, 4);
       fence_proxy_async_smem();
-      named_barrier_sync(1, 128);
-      if (threadIdx.x == 64) {
-        for (int c = 0; c < 2; ++c) {
-          tma_store_3d(&tm_dv, sQ + c * CHUNK_BYTES, kvh * D + c * 64, kv0, b);
-          tma_store_3d(&tm_dk, sQ + TILE_BYTES + c * CHUNK_BYTES, kvh * D + c * 64, kv0, b);
-        }
-        tma_store_commit();
-        tma_store_wait_all<0>();
+    }
+    // every compute warp reaches this barrier (also after a failed wait) so that none is left behind
+    named_barrier_sync(1, COMPUTE_THREADS);
+    if (have && threadIdx.x == 64) {
+      for (int c = 0; c < 2; ++c) {
+        tma_store_3d(&tm_dv, sQ + c * CHUNK_BYTES, kvh * D + c * 64, kv0, b);
+        tma_store_3d(&tm_dk, sQ + TILE_BYTES + c * CHUNK_BYTES, kvh * D + c * 64, kv0, b);
       }
+      tma_store_commit();
+      tma_store_wait_all<0>();
     }
   }
   tc_fence_before();
@@ -341,7 +370,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint64_t* sdp_full = bars + 5;    // [1]  S and dP both complete
   uint64_t* ds_ready = bars + 6;    // [1]
   uint64_t* acc_full = bars + 7;    // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* s_read = bars + 8;      // [4]  lower-half warp of a lane quarter has loaded its S / dP columns
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -355,7 +385,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     *abort_flag = 0;
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    mbar_init(sdp_full, 1); mbar_init(ds_ready, 4); mbar_init(acc_full, 1);
+    mbar_init(sdp_full, 1); mbar_init(ds_ready, 8); mbar_init(acc_full, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&s_read[i], 1);
     mbar_fence_init();
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
     tma_prefetch_desc(&tm_do); tma_prefetch_desc(&tm_dq);
@@ -420,7 +451,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     }
   } else {
+    // compute warps: one thread per (query row, half of the 128 key columns); warps 2-5 take keys
+    // 0-63 of the block, warps 6-9 keys 64-127 (see the dK/dV kernel for the hand-off rule).
     const int qtr = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = qtr * 32 + lane;
     const int q = q0 + row;
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
@@ -431,15 +465,21 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     for (int j = 0; j < n_it && ok; ++j) {
       if (!mbar_wait(sdp_full, j & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const int kv0 = j * BLK;
-      const bool need_mask = (p.causal && (kv0 + BLK - 1 > q0)) || (kv0 + BLK > p.S);
+      const int kv0 = j * BLK + half * 64;
+      const bool need_mask = (p.causal && (kv0 + 63 > q0)) || (kv0 + 64 > p.S);
       const int limit = p.causal ? min(q, p.S - 1) : (p.S - 1);
+      uint32_t ds[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32], ds[16];
-        tmem_ld_32x32b_x32(T_S + lane_off + c * 32, sv);
-        tmem_ld_32x32b_x32(T_DP + lane_off + c * 32, dv);
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(T_S + lane_off + half * 64 + c * 32, sv);
+        tmem_ld_32x32b_x32(T_DP + lane_off + half * 64 + c * 32, dv);
         tmem_ld_wait();
+        if (c == 1 && half == 0) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_read[qtr]);
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int c0 = kv0 + c * 32 + 2 * i;
@@ -449,26 +489,32 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (c0 > limit) p0 = 0.f;
             if (c0 + 1 > limit) p1 = 0.f;
           }
-          ds[i] = pack_bf16x2(p0 * (__uint_as_float(dv[2 * i]) - dlt), p1 * (__uint_as_float(dv[2 * i + 1]) - dlt));
+          ds[c * 16 + i] =
+              pack_bf16x2(p0 * (__uint_as_float(dv[2 * i]) - dlt), p1 * (__uint_as_float(dv[2 * i + 1]) - dlt));
         }
-        // dS (bf16) overwrites S: packed columns [16c, 16c+16) were read in an earlier chunk
-        tmem_st_32x32b_x16(T_S + lane_off + c * 16, ds);
       }
+      // dS (bf16) overwrites S: packed columns [32 * half, +32)
+      if (half == 1) {
+        if (!mbar_wait(&s_read[qtr], j & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+      }
+      tmem_st_32x32b_x32(T_S + lane_off + half * 32, ds);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_ready);
     }
-    if (n_it > 0 && ok && mbar_wait(acc_full, 0, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) {
+    const bool have = n_it > 0 && ok && mbar_wait(acc_full, 0, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL);
+    if (have) {
       tc_fence_after();
-      acc_to_staging(T_DQ + lane_off, sQ, row, p.scale);
+      acc_to_staging(T_DQ + lane_off, sQ, row, p.scale, half * 2, half * 2 + 2);
       fence_proxy_async_smem();
-      named_barrier_sync(1, 128);
-      if (threadIdx.x == 64) {
-        for (int c = 0; c < 2; ++c) tma_store_3d(&tm_dq, sQ + c * CHUNK_BYTES, h * D + c * 64, q0, b);
-        tma_store_commit();
-        tma_store_wait_all<0>();
-      }
+    }
+    named_barrier_sync(1, COMPUTE_THREADS);
+    if (have && threadIdx.x == 64) {
+      for (int c = 0; c < 2; ++c) tma_store_3d(&tm_dq, sQ + c * CHUNK_BYTES, h * D + c * 64, q0, b);
+      tma_store_commit();
+      tma_store_wait_all<0>();
     }
   }
   tc_fence_before();
