@@ -1,0 +1,147 @@
+"""Benchmark of the fused compute+collective kernels against "library collective, then GEMM".
+
+Run one process per GPU::
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        --master-port 29611 -m khaosz_b200.cli.comm_bench --tokens 8192
+
+Every case is timed on the device with CUDA events after warm-up, the reported time is the
+maximum over ranks, and each fused kernel is given as a fraction of its roofline: the slower of
+(FLOPs / GEMM peak) and (bytes that must cross NVLink per GPU / link bandwidth).  Shapes are the
+tensor-parallel linears of the 1B decoder (d_model 2048, ffn 5632) at ``--tokens`` tokens.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def _timed(fn, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--dim", type=int, default=2048)
+    ap.add_argument("--ffn", type=int, default=5632)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--gemm_peak_tflops", type=float, default=1399.5, help="measured sustained bf16 GEMM peak")
+    ap.add_argument("--link_gbs", type=float, default=770.0, help="measured peer copy bandwidth per direction")
+    ap.add_argument("--nvls", type=int, default=1)
+    args = ap.parse_args(argv)
+
+    rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not args.nvls:
+        os.environ["KHAOSZ_B200_NVLS"] = "0"
+    dist.init_process_group("nccl", device_id=dev)
+
+    from .. import ops
+    from ..ops import raise_on_device_error
+    from ..parallel.comm import PeerControl, SymmetricBuffer, allreduce_
+    from ..parallel.tensor_parallel import TPContext, _comm_gemm
+
+    tp = TPContext.get()
+    T, d, f = args.tokens, args.dim, args.ffn
+    gen = torch.Generator(device=dev).manual_seed(rank)
+
+    def rnd(*shape):
+        return (torch.randn(*shape, device=dev, generator=gen) * 0.05).to(torch.bfloat16)
+
+    results = []
+
+    def report(name, fused_ms, base_ms, flops, link_bytes):
+        t_flop = flops / (args.gemm_peak_tflops * 1e12) * 1e3
+        t_link = link_bytes / (args.link_gbs * 1e9) * 1e3
+        roof = max(t_flop, t_link)
+        results.append({"case": name, "fused_ms": round(fused_ms, 4), "library_ms": round(base_ms, 4),
+                        "speedup": round(base_ms / fused_ms, 3), "roofline_ms": round(roof, 4),
+                        "bound": "tensor" if t_flop >= t_link else "nvlink",
+                        "fraction_of_roofline": round(roof / fused_ms, 3)})
+
+    # ---- all-gather -> GEMM (column parallel gate|up): [T/ws, d] shards x W[2f/ws, d]
+    n_loc = (2 * f // ws) // 8 * 8
+    x_shard, w_col = rnd(T // ws, d), rnd(n_loc, d)
+    full = torch.empty(T, d, dtype=torch.bfloat16, device=dev)
+
+    def ag_fused():
+        return _comm_gemm(tp, x_shard, w_col, a_gather=True, tag="bench.col")
+
+    def ag_lib():
+        dist.all_gather_into_tensor(full, x_shard)
+        return ops.gemm(full, w_col)
+
+    report("all_gather->gemm (gate|up)", _timed(ag_fused, args.iters), _timed(ag_lib, args.iters),
+           2.0 * T * n_loc * d, (ws - 1) / ws * T * d * 2)
+
+    # ---- GEMM -> reduce-scatter (row parallel down): x[T, f/ws] x W[d, f/ws] -> rows T/ws
+    k_loc = (f // ws) // 8 * 8
+    x_row, w_row = rnd(T, k_loc), rnd(d, k_loc)
+    rs_out = torch.empty(T // ws, d, dtype=torch.bfloat16, device=dev)
+
+    def rs_fused():
+        return _comm_gemm(tp, x_row, w_row, c_mode=1, tag="bench.row")
+
+    def rs_lib():
+        dist.reduce_scatter_tensor(rs_out, ops.gemm(x_row, w_row))
+        return rs_out
+
+    report("gemm->reduce_scatter (down)", _timed(rs_fused, args.iters), _timed(rs_lib, args.iters),
+           2.0 * T * d * k_loc, (ws - 1) / ws * T * d * 2)
+
+    # ---- GEMM -> all-reduce (decode, 256 tokens)
+    Td = 256
+    xd = rnd(Td, k_loc)
+
+    def ar_fused():
+        return _comm_gemm(tp, xd, w_row, c_mode=2, tag="bench.dec")
+
+    def ar_lib():
+        y = ops.gemm(xd, w_row)
+        dist.all_reduce(y)
+        return y
+
+    report("gemm->all_reduce (decode, 256 tokens)", _timed(ar_fused, args.iters), _timed(ar_lib, args.iters),
+           2.0 * Td * d * k_loc, 2 * (ws - 1) / ws * Td * d * 2)
+
+    # ---- stand-alone all-reduce of a 256 MiB gradient bucket
+    n = 128 * 1024 * 1024
+    buf = SymmetricBuffer(n, torch.bfloat16, dev)
+    ctrl = PeerControl(dev)
+    buf.tensor.normal_(generator=gen)
+    plain = buf.tensor.clone()
+    torch.cuda.synchronize()
+    dist.barrier()
+    report("all_reduce 256 MiB (kernel vs NCCL)", _timed(lambda: allreduce_(buf, ctrl, scale=1.0 / ws), args.iters),
+           _timed(lambda: dist.all_reduce(plain), args.iters), 0.0, 2 * (ws - 1) / ws * n * 2)
+
+    torch.cuda.synchronize()
+    raise_on_device_error()
+    if rank == 0:
+        print(json.dumps({"world_size": ws, "tokens": T, "nvls": bool(args.nvls), "results": results}, indent=1))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

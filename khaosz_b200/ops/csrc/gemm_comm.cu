@@ -3,9 +3,14 @@
 //
 //   all-gather -> GEMM    an operand whose rows are sharded over the ranks (sequence-sharded
 //                         activations for column-parallel layers, or row-sharded weights under
-//                         FSDP) is never assembled: the TMA producer reads every tile straight
-//                         from the rank that owns it (plain cp.async.bulk.tensor on a peer
-//                         pointer, no multicast), local tiles first, then the peers in ring order.
+//                         FSDP).  Copy mode: a copier warp in every CTA pulls the peers' shards
+//                         once over NVLink (plain cp.async.bulk peer -> shared -> local memory,
+//                         no multicast) into the local image of the whole operand and publishes
+//                         128-row chunks through release counters; the TMA producer starts with
+//                         the tiles of the local shard and polls a chunk's counter (bounded)
+//                         before its first load from it, so the transfer hides behind the math.
+//                         Direct mode (shards that are not whole 128-row chunks): the producer
+//                         reads every tile straight from the owning rank's memory.
 //   GEMM -> reduce-scatter  each finished output tile is TMA-stored into the owner rank's staging
 //                         slot for this source rank while the next tile is being computed;
 //                         after a grid-wide + cross-rank barrier every rank sums the slots of
@@ -28,7 +33,9 @@ using comm::Peers;
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
+constexpr int COPY_PIECE = 16 * 1024;   // bytes per bulk copy of the gather copier
+constexpr int COPY_BUFS = 3;
+constexpr int CHUNK_ROWS = 128;          // rows of the gathered operand published per counter
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int B_STAGE_BYTES = BN * BK * 2;
@@ -37,8 +44,13 @@ constexpr int EPI_COLS = 64;
 constexpr int EPI_BUF_BYTES = BM * EPI_COLS * 2;
 constexpr int NUM_EPI_BUFS = 2;
 constexpr int TMEM_COLS = 512;
-constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + NUM_EPI_BUFS * EPI_BUF_BYTES + 256 + 1024;
+constexpr int NUM_THREADS = 224;  // TMA warp, MMA warp, 4 epilogue warps, gather copier warp
+constexpr int COPY_WARP = 6;
+template <int STAGES, bool COPY>
+constexpr int smem_bytes() {
+  return STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + NUM_EPI_BUFS * EPI_BUF_BYTES + (COPY ? COPY_BUFS * COPY_PIECE : 0) +
+         256 + 1024;
+}
 
 struct Maps {
   CUtensorMap m[MAX_RANKS];
@@ -61,7 +73,56 @@ struct Params {
   long ldo;
   unsigned int* grid_sync;     // two words, zero before the first launch
   int* err;
+  // copy-mode gather: peers' images of the whole operand (shard r valid at rows of rank r)
+  Peers gsrc;
+  uint8_t* gdst;               // this rank's image
+  unsigned int* ready;         // one counter per 128-row chunk of the image
+  unsigned int ready_target;   // value a complete chunk's counter reaches in this call
+  long long shard_bytes;       // bytes per rank's shard (whole chunks)
+  int chunk_bytes;             // 128 rows
+  int gather_rows;             // stored rows per rank of the gathered operand
 };
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void red_release_gpu_add(unsigned int* addr, unsigned int v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* addr) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// Bounded wait until the chunks covering stored rows [row0, row0 + nrows) of the gathered image
+// have arrived.  `last` caches the newest chunk already seen complete.
+__device__ __forceinline__ bool wait_gathered(const Params& p, int row0, int nrows, int& last, volatile int* abort_flag) {
+  const int c0 = row0 / CHUNK_ROWS, c1 = (row0 + nrows - 1) / CHUNK_ROWS;
+  bool fresh = false;
+  for (int c = c0; c <= c1; ++c) {
+    if (c == last || (c * CHUNK_ROWS) / p.gather_rows == p.rank) continue;
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned int it = 0;
+    while (ld_acquire_gpu(p.ready + c) != p.ready_target) {
+      if ((++it & 63u) == 0u && (*abort_flag || globaltimer_ns() - t0 > KB_WAIT_BUDGET_NS)) {
+        *abort_flag = 1;
+        atomicCAS(p.err, 0, KB_ERR_TIMEOUT_PEER);
+        return false;
+      }
+    }
+    last = c;
+    fresh = true;
+  }
+  if (fresh) fence_proxy_async_all();  // the chunk was written through the async proxy of other SMs
+  return true;
+}
 
 // Map index + coordinate inside that rank's shard for a stored row index.
 __device__ __forceinline__ void locate(int row, int rows_per_rank, int gather, int& which, int& local_row) {
@@ -74,6 +135,7 @@ __device__ __forceinline__ void locate(int row, int rows_per_rank, int gather, i
   }
 }
 
+template <int STAGES, bool COPY>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Maps maps_b,
                  const __grid_constant__ Maps maps_c, const Params p) {
@@ -83,12 +145,14 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
   uint8_t* sEpi = sB + STAGES * B_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + NUM_EPI_BUFS * EPI_BUF_BYTES);
+  uint8_t* sCopy = sEpi + NUM_EPI_BUFS * EPI_BUF_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sCopy + (COPY ? COPY_BUFS * COPY_PIECE : 0));
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* tfull = bars + 2 * STAGES;
   uint64_t* tempty = bars + 2 * STAGES + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* cbar = bars + 2 * STAGES + 4;  // [COPY_BUFS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + COPY_BUFS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -99,6 +163,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
     *abort_flag = 0;
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    for (int i = 0; i < COPY_BUFS; ++i) mbar_init(&cbar[i], 1);
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -114,39 +179,61 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
 
   // Tile order: rotate the m-tiles (K-major gathered A) so that this rank starts with its own
   // shard and the ranks walk the ring in step, spreading the load over the links.
-  const int m_rot = (p.a_gather && !p.a_mn) ? (p.rank * p.a_rows) / BM : 0;
+  // With a gathered K-major A the n-blocks of one m-block are consecutive, so that every tile of
+  // the local shard comes before the first tile that needs a peer's rows; a gathered K-major B
+  // rotates the n-blocks the same way; an MN-major gathered operand rotates the k-blocks.
+  const bool a_rows_gathered = p.a_gather && !p.a_mn, b_rows_gathered = p.b_gather && !p.b_mn;
+  const int m_rot = a_rows_gathered ? (p.rank * p.a_rows) / BM : 0;
+  const int n_rot = b_rows_gathered ? (p.rank * p.b_rows) / BN : 0;
+  const int k_rot = (p.a_gather && p.a_mn) ? (p.rank * p.a_rows) / BK : ((p.b_gather && p.b_mn) ? (p.rank * p.b_rows) / BK : 0);
   auto tile_of = [&](int t, int& m_blk, int& n_blk) {
-    m_blk = (t % num_m + m_rot) % num_m;
-    n_blk = t / num_m;
+    if (a_rows_gathered) {
+      m_blk = (t / num_n + m_rot) % num_m;
+      n_blk = t % num_n;
+    } else {
+      m_blk = t % num_m;
+      n_blk = (t / num_m + n_rot) % num_n;
+    }
   };
 
   if (warp == 0) {
     if (lane == 0 && peers_ok) {
       int s = 0; uint32_t ph = 0; bool ok = true;
+      int seen = -1;  // newest gathered chunk known to be complete
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
         int m_blk, n_blk;
         tile_of(t, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN;
-        for (int kb = 0; kb < num_k; ++kb) {
+        if (COPY) {
+          if (a_rows_gathered) ok = wait_gathered(p, m0, min(BM, p.M - m0), seen, abort_flag);
+          else if (b_rows_gathered) ok = wait_gathered(p, n0, min(BN, p.N - n0), seen, abort_flag);
+          if (!ok) break;
+        }
+        for (int kk = 0; kk < num_k; ++kk) {
+          const int kb = (kk + k_rot) % num_k;
+          const int k0 = kb * BK;
+          if (COPY && ((p.a_gather && p.a_mn) || (p.b_gather && p.b_mn))) {
+            if (!wait_gathered(p, k0, min(BK, p.K - k0), seen, abort_flag)) { ok = false; break; }
+          }
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(&full[s], A_STAGE_BYTES + B_STAGE_BYTES);
           uint8_t* a_dst = sA + s * A_STAGE_BYTES;
           uint8_t* b_dst = sB + s * B_STAGE_BYTES;
-          const int k0 = kb * BK;
           int which, lr;
+          const int a_split = COPY ? 0 : p.a_gather, b_split = COPY ? 0 : p.b_gather;  // copy mode reads the local image
           if (!p.a_mn) {
-            locate(m0, p.a_rows, p.a_gather, which, lr);
+            locate(m0, p.a_rows, a_split, which, lr);
             tma_load_2d(a_dst, &maps_a.m[which], &full[s], k0, lr);
           } else {
-            locate(k0, p.a_rows, p.a_gather, which, lr);
+            locate(k0, p.a_rows, a_split, which, lr);
 #pragma unroll
             for (int a = 0; a < BM / 64; ++a) tma_load_2d(a_dst + a * ATOM_BYTES, &maps_a.m[which], &full[s], m0 + a * 64, lr);
           }
           if (!p.b_mn) {
-            locate(n0, p.b_rows, p.b_gather, which, lr);
+            locate(n0, p.b_rows, b_split, which, lr);
             tma_load_2d(b_dst, &maps_b.m[which], &full[s], k0, lr);
           } else {
-            locate(k0, p.b_rows, p.b_gather, which, lr);
+            locate(k0, p.b_rows, b_split, which, lr);
 #pragma unroll
             for (int a = 0; a < BN / 64; ++a) tma_load_2d(b_dst + a * ATOM_BYTES, &maps_b.m[which], &full[s], n0 + a * 64, lr);
           }
@@ -170,7 +257,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
           for (int j = 0; j < BK / UMMA_K; ++j) {
             const uint64_t a_desc = p.a_mn ? umma_desc_mnmajor(a_addr, j * UMMA_K, ATOM_BYTES) : umma_desc_kmajor(a_addr, j * 32);
             const uint64_t b_desc = p.b_mn ? umma_desc_mnmajor(b_addr, j * UMMA_K, ATOM_BYTES) : umma_desc_kmajor(b_addr, j * 32);
-            umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);  // kb counts stages, in any k order
           }
           umma_commit(&empty[s]);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
@@ -178,6 +265,49 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
         if (!ok) break;
         umma_commit(&tfull[acc]);
         if (++acc == 2) { acc = 0; aph ^= 1u; }
+      }
+    }
+  } else if (warp == COPY_WARP) {
+    // ------------------------------- gather copier -------------------------------
+    // Piece g of the peers' shards (ring order from rank + 1, ascending addresses) belongs to CTA
+    // g % gridDim.x: every chunk is assembled by many SMs at once and the early chunks finish first.
+    if (COPY && lane == 0 && peers_ok && p.ws > 1) {
+      const int ppc = (p.chunk_bytes + COPY_PIECE - 1) / COPY_PIECE;       // pieces per chunk
+      const long long cps = p.shard_bytes / p.chunk_bytes;                   // chunks per shard
+      const long long n_pieces = (long long)(p.ws - 1) * cps * ppc;
+      auto piece = [&](long long g, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes, int& chunk) {
+        const long long ch = g / ppc;
+        const int pc = (int)(g - ch * ppc);
+        const int peer = (p.rank + 1 + (int)(ch / cps)) % p.ws;
+        const long long off = (long long)peer * p.shard_bytes + (ch % cps) * p.chunk_bytes + (long long)pc * COPY_PIECE;
+        src = static_cast<const uint8_t*>(p.gsrc.p[peer]) + off;
+        dst = p.gdst + off;
+        bytes = (uint32_t)min((long long)COPY_PIECE, (long long)p.chunk_bytes - (long long)pc * COPY_PIECE);
+        chunk = (int)(((long long)peer * p.shard_bytes + (ch % cps) * p.chunk_bytes) / p.chunk_bytes);
+      };
+      const long long first = blockIdx.x, stride = gridDim.x;
+      const long long mine = first < n_pieces ? (n_pieces - first + stride - 1) / stride : 0;
+      bool ok = true;
+      for (long long i = 0; i < mine + (COPY_BUFS - 1) && ok; ++i) {
+        if (i < mine) {  // issue the load of my piece i
+          const uint8_t* src; uint8_t* dst; uint32_t bytes; int chunk;
+          piece(first + i * stride, src, dst, bytes, chunk);
+          const int b = (int)(i % COPY_BUFS);
+          mbar_expect_tx(&cbar[b], bytes);
+          bulk_load(sCopy + b * COPY_PIECE, src, bytes, &cbar[b]);
+        }
+        const long long j = i - (COPY_BUFS - 1);
+        if (j >= 0) {    // forward my piece j to local memory and publish it
+          const uint8_t* src; uint8_t* dst; uint32_t bytes; int chunk;
+          piece(first + j * stride, src, dst, bytes, chunk);
+          const int b = (int)(j % COPY_BUFS);
+          if (!mbar_wait(&cbar[b], (uint32_t)((j / COPY_BUFS) & 1), abort_flag, p.err, KB_ERR_TIMEOUT_PEER)) { ok = false; break; }
+          bulk_store(dst, sCopy + b * COPY_PIECE, bytes);
+          tma_store_commit();
+          tma_store_wait_all<0>();   // the piece is in local memory (and its buffer is free again)
+          fence_proxy_async_all();
+          red_release_gpu_add(p.ready + chunk, 1u);
+        }
       }
     }
   } else {
@@ -303,16 +433,27 @@ extern "C" {
 //   c_mode 1: reduce-scatter: out [M / ws, N] on each rank; staging buffers [ws, M / ws, N]
 //   c_mode 2: all-reduce:     out [M, N] on every rank;     staging buffers [ws, roundup(M, 128), N]
 // epoch must grow by at least 2 per call; grid_sync: 2 uints, zero-initialised once.
+// gather_copy = 1 (copy mode): the gathered operand's pointers are every rank's image of the WHOLE
+// operand (contiguous rows, pitch = stored columns; rank r's shard already in place at its rows of
+// image r), `ready` is one zero-initialised counter per 128-row chunk of this rank's image and
+// `ready_target` = (number of copy-mode calls on this image, this one included) x ceil(128 rows in
+// bytes / 16 KiB).  Shards must be whole 128-row chunks.
 int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_local, const void* const* stage_ptrs,
                  const void* const* ctrl_ptrs, void* out, int M, int N, int K, long lda, long ldb, long ldc, long ldo,
                  int a_mn, int b_mn, int a_gather, int b_gather, int c_mode, int rank, int ws, unsigned int epoch,
-                 unsigned int* grid_sync, void* stream) {
+                 unsigned int* grid_sync, int gather_copy, unsigned int* ready, unsigned int ready_target,
+                 void* stream) {
   using namespace kb::gcomm;
   if (M <= 0 || N <= 0 || K <= 0 || ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws) return KB_STATUS_BAD_ARG;
   if ((lda & 7) || (ldb & 7) || (N & 7)) return KB_STATUS_BAD_ARG;
+  const bool copy = gather_copy && ws > 1 && (a_gather || b_gather);
+  if (copy && ((a_gather && b_gather) || !ready)) return KB_STATUS_BAD_ARG;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_comm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_comm_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem_bytes<4, false>()) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_comm_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem_bytes<3, true>()) != cudaSuccess)
       return KB_STATUS_CUDA_ERROR;
     attr_set = true;
   }
@@ -334,6 +475,19 @@ int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_l
   p.b_rows = b_gather ? b_stored_rows / ws : b_stored_rows;
   if (a_gather && (a_stored_rows % ws || p.a_rows % (a_mn ? BK : BM))) return KB_STATUS_BAD_ARG;
   if (b_gather && (b_stored_rows % ws || p.b_rows % (b_mn ? BK : BN))) return KB_STATUS_BAD_ARG;
+  if (copy) {
+    const long ld = a_gather ? lda : ldb;
+    const int cols = a_gather ? a_stored_cols : b_stored_cols;
+    p.gather_rows = a_gather ? p.a_rows : p.b_rows;
+    if (ld != cols || p.gather_rows % CHUNK_ROWS) return KB_STATUS_BAD_ARG;  // contiguous image, whole chunks
+    p.chunk_bytes = CHUNK_ROWS * cols * 2;
+    p.shard_bytes = (long long)p.gather_rows * cols * 2;
+    const void* const* gp = a_gather ? a_ptrs : b_ptrs;
+    for (int i = 0; i < MAX_RANKS; ++i) p.gsrc.p[i] = i < ws ? const_cast<void*>(gp[i]) : nullptr;
+    p.gdst = static_cast<uint8_t*>(const_cast<void*>(gp[rank]));
+    p.ready = ready;
+    p.ready_target = ready_target;
+  }
   p.c_rows = c_mode == 1 ? M / ws : M;
   p.c_slot_rows = (p.c_rows + BM - 1) / BM * BM;  // whole tiles per slot: a tile never spills into a neighbour
   if (c_mode == 1 && (M % ws || p.c_rows % BM)) return KB_STATUS_BAD_ARG;
@@ -347,11 +501,16 @@ int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_l
     const void* ap = a_ptrs[a_gather ? ia : (ws > 0 ? rank : 0)];
     const void* bp = b_ptrs[b_gather ? ib : (ws > 0 ? rank : 0)];
     int rc;
-    if (!a_mn) rc = kb::make_tmap_2d(&ma.m[i], ap, 2, p.a_rows, a_stored_cols, lda * 2, BM, BK, true);
-    else       rc = kb::make_tmap_2d(&ma.m[i], ap, 2, p.a_rows, a_stored_cols, lda * 2, BK, 64, true);
+    // copy mode: one map over the whole local image; direct mode: one map per rank's shard
+    const void* apc = copy && a_gather ? a_ptrs[rank] : ap;
+    const void* bpc = copy && b_gather ? b_ptrs[rank] : bp;
+    const int a_map_rows = copy && a_gather ? a_stored_rows : p.a_rows;
+    const int b_map_rows = copy && b_gather ? b_stored_rows : p.b_rows;
+    if (!a_mn) rc = kb::make_tmap_2d(&ma.m[i], apc, 2, a_map_rows, a_stored_cols, lda * 2, BM, BK, true);
+    else       rc = kb::make_tmap_2d(&ma.m[i], apc, 2, a_map_rows, a_stored_cols, lda * 2, BK, 64, true);
     if (rc) return KB_STATUS_TMAP_ERROR;
-    if (!b_mn) rc = kb::make_tmap_2d(&mb.m[i], bp, 2, p.b_rows, b_stored_cols, ldb * 2, BN, BK, true);
-    else       rc = kb::make_tmap_2d(&mb.m[i], bp, 2, p.b_rows, b_stored_cols, ldb * 2, BK, 64, true);
+    if (!b_mn) rc = kb::make_tmap_2d(&mb.m[i], bpc, 2, b_map_rows, b_stored_cols, ldb * 2, BN, BK, true);
+    else       rc = kb::make_tmap_2d(&mb.m[i], bpc, 2, b_map_rows, b_stored_cols, ldb * 2, BK, 64, true);
     if (rc) return KB_STATUS_TMAP_ERROR;
     if (c_mode == 0) {
       rc = kb::make_tmap_2d(&mc.m[i], c_local, 2, M, N, ldc * 2, BM, EPI_COLS, true);
@@ -364,7 +523,10 @@ int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_l
   const int total = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = total < sms ? total : sms;
   if (c_mode != 0 && grid < 1) grid = 1;
-  gemm_comm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ma, mb, mc, p);
+  if (copy)
+    gemm_comm_kernel<3, true><<<grid, NUM_THREADS, smem_bytes<3, true>(), static_cast<cudaStream_t>(stream)>>>(ma, mb, mc, p);
+  else
+    gemm_comm_kernel<4, false><<<grid, NUM_THREADS, smem_bytes<4, false>(), static_cast<cudaStream_t>(stream)>>>(ma, mb, mc, p);
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 

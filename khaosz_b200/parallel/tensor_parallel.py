@@ -40,6 +40,7 @@ class TPContext:
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.use_kernels = self.device.type == "cuda" and self.ws > 1 and self.ws <= 8 and _lib.has("kb_gemm_comm")
         self._pool: Dict[Tuple[str, int], SymmetricBuffer] = {}
+        self._images: Dict[Tuple[str, int, int], list] = {}
         if self.use_kernels:
             self.ctrl = PeerControl(self.device, self.group)
             self.grid_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
@@ -65,6 +66,23 @@ class TPContext:
             dist.barrier(group=self.group)
             self._pool[key] = buf
         return buf
+
+    def gather_image(self, tag: str, shard: torch.Tensor):
+        """Symmetric image of a whole row-sharded operand with this rank's shard copied into its
+        rows.  Returns ``(buffer, ready_counters, ready_target)`` for the copy-mode gather of the
+        fused kernel (peers pull the other shards inside the kernel)."""
+        rows, cols = shard.shape
+        key = (tag, rows, cols)
+        entry = self._images.get(key)
+        if entry is None:
+            buf = self.buffer(tag + ".img", self.ws * rows * cols)
+            ready = torch.zeros(self.ws * rows // 128, dtype=torch.int32, device=self.device)
+            entry = self._images[key] = [buf, ready, 0]
+        buf, ready, calls = entry
+        buf.tensor[: self.ws * rows * cols].view(self.ws * rows, cols)[self.rank * rows:(self.rank + 1) * rows].copy_(shard)
+        entry[2] = calls + 1
+        pieces_per_chunk = (128 * cols * 2 + 16383) // 16384
+        return buf, ready, entry[2] * pieces_per_chunk
 
     def stage_in(self, tag: str, t: torch.Tensor) -> SymmetricBuffer:
         """Copy a local tensor into symmetric memory so that peers can read it."""
@@ -92,13 +110,22 @@ def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, 
     N = b_cols if b_mn else B_rows
     Kb = B_rows if b_mn else b_cols
     assert K == Kb, (K, Kb)
-    if a_gather:
+    copy, ready, ready_target = 0, None, 0
+    if (a_gather and a_rows % 128 == 0) or (b_gather and b_rows % 128 == 0):
+        copy = 1  # whole 128-row chunks: peers' shards are pulled once into a local image
+    if a_gather and copy:
+        sa, ready, ready_target = ctx.gather_image(tag + ".a", a)
+        a_ptrs, lda = sa.ptrs, a_cols
+    elif a_gather:
         sa = ctx.stage_in(tag + ".a", a)
         a_ptrs, lda = sa.ptrs, a_cols
     else:
         a = a if a.stride(-1) == 1 else a.contiguous()
         a_ptrs, lda = _ptr_list([a.data_ptr()] * ws), a.stride(0)
-    if b_gather:
+    if b_gather and copy:
+        sb, ready, ready_target = ctx.gather_image(tag + ".b", b)
+        b_ptrs, ldb = sb.ptrs, b_cols
+    elif b_gather:
         sb = ctx.stage_in(tag + ".b", b)
         b_ptrs, ldb = sb.ptrs, b_cols
     else:
@@ -118,7 +145,8 @@ def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, 
         ldc, ldo = N, N
     check(lib().kb_gemm_comm(a_ptrs, b_ptrs, ptr(c_local), stage_ptrs, ctx.ctrl.flags.ptrs, ptr(out), M, N, K, lda, ldb,
                              ldc, ldo, int(a_mn), int(b_mn), int(a_gather), int(b_gather), c_mode, rank, ws,
-                             ctx.ctrl.next_epoch(), ptr(ctx.grid_sync), stream()), "gemm_comm")
+                             ctx.ctrl.next_epoch(), ptr(ctx.grid_sync), copy, ptr(ready), ready_target, stream()),
+          "gemm_comm")
     return c_local if c_mode == 0 else out
 
 

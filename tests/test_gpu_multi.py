@@ -233,6 +233,11 @@ def _tp_kernels_case():
     w2 = (torch.randn(N2 // ws, K, device=dev, generator=g) * 0.1).to(torch.bfloat16)
     y = _comm_gemm(tp, xa, w2, b_gather=True, tag="t5")
     close(y, xa.float() @ gather(w2).float().t())
+    # shards that are not whole 128-row chunks take the direct path (tiles read from the owner)
+    xs = torch.randn(192, K, device=dev, generator=g).to(torch.bfloat16)
+    dy2 = torch.randn(192 * ws, N, device=dev, generator=g).to(torch.bfloat16)
+    dw2 = _comm_gemm(tp, dy2, xs, a_mn=True, b_mn=True, b_gather=True, tag="t6")
+    close(dw2, dy2.float().t() @ gather(xs).float())
     torch.cuda.synchronize()
     raise_on_device_error()
 
