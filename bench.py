@@ -206,7 +206,8 @@ def run_own(args):
     from khaosz_b200.trainer import FusedAdamW, SchedulerFactory, StrategyFactory, Trainer
 
     cfg = AutoRegressiveLMConfig(**MODEL)
-    mode = "ddp" if ws > 1 else "none"
+    mode = args.parallel if ws > 1 else "none"
+    replicas = 1 if mode == "tp" else ws  # data-parallel replicas
     steps_total = args.warmup + args.steps
 
     def model_fn():
@@ -229,7 +230,7 @@ def run_own(args):
     opt = optimizer_fn(model)
     model, opt, _, sched = executor.prepare(model, opt, None, scheduler_fn(opt))
     strategy = StrategyFactory.create("seq", model, device, label_smoothing=SMOOTH)
-    g = torch.Generator(device="cpu").manual_seed(SEED + rank)
+    g = torch.Generator(device="cpu").manual_seed(SEED + (rank if replicas > 1 else 0))
     pool = torch.randint(0, MODEL["vocab_size"], (ACCUM, BPD, SEQ + 1), generator=g).to(device)
     model.train()
 
@@ -263,7 +264,7 @@ def run_own(args):
     clocks = sampler.stop()
     final_loss = float(loss)
     raise_on_device_error()
-    tokens = args.steps * ACCUM * BPD * SEQ * ws
+    tokens = args.steps * ACCUM * BPD * SEQ * replicas
     value = tokens / (ms / 1e3)
     del model, opt, sched, strategy, executor, pool
     torch.cuda.empty_cache()
@@ -271,7 +272,7 @@ def run_own(args):
     # ---- end to end through the public Trainer API ----
     e2e = None
     if not args.no_e2e:
-        n_samples = steps_total * ACCUM * BPD * ws
+        n_samples = steps_total * ACCUM * BPD * replicas
         dataset = SyntheticTokens(n_samples, SEQ, MODEL["vocab_size"], SEED)
         timer = StepTimer(args.warmup, args.steps, ACCUM, local_rank, _lib.launch_count)
         tmp = tempfile.mkdtemp(prefix="kb200_bench_")
@@ -294,6 +295,11 @@ def run_own(args):
                       "loss read back per micro-batch)"}
 
     payload = base_payload(args, ws, "khaosz_b200")
+    if mode in ("fsdp", "tp"):
+        payload["config"]["parallelism"] = f"{mode}{ws}"
+    if mode == "tp":
+        payload["scaling"] = "strong"
+        payload["config"]["global_batch"] = BPD * ACCUM
     payload.update({"value": value, "ms_per_step": ms / args.steps, "clocks": clocks, "gpu_launches": launches,
                     "final_loss": final_loss})
     if e2e is not None:
@@ -401,6 +407,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="khaosz_b200", choices=["khaosz_b200", "own", "reference"])
     ap.add_argument("--no-e2e", dest="no_e2e", action="store_true")
+    ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp", "tp"],
+                    help="own arm, N > 1: data parallel (default), sharded data parallel, or tensor parallel "
+                         "(tp: every rank reads the same batches, total work is fixed -> strong scaling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     ws = env_rank()[2]

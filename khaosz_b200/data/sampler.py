@@ -24,12 +24,20 @@ class ResumableDistributedSampler(Sampler[int]):
         self.rank = rank if rank is not None else get_rank()
         self.epoch, self.iter = start_epoch, start_iter
         self.seed, self.shuffle, self.drop_last = seed, shuffle, drop_last
-        n = len(data_source)
-        if drop_last and n % self.num_replicas:
+        self._size()
+
+    def _size(self) -> None:
+        n = len(self.data_source)
+        if self.drop_last and n % self.num_replicas:
             self.num_samples = n // self.num_replicas
         else:
             self.num_samples = (n + self.num_replicas - 1) // self.num_replicas
         self.total_size = self.num_samples * self.num_replicas
+
+    def set_replicas(self, num_replicas: int, rank: int) -> None:
+        """Re-partition the data (tensor-parallel ranks all read the same samples: one replica)."""
+        self.num_replicas, self.rank = num_replicas, rank
+        self._size()
 
     def _order(self) -> list:
         n = len(self.data_source)

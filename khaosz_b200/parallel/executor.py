@@ -364,3 +364,79 @@ class FSDPExecutor(BaseExecutor):
         sq = self.flat.grad[off:off + n].float().pow(2).sum()
         dist.all_reduce(sq)
         return sq
+
+
+@ExecutorFactory.register("tp")
+class TPExecutor(BaseExecutor):
+    """Tensor parallelism with sequence-sharded activations over the whole process group.
+
+    ``prepare`` rewrites the model into its tensor-parallel form (``khaosz_b200.parallel.tp_model``),
+    points the optimizer at the sharded parameters, and makes every rank read the same batches
+    (one data replica).  ``backward`` scales the local loss by ``1 / ws`` (each rank holds
+    ``tokens / ws`` of the batch) and, on synchronisation steps, sums the gradients of the
+    replicated parameters over the group.  ``unwrap_model`` returns the full state dict with
+    the reference's parameter names.  The reference has no counterpart: its ``parallel_mode``
+    choices are ``none/ddp/fsdp`` (``scripts/tools/train.py:171-176``).
+    """
+
+    def __init__(self, grad_accum_steps: int = 1, tp_size: Optional[int] = None, init_sync: bool = True, **_ignored):
+        super().__init__(grad_accum_steps)
+        self.tp_size = tp_size
+        self.init_sync = init_sync
+
+    def _prepare_model(self, model: nn.Module) -> nn.Module:
+        from .tp_model import tensorize
+
+        ws = get_world_size()
+        if self.tp_size not in (None, ws):
+            raise NotImplementedError(f"tp_size={self.tp_size}: the tensor-parallel group is the whole world ({ws} ranks)")
+        if self.init_sync:
+            _broadcast_parameters(model, None)
+        tp = tensorize(model) if ws > 1 or dist.is_initialized() else model
+        if self.flatten_on_cuda and _wants_flat(tp):
+            self.flat = FlatParameters(tp, with_grad=True)
+        self._model = tp
+        return tp
+
+    def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):
+        model = self._prepare_model(model)
+        sampler = getattr(dataloader, "sampler", None)
+        if hasattr(sampler, "set_replicas"):
+            sampler.set_replicas(1, 0)
+        if optimizer is not None:
+            if len(optimizer.param_groups) != 1:
+                raise NotImplementedError("tp: optimizers with several parameter groups are not re-pointed")
+            seen, params = set(), []
+            for p in model.parameters():
+                if p.requires_grad and id(p) not in seen:
+                    seen.add(id(p))
+                    params.append(p)
+            optimizer.param_groups[0]["params"] = params
+            optimizer.state.clear()
+            if self.flat is not None and hasattr(optimizer, "attach_flat"):
+                optimizer.attach_flat(self.flat)
+            if hasattr(optimizer, "set_norm_fn") and hasattr(model, "grad_norm_sq"):
+                optimizer.set_norm_fn(model.grad_norm_sq)
+            optimizer = AccumOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step)
+        if scheduler is not None:
+            scheduler = AccumScheduler(scheduler, self.gradient_state)
+        return model, optimizer, dataloader, scheduler
+
+    def backward(self, loss: torch.Tensor) -> None:
+        ws = get_world_size()
+        (loss / ws if ws > 1 else loss).backward()
+        if self.gradient_state.sync_gradients:
+            self._sync_gradients()
+
+    def _sync_gradients(self) -> None:
+        reduce = getattr(self._model, "reduce_replicated_grads", None)
+        if reduce is not None:
+            reduce()
+
+    def unwrap_model(self, model: nn.Module) -> Dict[str, torch.Tensor]:
+        full = getattr(model, "full_state_dict", None)
+        return full() if full is not None else model.state_dict()
+
+    def grad_norm_sq_extra(self) -> Optional[torch.Tensor]:
+        fn = getattr(self._model, "grad_norm_sq", None)
+        return fn() if fn is not None and get_world_size() > 1 else None

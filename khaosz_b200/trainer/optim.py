@@ -39,6 +39,12 @@ class FusedAdamW(Optimizer):
         self._lr_step_dev: Optional[torch.Tensor] = None
         self._gnorm_sq: Optional[torch.Tensor] = None
         self.last_grad_norm: Optional[torch.Tensor] = None
+        self._norm_fn = None
+
+    def set_norm_fn(self, fn) -> None:
+        """``fn() -> device scalar`` with the global squared gradient norm; executors whose
+        parameters are partly sharded and partly replicated (tensor parallel) install it."""
+        self._norm_fn = fn
 
     # -- wiring done by the executors -------------------------------------------------------
     def attach_flat(self, flat, shard: Optional[Tuple[int, int]] = None, allocate: bool = True) -> None:
@@ -106,7 +112,9 @@ class FusedAdamW(Optimizer):
         if self._reducer is not None and self._reducer.fuses_optimizer:
             self._reducer.fused_step(self, lr, beta1, beta2, eps, wd, clip, self._step_count)
             return
-        gn = self._global_norm_sq(g) if clip is not None else None
+        gn = None
+        if clip is not None:
+            gn = self._norm_fn().reshape(1).float() if self._norm_fn is not None else self._global_norm_sq(g)
         if gn is not None:
             self.last_grad_norm = gn.sqrt()
         if p.is_cuda and p.dtype == torch.bfloat16:
@@ -134,7 +142,13 @@ class FusedAdamW(Optimizer):
     def _step_per_param(self) -> None:
         if self._clip:
             params = [p for g in self.param_groups for p in g["params"] if p.grad is not None]
-            if params:
+            if params and self._norm_fn is not None:
+                norm = self._norm_fn().float().sqrt()
+                self.last_grad_norm = norm
+                factor = torch.clamp(self._clip / (norm + 1e-6), max=1.0)
+                for p in params:
+                    p.grad.mul_(factor.to(p.grad.dtype))
+            elif params:
                 self.last_grad_norm = torch.nn.utils.clip_grad_norm_(params, self._clip)
         for group in self.param_groups:
             beta1, beta2 = group["betas"]

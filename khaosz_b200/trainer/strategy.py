@@ -58,6 +58,17 @@ def get_logprobs(model, input_ids: Tensor, mask: Tensor, reduction: str) -> Tens
     return total / m.sum(dim=-1).clamp(min=1.0) if reduction == "mean" else total
 
 
+def local_loss(model, logits: Tensor, targets: Tensor, label_smoothing: float) -> Tensor:
+    """Mean label-smoothed cross entropy.  A tensor-parallel model returns the logits of its
+    token slice only: the targets are cut to that slice and the local mean is weighted so that
+    the ranks' losses add up to the global mean."""
+    shard = getattr(model, "shard_targets", None)
+    if shard is None:
+        return ops.cross_entropy(logits, targets, label_smoothing, IGNORE_INDEX)
+    local = shard(targets)
+    return ops.cross_entropy(logits, local, label_smoothing, IGNORE_INDEX) * model.loss_weight(local, IGNORE_INDEX)
+
+
 class BaseStrategy(ABC):
     def __init__(self, model, device, **kwargs):
         self.model, self.device = model, device
@@ -100,7 +111,7 @@ class SEQStrategy(BaseStrategy):
     def compute_loss(self, batch):
         batch = move_to_device(batch, self.device)
         logits = self.model(input_ids=batch["input_ids"])["logits"]
-        return ops.cross_entropy(logits, batch["target_ids"], self.label_smoothing, IGNORE_INDEX)
+        return local_loss(self.model, logits, batch["target_ids"], self.label_smoothing)
 
 
 @StrategyFactory.register("sft")
@@ -113,7 +124,7 @@ class SFTStrategy(BaseStrategy):
         batch = move_to_device(batch, self.device)
         targets = batch["target_ids"].masked_fill(batch["loss_mask"] == 0, IGNORE_INDEX)
         logits = self.model(input_ids=batch["input_ids"])["logits"]
-        return ops.cross_entropy(logits, targets, self.label_smoothing, IGNORE_INDEX)
+        return local_loss(self.model, logits, targets, self.label_smoothing)
 
 
 @StrategyFactory.register("dpo")

@@ -70,7 +70,8 @@ def _run_steps(mode, world, rank, steps=10, accum=1, fused=True):
     from khaosz_b200.trainer import FusedAdamW, StrategyFactory
 
     g = torch.Generator().manual_seed(3407)
-    data = torch.randint(0, 1000, (steps * accum, 2 * world, 129), generator=g)  # global batch = 2 per rank
+    # global batch = 2 per data-parallel rank; tensor-parallel ranks all read the same 4 sequences
+    data = torch.randint(0, 1000, (steps * accum, 4 if mode == "tp" else 2 * world, 129), generator=g)
     model = _make_model()
     ex = ExecutorFactory.create(mode, grad_accum_steps=accum)
     if fused:
@@ -81,7 +82,7 @@ def _run_steps(mode, world, rank, steps=10, accum=1, fused=True):
     strat = StrategyFactory.create("seq", model, "cpu", label_smoothing=0.05)
     losses = []
     for i in range(steps * accum):
-        mine = data[i, 2 * rank:2 * rank + 2]
+        mine = data[i] if mode == "tp" else data[i, 2 * rank:2 * rank + 2]
         with ex.accumulate(model):
             loss = strat({"input_ids": mine[:, :-1], "target_ids": mine[:, 1:]})
             ex.backward(loss / accum)
@@ -126,10 +127,11 @@ def _single_reference():
     return losses, model.state_dict()
 
 
-@pytest.mark.parametrize("mode,port", [("ddp", "29631"), ("fsdp", "29632")])
-def test_executor_matches_single_process(mode, port, tmp_path):
+@pytest.mark.parametrize("mode,port,world", [("ddp", "29631", 2), ("fsdp", "29632", 2), ("tp", "29633", 2),
+                                             ("tp", "29634", 4)])  # tp on 4 ranks: 2 KV heads shared by rank pairs
+def test_executor_matches_single_process(mode, port, world, tmp_path):
     out = str(tmp_path / "r.pt")
-    spawn_parallel_fn(_distributed_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port=port,
+    spawn_parallel_fn(_distributed_case, world_size=world, backend="gloo", master_addr="127.0.0.1", master_port=port,
                       mode=mode, out=out)
     got = torch.load(out)
     ref_losses, ref_sd = _single_reference()
