@@ -295,7 +295,7 @@ def run_own(args):
                       "loss read back per micro-batch)"}
 
     payload = base_payload(args, ws, "khaosz_b200")
-    if mode in ("fsdp", "tp"):
+    if mode in ("fsdp", "fsdp_full", "tp"):
         payload["config"]["parallelism"] = f"{mode}{ws}"
     if mode == "tp":
         payload["scaling"] = "strong"
@@ -407,7 +407,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="khaosz_b200", choices=["khaosz_b200", "own", "reference"])
     ap.add_argument("--no-e2e", dest="no_e2e", action="store_true")
-    ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp", "tp"],
+    ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp", "fsdp_full", "tp"],
                     help="own arm, N > 1: data parallel (default), sharded data parallel, or tensor parallel "
                          "(tp: every rank reads the same batches, total work is fixed -> strong scaling)")
     args = ap.parse_args()

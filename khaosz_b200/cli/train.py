@@ -18,6 +18,8 @@ from ..config import AutoRegressiveLMConfig, TrainConfig
 from ..data import DatasetFactory
 from ..models import AutoRegressiveLM
 from ..models.components.block import DecoderBlock
+from ..parallel.fsdp_model import ShardedBlock
+from ..parallel.tp_model import TPBlock
 from ..trainer import FusedAdamW, Muon, SchedulerFactory, Trainer
 
 
@@ -56,7 +58,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--master_port", type=str, default="29500")
     p.add_argument("--backend", type=str, default="nccl")
     p.add_argument("--nprocs", type=int, default=1)
-    p.add_argument("--parallel_mode", choices=["none", "ddp", "fsdp", "tp"], default="none")
+    p.add_argument("--parallel_mode", choices=["none", "ddp", "fsdp", "fsdp_full", "tp"], default="none")
     p.add_argument("--tp_size", type=int, default=None)
     p.add_argument("--fp8", action="store_true", default=False, help="block-scaled fp8 GEMMs (tp mode)")
     p.add_argument("--device_type", type=str, default="cuda")
@@ -84,7 +86,7 @@ def train(args: argparse.Namespace) -> None:
     if not os.path.exists(args.param_path):
         raise FileNotFoundError(args.param_path)
     if args.nprocs > 1 and args.parallel_mode == "none":
-        raise ValueError("--nprocs > 1 requires --parallel_mode to be 'ddp', 'fsdp' or 'tp'")
+        raise ValueError("--nprocs > 1 requires --parallel_mode to be 'ddp', 'fsdp', 'fsdp_full' or 'tp'")
     config = AutoRegressiveLMConfig.from_file(os.path.join(args.param_path, "config.json"))
     window = args.window_size or config.max_len
     dataset = DatasetFactory.load(train_type=args.train_type, load_path=args.data_root_path, window_size=window,
@@ -106,7 +108,7 @@ def train(args: argparse.Namespace) -> None:
         num_workers=args.num_workers, pin_memory=args.pin_memory, nprocs=args.nprocs, backend=args.backend,
         master_addr=args.master_addr, master_port=args.master_port, parallel_mode=args.parallel_mode,
         device_type=args.device_type, start_method=args.start_method,
-        gradient_checkpointing_modules=[DecoderBlock] if args.gradient_checkpointing else [],
+        gradient_checkpointing_modules=[DecoderBlock, TPBlock, ShardedBlock] if args.gradient_checkpointing else [],
         executor_kwargs=executor_kwargs,
         extra_kwargs={"beta": args.dpo_beta, "label_smoothing": args.label_smoothing, "clip_eps": args.grpo_clip_eps,
                       "kl_coef": args.grpo_kl_coef, "group_size": args.group_size,

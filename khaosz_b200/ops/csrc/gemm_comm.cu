@@ -473,8 +473,9 @@ int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_l
   const int b_stored_rows = b_mn ? K : N, b_stored_cols = b_mn ? N : K;
   p.a_rows = a_gather ? a_stored_rows / ws : a_stored_rows;
   p.b_rows = b_gather ? b_stored_rows / ws : b_stored_rows;
-  if (a_gather && (a_stored_rows % ws || p.a_rows % (a_mn ? BK : BM))) return KB_STATUS_BAD_ARG;
-  if (b_gather && (b_stored_rows % ws || p.b_rows % (b_mn ? BK : BN))) return KB_STATUS_BAD_ARG;
+  // direct mode: a tile (or k-block) must not straddle two ranks' shards; copy mode reads one contiguous image
+  if (a_gather && (a_stored_rows % ws || (!copy && p.a_rows % (a_mn ? BK : BM)))) return KB_STATUS_BAD_ARG;
+  if (b_gather && (b_stored_rows % ws || (!copy && p.b_rows % (b_mn ? BK : BN)))) return KB_STATUS_BAD_ARG;
   if (copy) {
     const long ld = a_gather ? lda : ldb;
     const int cols = a_gather ? a_stored_cols : b_stored_cols;

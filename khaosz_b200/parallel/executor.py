@@ -440,3 +440,35 @@ class TPExecutor(BaseExecutor):
     def grad_norm_sq_extra(self) -> Optional[torch.Tensor]:
         fn = getattr(self._model, "grad_norm_sq", None)
         return fn() if fn is not None and get_world_size() > 1 else None
+
+
+@ExecutorFactory.register("fsdp_full")
+class FullShardExecutor(TPExecutor):
+    """Fully sharded data parallel: block weights exist as row shards, every forward / backward
+    GEMM gathers its weight inside the kernel and reduce-scatters its weight gradient
+    (``khaosz_b200.parallel.fsdp_model``).  Each rank trains on its own batches, owns the
+    optimizer state of its shards and updates them without any further collective; the
+    replicated embedding / norm gradients take one all-reduce per optimizer step.  This is the
+    memory behaviour of the reference's ``ShardingStrategy.FULL_SHARD`` wrapper
+    (``astrai/parallel/executor.py:223-272``); the ``fsdp`` executor keeps whole parameters
+    resident and shards only gradients and optimizer state, which is faster while the model fits.
+    """
+
+    def _prepare_model(self, model: nn.Module) -> nn.Module:
+        from .fsdp_model import full_shard
+
+        if self.init_sync:
+            _broadcast_parameters(model, None)
+        fs = full_shard(model) if dist.is_initialized() else model
+        if self.flatten_on_cuda and _wants_flat(fs):
+            self.flat = FlatParameters(fs, with_grad=True)
+        self._model = fs
+        return fs
+
+    def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):
+        sampler = getattr(dataloader, "sampler", None)
+        replicas = (sampler.num_replicas, sampler.rank) if hasattr(sampler, "set_replicas") else None
+        out = super().prepare(model, optimizer, dataloader, scheduler)
+        if replicas is not None:
+            sampler.set_replicas(*replicas)  # data parallel: every rank keeps its own slice of the data
+        return out

@@ -1,0 +1,201 @@
+"""Fully sharded form of the decoder-only language model (weights sharded, gathered in the GEMM).
+
+``full_shard(model, group)`` turns every block's projection weights into row shards of the
+packed matrices ``[q;k;v]``, ``o``, ``[gate;up]`` and ``down``: rank ``r`` stores rows
+``[r * n / ws, (r + 1) * n / ws)`` only.  The forward and backward GEMMs gather the weight
+inside the kernel (peers' shards are pulled over NVLink while the tiles of the local shard are
+being computed) and the weight gradient leaves its GEMM through a reduce-scatter, so a rank
+never holds a whole gradient and holds a whole weight only in one reusable image per matrix
+shape (shared by all layers).  Embedding / LM head and the norm weights stay replicated; their
+gradients are averaged with one coalesced all-reduce per optimizer step.
+
+This is the behaviour of the reference's ``FULL_SHARD`` wrapper
+(``astrai/parallel/executor.py:223-272``: parameters sharded, gathered for each forward and
+backward, gradients reduce-scattered) without the separate all-gather and reduce-scatter
+launches.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch import Tensor
+
+from .. import ops
+from ..ops import attention as attn_ops
+from .tensor_parallel import sharded_weight_linear
+from .tp_model import TPInfo
+
+
+def _row_shard(w: Tensor, info: TPInfo) -> nn.Parameter:
+    n = w.shape[0]
+    if n % info.ws:
+        raise ValueError(f"{n} weight rows do not divide by {info.ws} ranks")
+    per = n // info.ws
+    p = nn.Parameter(w[info.rank * per:(info.rank + 1) * per].detach().clone().contiguous())
+    p.fs_sharded = True
+    return p
+
+
+class ShardedAttention(nn.Module):
+    def __init__(self, attn, info: TPInfo):
+        super().__init__()
+        if getattr(attn, "use_qk_norm", False) or getattr(attn, "use_gated_attention", False) or not hasattr(attn, "k_proj"):
+            raise NotImplementedError("full sharding covers plain GQA attention (no qk-norm, gate or MLA)")
+        self.info = info
+        self.n_heads, self.n_kv_heads, self.head_dim = attn.n_heads, attn.n_kv_heads, attn.head_dim
+        self.layer_id = attn.layer_id
+        with torch.no_grad():
+            packed = torch.cat([attn.q_proj.weight, attn.k_proj.weight, attn.v_proj.weight], dim=0)
+        self.qkv_shard = _row_shard(packed, info)
+        self.o_shard = _row_shard(attn.o_proj.weight, info)
+
+    def forward(self, x: Tensor, rotary) -> Tensor:
+        B, S, _ = x.shape
+        H, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
+        cs, pos = rotary
+        tp = self.info.ctx()
+        qkv = sharded_weight_linear(x, self.qkv_shard, tp).view(B, S, H + 2 * Hkv, D)
+        if attn_ops.fused_ok(qkv, D):
+            ctx = attn_ops.rope_attention_packed(qkv, cs, pos, H, Hkv, causal=True)
+        else:
+            qk = ops.rope(qkv[:, :, : H + Hkv], cs, pos)
+            ctx = attn_ops.attention(qk[:, :, :H], qk[:, :, H:], qkv[:, :, H + Hkv:], causal=True)
+        return sharded_weight_linear(ctx.reshape(B, S, H * D), self.o_shard, tp)
+
+
+class ShardedMLP(nn.Module):
+    def __init__(self, mlp, info: TPInfo):
+        super().__init__()
+        if not (hasattr(mlp, "gate") and hasattr(mlp, "up") and hasattr(mlp, "down")):
+            raise NotImplementedError("full sharding covers the dense SwiGLU MLP (no MoE)")
+        self.info = info
+        self.ffn = mlp.gate.weight.shape[0]
+        with torch.no_grad():
+            packed = torch.cat([mlp.gate.weight, mlp.up.weight], dim=0)
+        self.gate_up_shard = _row_shard(packed, info)
+        self.down_shard = _row_shard(mlp.down.weight, info)
+
+    def forward(self, x: Tensor) -> Tensor:
+        tp = self.info.ctx()
+        return sharded_weight_linear(ops.swiglu(sharded_weight_linear(x, self.gate_up_shard, tp)), self.down_shard, tp)
+
+
+class ShardedBlock(nn.Module):
+    def __init__(self, block, info: TPInfo):
+        super().__init__()
+        self.layer_id = block.layer_id
+        self.input_norm = block.input_norm
+        self.post_attention_norm = block.post_attention_norm
+        self.attention = ShardedAttention(block.attention, info)
+        self.mlp = ShardedMLP(block.mlp, info)
+
+    def forward(self, x: Tensor, rotary) -> Tensor:
+        h = x + self.attention(self.input_norm(x), rotary)
+        return h + self.mlp(self.post_attention_norm(h))
+
+
+class FullShardLM(nn.Module):
+    """Data-parallel decoder whose block weights exist as row shards only."""
+
+    def __init__(self, model, group=None):
+        super().__init__()
+        self.info = TPInfo(group)
+        self.config = model.config
+        self.rotary_embedding = model.rotary_embedding
+        self.embed_tokens = model.embed_tokens
+        self.layers = nn.ModuleList(ShardedBlock(b, self.info) for b in model.layers)
+        self.norm = model.norm
+        self.lm_head = model.lm_head
+
+    def forward(self, input_ids: Tensor, input_mask: Optional[Tensor] = None, paged_cache=None,
+                position_ids: Optional[Tensor] = None, logits_rows: Optional[Tensor] = None) -> Dict[str, Tensor]:
+        if paged_cache is not None or position_ids is not None or logits_rows is not None:
+            raise NotImplementedError("the fully sharded training model runs plain causal batches only")
+        x = self.embed_tokens(input_ids)
+        rotary = self.rotary_embedding(x, None)
+        for layer in self.layers:
+            x = layer(x, rotary)
+        hidden = self.norm(x)
+        return {"logits": self.lm_head(hidden), "hidden_states": hidden}
+
+    def _replicated(self) -> List[nn.Parameter]:
+        seen, out = set(), []
+        for p in self.parameters():
+            if id(p) not in seen and not getattr(p, "fs_sharded", False) and p.requires_grad:
+                seen.add(id(p))
+                out.append(p)
+        return out
+
+    @torch.no_grad()
+    def reduce_replicated_grads(self) -> None:
+        """Sum the replicated parameters' gradients over the group (the loss carries the 1/ws)."""
+        if self.info.ws <= 1:
+            return
+        grads = [p.grad for p in self._replicated() if p.grad is not None]
+        if not grads:
+            return
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        dist.all_reduce(flat, group=self.info.group)
+        off = 0
+        for g in grads:
+            g.copy_(flat[off:off + g.numel()].view(g.shape))
+            off += g.numel()
+
+    @torch.no_grad()
+    def grad_norm_sq(self) -> Tensor:
+        """Global squared gradient norm: shards summed over the group, replicated parts once."""
+        dev = next(self.parameters()).device
+        total = torch.zeros((), dtype=torch.float32, device=dev)
+        seen = set()
+        for p in self.parameters():
+            if id(p) in seen or p.grad is None:
+                continue
+            seen.add(id(p))
+            sq = p.grad.float().pow(2).sum()
+            total += sq if getattr(p, "fs_sharded", False) else sq / self.info.ws
+        if self.info.ws > 1:
+            dist.all_reduce(total, group=self.info.group)
+        return total
+
+    def _gather_rows(self, t: Tensor) -> Tensor:
+        if self.info.ws == 1:
+            return t.clone()
+        parts = [torch.empty_like(t) for _ in range(self.info.ws)]
+        dist.all_gather(parts, t.contiguous(), group=self.info.group)
+        return torch.cat(parts, dim=0)
+
+    @torch.no_grad()
+    def full_state_dict(self) -> Dict[str, Tensor]:
+        """Unsharded state dict with the reference's names, identical on every rank (collective)."""
+        sd: Dict[str, Tensor] = {"embed_tokens.weight": self.embed_tokens.weight.detach().clone()}
+        for i, layer in enumerate(self.layers):
+            att, mlp = layer.attention, layer.mlp
+            pre = f"layers.{i}."
+            D, H, Hkv = att.head_dim, att.n_heads, att.n_kv_heads
+            qkv = self._gather_rows(att.qkv_shard.detach())
+            sd[pre + "attention.q_proj.weight"] = qkv[: H * D].clone()
+            sd[pre + "attention.k_proj.weight"] = qkv[H * D:(H + Hkv) * D].clone()
+            sd[pre + "attention.v_proj.weight"] = qkv[(H + Hkv) * D:].clone()
+            sd[pre + "attention.o_proj.weight"] = self._gather_rows(att.o_shard.detach())
+            gu = self._gather_rows(mlp.gate_up_shard.detach())
+            sd[pre + "mlp.gate.weight"] = gu[: mlp.ffn].clone()
+            sd[pre + "mlp.up.weight"] = gu[mlp.ffn:].clone()
+            sd[pre + "mlp.down.weight"] = self._gather_rows(mlp.down_shard.detach())
+            sd[pre + "input_norm.weight"] = layer.input_norm.weight.detach().clone()
+            sd[pre + "post_attention_norm.weight"] = layer.post_attention_norm.weight.detach().clone()
+        sd["norm.weight"] = self.norm.weight.detach().clone()
+        if not getattr(self.config, "tie_weight", False):
+            sd["lm_head.weight"] = self.lm_head.weight.detach().clone()
+        return sd
+
+
+def full_shard(model, group=None) -> FullShardLM:
+    if isinstance(model, FullShardLM):
+        return model
+    if not (hasattr(model, "layers") and hasattr(model, "embed_tokens") and hasattr(model, "lm_head")):
+        raise NotImplementedError(f"full sharding is implemented for decoder LMs, not {type(model).__name__}")
+    return FullShardLM(model, group)

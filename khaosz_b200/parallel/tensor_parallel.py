@@ -226,6 +226,40 @@ class _RowParallelFn(torch.autograd.Function):
         return dx, dw, None, None
 
 
+class _ShardedWeightFn(torch.autograd.Function):
+    """``y = x @ all_gather(W_shard)^T`` for a weight whose rows are sharded over data-parallel
+    ranks (fully sharded data parallel).  Forward and ``dx`` gather the weight inside the GEMM;
+    ``dW`` is the GEMM -> reduce-scatter of ``dy^T x``, so every rank receives the rank-summed
+    gradient of exactly the rows it owns."""
+
+    @staticmethod
+    def forward(ctx, x, w_shard, tp):
+        ctx.tp = tp
+        ctx.save_for_backward(x, w_shard)
+        if _kernel_ok(tp, x, w_shard) and w_shard.shape[0] % 128 == 0:
+            return _comm_gemm(tp, x, w_shard, b_gather=True, tag="fs.fwd")
+        return x @ _all_gather_rows(w_shard, tp.group).t()
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w_shard = ctx.saved_tensors
+        tp = ctx.tp
+        dy = dy.contiguous()
+        if _kernel_ok(tp, dy, w_shard) and w_shard.shape[0] % 128 == 0:
+            dx = _comm_gemm(tp, dy, w_shard, b_mn=True, b_gather=True, tag="fs.dx")   # dy AG(W)
+            dw = _comm_gemm(tp, dy, x, a_mn=True, b_mn=True, c_mode=1, tag="fs.dw")    # RS(dy^T x)
+        else:
+            dx = dy @ _all_gather_rows(w_shard, tp.group)
+            dw = _reduce_scatter_rows(dy.t() @ x, tp.group)
+        return dx, dw, None
+
+
+def sharded_weight_linear(x: torch.Tensor, w_shard: torch.Tensor, tp: "TPContext") -> torch.Tensor:
+    shape = x.shape
+    y = _ShardedWeightFn.apply(x.reshape(-1, shape[-1]), w_shard, tp)
+    return y.view(*shape[:-1], y.shape[-1])
+
+
 def _shard(full: torch.Tensor, dim: int, rank: int, ws: int) -> torch.Tensor:
     n = full.shape[dim] // ws
     return full.narrow(dim, rank * n, n).contiguous()

@@ -149,13 +149,13 @@ def _dp_case(mode, out):
                     "m0": osd["state"][0]["exp_avg"]}, out)
 
 
-def _tp_train_case(out):
+def _tp_train_case(out, mode="tp"):
     from khaosz_b200.ops import raise_on_device_error
     from khaosz_b200.parallel.tensor_parallel import TPContext
 
     rank = dist.get_rank()
     dev = torch.device("cuda", rank)
-    losses, model, ex, opt = _train("tp", 2, rank, dev)
+    losses, model, ex, opt = _train(mode, 2, rank, dev)
     dist.all_reduce(losses)
     losses /= 2
     raise_on_device_error()
@@ -165,11 +165,11 @@ def _tp_train_case(out):
         torch.save({"losses": losses.cpu(), "sd": {k: v.cpu() for k, v in sd.items()}}, out)
 
 
-@pytest.mark.parametrize("mode,port", [("ddp", 29703), ("fsdp", 29704), ("tp", 29707)])
+@pytest.mark.parametrize("mode,port", [("ddp", 29703), ("fsdp", 29704), ("tp", 29707), ("fsdp_full", 29708)])
 def test_fused_data_parallel_step_matches_single_gpu(mode, port, tmp_path):
     out = str(tmp_path / "dp.pt")
-    if mode == "tp":
-        _spawn(_tp_train_case, port, out=out)
+    if mode in ("tp", "fsdp_full"):
+        _spawn(_tp_train_case, port, out=out, mode=mode)
     else:
         _spawn(_dp_case, port, mode=mode, out=out)
     got = torch.load(out)
