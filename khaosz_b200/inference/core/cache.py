@@ -318,6 +318,15 @@ class KvcacheView:
             if q2.stride(-1) != 1:
                 q2 = q2.contiguous()
             out = torch.empty((B, H * D), dtype=q.dtype, device=q.device)
+            if st.page_size in (16, 32, 64, 128) and _lib.has("kb_paged_decode_tc") and q2.data_ptr() % 16 == 0:
+                # tensor-core kernel: K/V pages stream through TMA once for the whole query group
+                check(lib().kb_paged_decode_tc(ptr(q2), ptr(st.k_cache[layer_id]), ptr(st.v_cache[layer_id]),
+                                               ptr(self._table32), ptr(self._lens32), ptr(self._scratch[0]),
+                                               ptr(self._scratch[1]), ptr(out), B, H, k.shape[2], D, st.page_size,
+                                               self._table32.shape[1], st.n_pages, self._n_splits, q2.stride(0),
+                                               out.stride(0), float(D ** -0.5), stream()), "paged_decode_tc")
+                _lib.add_launches(1 if self._n_splits > 1 else 0)
+                return out.view(B, 1, H, D)
             check(lib().kb_paged_decode_attn(ptr(q2), ptr(st.k_cache[layer_id]), ptr(st.v_cache[layer_id]),
                                              ptr(self._table32), ptr(self._lens32), ptr(self._scratch[0]),
                                              ptr(self._scratch[1]), ptr(out), B, H, k.shape[2], D, st.page_size,

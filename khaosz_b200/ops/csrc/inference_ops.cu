@@ -338,6 +338,16 @@ int kb_paged_decode_attn(const void* q, const void* k_pool, const void* v_pool, 
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 
+// Combines the split-KV partials of a decode step: out [B, H*128] (pitch out_pitch).
+int kb_decode_merge(const float* part_acc, const float* part_ml, void* out, int B, int H, int n_splits,
+                    long out_pitch, void* stream) {
+  using namespace kb::inf;
+  if (B <= 0) return KB_STATUS_OK;
+  decode_merge_kernel<<<B * H, DEC_D, 0, (cudaStream_t)stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, n_splits,
+                                                                 out_pitch, H);
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
 // logits bf16 [rows, V] (pitch ld); temperature/top_p fp32 [rows], top_k int32 [rows], uniform
 // fp32 [rows] in [0,1); out int64 [rows].  Any of temperature/top_k/top_p may be NULL.
 int kb_sample(const void* logits, const void* temperature, const void* top_k, const void* top_p,
