@@ -145,6 +145,7 @@ def parse_args(argv=None):
     p.add_argument("--max_batch_size", type=int, default=256)
     p.add_argument("--seed", type=int, default=3407)
     p.add_argument("--device", default="cuda")
+    p.add_argument("--int8", action="store_true", help="int8 weight-only linears (per-channel scales)")
     return p.parse_args(argv)
 
 
@@ -152,6 +153,10 @@ def main(argv=None):
     a = parse_args(argv)
     dtype = torch.bfloat16
     cfg, model = build_model(a.preset, a.device, dtype)
+    if a.int8:
+        from ..ops.quant import quantize_model_int8
+
+        quantize_model_int8(model)
     out = []
     if a.mode in ("prefill", "all"):
         out.append(bench_prefill(model, cfg, a.batch_size, a.prompt_length, a.trials, a.device))
@@ -162,6 +167,7 @@ def main(argv=None):
         out.append(bench_serve(model, cfg, a.requests, a.rate, a.min_prompt, a.max_prompt, a.gen_length,
                                a.max_batch_size, a.page_size if a.page_size != 128 else 16, a.seed))
     for row in out:
+        row["weights"] = "int8" if a.int8 else "bf16"
         print(json.dumps(row))
     return out
 

@@ -256,6 +256,23 @@ class Storage:
         return k[:, :total_len], v[:, :total_len]
 
 
+def _pick_splits(ctas_unsplit: int, longest: int, sms: int = 148) -> int:
+    """Split-KV factor of the decode kernel: the CTA count should fill whole waves of the SMs
+    (one CTA per SM) while every split keeps at least two 128-key tiles; each extra split costs
+    a little in the merge."""
+    max_tiles = max(1, (longest + 127) // 128)
+    best, best_cost = 1, None
+    for n in range(1, 17):
+        if n > 1 and (max_tiles + n - 1) // n < 2:
+            break
+        ctas = ctas_unsplit * n
+        waves = (ctas + sms - 1) // sms
+        cost = waves * sms / ctas * (1.0 + 0.03 * (n - 1))
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = n, cost
+    return best
+
+
 class KvcacheView:
     """What a model forward sees of the cache for one batch.
 
@@ -297,7 +314,8 @@ class KvcacheView:
     def _decode_kernel_ok(self, q: Tensor, k: Tensor, v: Tensor) -> bool:
         H, Hkv = q.shape[2], k.shape[2]
         return (self._seq_lens is not None and q.shape[1] == 1 and q.is_cuda and q.dtype == torch.bfloat16
-                and q.shape[-1] == 128 and v.shape[-1] == 128 and H % Hkv == 0 and H // Hkv <= 8
+                and q.shape[-1] == 128 and v.shape[-1] == 128 and H % Hkv == 0
+                and H // Hkv <= (32 if self._storage.page_size in (16, 32, 64, 128) else 8)
                 and _lib.has("kb_paged_decode_attn"))
 
     def attention(self, layer_id: int, q: Tensor, k: Tensor, v: Tensor) -> Tensor:
@@ -310,8 +328,7 @@ class KvcacheView:
                 self._table32 = self._page_table.to(torch.int32).contiguous()
                 self._lens32 = self._seq_lens.to(torch.int32).contiguous()
                 if not self._n_splits:
-                    longest = st.page_size * self._table32.shape[1]
-                    self._n_splits = max(1, min(16, (148 * 2) // max(1, B * k.shape[2]), (longest + 255) // 256))
+                    self._n_splits = _pick_splits(B * k.shape[2], st.page_size * self._table32.shape[1])
                 self._scratch = (torch.empty(B * H * self._n_splits * 128, dtype=torch.float32, device=q.device),
                                  torch.empty(B * H * self._n_splits * 2, dtype=torch.float32, device=q.device))
             q2 = q.reshape(B, H * D)
@@ -407,5 +424,7 @@ class KVCache:
     def make_table_tensor(self, task_ids: List[str], device, dtype=torch.long) -> Tensor:
         return self._table.table_tensor(task_ids, device, dtype)
 
-    def bind(self, page_table: Tensor, total_len: int = 0, seq_lens: Optional[Tensor] = None) -> KvcacheView:
-        return KvcacheView(self._storage, page_table, total_len, seq_lens)
+    def bind(self, page_table: Tensor, total_len: int = 0, seq_lens: Optional[Tensor] = None,
+             n_splits: int = 0) -> KvcacheView:
+        """``n_splits`` fixes the split-KV factor of the decode kernel (0: chosen from the batch)."""
+        return KvcacheView(self._storage, page_table, total_len, seq_lens, n_splits)

@@ -44,7 +44,7 @@ class InferenceScheduler:
         self._page_cache = KVCache(config.n_layers, n_pages, page_size, config.n_kv_heads, head_dim, self.device,
                                    self.dtype, v_dim)
         self._task_mgr = TaskManager(tokenizer, max_batch_size, max_seq_len, max_prompt_len)
-        self._executor = Executor(model, tokenizer, self._page_cache, self.device, self.dtype)
+        self._executor = Executor(model, tokenizer, self._page_cache, self.device, self.dtype, max_seq_len=max_seq_len)
         self._running = False
         self._fatal_error: Optional[Exception] = None
         self._loop_thread: Optional[threading.Thread] = None

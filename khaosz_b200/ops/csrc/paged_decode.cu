@@ -4,7 +4,7 @@
 // are the first G rows of a 128-row MMA tile (the other rows are zero fill and are ignored), so
 // the K and V pages are streamed from HBM exactly once for the whole group:
 //   warp 0   TMA producer: lane i fetches the id of page i of the current 128-key tile and issues
-//            its [page_size x 64] boxes into the 128B-swizzled K / V stages (2-stage rings)
+//            its [page_size x 64] boxes into the 128B-swizzled K / V stages (3-stage rings)
 //   warp 1   tcgen05.mma issuer: S = Q K^T into one of two TMEM buffers (the next tile's S is
 //            issued before this tile's softmax has finished), O += P V with P read from TMEM
 //   warp 4   online softmax of rows 0..G-1 (TMEM lanes 0..31 belong to the warp with id % 4 == 0)
@@ -25,7 +25,7 @@ constexpr int D = 128;
 constexpr int BKV = 128;
 constexpr int CHUNK_BYTES = 128 * 64 * 2;
 constexpr int TILE_BYTES = 2 * CHUNK_BYTES;
-constexpr int STAGES = 2;
+constexpr int STAGES = 3;
 constexpr int NUM_THREADS = 160;
 constexpr int SOFTMAX_WARP = 4;
 constexpr int SMEM_BYTES = TILE_BYTES + 2 * STAGES * TILE_BYTES + 256 + 1024;
@@ -52,15 +52,15 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   uint8_t* sK = sQ + TILE_BYTES;
   uint8_t* sV = sK + STAGES * TILE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sV + STAGES * TILE_BYTES);
-  uint64_t* q_full = bars;        // [1]
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;    // [2]
-  uint64_t* p_ready = bars + 11;  // [1]
-  uint64_t* pv_done = bars + 12;  // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* q_full = bars;                       // [1]
+  uint64_t* k_full = bars + 1;                   // [STAGES]
+  uint64_t* k_empty = k_full + STAGES;           // [STAGES]
+  uint64_t* v_full = k_empty + STAGES;           // [STAGES]
+  uint64_t* v_empty = v_full + STAGES;           // [STAGES]
+  uint64_t* s_full = v_empty + STAGES;           // [2]
+  uint64_t* p_ready = s_full + 2;                // [1]
+  uint64_t* pv_done = p_ready + 1;               // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,11 +80,11 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < STAGES; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
     }
+    for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1);
     mbar_init(p_ready, 1); mbar_init(pv_done, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
@@ -107,8 +107,8 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const int* table = p.block_table + (size_t)b * p.max_pages;
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int s = j % STAGES;
+        const uint32_t ph = (j / STAGES) & 1;
         const int page0 = (tile0 + j) * ppt;
         int pg = -1;
         if (lane < ppt && page0 + lane < seq_pages && page0 + lane < p.max_pages) pg = table[page0 + lane];
@@ -140,7 +140,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const uint32_t idesc_o = umma_idesc(128, 128, false, true);
       const uint32_t q_addr = smem_u32(sQ);
       auto issue_s = [&](int j) {
-        const uint32_t k_addr = smem_u32(sK + (j & 1) * TILE_BYTES);
+        const uint32_t k_addr = smem_u32(sK + (j % STAGES) * TILE_BYTES);
         const uint32_t d = T_S + (j & 1) * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -148,16 +148,16 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           umma_f16(d, umma_desc_kmajor(q_addr, off), umma_desc_kmajor(k_addr, off), idesc_s, ks ? 1u : 0u);
         }
         umma_commit(&s_full[j & 1]);
-        umma_commit(&k_empty[j & 1]);
+        umma_commit(&k_empty[j % STAGES]);
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, KB_ERR_TIMEOUT_FULL);
       if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, p.err, KB_ERR_TIMEOUT_FULL);
       if (ok) { tc_fence_after(); issue_s(0); }
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int s = j % STAGES;
+        const uint32_t ph = (j / STAGES) & 1;
         if (j + 1 < n_tiles) {
-          if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, p.err, KB_ERR_TIMEOUT_FULL)) { ok = false; break; }
+          if (!mbar_wait(&k_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1, abort_flag, p.err, KB_ERR_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
           issue_s(j + 1);
         }
@@ -165,7 +165,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (!mbar_wait(p_ready, j & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sV + s * TILE_BYTES);
-        const uint32_t a = T_S + s * 128;  // P: bf16 pairs in the first 64 columns of this tile's S
+        const uint32_t a = T_S + (j & 1) * 128;  // P: bf16 pairs in the first 64 columns of this tile's S
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           umma_f16_ts(T_O, a + ks * 8, umma_desc_mnmajor(v_addr, ks * 16, CHUNK_BYTES), idesc_o, (j > 0 || ks) ? 1u : 0u);

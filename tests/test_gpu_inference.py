@@ -12,8 +12,9 @@ from khaosz_b200.inference.sample import SamplingPipeline, TemperatureStrategy, 
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("B,H,Hkv,page", [(3, 8, 2, 16), (5, 16, 4, 16), (2, 4, 4, 64), (1, 8, 1, 128)])
-def test_paged_decode_matches_dense(B, H, Hkv, page):
+@pytest.mark.parametrize("B,H,Hkv,page,splits", [(3, 8, 2, 16, 0), (5, 16, 4, 16, 1), (2, 4, 4, 64, 0), (1, 8, 1, 128, 0),
+                                                 (4, 16, 4, 32, 1), (2, 32, 1, 16, 3)])
+def test_paged_decode_matches_dense(B, H, Hkv, page, splits):
     D, n_layers = 128, 2
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(B)
@@ -35,7 +36,7 @@ def test_paged_decode_matches_dense(B, H, Hkv, page):
     q = torch.randn(B, 1, H, D, device=dev, generator=g).to(torch.bfloat16)
     k_new = torch.randn(B, 1, Hkv, D, device=dev, generator=g).to(torch.bfloat16)
     v_new = torch.randn(B, 1, Hkv, D, device=dev, generator=g).to(torch.bfloat16)
-    out = kv.bind(table, seq_lens=lens).attention(layer, q, k_new, v_new)
+    out = kv.bind(table, seq_lens=lens, n_splits=splits).attention(layer, q, k_new, v_new)
     torch.cuda.synchronize()
     for i, l in enumerate(lens.tolist()):
         kk = torch.cat([hist_k[i, :l - 1], k_new[i]], 0).unsqueeze(0)
