@@ -16,6 +16,12 @@
 //   warps 2-5   epilogue: tcgen05.ld -> (+residual) -> bf16 -> swizzled staging tile ->
 //               TMA store, overlapped with the next tile's main loop through the second
 //               accumulator
+// Tail balancing: tiles that fill whole waves of the SMs run as above; the tiles of the last,
+// partial wave are cut into `split` slices of the K dimension so that the wave again covers
+// (almost) all SMs.  A slice writes its fp32 accumulator to a workspace and bumps the tile's
+// counter; the CTA whose slice arrives last sums the slices in slice order (deterministic) and
+// runs the normal epilogue.  Nobody waits for anybody.  The same mechanism turns skinny
+// problems (decode: M <= 256, a handful of tiles) into split-K over all SMs.
 // All waits are bounded (see common.cuh).
 #include "common.cuh"
 #include "kb_api.h"
@@ -52,7 +58,28 @@ struct Params {
   int a_mn, b_mn;
   int epi;  // 0: none, 1: += R
   int* err;
+  // tail balancing
+  int full_tiles;           // tiles [0, full_tiles) are computed whole
+  int split;                // K slices per remaining tile (1: no splitting)
+  float* ws;                // [(total - full_tiles) * split][BM][BN] fp32 partial accumulators
+  unsigned int* counters;   // one per remaining tile, zero between launches
 };
+
+// Work unit u -> tile and k-block range.
+__device__ __forceinline__ void unit_info(const Params& p, int u, int num_k, int& tile, int& kb0, int& kb1, int& rem_idx,
+                                          int& slice) {
+  if (u < p.full_tiles || p.split <= 1) {
+    tile = u; kb0 = 0; kb1 = num_k; rem_idx = -1; slice = 0;
+    return;
+  }
+  const int r = u - p.full_tiles;
+  rem_idx = r / p.split;
+  slice = r - rem_idx * p.split;
+  tile = p.full_tiles + rem_idx;
+  const int per = (num_k + p.split - 1) / p.split;
+  kb0 = slice * per;
+  kb1 = min(num_k, kb0 + per);
+}
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
   const int group_size = GROUP_M * num_n;
@@ -92,7 +119,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
   const int num_k = (p.K + BK - 1) / BK;
-  const int total = num_m * num_n;
+  const int total = p.full_tiles + (num_m * num_n - p.full_tiles) * p.split;  // work units
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -124,11 +151,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        int m_blk, n_blk;
+      for (int u = blockIdx.x; u < total && ok; u += gridDim.x) {
+        int t, kb0, kb1, rem_idx, slice, m_blk, n_blk;
+        unit_info(p, u, num_k, t, kb0, kb1, rem_idx, slice);
         tile_coords(t, num_m, num_n, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN;
-        for (int kb = 0; kb < num_k; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_EMPTY)) {
             ok = false;
             break;
@@ -167,14 +195,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t aph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      for (int u = blockIdx.x; u < total && ok; u += gridDim.x) {
+        int t, kb0, kb1, rem_idx, slice;
+        unit_info(p, u, num_k, t, kb0, kb1, rem_idx, slice);
         if (!mbar_wait(&tempty[acc], aph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_k; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[s], ph, abort_flag, p.err, KB_ERR_TIMEOUT_FULL)) {
             ok = false;
             break;
@@ -188,7 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                            : umma_desc_kmajor(a_addr, j * UMMA_K * 2);
             const uint64_t b_desc = p.b_mn ? umma_desc_mnmajor(b_addr, j * UMMA_K, ATOM_BYTES)
                                            : umma_desc_kmajor(b_addr, j * UMMA_K * 2);
-            umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, a_desc, b_desc, idesc, (kb > kb0 || j) ? 1u : 0u);
           }
           umma_commit(&empty[s]);
           if (++s == STAGES) {
@@ -213,8 +243,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t aph = 0;
     int buf = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-      int m_blk, n_blk;
+    __shared__ int s_last;
+    for (int u = blockIdx.x; u < total && ok; u += gridDim.x) {
+      int t, kb0, kb1, rem_idx, slice, m_blk, n_blk;
+      unit_info(p, u, num_k, t, kb0, kb1, rem_idx, slice);
       tile_coords(t, num_m, num_n, m_blk, n_blk);
       const int m0 = m_blk * BM, n0 = n_blk * BN;
       if (!mbar_wait(&tfull[acc], aph, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) {
@@ -224,14 +256,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
       const int grow = m0 + row_in_tile;
-#pragma unroll 1
-      for (int c = 0; c < BN / EPI_COLS; ++c) {
+      // one 64-column chunk of fp32 values -> (+R) -> bf16 -> staging -> TMA store
+      auto emit_chunk = [&](int c, const uint32_t (&v)[EPI_COLS]) {
         const int col0 = n0 + c * EPI_COLS;
-        if (col0 >= p.N) break;  // uniform across the CTA
-        uint32_t v[EPI_COLS];
-        tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
-        tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
-        tmem_ld_wait();
         // staging buffer `buf` must have been drained by the TMA store issued 2 chunks ago
         if (epi_tid == 0) tma_store_wait_read<NUM_EPI_BUFS - 1>();
         named_barrier_sync(1, 128);
@@ -263,6 +290,64 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tma_store_commit();
         }
         buf ^= 1;
+      };
+      if (rem_idx < 0) {
+#pragma unroll 1
+        for (int c = 0; c < BN / EPI_COLS; ++c) {
+          if (n0 + c * EPI_COLS >= p.N) break;  // uniform across the CTA
+          uint32_t v[EPI_COLS];
+          tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
+          tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
+          tmem_ld_wait();
+          emit_chunk(c, v);
+        }
+      } else {
+        // K slice of a tail tile: park the fp32 accumulator, the last slice to arrive finishes the tile
+        // workspace layout per slice: [chunk][16-byte group][row] so that a warp's accesses are contiguous
+        uint4* mine = reinterpret_cast<uint4*>(p.ws + ((size_t)rem_idx * p.split + slice) * (BM * BN)) + row_in_tile;
+#pragma unroll 1
+        for (int c = 0; c < BN / EPI_COLS; ++c) {
+          if (n0 + c * EPI_COLS >= p.N) break;
+          uint32_t v[EPI_COLS];
+          tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
+          tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < EPI_COLS / 4; ++i)
+            __stcg(mine + (size_t)(c * (EPI_COLS / 4) + i) * BM, make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+        }
+        __threadfence();
+        named_barrier_sync(1, 128);
+        if (epi_tid == 0) {
+          const unsigned int prev = atomicAdd(&p.counters[rem_idx], 1u);
+          const int last = prev == (unsigned int)(p.split - 1);
+          if (last) p.counters[rem_idx] = 0u;  // re-armed for the next launch
+          s_last = last;
+          __threadfence();
+        }
+        named_barrier_sync(1, 128);
+        if (s_last) {
+          const uint4* base = reinterpret_cast<const uint4*>(p.ws + (size_t)rem_idx * p.split * (BM * BN)) + row_in_tile;
+#pragma unroll 1
+          for (int c = 0; c < BN / EPI_COLS; ++c) {
+            if (n0 + c * EPI_COLS >= p.N) break;
+            uint32_t v[EPI_COLS];
+#pragma unroll
+            for (int i = 0; i < EPI_COLS; ++i) v[i] = 0u;
+            for (int sl = 0; sl < p.split; ++sl) {
+              const uint4* src = base + (size_t)sl * (BM * BN / 4) + (size_t)c * (EPI_COLS / 4) * BM;
+#pragma unroll
+              for (int i = 0; i < EPI_COLS / 4; ++i) {
+                const uint4 w = __ldcg(src + (size_t)i * BM);
+                v[4 * i + 0] = __float_as_uint(__uint_as_float(v[4 * i + 0]) + __uint_as_float(w.x));
+                v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + __uint_as_float(w.y));
+                v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + __uint_as_float(w.z));
+                v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + __uint_as_float(w.w));
+              }
+            }
+            emit_chunk(c, v);
+          }
+        }
       }
       // accumulator fully read: hand it back to the MMA warp
       tc_fence_before();
@@ -290,9 +375,48 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 namespace kb {
 namespace gemm {
 
+// k-blocks per slice at least: the workspace round trip of a slice costs about as much as 6-8
+// k-blocks of main loop, so a tail is only split when its slices stay long; a problem with no
+// full wave at all (decode) gains from any extra SMs
+constexpr int MIN_SLICE_KB = 24;
+constexpr int MIN_SLICE_KB_SKINNY = 8;
+constexpr int MAX_SPLIT = 16;
+
+// Per-device workspace of the tail slices (at most one slice per SM) and the tile counters.
+// Launches that split are expected on one stream per device at a time (they share it).
+struct SplitSpace {
+  float* ws = nullptr;
+  unsigned int* counters = nullptr;
+  bool failed = false;
+};
+static SplitSpace* split_space(int dev, int sms) {
+  static SplitSpace spaces[64];
+  SplitSpace& sp = spaces[dev];
+  if (sp.ws == nullptr && !sp.failed) {
+    static const bool enabled = []() {
+      const char* e = getenv("KHAOSZ_B200_GEMM_SPLIT");
+      return !(e && e[0] == '0');
+    }();
+    void* w = nullptr;
+    void* c = nullptr;
+    if (!enabled || cudaMalloc(&w, (size_t)sms * BM * 256 * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&c, (size_t)sms * sizeof(unsigned int)) != cudaSuccess ||
+        cudaMemset(c, 0, (size_t)sms * sizeof(unsigned int)) != cudaSuccess) {
+      cudaGetLastError();  // e.g. allocation refused during stream capture: run without splitting
+      if (w) cudaFree(w);
+      sp.failed = !enabled;
+      return nullptr;
+    }
+    sp.ws = static_cast<float*>(w);
+    sp.counters = static_cast<unsigned int*>(c);
+  }
+  return sp.ws ? &sp : nullptr;
+}
+
 template <int BN>
-static int launch(const void* A, const void* B, void* C, const Params& p, long lda, long ldb, long ldc, int grid_cap,
+static int launch(const void* A, const void* B, void* C, const Params& p_in, long lda, long ldb, long ldc, int grid_cap,
                   cudaStream_t stream) {
+  Params p = p_in;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -311,20 +435,57 @@ static int launch(const void* A, const void* B, void* C, const Params& p, long l
   rc = kb::make_tmap_2d(&tc, C, 2, p.M, p.N, ldc * 2, BM, EPI_COLS, true);
   if (rc) return KB_STATUS_TMAP_ERROR;
   const int total = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = total < grid_cap ? total : grid_cap;
+  const int num_k = (p.K + BK - 1) / BK;
+  // tail balancing: cut the tiles of the last partial wave into K slices (see the file header)
+  p.full_tiles = total;
+  p.split = 1;
+  p.ws = nullptr;
+  p.counters = nullptr;
+  const int rem = total % grid_cap;
+  if (rem > 0) {
+    int split = grid_cap / rem;
+    if (split > MAX_SPLIT) split = MAX_SPLIT;
+    const int min_kb = total < grid_cap ? MIN_SLICE_KB_SKINNY : MIN_SLICE_KB;
+    if (split > num_k / min_kb) split = num_k / min_kb;
+    while (split > 1 && (split - 1) * ((num_k + split - 1) / split) >= num_k) --split;  // no empty slice
+    if (split > 1) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (SplitSpace* sp = split_space(dev, grid_cap)) {
+        p.full_tiles = total - rem;
+        p.split = split;
+        p.ws = sp->ws;
+        p.counters = sp->counters;
+      }
+    }
+  }
+  const int units = p.full_tiles + (total - p.full_tiles) * p.split;
+  const int grid = units < grid_cap ? units : grid_cap;
   gemm_bf16_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, tc, p);
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 
 // Estimated relative cost of running the problem with tile width bn: SM-waves times the work of
 // one tile, with a small penalty for the lower operand reuse of narrower tiles.
-static double tile_cost(int M, int N, int bn, int sms) {
+static double tile_cost(int M, int N, int K, int bn, int sms) {
   const long tiles = (long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-  const long waves = (tiles + sms - 1) / sms;
+  const long full_waves = tiles / sms;
+  const int rem = (int)(tiles % sms);
+  double tail = 0.0;
+  if (rem > 0) {
+    const int num_k = (K + BK - 1) / BK;
+    int split = sms / rem;
+    if (split > MAX_SPLIT) split = MAX_SPLIT;
+    const int min_kb = tiles < sms ? MIN_SLICE_KB_SKINNY : MIN_SLICE_KB;
+    if (split > num_k / min_kb) split = num_k / min_kb;
+    // a split tail costs its share of the main loop plus the workspace round trip
+    tail = split > 1 ? 1.0 / split + 0.12 : 1.0;
+    if (tail > 1.0) tail = 1.0;
+  }
   // measured on B200: narrower tiles are shared-memory-bandwidth bound (A is re-read per tile),
   // a 192-wide tile runs at ~79 % and a 128-wide one at ~58 % of the 256-wide tile's rate
   const double per_tile = bn == 256 ? 1.0 : bn == 192 ? 0.95 : 0.88;
-  return waves * per_tile;
+  return (full_waves + tail) * per_tile;
 }
 
 }  // namespace gemm
@@ -346,9 +507,9 @@ extern "C" int kb_gemm_bf16_bn(const void* A, const void* B, void* C, const void
   const int sms = sm_count[dev];
   if (bn == 0) {
     bn = 256;
-    double best = tile_cost(M, N, 256, sms);
+    double best = tile_cost(M, N, K, 256, sms);
     for (int cand : {192, 128}) {
-      const double c = tile_cost(M, N, cand, sms);
+      const double c = tile_cost(M, N, K, cand, sms);
       if (c < best * 0.999) { best = c; bn = cand; }
     }
   }
