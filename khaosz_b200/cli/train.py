@@ -60,7 +60,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--nprocs", type=int, default=1)
     p.add_argument("--parallel_mode", choices=["none", "ddp", "fsdp", "fsdp_full", "tp"], default="none")
     p.add_argument("--tp_size", type=int, default=None)
-    p.add_argument("--fp8", action="store_true", default=False, help="block-scaled fp8 GEMMs (tp mode)")
+    p.add_argument("--fp8", action="store_true", default=False, help="forward GEMMs of the linear layers in block-scaled fp8 (bf16 master weights)")
     p.add_argument("--device_type", type=str, default="cuda")
     p.add_argument("--start_method", type=str, default="spawn")
     return p.parse_args(argv)
@@ -94,8 +94,10 @@ def train(args: argparse.Namespace) -> None:
     total = compute_total_steps(len(dataset), args.n_epoch, args.batch_per_device, args.nprocs, args.grad_accum_steps)
     warmup = min(int(args.warmup_ratio * total), total)
     executor_kwargs = {"gradient_as_bucket_view": True, "broadcast_buffers": False}
+    if args.fp8:
+        executor_kwargs["fp8"] = True
     if args.parallel_mode == "tp":
-        executor_kwargs.update(tp_size=args.tp_size or args.nprocs, fp8=args.fp8)
+        executor_kwargs["tp_size"] = args.tp_size or args.nprocs
     cfg = TrainConfig(
         model_fn=partial(create_model, config), strategy=args.train_type, dataset=dataset,
         optimizer_fn=partial(create_optimizer, kind=args.optimizer, lr=args.max_lr,

@@ -6,6 +6,7 @@ from .functional import (
     cross_entropy,
     cross_entropy_rows,
     embedding,
+    fp8_linear_enabled,
     gemm,
     linear,
     multi_linear,
@@ -13,6 +14,7 @@ from .functional import (
     rope,
     rope_table,
     sdpa_reference,
+    set_fp8_linear,
     swiglu,
     token_logprobs,
 )
@@ -20,5 +22,5 @@ from .functional import (
 __all__ = [
     "KernelError", "available", "launch_count", "raise_on_device_error", "add_rms_norm", "cross_entropy",
     "cross_entropy_rows", "embedding", "gemm", "linear", "multi_linear", "rms_norm", "rope", "rope_table",
-    "sdpa_reference", "swiglu", "token_logprobs",
+    "sdpa_reference", "swiglu", "token_logprobs", "set_fp8_linear", "fp8_linear_enabled",
 ]

@@ -66,6 +66,32 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+_FP8_FORWARD = False
+
+
+def set_fp8_linear(enabled: bool) -> None:
+    """Run the forward GEMM of every bf16 linear layer in block-scaled fp8 (e4m3; 1x128
+    activation scales, 128x128 weight scales, quantised on the fly from the bf16 master
+    weights).  Input and weight gradients stay bf16 GEMMs."""
+    global _FP8_FORWARD
+    _FP8_FORWARD = bool(enabled)
+
+
+def fp8_linear_enabled() -> bool:
+    return _FP8_FORWARD
+
+
+def _forward_gemm(x2: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if _FP8_FORWARD and x2.shape[1] % 128 == 0 and w.shape[0] % 8 == 0 and _lib.has("kb_gemm_fp8"):
+        from .quant import gemm_fp8, quantize_fp8_1x128, quantize_fp8_128x128
+
+        a8, sa = quantize_fp8_1x128(x2)
+        b8, sb = quantize_fp8_128x128(w)
+        y = gemm_fp8(a8, sa, b8, sb)
+        return y if residual is None else y.add_(residual)
+    return gemm(x2, w, residual=residual)
+
+
 class _LinearFn(torch.autograd.Function):
     """y = x W^T (+ residual); dgrad and wgrad run on the same kernel with MN-major operands."""
 
@@ -73,7 +99,7 @@ class _LinearFn(torch.autograd.Function):
     def forward(ctx, x, w, residual):
         x2 = _as2d(x)
         res2 = _as2d(residual) if residual is not None else None
-        y = gemm(x2, w, residual=res2)
+        y = _forward_gemm(x2, w, res2)
         ctx.save_for_backward(x2, w)
         ctx.w_ref = w
         ctx.x_shape = x.shape
@@ -130,7 +156,7 @@ class _MultiLinearFn(torch.autograd.Function):
         x2 = _as2d(x)
         wcat = _adjacent([w.detach() for w in ws])
         assert wcat is not None
-        y = gemm(x2, wcat)
+        y = _forward_gemm(x2, wcat)
         ctx.save_for_backward(x2, wcat)
         ctx.ws = ws
         ctx.x_shape = x.shape

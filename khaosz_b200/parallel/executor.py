@@ -118,9 +118,15 @@ def _wants_flat(model: nn.Module) -> bool:
 class BaseExecutor:
     flatten_on_cuda = True
 
-    def __init__(self, grad_accum_steps: int = 1):
+    def __init__(self, grad_accum_steps: int = 1, fp8: bool = False):
         self.gradient_state = GradientState(grad_accum_steps)
         self.flat: Optional[FlatParameters] = None
+        self.fp8 = bool(fp8)
+        if self.fp8:
+            # forward GEMMs of the local linear layers in block-scaled fp8 (bf16 master weights)
+            from ..ops.functional import set_fp8_linear
+
+            set_fp8_linear(True)
 
     # -- preparation ------------------------------------------------------------------------
     def prepare(self, model: nn.Module, optimizer=None, dataloader=None, scheduler=None) -> Tuple[Any, Any, Any, Any]:
@@ -211,8 +217,8 @@ class DDPExecutor(BaseExecutor):
 
     def __init__(self, grad_accum_steps: int = 1, find_unused_parameters: bool = False, bucket_cap_mb: int = 25,
                  gradient_as_bucket_view: bool = True, broadcast_buffers: bool = False, static_graph: bool = False,
-                 init_sync: bool = True, comm: str = "auto", **_ignored):
-        super().__init__(grad_accum_steps)
+                 init_sync: bool = True, comm: str = "auto", fp8: bool = False, **_ignored):
+        super().__init__(grad_accum_steps, fp8)
         self.bucket_cap_mb = bucket_cap_mb
         self.init_sync = init_sync
         self.comm = comm  # "auto" | "nccl" | "kernel"
@@ -277,8 +283,8 @@ class FSDPExecutor(BaseExecutor):
     rank, as the reference's ``FULL_STATE_DICT`` gather does (``astrai/parallel/executor.py:263-272``).
     """
 
-    def __init__(self, grad_accum_steps: int = 1, comm: str = "auto", **_ignored):
-        super().__init__(grad_accum_steps)
+    def __init__(self, grad_accum_steps: int = 1, comm: str = "auto", fp8: bool = False, **_ignored):
+        super().__init__(grad_accum_steps, fp8)
         self.comm = comm
         self.shard: Optional[Tuple[int, int]] = None
         self._reducer = None
@@ -379,8 +385,11 @@ class TPExecutor(BaseExecutor):
     choices are ``none/ddp/fsdp`` (``scripts/tools/train.py:171-176``).
     """
 
-    def __init__(self, grad_accum_steps: int = 1, tp_size: Optional[int] = None, init_sync: bool = True, **_ignored):
-        super().__init__(grad_accum_steps)
+    def __init__(self, grad_accum_steps: int = 1, tp_size: Optional[int] = None, init_sync: bool = True,
+                 fp8: bool = False, **_ignored):
+        # fp8 covers the GEMMs that run locally (embedding-side LM head); the fused
+        # collective GEMMs of the tensor-parallel layers are bf16
+        super().__init__(grad_accum_steps, fp8)
         self.tp_size = tp_size
         self.init_sync = init_sync
 

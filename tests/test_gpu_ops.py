@@ -124,3 +124,27 @@ def test_embedding_fwd_bwd():
     tf = table.detach().float().requires_grad_()
     F.embedding(ids, tf).backward(g.float())
     _close(table.grad, tf.grad)
+
+
+def test_fp8_forward_linear_matches_bf16_within_fp8_error():
+    """The fp8 switch changes only the forward GEMM: outputs agree with bf16 to e4m3 precision and
+    the gradients (bf16 GEMMs on the same saved operands) are identical in form."""
+    from khaosz_b200.ops import set_fp8_linear
+
+    torch.manual_seed(0)
+    x = (torch.randn(512, 1024, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(768, 1024, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    ref = ops.linear(x, w)
+    gref = torch.autograd.grad(ref.float().pow(2).sum(), (x, w))
+    set_fp8_linear(True)
+    try:
+        out = ops.linear(x, w)
+        g = torch.autograd.grad(out.float().pow(2).sum(), (x, w))
+    finally:
+        set_fp8_linear(False)
+    full = x.float() @ w.float().t()
+    rel = (out.float() - full).norm() / full.norm()
+    assert rel < 0.06, rel            # e4m3 has 3 mantissa bits
+    assert (ref.float() - full).norm() / full.norm() < 0.01
+    for a, b in zip(g, gref):
+        assert (a.float() - b.float()).norm() / b.float().norm() < 0.08
