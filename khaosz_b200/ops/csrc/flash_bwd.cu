@@ -13,7 +13,7 @@
 // A [128 x 64] 128B-swizzled TMA box is used both as a K-major operand (rows = M/N, columns =
 // reduction) and as an MN-major operand (rows = reduction, columns = N): the same shared
 // memory image of Q / dO / K serves both products it appears in.
-// TMEM: kernel 2 uses S^T | dP^T | dV | dK, kernel 3 uses S | dP | dQ (128 fp32 columns each).
+// TMEM: kernel 2 uses S^T | dP^T | dV | dK, kernel 3 uses S(even) | dP | S(odd) | dQ (128 fp32 columns each).
 #include "common.cuh"
 #include "kb_api.h"
 
@@ -352,6 +352,15 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 // ---------------------------------------------------------------------------------------
 // Kernel 3: dQ
 // ---------------------------------------------------------------------------------------
+// TMEM: SA | DP | SB | DQ (128 fp32 columns each).  S of key block j lands in SA (j even) or SB
+// (j odd) and dP always in DP, so that the tensor pipe never waits for the score-gradient warps:
+// while they turn (S_j, dP_j) into dS_j (bf16, written over S_j), S_{j+1} is already complete,
+// and as soon as dS_j is ready the pipe runs dP_{j+1}, dQ += dS_j K_j and S_{j+2} back to back.
+// K lives in a 3-stage ring (it is read by S_j early and by the dQ product late), V in 2 stages.
+constexpr int DQ_K_STAGES = 3;
+constexpr int DQ_V_STAGES = 2;
+constexpr int SMEM_BYTES_DQ = (2 + DQ_K_STAGES + DQ_V_STAGES) * TILE_BYTES + 256 + 1024;
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -361,17 +370,20 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + TILE_BYTES;
-  uint8_t* sK = sdO + TILE_BYTES;      // [2 stages]
-  uint8_t* sV = sK + 2 * TILE_BYTES;   // [2 stages]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * TILE_BYTES + 4 * 128 * 4);
-  uint64_t* q_full = bars;          // [1]
-  uint64_t* kv_full = bars + 1;     // [2]
-  uint64_t* kv_empty = bars + 3;    // [2]
-  uint64_t* sdp_full = bars + 5;    // [1]  S and dP both complete
-  uint64_t* ds_ready = bars + 6;    // [1]
-  uint64_t* acc_full = bars + 7;    // [1]
-  uint64_t* s_read = bars + 8;      // [4]  lower-half warp of a lane quarter has loaded its S / dP columns
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint8_t* sK = sdO + TILE_BYTES;                 // [DQ_K_STAGES]
+  uint8_t* sV = sK + DQ_K_STAGES * TILE_BYTES;    // [DQ_V_STAGES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + DQ_V_STAGES * TILE_BYTES);
+  uint64_t* q_full = bars;                    // [1]
+  uint64_t* k_full = bars + 1;                // [3]
+  uint64_t* k_empty = k_full + DQ_K_STAGES;   // [3]
+  uint64_t* v_full = k_empty + DQ_K_STAGES;   // [2]
+  uint64_t* v_empty = v_full + DQ_V_STAGES;   // [2]
+  uint64_t* s_full = v_empty + DQ_V_STAGES;   // [2]  SA / SB
+  uint64_t* dp_full = s_full + 2;             // [1]
+  uint64_t* ds_ready = dp_full + 1;           // [1]
+  uint64_t* acc_full = ds_ready + 1;          // [1]
+  uint64_t* s_read = acc_full + 1;            // [4]  lower-half warp of a lane quarter has loaded its S columns
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_read + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -384,8 +396,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    mbar_init(sdp_full, 1); mbar_init(ds_ready, 8); mbar_init(acc_full, 1);
+    for (int i = 0; i < DQ_K_STAGES; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
+    for (int i = 0; i < DQ_V_STAGES; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1);
+    mbar_init(dp_full, 1); mbar_init(ds_ready, 8); mbar_init(acc_full, 1);
     for (int i = 0; i < 4; ++i) mbar_init(&s_read[i], 1);
     mbar_fence_init();
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
@@ -396,7 +410,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t T_S = tmem_base, T_DP = tmem_base + 128, T_DQ = tmem_base + 256;
+  const uint32_t T_DP = tmem_base + 128, T_DQ = tmem_base + 384;
+  auto s_region = [&](int j) -> uint32_t { return tmem_base + ((j & 1) ? 256u : 0u); };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -407,14 +422,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       bool ok = true;
       for (int j = 0; j < n_it && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
-        mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
-        for (int c = 0; c < 2; ++c) {
-          tma_load_3d(sK + s * TILE_BYTES + c * CHUNK_BYTES, &tm_k, &kv_full[s], kvh * D + c * 64, j * BLK, b);
-          tma_load_3d(sV + s * TILE_BYTES + c * CHUNK_BYTES, &tm_v, &kv_full[s], kvh * D + c * 64, j * BLK, b);
-        }
+        const int ks = j % DQ_K_STAGES, vs = j % DQ_V_STAGES;
+        if (!mbar_wait(&k_empty[ks], ((j / DQ_K_STAGES) & 1) ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
+        mbar_expect_tx(&k_full[ks], TILE_BYTES);
+        for (int c = 0; c < 2; ++c)
+          tma_load_3d(sK + ks * TILE_BYTES + c * CHUNK_BYTES, &tm_k, &k_full[ks], kvh * D + c * 64, j * BLK, b);
+        if (!mbar_wait(&v_empty[vs], ((j / DQ_V_STAGES) & 1) ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
+        mbar_expect_tx(&v_full[vs], TILE_BYTES);
+        for (int c = 0; c < 2; ++c)
+          tma_load_3d(sV + vs * TILE_BYTES + c * CHUNK_BYTES, &tm_v, &v_full[vs], kvh * D + c * 64, j * BLK, b);
       }
     }
   } else if (warp == 1) {
@@ -422,31 +438,54 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const uint32_t idesc_kk = umma_idesc(128, 128, false, false);
       const uint32_t idesc_ts = umma_idesc(128, 128, false, true);
       const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
+      auto k_addr = [&](int j) { return smem_u32(sK + (j % DQ_K_STAGES) * TILE_BYTES); };
+      auto wait_k = [&](int j) {
+        return mbar_wait(&k_full[j % DQ_K_STAGES], (j / DQ_K_STAGES) & 1, abort_flag, p.err, KB_ERR_TIMEOUT_FULL);
+      };
+      auto wait_v = [&](int j) {
+        return mbar_wait(&v_full[j % DQ_V_STAGES], (j / DQ_V_STAGES) & 1, abort_flag, p.err, KB_ERR_TIMEOUT_FULL);
+      };
+      auto issue_dp = [&](int j) {
+        issue_ss(T_DP, do_addr, smem_u32(sV + (j % DQ_V_STAGES) * TILE_BYTES), idesc_kk);
+        umma_commit(dp_full);
+        umma_commit(&v_empty[j % DQ_V_STAGES]);
+      };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, KB_ERR_TIMEOUT_FULL);
-      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, p.err, KB_ERR_TIMEOUT_FULL);
+      if (ok) ok = wait_k(0);
       if (ok) {
         tc_fence_after();
-        issue_ss(T_S, q_addr, smem_u32(sK), idesc_kk);
-        issue_ss(T_DP, do_addr, smem_u32(sV), idesc_kk);
-        umma_commit(sdp_full);
+        issue_ss(s_region(0), q_addr, k_addr(0), idesc_kk);
+        umma_commit(&s_full[0]);
+        ok = wait_v(0);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_dp(0);
+        if (n_it > 1) {
+          ok = wait_k(1);
+          if (ok) {
+            tc_fence_after();
+            issue_ss(s_region(1), q_addr, k_addr(1), idesc_kk);
+            umma_commit(&s_full[1]);
+          }
+        }
       }
       for (int j = 0; j < n_it && ok; ++j) {
-        const int s = j & 1;
-        const bool has_next = j + 1 < n_it;
-        const int sn = (j + 1) & 1;
-        const uint32_t phn = ((j + 1) >> 1) & 1;
         if (!mbar_wait(ds_ready, j & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
-        issue_ts(T_DQ, T_S, smem_u32(sK + s * TILE_BYTES), idesc_ts, j > 0);  // dQ += dS K
-        umma_commit(&kv_empty[s]);
-        if (has_next) {
-          if (!mbar_wait(&kv_full[sn], phn, abort_flag, p.err, KB_ERR_TIMEOUT_FULL)) { ok = false; break; }
+        if (j + 1 < n_it) {           // dP of the next block: its region was released with dS_j
+          if (!wait_v(j + 1)) { ok = false; break; }
           tc_fence_after();
-          issue_ss(T_S, q_addr, smem_u32(sK + sn * TILE_BYTES), idesc_kk);
-          issue_ss(T_DP, do_addr, smem_u32(sV + sn * TILE_BYTES), idesc_kk);
-          umma_commit(sdp_full);
-        } else {
-          umma_commit(acc_full);
+          issue_dp(j + 1);
+        }
+        issue_ts(T_DQ, s_region(j), k_addr(j), idesc_ts, j > 0);   // dQ += dS_j K_j
+        umma_commit(&k_empty[j % DQ_K_STAGES]);
+        if (j + 1 == n_it) umma_commit(acc_full);
+        if (j + 2 < n_it) {           // S of block j+2 reuses the region dS_j is being read from (in order)
+          if (!wait_k(j + 2)) { ok = false; break; }
+          tc_fence_after();
+          issue_ss(s_region(j), q_addr, k_addr(j + 2), idesc_kk);
+          umma_commit(&s_full[j & 1]);
         }
       }
     }
@@ -463,42 +502,49 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const float dlt = q < p.S ? p.delta[row_base + q] : 0.f;
     bool ok = true;
     for (int j = 0; j < n_it && ok; ++j) {
-      if (!mbar_wait(sdp_full, j & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
+      const uint32_t t_s = s_region(j) + lane_off;
       const int kv0 = j * BLK + half * 64;
       const bool need_mask = (p.causal && (kv0 + 63 > q0)) || (kv0 + 64 > p.S);
       const int limit = p.causal ? min(q, p.S - 1) : (p.S - 1);
-      uint32_t ds[32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(T_S + lane_off + half * 64 + c * 32, sv);
-        tmem_ld_32x32b_x32(T_DP + lane_off + half * 64 + c * 32, dv);
+      float pr[64];
+      {
+        uint32_t sv[64];
+        tmem_ld_32x32b_x32(t_s + half * 64, sv);
+        tmem_ld_32x32b_x32(t_s + half * 64 + 32, sv + 32);
         tmem_ld_wait();
-        if (c == 1 && half == 0) {
+        if (half == 0) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&s_read[qtr]);
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int c0 = kv0 + c * 32 + 2 * i;
-          float p0 = exp2f(__uint_as_float(sv[2 * i]) * p.scale_log2 - lse2);
-          float p1 = exp2f(__uint_as_float(sv[2 * i + 1]) * p.scale_log2 - lse2);
-          if (need_mask) {
-            if (c0 > limit) p0 = 0.f;
-            if (c0 + 1 > limit) p1 = 0.f;
-          }
-          ds[c * 16 + i] =
-              pack_bf16x2(p0 * (__uint_as_float(dv[2 * i]) - dlt), p1 * (__uint_as_float(dv[2 * i + 1]) - dlt));
+        for (int i = 0; i < 64; ++i) {
+          float pv = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - lse2);
+          if (need_mask && kv0 + i > limit) pv = 0.f;
+          pr[i] = pv;
         }
+      }
+      if (!mbar_wait(dp_full, j & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t ds[32];
+      {
+        uint32_t dv[64];
+        tmem_ld_32x32b_x32(T_DP + lane_off + half * 64, dv);
+        tmem_ld_32x32b_x32(T_DP + lane_off + half * 64 + 32, dv + 32);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          ds[i] = pack_bf16x2(pr[2 * i] * (__uint_as_float(dv[2 * i]) - dlt),
+                              pr[2 * i + 1] * (__uint_as_float(dv[2 * i + 1]) - dlt));
       }
       // dS (bf16) overwrites S: packed columns [32 * half, +32)
       if (half == 1) {
         if (!mbar_wait(&s_read[qtr], j & 1, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
       }
-      tmem_st_32x32b_x32(T_S + lane_off + half * 32, ds);
+      tmem_st_32x32b_x32(t_s + half * 32, ds);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -546,7 +592,7 @@ extern "C" int kb_flash_bwd(const void* q, const void* k, const void* v, const v
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(flash_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+        cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_DQ) != cudaSuccess)
       return KB_STATUS_CUDA_ERROR;
     attr_set = true;
   }
@@ -571,6 +617,6 @@ extern "C" int kb_flash_bwd(const void* q, const void* k, const void* v, const v
   delta_kernel<<<(unsigned)((pairs * 16 + 255) / 256), 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, B, S, H, o_pitch, do_pitch);
   flash_bwd_dkdv_kernel<<<dim3(p.n_blocks, Hkv, B), NUM_THREADS, SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdk, tdv, p);
-  flash_bwd_dq_kernel<<<dim3(p.n_blocks, H, B), NUM_THREADS, SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, p);
+  flash_bwd_dq_kernel<<<dim3(p.n_blocks, H, B), NUM_THREADS, SMEM_BYTES_DQ, st>>>(tq, tk, tv, tdo, tdq, p);
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
