@@ -102,6 +102,52 @@ int kb_flash_bwd(const void* q, const void* k, const void* v, const void* o, con
                  long do_pitch, long dq_pitch, long dk_pitch, long dv_pitch, float scale,
                  int causal, void* stream);
 
+// ---- more GEMMs ---------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2, 256 x 256 output per pair of SMs); same contract as kb_gemm_bf16.
+int kb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                      long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn, int epi, void* stream);
+// int8 weight-only: C[M,N] = A[M,K] (bf16) * dequant(Wq[N,K] int8, scale[N] fp32)^T.
+int kb_gemm_w8(const void* A, const void* Wq, const float* scale, void* C, int M, int N, int K,
+               long lda, long ldw, long ldc, void* stream);
+int kb_quant_w8(const void* W, void* Wq, float* scale, int N, int K, void* stream);
+// Block-scaled fp8 (e4m3): activations with one fp32 scale per 1 x 128 block, weights per 128 x 128.
+int kb_quant_fp8_1x128(const void* x, void* q, void* scale, int M, int K, long ldx, void* stream);
+int kb_quant_fp8_128x128(const void* w, void* q, void* scale, int N, int K, long ldw, void* stream);
+int kb_gemm_fp8(const void* A8, const void* B8, const void* sa, const void* sb, void* C, int M, int N,
+                int K, long lda, long ldb, long ldc, void* stream);
+
+// ---- inference ----------------------------------------------------------------------------
+int kb_paged_kv_write(const void* k, const void* v, void* k_pool, void* v_pool, const void* slots,
+                      int tokens, int row_elems, long k_pitch, long v_pitch, void* stream);
+// CUDA-core split-KV decode attention (any page size, group size <= 8) and its tcgen05 counterpart
+// (page size 16/32/64/128, group size <= 32; needs the pool's page count for its tensor maps).
+int kb_paged_decode_attn(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
+                         const int* seq_lens, float* part_acc, float* part_ml, void* out, int B, int H,
+                         int Hkv, int D, int page_size, int max_pages, int n_splits, long q_pitch,
+                         long out_pitch, float scale, void* stream);
+int kb_paged_decode_tc(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
+                       const int* seq_lens, float* part_acc, float* part_ml, void* out, int B, int H,
+                       int Hkv, int D, int page_size, int max_pages, int n_pool_pages, int n_splits,
+                       long q_pitch, long out_pitch, float scale, void* stream);
+int kb_decode_merge(const float* part_acc, const float* part_ml, void* out, int B, int H, int n_splits,
+                    long out_pitch, void* stream);
+int kb_sample(const void* logits, const void* temperature, const void* top_k, const void* top_p,
+              const void* uniform, void* out, int rows, int V, long ld, long long reserved, void* stream);
+
+// ---- collectives over NVLink peer memory (pointer arrays hold one address per rank) ----------
+int kb_comm_slots(void);
+int kb_peer_barrier(const void* const* ctrl_ptrs, int rank, int ws, int slot, unsigned int epoch,
+                    int budget_ms, void* stream);
+int kb_allreduce_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, void* mc_ptr, int rank,
+                      int ws, long long n, float scale, unsigned int epoch, void* stream);
+// GEMM fused with all-gather of an operand and / or reduce-scatter / all-reduce of the result;
+// the argument list is documented at the definition in gemm_comm.cu.
+int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_local,
+                 const void* const* stage_ptrs, const void* const* ctrl_ptrs, void* out, int M, int N, int K,
+                 long lda, long ldb, long ldc, long ldo, int a_mn, int b_mn, int a_gather, int b_gather,
+                 int c_mode, int rank, int ws, unsigned int epoch, unsigned int* grid_sync, int gather_copy,
+                 unsigned int* ready, unsigned int ready_target, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

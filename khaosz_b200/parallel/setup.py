@@ -8,8 +8,10 @@ them fails.  ``setup_parallel`` exports ``MASTER_*``, ``LOCAL_RANK``, ``WORLD_SI
 ``LOCAL_DEVICE`` and owns ``init_process_group`` / ``destroy_process_group``.
 
 Unlike the reference a CUDA ``device_type`` degrades to CPU when no GPU is visible (so gloo
-ranks work on a CPU-only host) and NCCL groups get a CPU (gloo) companion group, used for
-object broadcasts and for the symmetric-memory rendezvous of the in-kernel collectives.
+ranks work on a CPU-only host), ``KHAOSZ_B200_PG_TIMEOUT_S`` shortens the process-group timeout,
+and a rank that unwinds an exception leaves without the collective tear-down so that the
+launcher can stop the others.  The symmetric-memory rendezvous of the in-kernel collectives
+runs over the same process group (``khaosz_b200.parallel.comm``).
 """
 
 from __future__ import annotations
