@@ -69,52 +69,62 @@ def main(argv=None) -> None:
         return (torch.randn(*shape, device=dev, generator=gen) * 0.05).to(torch.bfloat16)
 
     results = []
+    trace = torch.zeros(6, dtype=torch.int64, device=dev)
 
-    def report(name, fused_ms, base_ms, flops, link_bytes):
+    def phases(fn):
+        """One extra launch with CTA 0's phase timestamps (microseconds between the marks)."""
+        trace.zero_()
+        fn(trace)
+        torch.cuda.synchronize()
+        t = trace.tolist()
+        names = ["wait_all_ranks_entered", "own_tiles_and_copies", "wait_all_ctas", "wait_all_ranks_done", "reduce"]
+        return {n: round((t[i + 1] - t[i]) / 1e3, 1) for i, n in enumerate(names) if t[i + 1] and t[i]}
+
+    def report(name, fused_ms, base_ms, flops, link_bytes, phase=None):
         t_flop = flops / (args.gemm_peak_tflops * 1e12) * 1e3
         t_link = link_bytes / (args.link_gbs * 1e9) * 1e3
         roof = max(t_flop, t_link)
         results.append({"case": name, "fused_ms": round(fused_ms, 4), "library_ms": round(base_ms, 4),
                         "speedup": round(base_ms / fused_ms, 3), "roofline_ms": round(roof, 4),
                         "bound": "tensor" if t_flop >= t_link else "nvlink",
-                        "fraction_of_roofline": round(roof / fused_ms, 3)})
+                        "fraction_of_roofline": round(roof / fused_ms, 3), "phases_us": phase})
 
     # ---- all-gather -> GEMM (column parallel gate|up): [T/ws, d] shards x W[2f/ws, d]
     n_loc = (2 * f // ws) // 8 * 8
     x_shard, w_col = rnd(T // ws, d), rnd(n_loc, d)
     full = torch.empty(T, d, dtype=torch.bfloat16, device=dev)
 
-    def ag_fused():
-        return _comm_gemm(tp, x_shard, w_col, a_gather=True, tag="bench.col")
+    def ag_fused(tr=None):
+        return _comm_gemm(tp, x_shard, w_col, a_gather=True, tag="bench.col", trace=tr)
 
     def ag_lib():
         dist.all_gather_into_tensor(full, x_shard)
         return ops.gemm(full, w_col)
 
     report("all_gather->gemm (gate|up)", _timed(ag_fused, args.iters), _timed(ag_lib, args.iters),
-           2.0 * T * n_loc * d, (ws - 1) / ws * T * d * 2)
+           2.0 * T * n_loc * d, (ws - 1) / ws * T * d * 2, phases(ag_fused))
 
     # ---- GEMM -> reduce-scatter (row parallel down): x[T, f/ws] x W[d, f/ws] -> rows T/ws
     k_loc = (f // ws) // 8 * 8
     x_row, w_row = rnd(T, k_loc), rnd(d, k_loc)
     rs_out = torch.empty(T // ws, d, dtype=torch.bfloat16, device=dev)
 
-    def rs_fused():
-        return _comm_gemm(tp, x_row, w_row, c_mode=1, tag="bench.row")
+    def rs_fused(tr=None):
+        return _comm_gemm(tp, x_row, w_row, c_mode=1, tag="bench.row", trace=tr)
 
     def rs_lib():
         dist.reduce_scatter_tensor(rs_out, ops.gemm(x_row, w_row))
         return rs_out
 
     report("gemm->reduce_scatter (down)", _timed(rs_fused, args.iters), _timed(rs_lib, args.iters),
-           2.0 * T * d * k_loc, (ws - 1) / ws * T * d * 2)
+           2.0 * T * d * k_loc, (ws - 1) / ws * T * d * 2, phases(rs_fused))
 
     # ---- GEMM -> all-reduce (decode, 256 tokens)
     Td = 256
     xd = rnd(Td, k_loc)
 
-    def ar_fused():
-        return _comm_gemm(tp, xd, w_row, c_mode=2, tag="bench.dec")
+    def ar_fused(tr=None):
+        return _comm_gemm(tp, xd, w_row, c_mode=2, tag="bench.dec", trace=tr)
 
     def ar_lib():
         y = ops.gemm(xd, w_row)
@@ -122,7 +132,7 @@ def main(argv=None) -> None:
         return y
 
     report("gemm->all_reduce (decode, 256 tokens)", _timed(ar_fused, args.iters), _timed(ar_lib, args.iters),
-           2.0 * Td * d * k_loc, 2 * (ws - 1) / ws * Td * d * 2)
+           2.0 * Td * d * k_loc, 2 * (ws - 1) / ws * Td * d * 2, phases(ar_fused))
 
     # ---- stand-alone all-reduce of a 256 MiB gradient bucket
     n = 128 * 1024 * 1024
@@ -138,7 +148,7 @@ def main(argv=None) -> None:
     torch.cuda.synchronize()
     raise_on_device_error()
     if rank == 0:
-        print(json.dumps({"world_size": ws, "tokens": T, "nvls": bool(args.nvls), "results": results}, indent=1))
+        print(json.dumps({"world_size": ws, "tokens": T, "nvls": bool(args.nvls), "results": results}))
     dist.barrier()
     dist.destroy_process_group()
 

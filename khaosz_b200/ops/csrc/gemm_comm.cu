@@ -81,6 +81,8 @@ struct Params {
   long long shard_bytes;       // bytes per rank's shard (whole chunks)
   int chunk_bytes;             // 128 rows
   int gather_rows;             // stored rows per rank of the gathered operand
+  unsigned long long* trace;   // optional: 6 globaltimer stamps of CTA 0 (phase boundaries)
+  int exit_barrier;            // 0: (c_mode 0 only) peers' reads of this rank's operand are fenced by the caller's buffer rotation
 };
 
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -174,8 +176,11 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
 
   // Every rank's inputs are complete (and its staging buffer free) before anyone reads or writes
   // peer memory.
+  const bool tracer = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+  if (tracer) p.trace[0] = globaltimer_ns();   // kernel entered
   bool peers_ok = true;
   if (p.ws > 1) peers_ok = comm::cta_peer_barrier(p.ctrl, p.rank, p.ws, blockIdx.x, p.epoch, p.err, KB_WAIT_BUDGET_NS);
+  if (tracer) p.trace[1] = globaltimer_ns();   // every rank has entered
 
   // Tile order: rotate the m-tiles (K-major gathered A) so that this rank starts with its own
   // shard and the ranks walk the ring in step, spreading the load over the links.
@@ -374,8 +379,9 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 
+  if (tracer) p.trace[2] = globaltimer_ns();     // this CTA's tiles (and copies) done
   // ---------------- phase 2: cross-rank completion, then the reduction of the staged tiles ----------------
-  if (p.ws > 1) {
+  if (p.ws > 1 && (p.c_mode != 0 || p.exit_barrier)) {
     // grid-wide arrival on this rank (all CTAs are resident: grid <= SM count, one CTA per SM)
     __shared__ int s_go;
     if (threadIdx.x == 0) {
@@ -395,30 +401,58 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
       }
     }
     __syncthreads();
+    if (tracer) p.trace[3] = globaltimer_ns();   // all CTAs of this rank done
     const bool go = s_go != 0;
     // every CTA of every rank has issued (and completed) its stores
     const bool all_ok = go && comm::cta_peer_barrier(p.ctrl, p.rank, p.ws, blockIdx.x, p.epoch + 1, p.err, KB_WAIT_BUDGET_NS);
+    if (tracer) p.trace[4] = globaltimer_ns();   // all ranks done
     if (p.c_mode != 0 && all_ok && peers_ok) {
       const int rows = p.c_rows;
       const int cpr = p.N >> 3;
       const long total_chunks = (long)rows * cpr;
-      for (long i = blockIdx.x * (long)NUM_THREADS + threadIdx.x; i < total_chunks; i += (long)gridDim.x * NUM_THREADS) {
-        const long r = i / cpr;
-        const int c = (int)(i - r * cpr);
-        float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int s = 0; s < p.ws; ++s) {
-          const uint4 v = *reinterpret_cast<const uint4*>(p.stage + ((size_t)s * p.c_slot_rows + r) * p.N + c * 8);
-          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      const long stride = (long)gridDim.x * NUM_THREADS;
+      constexpr int UNROLL = 4;  // independent 16-byte loads in flight per thread and slot
+      for (long i0 = blockIdx.x * (long)NUM_THREADS + threadIdx.x; i0 < total_chunks; i0 += stride * UNROLL) {
+        float acc8[UNROLL][8];
 #pragma unroll
-          for (int k = 0; k < 4; ++k) { const float2 f = unpack_bf16x2(w[k]); acc8[2 * k] += f.x; acc8[2 * k + 1] += f.y; }
+        for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc8[u][k] = 0.f;
+        for (int s = 0; s < p.ws; ++s) {
+          uint4 v[UNROLL];
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const long i = i0 + u * stride;
+            v[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (i < total_chunks) {
+              const long r = i / cpr;
+              const int c = (int)(i - r * cpr);
+              v[u] = *reinterpret_cast<const uint4*>(p.stage + ((size_t)s * p.c_slot_rows + r) * p.N + c * 8);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const float2 f = unpack_bf16x2(w[k]); acc8[u][2 * k] += f.x; acc8[u][2 * k + 1] += f.y; }
+          }
         }
-        uint4 o;
-        o.x = pack_bf16x2(acc8[0], acc8[1]); o.y = pack_bf16x2(acc8[2], acc8[3]);
-        o.z = pack_bf16x2(acc8[4], acc8[5]); o.w = pack_bf16x2(acc8[6], acc8[7]);
-        *reinterpret_cast<uint4*>(p.out + r * p.ldo + c * 8) = o;
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const long i = i0 + u * stride;
+          if (i < total_chunks) {
+            const long r = i / cpr;
+            const int c = (int)(i - r * cpr);
+            uint4 o;
+            o.x = pack_bf16x2(acc8[u][0], acc8[u][1]); o.y = pack_bf16x2(acc8[u][2], acc8[u][3]);
+            o.z = pack_bf16x2(acc8[u][4], acc8[u][5]); o.w = pack_bf16x2(acc8[u][6], acc8[u][7]);
+            *reinterpret_cast<uint4*>(p.out + r * p.ldo + c * 8) = o;
+          }
+        }
       }
     }
   }
+  if (tracer) p.trace[5] = globaltimer_ns();     // reduction of the staged tiles done
 }
 
 }  // namespace gcomm
@@ -438,11 +472,14 @@ extern "C" {
 // image r), `ready` is one zero-initialised counter per 128-row chunk of this rank's image and
 // `ready_target` = (number of copy-mode calls on this image, this one included) x ceil(128 rows in
 // bytes / 16 KiB).  Shards must be whole 128-row chunks.
+// exit_barrier = 0 (allowed with c_mode 0): the kernel returns without waiting for the peers to
+// finish reading this rank's operand; the caller must then not overwrite that operand before the
+// NEXT fused kernel of the group has started on every rank (e.g. by alternating two buffers).
 int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_local, const void* const* stage_ptrs,
                  const void* const* ctrl_ptrs, void* out, int M, int N, int K, long lda, long ldb, long ldc, long ldo,
                  int a_mn, int b_mn, int a_gather, int b_gather, int c_mode, int rank, int ws, unsigned int epoch,
                  unsigned int* grid_sync, int gather_copy, unsigned int* ready, unsigned int ready_target,
-                 void* stream) {
+                 unsigned long long* trace, int exit_barrier, void* stream) {
   using namespace kb::gcomm;
   if (M <= 0 || N <= 0 || K <= 0 || ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws) return KB_STATUS_BAD_ARG;
   if ((lda & 7) || (ldb & 7) || (N & 7)) return KB_STATUS_BAD_ARG;
@@ -466,6 +503,8 @@ int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_l
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.a_gather = a_gather; p.b_gather = b_gather;
   p.c_mode = c_mode; p.rank = rank; p.ws = ws; p.epoch = epoch; p.err = kb::error_word(dev);
   p.grid_sync = grid_sync; p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo;
+  p.trace = trace;
+  p.exit_barrier = exit_barrier;
   for (int i = 0; i < MAX_RANKS; ++i) p.ctrl.p[i] = (ctrl_ptrs && i < ws) ? const_cast<void*>(ctrl_ptrs[i]) : nullptr;
 
   // stored-row extents of the operands

@@ -40,7 +40,8 @@ class TPContext:
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.use_kernels = self.device.type == "cuda" and self.ws > 1 and self.ws <= 8 and _lib.has("kb_gemm_comm")
         self._pool: Dict[Tuple[str, int], SymmetricBuffer] = {}
-        self._images: Dict[Tuple[str, int, int], list] = {}
+        self._images: Dict[Tuple[str, int, int, int], list] = {}
+        self._turns: Dict[Tuple[str, int, int], int] = {}
         if self.use_kernels:
             self.ctrl = PeerControl(self.device, self.group)
             self.grid_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
@@ -72,10 +73,14 @@ class TPContext:
         rows.  Returns ``(buffer, ready_counters, ready_target)`` for the copy-mode gather of the
         fused kernel (peers pull the other shards inside the kernel)."""
         rows, cols = shard.shape
-        key = (tag, rows, cols)
+        # two images per tag, used alternately: a peer may still be reading the image of the
+        # previous call when this rank prepares the next one (the kernel has no exit barrier)
+        turn = self._turns.get((tag, rows, cols), 0)
+        self._turns[(tag, rows, cols)] = turn ^ 1
+        key = (tag, rows, cols, turn)
         entry = self._images.get(key)
         if entry is None:
-            buf = self.buffer(tag + ".img", self.ws * rows * cols)
+            buf = self.buffer(f"{tag}.img{turn}", self.ws * rows * cols)
             ready = torch.zeros(self.ws * rows // 128, dtype=torch.int32, device=self.device)
             entry = self._images[key] = [buf, ready, 0]
         buf, ready, calls = entry
@@ -85,8 +90,11 @@ class TPContext:
         return buf, ready, entry[2] * pieces_per_chunk
 
     def stage_in(self, tag: str, t: torch.Tensor) -> SymmetricBuffer:
-        """Copy a local tensor into symmetric memory so that peers can read it."""
-        buf = self.buffer(tag, t.numel())
+        """Copy a local tensor into symmetric memory so that peers can read it (two buffers per
+        tag, used alternately, for the same reason as in ``gather_image``)."""
+        turn = self._turns.get((tag, t.numel(), -1), 0)
+        self._turns[(tag, t.numel(), -1)] = turn ^ 1
+        buf = self.buffer(f"{tag}.{turn}", t.numel())
         buf.tensor[: t.numel()].view(t.shape).copy_(t)
         return buf
 
@@ -96,10 +104,11 @@ def _ptr_list(values):
 
 
 def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, b_gather=False, c_mode=0,
-               tag="tp") -> torch.Tensor:
+               tag="tp", trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``op(A) op(B)^T`` with the fused collective.  ``a`` / ``b`` are local tensors (gathered
     operands are this rank's shard).  Returns the local result (c_mode 0), this rank's rows of the
-    sum (c_mode 1) or the full sum (c_mode 2)."""
+    sum (c_mode 1) or the full sum (c_mode 2).  ``trace`` (int64 [6], device) receives CTA 0's
+    timestamps: entered, all ranks entered, own tiles done, all CTAs done, all ranks done, reduced."""
     ws, rank = ctx.ws, ctx.rank
     a_rows, a_cols = a.shape
     b_rows, b_cols = b.shape
@@ -145,7 +154,7 @@ def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, 
         ldc, ldo = N, N
     check(lib().kb_gemm_comm(a_ptrs, b_ptrs, ptr(c_local), stage_ptrs, ctx.ctrl.flags.ptrs, ptr(out), M, N, K, lda, ldb,
                              ldc, ldo, int(a_mn), int(b_mn), int(a_gather), int(b_gather), c_mode, rank, ws,
-                             ctx.ctrl.next_epoch(), ptr(ctx.grid_sync), copy, ptr(ready), ready_target, stream()),
+                             ctx.ctrl.next_epoch(), ptr(ctx.grid_sync), copy, ptr(ready), ready_target, ptr(trace), 0, stream()),
           "gemm_comm")
     return c_local if c_mode == 0 else out
 
