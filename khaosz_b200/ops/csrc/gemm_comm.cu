@@ -411,30 +411,43 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
       const int cpr = p.N >> 3;
       const long total_chunks = (long)rows * cpr;
       const long stride = (long)gridDim.x * NUM_THREADS;
-      constexpr int UNROLL = 4;  // independent 16-byte loads in flight per thread and slot
+      // The CTA has few threads for a streaming pass, so each thread keeps 16 independent 16-byte
+      // loads in flight (8 chunks x 2 slots) to cover the memory latency.
+      constexpr int UNROLL = 8;
       for (long i0 = blockIdx.x * (long)NUM_THREADS + threadIdx.x; i0 < total_chunks; i0 += stride * UNROLL) {
         float acc8[UNROLL][8];
+        size_t off[UNROLL];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
+        for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) acc8[u][k] = 0.f;
-        for (int s = 0; s < p.ws; ++s) {
-          uint4 v[UNROLL];
+          const long i = min(i0 + u * stride, total_chunks - 1);  // clamped: the tail re-reads a valid chunk
+          const long r = i / cpr;
+          off[u] = (size_t)r * p.N + (size_t)(i - r * cpr) * 8;
+        }
+        for (int s = 0; s < p.ws; s += 2) {
+          const bool two = s + 1 < p.ws;
+          const __nv_bfloat16* b0 = p.stage + (size_t)s * p.c_slot_rows * p.N;
+          const __nv_bfloat16* b1 = p.stage + (size_t)(two ? s + 1 : s) * p.c_slot_rows * p.N;
+          uint4 v0[UNROLL], v1[UNROLL];
 #pragma unroll
           for (int u = 0; u < UNROLL; ++u) {
-            const long i = i0 + u * stride;
-            v[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (i < total_chunks) {
-              const long r = i / cpr;
-              const int c = (int)(i - r * cpr);
-              v[u] = *reinterpret_cast<const uint4*>(p.stage + ((size_t)s * p.c_slot_rows + r) * p.N + c * 8);
-            }
+            v0[u] = *reinterpret_cast<const uint4*>(b0 + off[u]);
+            v1[u] = *reinterpret_cast<const uint4*>(b1 + off[u]);
           }
 #pragma unroll
           for (int u = 0; u < UNROLL; ++u) {
-            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+            const uint32_t w0[4] = {v0[u].x, v0[u].y, v0[u].z, v0[u].w};
+            const uint32_t w1[4] = {v1[u].x, v1[u].y, v1[u].z, v1[u].w};
 #pragma unroll
-            for (int k = 0; k < 4; ++k) { const float2 f = unpack_bf16x2(w[k]); acc8[u][2 * k] += f.x; acc8[u][2 * k + 1] += f.y; }
+            for (int k = 0; k < 4; ++k) {
+              const float2 f = unpack_bf16x2(w0[k]);
+              acc8[u][2 * k] += f.x; acc8[u][2 * k + 1] += f.y;
+              if (two) {
+                const float2 g = unpack_bf16x2(w1[k]);
+                acc8[u][2 * k] += g.x; acc8[u][2 * k + 1] += g.y;
+              }
+            }
           }
         }
 #pragma unroll
