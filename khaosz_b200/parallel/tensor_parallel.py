@@ -104,11 +104,14 @@ def _ptr_list(values):
 
 
 def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, b_gather=False, c_mode=0,
-               tag="tp", trace: Optional[torch.Tensor] = None) -> torch.Tensor:
+               tag="tp", trace: Optional[torch.Tensor] = None, want_image: bool = False):
     """``op(A) op(B)^T`` with the fused collective.  ``a`` / ``b`` are local tensors (gathered
     operands are this rank's shard).  Returns the local result (c_mode 0), this rank's rows of the
     sum (c_mode 1) or the full sum (c_mode 2).  ``trace`` (int64 [6], device) receives CTA 0's
-    timestamps: entered, all ranks entered, own tiles done, all CTAs done, all ranks done, reduced."""
+    timestamps: entered, all ranks entered, own tiles done, all CTAs done, all ranks done, reduced.
+    ``want_image=True`` returns ``(result, image)`` where ``image`` is the local copy of the whole
+    gathered operand that the kernel assembled (``None`` when the direct mode ran); it stays valid
+    until the second-next call with the same tag and shape."""
     ws, rank = ctx.ws, ctx.rank
     a_rows, a_cols = a.shape
     b_rows, b_cols = b.shape
@@ -122,9 +125,11 @@ def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, 
     copy, ready, ready_target = 0, None, 0
     if (a_gather and a_rows % 128 == 0) or (b_gather and b_rows % 128 == 0):
         copy = 1  # whole 128-row chunks: peers' shards are pulled once into a local image
+    image = None
     if a_gather and copy:
         sa, ready, ready_target = ctx.gather_image(tag + ".a", a)
         a_ptrs, lda = sa.ptrs, a_cols
+        image = sa.tensor[: ws * a_rows * a_cols].view(ws * a_rows, a_cols)
     elif a_gather:
         sa = ctx.stage_in(tag + ".a", a)
         a_ptrs, lda = sa.ptrs, a_cols
@@ -134,6 +139,7 @@ def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, 
     if b_gather and copy:
         sb, ready, ready_target = ctx.gather_image(tag + ".b", b)
         b_ptrs, ldb = sb.ptrs, b_cols
+        image = sb.tensor[: ws * b_rows * b_cols].view(ws * b_rows, b_cols)
     elif b_gather:
         sb = ctx.stage_in(tag + ".b", b)
         b_ptrs, ldb = sb.ptrs, b_cols
@@ -156,7 +162,8 @@ def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, 
                              ldc, ldo, int(a_mn), int(b_mn), int(a_gather), int(b_gather), c_mode, rank, ws,
                              ctx.ctrl.next_epoch(), ptr(ctx.grid_sync), copy, ptr(ready), ready_target, ptr(trace), 0, stream()),
           "gemm_comm")
-    return c_local if c_mode == 0 else out
+    result = c_local if c_mode == 0 else out
+    return (result, image) if want_image else result
 
 
 # ---- reference collectives (CPU/gloo and the oracle of the GPU tests) -----------------------
@@ -184,9 +191,16 @@ class _ColumnParallelFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, w, tp):
         ctx.tp = tp
-        ctx.save_for_backward(x_shard, w)
+        ctx.full_x = None
         if _kernel_ok(tp, x_shard, w) and x_shard.shape[0] % 128 == 0:
-            return _comm_gemm(tp, x_shard, w, a_gather=True, tag="col.fwd")
+            # the image of the gathered input assembled by the kernel is kept for the weight
+            # gradient (one image pair per layer: the tag carries the weight's identity), so the
+            # backward pass needs no second gather
+            y, full_x = _comm_gemm(tp, x_shard, w, a_gather=True, tag=f"col.fwd.{id(w)}", want_image=True)
+            ctx.full_x = full_x
+            ctx.save_for_backward(x_shard if full_x is None else x_shard.new_empty(0), w)
+            return y
+        ctx.save_for_backward(x_shard, w)
         return _all_gather_rows(x_shard, tp.group) @ w.t()
 
     @staticmethod
@@ -194,7 +208,12 @@ class _ColumnParallelFn(torch.autograd.Function):
         x_shard, w = ctx.saved_tensors
         tp = ctx.tp
         dy = dy.contiguous()
-        if _kernel_ok(tp, dy, w) and x_shard.shape[0] % 128 == 0:
+        if ctx.full_x is not None:
+            from ..ops.functional import gemm
+
+            dx = _comm_gemm(tp, dy, w, b_mn=True, c_mode=1, tag="col.dx")                   # RS(dy W)
+            dw = gemm(dy, ctx.full_x, a_mn=True, b_mn=True)                                  # dy^T AG(x), local
+        elif _kernel_ok(tp, dy, w) and x_shard.shape[0] % 128 == 0:
             dx = _comm_gemm(tp, dy, w, b_mn=True, c_mode=1, tag="col.dx")                   # RS(dy W)
             dw = _comm_gemm(tp, dy, x_shard, a_mn=True, b_mn=True, b_gather=True, tag="col.dw")  # dy^T AG(x)
         else:
@@ -227,8 +246,13 @@ class _RowParallelFn(torch.autograd.Function):
         if ctx.all_reduce:  # dy is already complete on every rank
             return dy @ w, dy.t() @ x, None, None
         if _kernel_ok(tp, dy, w) and dy.shape[0] % 128 == 0:
-            dx = _comm_gemm(tp, dy, w, a_gather=True, b_mn=True, tag="row.dx")                  # AG(dy) W
-            dw = _comm_gemm(tp, dy, x, a_mn=True, b_mn=True, a_gather=True, tag="row.dw")       # AG(dy)^T x
+            from ..ops.functional import gemm
+
+            dx, full_dy = _comm_gemm(tp, dy, w, a_gather=True, b_mn=True, tag="row.dx", want_image=True)  # AG(dy) W
+            if full_dy is not None:   # the gathered dy is already in local memory
+                dw = gemm(full_dy, x, a_mn=True, b_mn=True)                                          # AG(dy)^T x
+            else:
+                dw = _comm_gemm(tp, dy, x, a_mn=True, b_mn=True, a_gather=True, tag="row.dw")
         else:
             full = _all_gather_rows(dy, tp.group)
             dx, dw = full @ w, full.t() @ x
