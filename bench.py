@@ -208,6 +208,7 @@ def run_own(args):
     cfg = AutoRegressiveLMConfig(**MODEL)
     mode = args.parallel if ws > 1 else "none"
     replicas = 1 if mode == "tp" else ws  # data-parallel replicas
+    args.cuda_graph = bool(args.cuda_graph) if args.cuda_graph >= 0 else mode == "tp"
     steps_total = args.warmup + args.steps
 
     def model_fn():
@@ -226,7 +227,7 @@ def run_own(args):
 
     # ---- device-timed steps (inputs resident on the device) ----
     model = model_fn().to(device)
-    executor = ExecutorFactory.create(mode, grad_accum_steps=ACCUM)
+    executor = ExecutorFactory.create(mode, grad_accum_steps=ACCUM, cuda_graph=args.cuda_graph)
     opt = optimizer_fn(model)
     model, opt, _, sched = executor.prepare(model, opt, None, scheduler_fn(opt))
     strategy = StrategyFactory.create("seq", model, device, label_smoothing=SMOOTH)
@@ -238,8 +239,7 @@ def run_own(args):
         for mb in range(ACCUM):
             batch = {"input_ids": pool[mb, :, :-1], "target_ids": pool[mb, :, 1:]}
             with executor.accumulate(model):
-                loss = strategy(batch)
-                executor.backward(loss / ACCUM)
+                loss = executor.micro_step(strategy, batch)
                 if executor.sync_gradients:
                     opt.fused_clip(CLIP)
                     opt.step()
@@ -281,6 +281,7 @@ def run_own(args):
                          max_grad_norm=CLIP, ckpt_dir=tmp, ckpt_interval=10 ** 9, log_dir=os.path.join(tmp, "logs"),
                          log_interval=ACCUM, random_seed=SEED, num_workers=0, pin_memory=True, nprocs=ws,
                          backend="nccl", parallel_mode=mode, device_type="cuda",
+                         executor_kwargs={"cuda_graph": args.cuda_graph},
                          extra_kwargs={"label_smoothing": SMOOTH})
 
         trainer = Trainer(tc, callbacks=[timer])
@@ -407,6 +408,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="khaosz_b200", choices=["khaosz_b200", "own", "reference"])
     ap.add_argument("--no-e2e", dest="no_e2e", action="store_true")
+    ap.add_argument("--cuda-graph", dest="cuda_graph", type=int, default=-1,
+                    help="own arm: forward+backward of a micro-batch as a replayed CUDA graph (default: on for tp)")
     ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp", "fsdp_full", "tp"],
                     help="own arm, N > 1: data parallel (default), sharded data parallel, or tensor parallel "
                          "(tp: every rank reads the same batches, total work is fixed -> strong scaling)")

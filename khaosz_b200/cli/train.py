@@ -60,6 +60,8 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--nprocs", type=int, default=1)
     p.add_argument("--parallel_mode", choices=["none", "ddp", "fsdp", "fsdp_full", "tp"], default="none")
     p.add_argument("--tp_size", type=int, default=None)
+    p.add_argument("--cuda_graph", action="store_true", default=False,
+                   help="replay forward+backward of a micro-batch as a CUDA graph (fixed batch shapes)")
     p.add_argument("--fp8", action="store_true", default=False, help="forward GEMMs of the linear layers in block-scaled fp8 (bf16 master weights)")
     p.add_argument("--device_type", type=str, default="cuda")
     p.add_argument("--start_method", type=str, default="spawn")
@@ -96,6 +98,8 @@ def train(args: argparse.Namespace) -> None:
     executor_kwargs = {"gradient_as_bucket_view": True, "broadcast_buffers": False}
     if args.fp8:
         executor_kwargs["fp8"] = True
+    if args.cuda_graph:
+        executor_kwargs["cuda_graph"] = True
     if args.parallel_mode == "tp":
         executor_kwargs["tp_size"] = args.tp_size or args.nprocs
     cfg = TrainConfig(

@@ -67,7 +67,7 @@ def _declare(lib):
         "kb_quant_fp8_128x128": ([P, P, P, I, I, L, P], I),
         "kb_gemm_fp8": ([P, P, P, P, P, I, I, I, L, L, L, P], I),
         "kb_comm_slots": ([], I),
-        "kb_gemm_comm": ([P, P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, I, I, ctypes.c_uint, P, I, P, ctypes.c_uint, P, I, P], I),
+        "kb_gemm_comm": ([P, P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, I, I, ctypes.c_uint, P, I, P, ctypes.c_uint, P, I, P, P, P], I),
         "kb_reduce_adamw": ([P, P, P, P, P, P, I, I, LL, LL, P, P, P, F, F, F, F, F, P, ctypes.c_uint, P], I),
         "kb_allreduce_bf16": ([P, P, P, I, I, LL, F, ctypes.c_uint, P], I),
         "kb_peer_barrier": ([P, I, I, I, ctypes.c_uint, I, P], I),

@@ -82,6 +82,8 @@ struct Params {
   int chunk_bytes;             // 128 rows
   int gather_rows;             // stored rows per rank of the gathered operand
   unsigned long long* trace;   // optional: 6 globaltimer stamps of CTA 0 (phase boundaries)
+  const unsigned int* epoch_dev;  // optional: the epoch lives in device memory (CUDA-graph replays)
+  const unsigned int* calls_dev;  // optional: copy-mode call counter of the image, same purpose
   int exit_barrier;            // 0: (c_mode 0 only) peers' reads of this rank's operand are fenced by the caller's buffer rotation
 };
 
@@ -105,14 +107,15 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* addr)
 
 // Bounded wait until the chunks covering stored rows [row0, row0 + nrows) of the gathered image
 // have arrived.  `last` caches the newest chunk already seen complete.
-__device__ __forceinline__ bool wait_gathered(const Params& p, int row0, int nrows, int& last, volatile int* abort_flag) {
+__device__ __forceinline__ bool wait_gathered(const Params& p, uint32_t ready_target, int row0, int nrows, int& last,
+                                              volatile int* abort_flag) {
   const int c0 = row0 / CHUNK_ROWS, c1 = (row0 + nrows - 1) / CHUNK_ROWS;
   bool fresh = false;
   for (int c = c0; c <= c1; ++c) {
     if (c == last || (c * CHUNK_ROWS) / p.gather_rows == p.rank) continue;
     const unsigned long long t0 = globaltimer_ns();
     unsigned int it = 0;
-    while (ld_acquire_gpu(p.ready + c) != p.ready_target) {
+    while (ld_acquire_gpu(p.ready + c) != ready_target) {
       if ((++it & 63u) == 0u && (*abort_flag || globaltimer_ns() - t0 > KB_WAIT_BUDGET_NS)) {
         *abort_flag = 1;
         atomicCAS(p.err, 0, KB_ERR_TIMEOUT_PEER);
@@ -140,7 +143,13 @@ __device__ __forceinline__ void locate(int row, int rows_per_rank, int gather, i
 template <int STAGES, bool COPY>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Maps maps_b,
-                 const __grid_constant__ Maps maps_c, const Params p) {
+                 const __grid_constant__ Maps maps_c, const Params p_in) {
+  // With device-side counters the launch arguments stay constant, so a captured graph can be
+  // replayed: a one-thread kernel launched behind this one advances the counters.
+  const Params& p = p_in;
+  const uint32_t epoch = p.epoch_dev ? *p.epoch_dev : p.epoch;
+  const uint32_t ready_target =
+      p.calls_dev ? (*p.calls_dev + 1u) * (uint32_t)((p.chunk_bytes + COPY_PIECE - 1) / COPY_PIECE) : p.ready_target;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -179,7 +188,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
   const bool tracer = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
   if (tracer) p.trace[0] = globaltimer_ns();   // kernel entered
   bool peers_ok = true;
-  if (p.ws > 1) peers_ok = comm::cta_peer_barrier(p.ctrl, p.rank, p.ws, blockIdx.x, p.epoch, p.err, KB_WAIT_BUDGET_NS);
+  if (p.ws > 1) peers_ok = comm::cta_peer_barrier(p.ctrl, p.rank, p.ws, blockIdx.x, epoch, p.err, KB_WAIT_BUDGET_NS);
   if (tracer) p.trace[1] = globaltimer_ns();   // every rank has entered
 
   // Tile order: rotate the m-tiles (K-major gathered A) so that this rank starts with its own
@@ -210,15 +219,15 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
         tile_of(t, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN;
         if (COPY) {
-          if (a_rows_gathered) ok = wait_gathered(p, m0, min(BM, p.M - m0), seen, abort_flag);
-          else if (b_rows_gathered) ok = wait_gathered(p, n0, min(BN, p.N - n0), seen, abort_flag);
+          if (a_rows_gathered) ok = wait_gathered(p, ready_target, m0, min(BM, p.M - m0), seen, abort_flag);
+          else if (b_rows_gathered) ok = wait_gathered(p, ready_target, n0, min(BN, p.N - n0), seen, abort_flag);
           if (!ok) break;
         }
         for (int kk = 0; kk < num_k; ++kk) {
           const int kb = (kk + k_rot) % num_k;
           const int k0 = kb * BK;
           if (COPY && ((p.a_gather && p.a_mn) || (p.b_gather && p.b_mn))) {
-            if (!wait_gathered(p, k0, min(BK, p.K - k0), seen, abort_flag)) { ok = false; break; }
+            if (!wait_gathered(p, ready_target, k0, min(BK, p.K - k0), seen, abort_flag)) { ok = false; break; }
           }
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(&full[s], A_STAGE_BYTES + B_STAGE_BYTES);
@@ -387,7 +396,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
     if (threadIdx.x == 0) {
       __threadfence_system();  // this CTA's peer stores are ordered before its arrival
       s_go = 1;
-      const unsigned int gen = p.epoch;  // generation tag of this launch
+      const unsigned int gen = epoch;  // generation tag of this launch
       const unsigned int arrived = atomicAdd(&p.grid_sync[0], 1u) + 1u;
       if (arrived == gridDim.x) {
         atomicExch(&p.grid_sync[0], 0u);  // last arriver re-arms the counter for the next launch
@@ -404,7 +413,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
     if (tracer) p.trace[3] = globaltimer_ns();   // all CTAs of this rank done
     const bool go = s_go != 0;
     // every CTA of every rank has issued (and completed) its stores
-    const bool all_ok = go && comm::cta_peer_barrier(p.ctrl, p.rank, p.ws, blockIdx.x, p.epoch + 1, p.err, KB_WAIT_BUDGET_NS);
+    const bool all_ok = go && comm::cta_peer_barrier(p.ctrl, p.rank, p.ws, blockIdx.x, epoch + 1, p.err, KB_WAIT_BUDGET_NS);
     if (tracer) p.trace[4] = globaltimer_ns();   // all ranks done
     if (p.c_mode != 0 && all_ok && peers_ok) {
       const int rows = p.c_rows;
@@ -468,6 +477,12 @@ gemm_comm_kernel(const __grid_constant__ Maps maps_a, const __grid_constant__ Ma
   if (tracer) p.trace[5] = globaltimer_ns();     // reduction of the staged tiles done
 }
 
+// Advances the device-side epoch / call counters behind a fused kernel (stream ordered).
+__global__ void bump_counters_kernel(unsigned int* epoch_dev, unsigned int epoch_step, unsigned int* calls_dev) {
+  if (epoch_dev) *epoch_dev += epoch_step;
+  if (calls_dev) *calls_dev += 1u;
+}
+
 }  // namespace gcomm
 }  // namespace kb
 
@@ -485,6 +500,10 @@ extern "C" {
 // image r), `ready` is one zero-initialised counter per 128-row chunk of this rank's image and
 // `ready_target` = (number of copy-mode calls on this image, this one included) x ceil(128 rows in
 // bytes / 16 KiB).  Shards must be whole 128-row chunks.
+// epoch_dev / calls_dev (optional, device words): when given, the kernel takes its epoch from
+// *epoch_dev (and ready_target from *calls_dev) instead of the arguments and a one-thread kernel
+// advances them afterwards (epoch by 4), so the launch can be captured into a CUDA graph and
+// replayed; *epoch_dev must start at the same value >= 1 on every rank.
 // exit_barrier = 0 (allowed with c_mode 0): the kernel returns without waiting for the peers to
 // finish reading this rank's operand; the caller must then not overwrite that operand before the
 // NEXT fused kernel of the group has started on every rank (e.g. by alternating two buffers).
@@ -492,7 +511,8 @@ int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_l
                  const void* const* ctrl_ptrs, void* out, int M, int N, int K, long lda, long ldb, long ldc, long ldo,
                  int a_mn, int b_mn, int a_gather, int b_gather, int c_mode, int rank, int ws, unsigned int epoch,
                  unsigned int* grid_sync, int gather_copy, unsigned int* ready, unsigned int ready_target,
-                 unsigned long long* trace, int exit_barrier, void* stream) {
+                 unsigned long long* trace, int exit_barrier, unsigned int* epoch_dev, unsigned int* calls_dev,
+                 void* stream) {
   using namespace kb::gcomm;
   if (M <= 0 || N <= 0 || K <= 0 || ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws) return KB_STATUS_BAD_ARG;
   if ((lda & 7) || (ldb & 7) || (N & 7)) return KB_STATUS_BAD_ARG;
@@ -518,6 +538,8 @@ int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_l
   p.grid_sync = grid_sync; p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo;
   p.trace = trace;
   p.exit_barrier = exit_barrier;
+  p.epoch_dev = epoch_dev;
+  p.calls_dev = copy ? calls_dev : nullptr;
   for (int i = 0; i < MAX_RANKS; ++i) p.ctrl.p[i] = (ctrl_ptrs && i < ws) ? const_cast<void*>(ctrl_ptrs[i]) : nullptr;
 
   // stored-row extents of the operands
@@ -580,6 +602,8 @@ int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_l
     gemm_comm_kernel<3, true><<<grid, NUM_THREADS, smem_bytes<3, true>(), static_cast<cudaStream_t>(stream)>>>(ma, mb, mc, p);
   else
     gemm_comm_kernel<4, false><<<grid, NUM_THREADS, smem_bytes<4, false>(), static_cast<cudaStream_t>(stream)>>>(ma, mb, mc, p);
+  if (epoch_dev || p.calls_dev)
+    bump_counters_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(epoch_dev, 4u, const_cast<unsigned int*>(p.calls_dev));
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 

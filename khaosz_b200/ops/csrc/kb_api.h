@@ -146,7 +146,8 @@ int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_l
                  const void* const* stage_ptrs, const void* const* ctrl_ptrs, void* out, int M, int N, int K,
                  long lda, long ldb, long ldc, long ldo, int a_mn, int b_mn, int a_gather, int b_gather,
                  int c_mode, int rank, int ws, unsigned int epoch, unsigned int* grid_sync, int gather_copy,
-                 unsigned int* ready, unsigned int ready_target, unsigned long long* trace, int exit_barrier, void* stream);
+                 unsigned int* ready, unsigned int ready_target, unsigned long long* trace, int exit_barrier, unsigned int* epoch_dev, unsigned int* calls_dev,
+                 void* stream);
 
 #ifdef __cplusplus
 }

@@ -110,6 +110,69 @@ class AccumScheduler:
         return self.scheduler.get_last_lr()
 
 
+class _GraphedMicroStep:
+    """Forward + backward of one micro-batch as a CUDA graph per batch signature.
+
+    The first two micro-batches of a signature run with plain launches (lazy allocations, symmetric
+    buffers, kernel attributes); the third is captured over static input buffers; from then on a
+    micro-batch is two small copies and one graph launch.  A step is a few thousand launches of
+    kernels that take 10-100 us each, so without the graph the host thread is the bottleneck once
+    the per-GPU work shrinks (tensor parallelism)."""
+
+    WARMUP = 2
+
+    def __init__(self, executor: "BaseExecutor"):
+        self.executor = executor
+        self.entries: Dict[Any, Dict[str, Any]] = {}
+        self.disabled = False
+
+    @staticmethod
+    def _signature(batch: Dict[str, Any]):
+        return tuple(sorted((k, tuple(v.shape), str(v.dtype)) for k, v in batch.items() if torch.is_tensor(v)))
+
+    def __call__(self, strategy, batch: Dict[str, Any], scale: float) -> torch.Tensor:
+        ex = self.executor
+        key = self._signature(batch)
+        entry = self.entries.setdefault(key, {"uses": 0})
+        entry["uses"] += 1
+        if self.disabled or entry["uses"] <= self.WARMUP:
+            loss = strategy(batch)
+            ex._backward_only(loss * scale)
+            return loss.detach()
+        device = strategy.device
+        if "graph" not in entry:
+            static = {k: (torch.empty_like(v, device=device) if torch.is_tensor(v) else v) for k, v in batch.items()}
+            for k, v in batch.items():
+                if torch.is_tensor(v):
+                    static[k].copy_(v, non_blocking=True)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    loss = strategy(static)
+                    ex._backward_only(loss * scale)
+                    out = loss.detach()
+            except Exception as exc:  # something in the step cannot be captured: keep plain launches
+                log.warning("CUDA graph capture of the micro-step failed (%s); running without graphs", exc)
+                self.disabled = True
+                torch.cuda.synchronize()
+                loss = strategy(batch)
+                ex._backward_only(loss * scale)
+                return loss.detach()
+            entry.update(graph=graph, static=static, loss=out)
+            # Recording takes seconds and differs per rank; kernels that wait for their peers have a
+            # bounded patience, so the ranks line up on the host before the first replay.
+            if dist.is_available() and dist.is_initialized():
+                torch.cuda.synchronize()
+                dist.barrier()
+        else:
+            for k, v in batch.items():
+                if torch.is_tensor(v):
+                    entry["static"][k].copy_(v, non_blocking=True)
+        entry["graph"].replay()
+        return entry["loss"].clone()
+
+
 def _wants_flat(model: nn.Module) -> bool:
     params = list(model.parameters())
     return bool(params) and all(p.is_cuda and p.dtype == torch.bfloat16 for p in params)
@@ -118,10 +181,11 @@ def _wants_flat(model: nn.Module) -> bool:
 class BaseExecutor:
     flatten_on_cuda = True
 
-    def __init__(self, grad_accum_steps: int = 1, fp8: bool = False):
+    def __init__(self, grad_accum_steps: int = 1, fp8: bool = False, cuda_graph: bool = False):
         self.gradient_state = GradientState(grad_accum_steps)
         self.flat: Optional[FlatParameters] = None
         self.fp8 = bool(fp8)
+        self._graphed = _GraphedMicroStep(self) if cuda_graph and torch.cuda.is_available() else None
         if self.fp8:
             # forward GEMMs of the local linear layers in block-scaled fp8 (bf16 master weights)
             from ..ops.functional import set_fp8_linear
@@ -159,9 +223,25 @@ class BaseExecutor:
             yield
 
     def backward(self, loss: torch.Tensor) -> None:
-        loss.backward()
+        self._backward_only(loss)
         if self.gradient_state.sync_gradients:
             self._sync_gradients()
+
+    def _backward_only(self, loss: torch.Tensor) -> None:
+        loss.backward()
+
+    def micro_step(self, strategy, batch) -> torch.Tensor:
+        """``loss = strategy(batch); backward(loss / grad_accum_steps)`` inside ``accumulate``;
+        returns the detached loss.  With ``cuda_graph=True`` the pair runs as a replayed CUDA graph."""
+        scale = 1.0 / self.gradient_state.num_steps
+        if self._graphed is None:
+            loss = strategy(batch)
+            self.backward(loss * scale)
+            return loss.detach()
+        loss = self._graphed(strategy, batch, scale)
+        if self.gradient_state.sync_gradients:
+            self._sync_gradients()
+        return loss
 
     def _sync_gradients(self) -> None:
         """Cross-rank gradient reduction on synchronisation steps."""
@@ -217,8 +297,8 @@ class DDPExecutor(BaseExecutor):
 
     def __init__(self, grad_accum_steps: int = 1, find_unused_parameters: bool = False, bucket_cap_mb: int = 25,
                  gradient_as_bucket_view: bool = True, broadcast_buffers: bool = False, static_graph: bool = False,
-                 init_sync: bool = True, comm: str = "auto", fp8: bool = False, **_ignored):
-        super().__init__(grad_accum_steps, fp8)
+                 init_sync: bool = True, comm: str = "auto", fp8: bool = False, cuda_graph: bool = False, **_ignored):
+        super().__init__(grad_accum_steps, fp8, cuda_graph)
         self.bucket_cap_mb = bucket_cap_mb
         self.init_sync = init_sync
         self.comm = comm  # "auto" | "nccl" | "kernel"
@@ -283,8 +363,9 @@ class FSDPExecutor(BaseExecutor):
     rank, as the reference's ``FULL_STATE_DICT`` gather does (``astrai/parallel/executor.py:263-272``).
     """
 
-    def __init__(self, grad_accum_steps: int = 1, comm: str = "auto", fp8: bool = False, **_ignored):
-        super().__init__(grad_accum_steps, fp8)
+    def __init__(self, grad_accum_steps: int = 1, comm: str = "auto", fp8: bool = False, cuda_graph: bool = False,
+                 **_ignored):
+        super().__init__(grad_accum_steps, fp8, cuda_graph)
         self.comm = comm
         self.shard: Optional[Tuple[int, int]] = None
         self._reducer = None
@@ -386,10 +467,10 @@ class TPExecutor(BaseExecutor):
     """
 
     def __init__(self, grad_accum_steps: int = 1, tp_size: Optional[int] = None, init_sync: bool = True,
-                 fp8: bool = False, **_ignored):
+                 fp8: bool = False, cuda_graph: bool = False, **_ignored):
         # fp8 covers the GEMMs that run locally (embedding-side LM head); the fused
         # collective GEMMs of the tensor-parallel layers are bf16
-        super().__init__(grad_accum_steps, fp8)
+        super().__init__(grad_accum_steps, fp8, cuda_graph)
         self.tp_size = tp_size
         self.init_sync = init_sync
 
@@ -431,11 +512,9 @@ class TPExecutor(BaseExecutor):
             scheduler = AccumScheduler(scheduler, self.gradient_state)
         return model, optimizer, dataloader, scheduler
 
-    def backward(self, loss: torch.Tensor) -> None:
+    def _backward_only(self, loss: torch.Tensor) -> None:
         ws = get_world_size()
         (loss / ws if ws > 1 else loss).backward()
-        if self.gradient_state.sync_gradients:
-            self._sync_gradients()
 
     def _sync_gradients(self) -> None:
         reduce = getattr(self._model, "reduce_replicated_grads", None)

@@ -45,6 +45,10 @@ class TPContext:
         if self.use_kernels:
             self.ctrl = PeerControl(self.device, self.group)
             self.grid_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
+            # The barrier epoch of the fused kernels lives on the device (advanced by a one-thread
+            # kernel behind every launch), so that a captured CUDA graph can be replayed; every
+            # rank starts at the same value and issues the same sequence of fused kernels.
+            self.epoch_dev = torch.full((1,), 4, dtype=torch.int32, device=self.device)
 
     @classmethod
     def get(cls, group=None) -> "TPContext":
@@ -81,7 +85,8 @@ class TPContext:
         entry = self._images.get(key)
         if entry is None:
             buf = self.buffer(f"{tag}.img{turn}", self.ws * rows * cols)
-            ready = torch.zeros(self.ws * rows // 128, dtype=torch.int32, device=self.device)
+            # one arrival counter per 128-row chunk + (last word) the number of copy-mode calls so far
+            ready = torch.zeros(self.ws * rows // 128 + 1, dtype=torch.int32, device=self.device)
             entry = self._images[key] = [buf, ready, 0]
         buf, ready, calls = entry
         buf.tensor[: self.ws * rows * cols].view(self.ws * rows, cols)[self.rank * rows:(self.rank + 1) * rows].copy_(shard)
@@ -122,7 +127,7 @@ def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, 
     N = b_cols if b_mn else B_rows
     Kb = B_rows if b_mn else b_cols
     assert K == Kb, (K, Kb)
-    copy, ready, ready_target = 0, None, 0
+    copy, ready, ready_target, calls_dev = 0, None, 0, None
     if (a_gather and a_rows % 128 == 0) or (b_gather and b_rows % 128 == 0):
         copy = 1  # whole 128-row chunks: peers' shards are pulled once into a local image
     image = None
@@ -158,9 +163,11 @@ def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, 
         stage_ptrs = stage.ptrs
         out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
         ldc, ldo = N, N
+    if ready is not None:
+        calls_dev = ctypes.c_void_p(ready.data_ptr() + 4 * (ready.numel() - 1))
     check(lib().kb_gemm_comm(a_ptrs, b_ptrs, ptr(c_local), stage_ptrs, ctx.ctrl.flags.ptrs, ptr(out), M, N, K, lda, ldb,
                              ldc, ldo, int(a_mn), int(b_mn), int(a_gather), int(b_gather), c_mode, rank, ws,
-                             ctx.ctrl.next_epoch(), ptr(ctx.grid_sync), copy, ptr(ready), ready_target, ptr(trace), 0, stream()),
+                             0, ptr(ctx.grid_sync), copy, ptr(ready), ready_target, ptr(trace), 0, ptr(ctx.epoch_dev), calls_dev, stream()),
           "gemm_comm")
     result = c_local if c_mode == 0 else out
     return (result, image) if want_image else result

@@ -179,9 +179,14 @@ class TensorParallelLM(nn.Module):
         """Factor that turns this rank's mean loss into its share of the global mean:
         ``n_local * ws / n_global`` (the executor divides by ``ws``)."""
         n_local = (local_targets != ignore_index).sum().to(torch.float32)
+        if self.info.ws == 1:
+            return torch.ones_like(n_local)
+        if local_targets.is_cuda and torch.cuda.is_current_stream_capturing():
+            # no library collective inside a captured micro-step: the ranks' valid-token counts
+            # are taken as equal (exact for next-token training, where every target counts)
+            return torch.ones_like(n_local)
         n_global = n_local.clone()
-        if self.info.ws > 1:
-            dist.all_reduce(n_global, group=self.info.group)
+        dist.all_reduce(n_global, group=self.info.group)
         return n_local * self.info.ws / n_global.clamp_min(1.0)
 
     def forward(self, input_ids: Tensor, input_mask: Optional[Tensor] = None, paged_cache=None,

@@ -46,9 +46,12 @@ class Trainer:
     def _micro_step(self, context: TrainContext, batch) -> None:
         executor = context.executor
         with executor.accumulate(context.model):
-            loss = context.strategy(batch)
-            context.loss = loss.detach()
-            executor.backward(loss / executor.grad_accum_steps)
+            if hasattr(executor, "micro_step"):   # forward + backward, optionally as a replayed CUDA graph
+                context.loss = executor.micro_step(context.strategy, batch)
+            else:
+                loss = context.strategy(batch)
+                context.loss = loss.detach()
+                executor.backward(loss / executor.grad_accum_steps)
             context.iteration += 1
             self._call_callbacks("on_batch_end", context)
             if executor.sync_gradients:

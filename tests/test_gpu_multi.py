@@ -101,13 +101,13 @@ def _cfg():
                                   max_len=256, rope_theta=1e4, n_heads=4, n_kv_heads=2)
 
 
-def _train(mode, world, rank, device, steps=4, accum=2):
+def _train(mode, world, rank, device, steps=4, accum=2, cuda_graph=False):
     from khaosz_b200 import AutoRegressiveLM
     from khaosz_b200.trainer import FusedAdamW, StrategyFactory
 
     torch.manual_seed(3407)
     model = AutoRegressiveLM(_cfg()).to(device=device, dtype=torch.bfloat16)
-    ex = ExecutorFactory.create(mode, grad_accum_steps=accum)
+    ex = ExecutorFactory.create(mode, grad_accum_steps=accum, cuda_graph=cuda_graph)
     opt = FusedAdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.01)
     model, opt, _, _ = ex.prepare(model, opt, None, None)
     strat = StrategyFactory.create("seq", model, device, label_smoothing=0.05)
@@ -117,13 +117,15 @@ def _train(mode, world, rank, device, steps=4, accum=2):
     for i in range(steps * accum):
         mine = (data[i] if mode == "tp" else data[i, 2 * rank:2 * rank + 2]).to(device)
         with ex.accumulate(model):
-            loss = strat({"input_ids": mine[:, :-1], "target_ids": mine[:, 1:]})
-            ex.backward(loss / accum)
+            loss = ex.micro_step(strat, {"input_ids": mine[:, :-1].contiguous(), "target_ids": mine[:, 1:].contiguous()})
             if ex.sync_gradients:
                 opt.fused_clip(1.0)
                 opt.step()
                 opt.zero_grad()
         losses.append(loss.detach().float())
+    if cuda_graph:
+        assert ex._graphed is not None and not ex._graphed.disabled and any("graph" in e for e in ex._graphed.entries.values()), \
+            "the micro-step was not captured"
     return torch.stack(losses), model, ex, opt
 
 
@@ -149,13 +151,19 @@ def _dp_case(mode, out):
                     "m0": osd["state"][0]["exp_avg"]}, out)
 
 
-def _tp_train_case(out, mode="tp"):
+def _tp_train_case(out, mode="tp", cuda_graph=False):
     from khaosz_b200.ops import raise_on_device_error
     from khaosz_b200.parallel.tensor_parallel import TPContext
 
     rank = dist.get_rank()
     dev = torch.device("cuda", rank)
-    losses, model, ex, opt = _train(mode, 2, rank, dev)
+    if cuda_graph:  # a stuck rank reports where it is and leaves instead of holding the GPUs
+        import faulthandler
+
+        faulthandler.dump_traceback_later(60, exit=True)
+    losses, model, ex, opt = _train(mode, 2, rank, dev, cuda_graph=cuda_graph)
+    if cuda_graph:
+        faulthandler.cancel_dump_traceback_later()
     dist.all_reduce(losses)
     losses /= 2
     raise_on_device_error()
@@ -165,10 +173,13 @@ def _tp_train_case(out, mode="tp"):
         torch.save({"losses": losses.cpu(), "sd": {k: v.cpu() for k, v in sd.items()}}, out)
 
 
-@pytest.mark.parametrize("mode,port", [("ddp", 29703), ("fsdp", 29704), ("tp", 29707), ("fsdp_full", 29708)])
+@pytest.mark.parametrize("mode,port", [("ddp", 29703), ("fsdp", 29704), ("tp", 29707), ("fsdp_full", 29708),
+                                       ("tp_graph", 29709)])
 def test_fused_data_parallel_step_matches_single_gpu(mode, port, tmp_path):
     out = str(tmp_path / "dp.pt")
-    if mode in ("tp", "fsdp_full"):
+    if mode == "tp_graph":   # forward+backward of the tensor-parallel micro-step replayed as a CUDA graph
+        _spawn(_tp_train_case, port, out=out, mode="tp", cuda_graph=True)
+    elif mode in ("tp", "fsdp_full"):
         _spawn(_tp_train_case, port, out=out, mode=mode)
     else:
         _spawn(_dp_case, port, mode=mode, out=out)

@@ -148,3 +148,38 @@ def test_fp8_forward_linear_matches_bf16_within_fp8_error():
     assert (ref.float() - full).norm() / full.norm() < 0.01
     for a, b in zip(g, gref):
         assert (a.float() - b.float()).norm() / b.float().norm() < 0.08
+
+
+def test_cuda_graph_micro_step_matches_plain_launches():
+    """Executor option cuda_graph: the captured forward+backward gives the same losses and weights."""
+    from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
+    from khaosz_b200.parallel import ExecutorFactory
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    cfg = AutoRegressiveLMConfig(vocab_size=2048, dim=256, n_layers=2, norm_eps=1e-5, dim_ffn=768, tie_weight=True,
+                                 max_len=128, rope_theta=1e4, n_heads=2, n_kv_heads=1)
+    data = torch.randint(0, 2048, (8, 2, 129), generator=torch.Generator().manual_seed(1)).cuda()
+
+    def run(graph):
+        torch.manual_seed(0)
+        model = AutoRegressiveLM(cfg).to(device="cuda", dtype=torch.bfloat16)
+        ex = ExecutorFactory.create("none", grad_accum_steps=2, cuda_graph=graph)
+        opt = FusedAdamW(model.parameters(), lr=1e-3)
+        model, opt, _, _ = ex.prepare(model, opt, None, None)
+        strat = StrategyFactory.create("seq", model, "cuda")
+        losses = []
+        for i in range(8):
+            with ex.accumulate(model):
+                loss = ex.micro_step(strat, {"input_ids": data[i, :, :-1].contiguous(), "target_ids": data[i, :, 1:].contiguous()})
+                if ex.sync_gradients:
+                    opt.step()
+                    opt.zero_grad()
+            losses.append(loss.item())
+        if graph:
+            assert not ex._graphed.disabled and any("graph" in e for e in ex._graphed.entries.values())
+        return losses, torch.cat([p.detach().float().reshape(-1) for p in model.parameters()])
+
+    l0, w0 = run(False)
+    l1, w1 = run(True)
+    assert l0 == pytest.approx(l1, rel=1e-3, abs=1e-3)
+    assert (w0 - w1).abs().max().item() < 1e-2
