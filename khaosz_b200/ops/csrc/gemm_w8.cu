@@ -38,7 +38,18 @@ struct Params {
   int* err;
 };
 
-__device__ __forceinline__ uint32_t cvt2(int lo, int hi) { return pack_bf16x2((float)lo, (float)hi); }
+// Four int8 -> four bf16 without integer-to-float conversions: each byte, biased by 128, becomes the
+// low mantissa byte of 2^23 (bit pattern 0x4B0000uu = 8388608 + u), and subtracting 8388736 leaves
+// the signed value exactly; bf16 holds every integer of that range exactly.
+__device__ __forceinline__ void cvt4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t u = w ^ 0x80808080u;
+  const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.f;
+  const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.f;
+  const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.f;
+  const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.f;
+  lo = pack_bf16x2(f0, f1);
+  hi = pack_bf16x2(f2, f3);
+}
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_w8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -138,12 +149,7 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
             uint32_t o[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int b0 = (int)(signed char)(w[i] & 0xff), b1 = (int)(signed char)((w[i] >> 8) & 0xff);
-              const int b2 = (int)(signed char)((w[i] >> 16) & 0xff), b3 = (int)(signed char)(w[i] >> 24);
-              o[2 * i] = cvt2(b0, b1);
-              o[2 * i + 1] = cvt2(b2, b3);
-            }
+            for (int i = 0; i < 4; ++i) cvt4(w[i], o[2 * i], o[2 * i + 1]);
             *reinterpret_cast<uint4*>(dst + sw128_offset(row, q16 * 2)) = make_uint4(o[0], o[1], o[2], o[3]);
             *reinterpret_cast<uint4*>(dst + sw128_offset(row, q16 * 2 + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
           }
