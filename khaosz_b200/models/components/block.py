@@ -30,5 +30,7 @@ class DecoderBlock(nn.Module):
 
     def forward(self, x: Tensor, rotary_emb, attention_mask: Optional[Tensor] = None, paged_cache=None,
                 causal: bool = True) -> Tensor:
-        h = self.attention(self.input_norm(x), rotary_emb, attention_mask, paged_cache, residual=x, causal=causal)
-        return self.mlp(self.post_attention_norm(h), residual=h)
+        y, x = self.input_norm.fork(x)
+        h = self.attention(y, rotary_emb, attention_mask, paged_cache, residual=x, causal=causal)
+        y, h = self.post_attention_norm.fork(h)
+        return self.mlp(y, residual=h)

@@ -67,6 +67,11 @@ class RMSNorm(nn.Module):
     def forward(self, x: Tensor) -> Tensor:
         return ops.rms_norm(x, self.weight, self.eps)
 
+    def fork(self, x: Tensor) -> Tuple[Tensor, Tensor]:
+        """``(norm(x), x)`` for a pre-norm residual block: pass the second value on as the residual
+        so that both gradient paths meet inside the norm's backward kernel."""
+        return ops.rms_norm_fork(x, self.weight, self.eps)
+
 
 def ntk_scaled_base(base: float, factor: float, dim: int) -> float:
     """NTK-aware base: ``base * factor^(dim / (dim - 2))``."""

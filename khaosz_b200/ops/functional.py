@@ -200,8 +200,12 @@ def multi_linear(x: torch.Tensor, ws) -> torch.Tensor:
 
 
 class _RMSNormFn(torch.autograd.Function):
+    """``fork=True`` (no ``res``) also returns ``x`` itself as a second output: the caller feeds that
+    alias to the residual connection, so the gradient of the residual path arrives here and is
+    added inside the backward kernel instead of by a separate accumulation pass."""
+
     @staticmethod
-    def forward(ctx, x, res, w, eps):
+    def forward(ctx, x, res, w, eps, fork=False):
         shape = x.shape
         dim = shape[-1]
         x2 = x.reshape(-1, dim).contiguous()
@@ -222,6 +226,8 @@ class _RMSNormFn(torch.autograd.Function):
         ctx.shape = shape
         if res is not None:
             return y.view(shape), s.view(shape)
+        if fork:
+            return y.view(shape), x.view_as(x)
         return y.view(shape), None
 
     @staticmethod
@@ -238,13 +244,21 @@ class _RMSNormFn(torch.autograd.Function):
                                    ptr(partial), rows, dim, stream()), "rmsnorm_bwd")
         _lib.add_launches(1)
         dxv = dx.view(ctx.shape)
-        return dxv, (dxv if ctx.has_res else None), dw.to(w.dtype), None
+        return dxv, (dxv if ctx.has_res else None), dw.to(w.dtype), None, None
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     if not use_kernels(x) or x.shape[-1] % 8 or x.shape[-1] > 8192:
         return F.rms_norm(x, (x.shape[-1],), w, eps)
     return _RMSNormFn.apply(x, None, w, eps)[0]
+
+
+def rms_norm_fork(x: torch.Tensor, w: torch.Tensor, eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns ``(rmsnorm(x) * w, x)``; use the second value for the residual connection (see
+    ``_RMSNormFn``)."""
+    if not use_kernels(x) or x.shape[-1] % 8 or x.shape[-1] > 8192 or not torch.is_grad_enabled():
+        return rms_norm(x, w, eps), x
+    return _RMSNormFn.apply(x, None, w, eps, True)
 
 
 def add_rms_norm(x: torch.Tensor, res: torch.Tensor, w: torch.Tensor, eps: float) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -94,8 +94,10 @@ class ShardedBlock(nn.Module):
         self.mlp = ShardedMLP(block.mlp, info)
 
     def forward(self, x: Tensor, rotary) -> Tensor:
-        h = x + self.attention(self.input_norm(x), rotary)
-        return h + self.mlp(self.post_attention_norm(h))
+        y, x = self.input_norm.fork(x)
+        h = x + self.attention(y, rotary)
+        y, h = self.post_attention_norm.fork(h)
+        return h + self.mlp(y)
 
 
 class FullShardLM(nn.Module):

@@ -143,8 +143,10 @@ class TPBlock(nn.Module):
         self.mlp = TPMLP(block.mlp, info)
 
     def forward(self, x: Tensor, rotary, batch: int, seq: int) -> Tensor:
-        h = x + self.attention(self.input_norm(x), rotary, batch, seq)
-        return h + self.mlp(self.post_attention_norm(h))
+        y, x = self.input_norm.fork(x)
+        h = x + self.attention(y, rotary, batch, seq)
+        y, h = self.post_attention_norm.fork(h)
+        return h + self.mlp(y)
 
 
 class TensorParallelLM(nn.Module):
