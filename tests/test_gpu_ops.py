@@ -183,3 +183,19 @@ def test_cuda_graph_micro_step_matches_plain_launches():
     l1, w1 = run(True)
     assert l0 == pytest.approx(l1, rel=1e-3, abs=1e-3)
     assert (w0 - w1).abs().max().item() < 1e-2
+
+
+def test_rms_norm_fork_fuses_the_residual_gradient():
+    torch.manual_seed(3)
+    x = torch.randn(300, 512, device="cuda").to(torch.bfloat16).requires_grad_()
+    w = (1 + 0.1 * torch.randn(512, device="cuda")).to(torch.bfloat16).requires_grad_()
+    a = torch.randn(300, 512, device="cuda").to(torch.bfloat16)
+    b = torch.randn(300, 512, device="cuda").to(torch.bfloat16)
+    y, xr = ops.rms_norm_fork(x, w, 1e-5)
+    gx, gw = torch.autograd.grad((y.float() * a.float()).sum() + (xr.float() * b.float()).sum(), (x, w))
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    ref = F.rms_norm(xf, (512,), wf, 1e-5)
+    rx, rw = torch.autograd.grad((ref * a.float()).sum() + (xf * b.float()).sum(), (xf, wf))
+    assert torch.equal(xr, x)
+    assert (gx.float() - rx).abs().max().item() < 3e-2 * rx.abs().max().item() + 2e-2
+    assert (gw.float() - rw).abs().max().item() < 3e-2 * rw.abs().max().item() + 0.5

@@ -270,3 +270,13 @@ def test_kv_exhaustion_aborts_instead_of_hanging(tokenizer):
     out = eng.generate("hello world this is a test", max_tokens=12, top_k=1)
     assert time.time() - t0 < 20 and isinstance(out, str)
     eng.shutdown()
+
+
+def test_split_kv_factor_fills_whole_waves():
+    from khaosz_b200.inference.core.cache import _pick_splits
+
+    assert _pick_splits(1024, 2048) == 1            # already many CTAs per SM
+    n = _pick_splits(256, 2048)                     # 256 CTAs on 148 SMs: 1.7 waves -> split
+    assert n > 1 and (256 * n) % 148 <= 148 and -(-256 * n // 148) * 148 / (256 * n) < 1.1
+    assert _pick_splits(4, 128) == 1                # a single 128-key tile cannot be split
+    assert 1 <= _pick_splits(4, 4096) <= 16
