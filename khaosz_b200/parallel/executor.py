@@ -147,6 +147,9 @@ class _GraphedMicroStep:
                     static[k].copy_(v, non_blocking=True)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
+            from ..ops import _lib
+
+            before = _lib.launch_count()
             try:
                 with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                     loss = strategy(static)
@@ -159,7 +162,9 @@ class _GraphedMicroStep:
                 loss = strategy(batch)
                 ex._backward_only(loss * scale)
                 return loss.detach()
-            entry.update(graph=graph, static=static, loss=out)
+            # kernel-library launches recorded in the graph: every replay issues them again
+            entry.update(graph=graph, static=static, loss=out, launches=_lib.launch_count() - before)
+            _lib.add_launches(-entry["launches"])  # the recording itself launched nothing
             # Recording takes seconds and differs per rank; kernels that wait for their peers have a
             # bounded patience, so the ranks line up on the host before the first replay.
             if dist.is_available() and dist.is_initialized():
@@ -170,6 +175,10 @@ class _GraphedMicroStep:
                 if torch.is_tensor(v):
                     entry["static"][k].copy_(v, non_blocking=True)
         entry["graph"].replay()
+        if entry.get("launches"):
+            from ..ops import _lib
+
+            _lib.add_launches(entry["launches"])
         return entry["loss"].clone()
 
 
