@@ -149,9 +149,44 @@ def parse_args(argv=None):
     return p.parse_args(argv)
 
 
+def _tensor_parallel(a, dtype):
+    """Under a multi-rank launcher (``torchrun``): rank 0 benchmarks, the others serve their slice."""
+    import os
+
+    import torch.distributed as dist
+
+    from ..inference.tp import TPInferenceLM, serve_worker
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    device = f"cuda:{local}"
+    dist.init_process_group("nccl", device_id=torch.device(device))
+    torch.manual_seed(a.seed)  # identical random weights on every rank
+    cfg = AutoRegressiveLMConfig(**PRESETS[a.preset])
+    model = AutoRegressiveLM(cfg).to(device=device, dtype=dtype).eval()
+    model = TPInferenceLM(model, int8=a.int8).eval()
+    page = a.page_size if a.page_size != 128 else 16
+    if dist.get_rank() != 0:
+        serve_worker(model, _IdTokenizer(), max_batch_size=a.max_batch_size, max_seq_len=a.max_prompt + a.gen_length + 1,
+                     page_size=page)
+    else:
+        row = bench_serve(model, cfg, a.requests, a.rate, a.min_prompt, a.max_prompt, a.gen_length, a.max_batch_size,
+                          page, a.seed)
+        row.update(weights="int8" if a.int8 else "bf16", tensor_parallel=dist.get_world_size())
+        print(json.dumps(row))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main(argv=None):
+    import os
+
     a = parse_args(argv)
     dtype = torch.bfloat16
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        if a.mode != "serve":
+            raise SystemExit("tensor-parallel benchmarking covers the serve mode")
+        return _tensor_parallel(a, dtype)
     cfg, model = build_model(a.preset, a.device, dtype)
     if a.int8:
         from ..ops.quant import quantize_model_int8

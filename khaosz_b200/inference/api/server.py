@@ -64,18 +64,48 @@ class MessagesRequest(BaseModel):
     stop_sequences: Optional[List[str]] = None
 
 
-def _create_engine(param_path: Optional[Path] = None, device: str = "cuda", dtype: torch.dtype = torch.bfloat16,
-                   max_batch_size: int = 16, page_size: int = 16, max_seq_len: Optional[int] = None) -> InferenceEngine:
+def _load(param_path: Optional[Path], device: str, dtype: torch.dtype, int8: bool = False, tp: bool = False):
     root = Path(param_path) if param_path is not None else DEFAULT_PARAM_DIR
     if not root.exists():
         raise FileNotFoundError(f"Parameter directory not found: {root}")
     tokenizer = AutoTokenizer.from_pretrained(root)
     model = AutoModel.from_pretrained(root).to(device=device, dtype=dtype).eval()
-    if next(model.parameters()).is_cuda and hasattr(model, "pack_parameters"):
+    if tp:
+        from ..tp import TPInferenceLM
+
+        model = TPInferenceLM(model, int8=int8).eval()  # this rank's slices (quantised after slicing)
+    elif int8:
+        from ...ops.quant import quantize_model_int8
+
+        quantize_model_int8(model)
+    return model, tokenizer
+
+
+def _create_engine(param_path: Optional[Path] = None, device: str = "cuda", dtype: torch.dtype = torch.bfloat16,
+                   max_batch_size: int = 16, page_size: int = 16, max_seq_len: Optional[int] = None,
+                   int8: bool = False) -> InferenceEngine:
+    """Single-process engine, or rank 0 of a tensor-parallel group when a process group is up (the
+    other ranks run ``serve_worker_rank``)."""
+    import torch.distributed as dist
+
+    tp = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+    model, tokenizer = _load(param_path, device, dtype, int8, tp)
+    if not tp and next(model.parameters()).is_cuda and hasattr(model, "pack_parameters") and not int8:
         model.pack_parameters(with_grad=False)  # adjacent q/k/v and gate/up weights -> single GEMMs
     log.info("Model loaded on %s with dtype %s", device, dtype)
     return InferenceEngine(model=model, tokenizer=tokenizer, max_batch_size=max_batch_size, page_size=page_size,
                            max_seq_len=max_seq_len)
+
+
+def serve_worker_rank(param_path: Optional[Path] = None, device: str = "cuda", dtype: torch.dtype = torch.bfloat16,
+                      max_batch_size: int = 16, page_size: int = 16, max_seq_len: Optional[int] = None,
+                      int8: bool = False) -> None:
+    """Ranks > 0 of a tensor-parallel server: load the same weights, keep this rank's slice, replay
+    the steps rank 0 announces until it shuts down."""
+    from ..tp import serve_worker
+
+    model, tokenizer = _load(param_path, device, dtype, int8, tp=True)
+    serve_worker(model, tokenizer, max_batch_size=max_batch_size, max_seq_len=max_seq_len, page_size=page_size)
 
 
 @asynccontextmanager
@@ -126,7 +156,8 @@ async def create_message(request: MessagesRequest):
 
 def run_server(host: str = "0.0.0.0", port: int = 8000, reload: bool = False, device: str = "cuda",
                dtype: torch.dtype = torch.bfloat16, param_path: Optional[Path] = None, max_batch_size: int = 16,
-               page_size: int = 16, max_seq_len: Optional[int] = None) -> None:
+               page_size: int = 16, max_seq_len: Optional[int] = None, int8: bool = False) -> None:
     app.state.server_config = {"device": device, "dtype": dtype, "param_path": param_path,
-                               "max_batch_size": max_batch_size, "page_size": page_size, "max_seq_len": max_seq_len}
+                               "max_batch_size": max_batch_size, "page_size": page_size, "max_seq_len": max_seq_len,
+                               "int8": int8}
     uvicorn.run(app, host=host, port=port, reload=reload)

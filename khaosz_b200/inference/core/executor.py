@@ -58,32 +58,72 @@ class Executor:
         top_p = torch.tensor([t.top_p for t in tasks], dtype=torch.float32, device=self.device)
         return sample(logits, temperature, top_k, top_p).tolist()
 
-    @torch.inference_mode()
-    def execute_prefill(self, tasks: List[Task], prompt_len: int, start_pos: int = 0) -> List[int]:
-        """Run ``prompt[start_pos:prompt_len]`` of equally shaped tasks through the model, fill
-        their pages and return the first generated token of each."""
-        ids = torch.tensor([t.prompt_ids[start_pos:prompt_len] for t in tasks], dtype=torch.long, device=self.device)
+    # -- tensor-level bodies (what a tensor-parallel worker rank replays) ------------------------------
+    def _prefill_body(self, ids: torch.Tensor, table: torch.Tensor, start_pos: int, prompt_len: int) -> torch.Tensor:
+        """Logits ``[B, vocab]`` of the last prompt position."""
         B, T = ids.shape
-        table = self.page_cache.make_table_tensor([t.task_id for t in tasks], self.device)
-        positions = torch.arange(start_pos, prompt_len, device=self.device).unsqueeze(0).expand(B, T)
+        positions = torch.arange(start_pos, prompt_len, device=ids.device).unsqueeze(0).expand(B, T)
         view = self.page_cache.bind(table, total_len=prompt_len)
-        rows = torch.arange(B, device=self.device) * T + (T - 1)
+        rows = torch.arange(B, device=ids.device) * T + (T - 1)
         out = self.model(ids, paged_cache=view, position_ids=positions if start_pos else None, logits_rows=rows)
-        return self._sample(out["logits"].reshape(B, -1), tasks)
+        return out["logits"].reshape(B, -1)
 
     def _decode_body(self, ids, positions, lens, table, temperature, top_k, top_p) -> torch.Tensor:
         view = self.page_cache.bind(table, seq_lens=lens)
         out = self.model(ids, paged_cache=view, position_ids=positions)
         return sample(out["logits"].reshape(ids.shape[0], -1), temperature, top_k, top_p)
 
-    def _decode_graphed(self, tasks: List[Task], last: List[int], pos: List[int]) -> List[int]:
-        n = len(tasks)
-        bucket = 1 << max(0, math.ceil(math.log2(n)))
+    # -- hooks of the multi-rank executor (single process: nothing to do) ------------------------------
+    def _announce_prefill(self, ids: torch.Tensor, table: torch.Tensor, start_pos: int, prompt_len: int) -> None:
+        pass
+
+    def _announce_decode(self, ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor) -> None:
+        pass
+
+    def _announce_slot(self, slot: "_DecodeSlot", n: int) -> None:
+        pass
+
+    @torch.inference_mode()
+    def execute_prefill(self, tasks: List[Task], prompt_len: int, start_pos: int = 0) -> List[int]:
+        """Run ``prompt[start_pos:prompt_len]`` of equally shaped tasks through the model, fill
+        their pages and return the first generated token of each."""
+        ids = torch.tensor([t.prompt_ids[start_pos:prompt_len] for t in tasks], dtype=torch.long, device=self.device)
+        table = self.page_cache.make_table_tensor([t.task_id for t in tasks], self.device)
+        self._announce_prefill(ids, table, start_pos, prompt_len)
+        return self._sample(self._prefill_body(ids, table, start_pos, prompt_len), tasks)
+
+    def _slot(self, bucket: int) -> "_DecodeSlot":
         slot = self._slots.get(bucket)
         if slot is None:
             width = (self.max_seq_len + self.page_cache.page_size - 1) // self.page_cache.page_size + 1
             slot = self._slots[bucket] = _DecodeSlot(bucket, width, self.device)
-        pad = bucket - n
+        return slot
+
+    def _run_slot(self, slot: "_DecodeSlot") -> torch.Tensor:
+        """One decode step over the slot's static buffers: plain launches on first use, recorded on
+        the second, replayed afterwards.  Returns the sampled tokens ``[bucket]``."""
+        args = (slot.ids, slot.pos, slot.lens, slot.table, slot.temperature, slot.top_k, slot.top_p)
+        slot.uses += 1
+        if slot.uses == 1 or not self.cuda_graphs:
+            return self._decode_body(*args)
+        if slot.graph is None:
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    slot.out = self._decode_body(*args)
+            except Exception:  # an op that cannot be captured: keep decoding with plain launches
+                self.cuda_graphs = False
+                torch.cuda.synchronize()
+                return self._decode_body(*args)
+            slot.graph = graph
+        slot.graph.replay()
+        return slot.out
+
+    def _decode_graphed(self, tasks: List[Task], last: List[int], pos: List[int]) -> List[int]:
+        n = len(tasks)
+        slot = self._slot(1 << max(0, math.ceil(math.log2(n))))
+        pad = slot.bucket - n
         table = self.page_cache.make_table_tensor([t.task_id for t in tasks], "cpu")
         if table.shape[1] > slot.table.shape[1]:
             raise RuntimeError("block table wider than the decode graph's static table")
@@ -95,23 +135,8 @@ class Executor:
         slot.temperature.copy_(torch.tensor([t.temperature for t in tasks] + [1.0] * pad, dtype=torch.float32))
         slot.top_k.copy_(torch.tensor([t.top_k for t in tasks] + [1] * pad, dtype=torch.int32))
         slot.top_p.copy_(torch.tensor([t.top_p for t in tasks] + [1.0] * pad, dtype=torch.float32))
-        args = (slot.ids, slot.pos, slot.lens, slot.table, slot.temperature, slot.top_k, slot.top_p)
-        slot.uses += 1
-        if slot.uses == 1:      # first use of this bucket: plain launches (also warms every kernel up)
-            return self._decode_body(*args)[:n].tolist()
-        if slot.graph is None:  # second use: record
-            torch.cuda.current_stream().synchronize()
-            graph = torch.cuda.CUDAGraph()
-            try:
-                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                    slot.out = self._decode_body(*args)
-            except Exception:  # an op that cannot be captured: keep decoding with plain launches
-                self.cuda_graphs = False
-                torch.cuda.synchronize()
-                return self._decode_body(*args)[:n].tolist()
-            slot.graph = graph
-        slot.graph.replay()
-        return slot.out[:n].tolist()
+        self._announce_slot(slot, n)
+        return self._run_slot(slot)[:n].tolist()
 
     @torch.inference_mode()
     def execute_decode(self, tasks: List[Task]) -> List[int]:
@@ -123,6 +148,10 @@ class Executor:
         ids = torch.tensor(last, dtype=torch.long, device=self.device).unsqueeze(1)
         positions = torch.tensor(pos, dtype=torch.long, device=self.device).unsqueeze(1)
         table = self.page_cache.make_table_tensor([t.task_id for t in tasks], self.device)
+        self._announce_decode(ids, positions, table)
         view = self.page_cache.bind(table, seq_lens=positions.squeeze(1) + 1)
         out = self.model(ids, paged_cache=view, position_ids=positions)
         return self._sample(out["logits"].reshape(len(tasks), -1), tasks)
+
+    def close(self) -> None:
+        """Release whatever the executor holds outside this process (worker ranks)."""

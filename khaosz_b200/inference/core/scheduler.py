@@ -41,10 +41,14 @@ class InferenceScheduler:
         v_dim = None
         if getattr(config, "attn_type", "gqa") == "mla":
             head_dim = config.qk_nope_head_dim + config.qk_rope_head_dim
-        self._page_cache = KVCache(config.n_layers, n_pages, page_size, config.n_kv_heads, head_dim, self.device,
+        # a tensor-parallel model keeps only this rank's KV heads and brings its own executor class
+        n_kv_heads = getattr(model, "kv_heads_local", config.n_kv_heads)
+        self._page_cache = KVCache(config.n_layers, n_pages, page_size, n_kv_heads, head_dim, self.device,
                                    self.dtype, v_dim)
         self._task_mgr = TaskManager(tokenizer, max_batch_size, max_seq_len, max_prompt_len)
-        self._executor = Executor(model, tokenizer, self._page_cache, self.device, self.dtype, max_seq_len=max_seq_len)
+        executor_cls = getattr(model, "executor_cls", None) or Executor
+        self._executor = executor_cls(model, tokenizer, self._page_cache, self.device, self.dtype,
+                                      max_seq_len=max_seq_len)
         self._running = False
         self._fatal_error: Optional[Exception] = None
         self._loop_thread: Optional[threading.Thread] = None
@@ -81,6 +85,7 @@ class InferenceScheduler:
         if self._loop_thread is not None:
             self._loop_thread.join(timeout=5.0)
         self._drain()
+        self._executor.close()
         if torch.cuda.is_available():
             torch.cuda.empty_cache()
 

@@ -1,0 +1,255 @@
+"""Tensor-parallel serving: one process per GPU, rank 0 owns the scheduler (and the HTTP server).
+
+The reference's engine is a single process on a single GPU (``astrai/inference/engine.py:93-116``).
+Here every rank holds its slice of the weights (the same slicing as tensor-parallel training:
+this rank's query heads with their KV heads, its slice of the MLP) and the KV pages of its own KV
+heads; activations are replicated.  Column-parallel projections are plain local GEMMs, the
+row-parallel ones (``o_proj``, ``down``) end in an all-reduce that the decode path runs as the fused
+GEMM -> all-reduce kernel over NVLink (``khaosz_b200.parallel.tensor_parallel``; ``torch.distributed``
+on CPU/gloo and for very long prefills).
+
+Control flow: rank 0 runs the normal ``InferenceScheduler`` with a ``DistributedExecutor``; before
+every model call it announces the call to the other ranks - a small header on a gloo control group
+(so that idle workers block on the host, not in a device collective) followed by the input tensors
+on the main group - and every rank then executes the same tensor-level step
+(``Executor._prefill_body`` / ``_run_slot``).  Only rank 0 uses the sampled tokens; the next step's
+inputs are announced again, so the workers carry no request state besides their KV pages.
+"""
+
+from __future__ import annotations
+
+import datetime
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch import Tensor
+
+from .. import ops
+from ..ops import attention as attn_ops
+from ..parallel.tensor_parallel import TPContext, _RowParallelFn
+from ..parallel.tp_model import TPAttention, TPInfo, TPMLP
+from .core.cache import KVCache
+from .core.executor import Executor
+
+OP_STOP, OP_PREFILL, OP_DECODE, OP_SLOT = 0, 1, 2, 3
+FUSED_ALLREDUCE_MAX_ROWS = 4096  # beyond this the staging buffers of the fused kernel get large
+
+
+def _row_all_reduce(x: Tensor, w: Tensor, info: TPInfo) -> Tensor:
+    """``all_reduce(x @ w.T)`` over the tensor-parallel group; ``x`` is ``[rows, k_local]``."""
+    if info.ws == 1:
+        return ops.linear(x, w)
+    if x.is_cuda and x.shape[0] <= FUSED_ALLREDUCE_MAX_ROWS:
+        return _RowParallelFn.apply(x, w, info.ctx(), True)   # fused GEMM -> all-reduce kernel
+    y = ops.linear(x, w)
+    dist.all_reduce(y, group=info.group)
+    return y
+
+
+def _local_linear(x: Tensor, w: Optional[Tensor], q8) -> Tensor:
+    if q8 is not None:
+        from ..ops.quant import linear_w8
+
+        return linear_w8(x, q8[0], q8[1])
+    return ops.linear(x, w)
+
+
+def _row_linear(x2: Tensor, w: Optional[Tensor], q8, info: TPInfo) -> Tensor:
+    if q8 is None:
+        return _row_all_reduce(x2, w, info)
+    y = _local_linear(x2, None, q8)   # int8 weights: local GEMM with in-kernel dequantisation, then the sum
+    if info.ws > 1:
+        dist.all_reduce(y, group=info.group)
+    return y
+
+
+def _quantize(param: nn.Parameter):
+    from ..ops.quant import quantize_w8
+
+    q, s = quantize_w8(param.data)
+    return q, s
+
+
+class _Attention(nn.Module):
+    def __init__(self, attn, info: TPInfo):
+        super().__init__()
+        self.inner = TPAttention(attn, info)   # weight slicing shared with tensor-parallel training
+        self.info = info
+        self.qkv8 = self.o8 = None
+
+    def quantize(self) -> None:
+        """Weight-only int8 (per output channel of this rank's slices); the bf16 copies are dropped."""
+        self.qkv8, self.o8 = _quantize(self.inner.qkv_weight), _quantize(self.inner.o_weight)
+        self.inner.qkv_weight = self.inner.o_weight = None
+
+    def forward(self, x: Tensor, rotary, paged_cache, residual: Tensor) -> Tensor:
+        a = self.inner
+        B, S, _ = x.shape
+        hl, kl, D = a.h_local, a.kv_local, a.head_dim
+        cs, pos = rotary
+        qkv = _local_linear(x, a.qkv_weight, self.qkv8).view(B, S, hl + 2 * kl, D)
+        qk = ops.rope(qkv[:, :, : hl + kl], cs, pos)
+        q, k, v = qk[:, :, :hl], qk[:, :, hl:], qkv[:, :, hl + kl:]
+        if paged_cache is not None:
+            ctx = paged_cache.attention(a.layer_id, q, k, v)
+        else:
+            ctx = attn_ops.attention(q, k, v, causal=True)
+        out = _row_linear(ctx.reshape(B * S, hl * D), a.o_weight, self.o8, self.info)
+        return out.view(B, S, -1) + residual
+
+
+class _MLP(nn.Module):
+    def __init__(self, mlp, info: TPInfo):
+        super().__init__()
+        self.inner = TPMLP(mlp, info)
+        self.info = info
+        self.gu8 = self.down8 = None
+
+    def quantize(self) -> None:
+        self.gu8, self.down8 = _quantize(self.inner.gate_up_weight), _quantize(self.inner.down_weight)
+        self.inner.gate_up_weight = self.inner.down_weight = None
+
+    def forward(self, x: Tensor, residual: Tensor) -> Tensor:
+        m = self.inner
+        B, S, _ = x.shape
+        h = ops.swiglu(_local_linear(x, m.gate_up_weight, self.gu8))
+        out = _row_linear(h.reshape(B * S, -1), m.down_weight, self.down8, self.info)
+        return out.view(B, S, -1) + residual
+
+
+class _Block(nn.Module):
+    def __init__(self, block, info: TPInfo):
+        super().__init__()
+        self.input_norm, self.post_attention_norm = block.input_norm, block.post_attention_norm
+        self.attention = _Attention(block.attention, info)
+        self.mlp = _MLP(block.mlp, info)
+
+    def forward(self, x: Tensor, rotary, paged_cache) -> Tensor:
+        h = self.attention(self.input_norm(x), rotary, paged_cache, x)
+        return self.mlp(self.post_attention_norm(h), h)
+
+
+class TPInferenceLM(nn.Module):
+    """Tensor-parallel decoder for serving, built from a full ``AutoRegressiveLM`` that holds the same
+    weights on every rank.  Same ``forward`` contract as the dense model (full logits on every rank)."""
+
+    def __init__(self, model, group=None, int8: bool = False):
+        super().__init__()
+        self.info = TPInfo(group)
+        self.config = model.config
+        self.rotary_embedding = model.rotary_embedding
+        self.embed_tokens = model.embed_tokens
+        self.layers = nn.ModuleList(_Block(b, self.info) for b in model.layers)
+        self.norm, self.lm_head = model.norm, model.lm_head
+        if int8:
+            for layer in self.layers:
+                layer.attention.quantize()
+                layer.mlp.quantize()
+        self.kv_heads_local = self.layers[0].attention.inner.kv_local
+        self.executor_cls = DistributedExecutor
+        # the decode step is recorded as a CUDA graph only when it contains no library collective
+        # (the int8 row-parallel layers sum their partial results with torch.distributed)
+        self.graph_safe = not int8
+        # host-side control channel (collective: every rank builds the model at the same point)
+        self.control = None
+        if self.info.ws > 1:
+            self.control = dist.new_group(backend="gloo", timeout=datetime.timedelta(days=7))
+
+    def forward(self, input_ids: Tensor, input_mask: Optional[Tensor] = None, paged_cache=None,
+                position_ids: Optional[Tensor] = None, logits_rows: Optional[Tensor] = None) -> Dict[str, Tensor]:
+        x = self.embed_tokens(input_ids)
+        rotary = self.rotary_embedding(x, position_ids)
+        for layer in self.layers:
+            x = layer(x, rotary, paged_cache)
+        hidden = self.norm(x)
+        if logits_rows is not None:
+            logits = self.lm_head(hidden.reshape(-1, hidden.shape[-1])[logits_rows])
+        else:
+            logits = self.lm_head(hidden)
+        return {"logits": logits, "hidden_states": hidden}
+
+
+class DistributedExecutor(Executor):
+    """Rank 0: announces every model call to the workers, then runs it.  Workers: ``worker_loop``."""
+
+    def __init__(self, model: TPInferenceLM, tokenizer, page_cache: KVCache, device, dtype,
+                 max_seq_len: Optional[int] = None, cuda_graphs: bool = True):
+        super().__init__(model, tokenizer, page_cache, device, dtype, max_seq_len=max_seq_len,
+                         cuda_graphs=cuda_graphs and getattr(model, "graph_safe", True))
+        self.info = model.info
+        self.control = model.control
+        self._closed = False
+
+    # -- wire format -----------------------------------------------------------------------------
+    def _header(self, values) -> None:
+        if self.control is None:
+            return
+        h = torch.tensor(list(values) + [0] * (6 - len(values)), dtype=torch.int64)
+        dist.broadcast(h, src=0, group=self.control)
+
+    def _send(self, *tensors: Tensor) -> None:
+        if self.info.ws > 1:
+            for t in tensors:
+                dist.broadcast(t, src=0, group=self.info.group)
+
+    def _recv(self, shape, dtype) -> Tensor:
+        t = torch.empty(shape, dtype=dtype, device=self.device)
+        dist.broadcast(t, src=0, group=self.info.group)
+        return t
+
+    # -- rank 0 ------------------------------------------------------------------------------------
+    def _announce_prefill(self, ids, table, start_pos, prompt_len) -> None:
+        self._header([OP_PREFILL, ids.shape[0], ids.shape[1], table.shape[1], start_pos, prompt_len])
+        self._send(ids, table)
+
+    def _announce_decode(self, ids, positions, table) -> None:
+        self._header([OP_DECODE, ids.shape[0], 1, table.shape[1]])
+        self._send(ids, positions, table)
+
+    def _announce_slot(self, slot, n) -> None:
+        self._header([OP_SLOT, slot.bucket, n])
+        self._send(slot.ids, slot.pos, slot.lens, slot.table)
+
+    def close(self) -> None:
+        if not self._closed and self.info.rank == 0:
+            self._closed = True
+            self._header([OP_STOP])
+
+    # -- ranks > 0 ---------------------------------------------------------------------------------
+    @torch.inference_mode()
+    def worker_loop(self) -> None:
+        """Execute announced steps until rank 0 closes."""
+        while True:
+            h = torch.zeros(6, dtype=torch.int64)
+            dist.broadcast(h, src=0, group=self.control)
+            op, a, b, c, d, e = h.tolist()
+            if op == OP_STOP:
+                return
+            if op == OP_PREFILL:
+                ids, table = self._recv((a, b), torch.long), self._recv((a, c), torch.long)
+                self._prefill_body(ids, table, d, e)
+            elif op == OP_DECODE:
+                ids, pos, table = self._recv((a, 1), torch.long), self._recv((a, 1), torch.long), self._recv((a, c), torch.long)
+                view = self.page_cache.bind(table, seq_lens=pos.squeeze(1) + 1)
+                self.model(ids, paged_cache=view, position_ids=pos)
+            elif op == OP_SLOT:
+                slot = self._slot(a)
+                for t in (slot.ids, slot.pos, slot.lens, slot.table):
+                    dist.broadcast(t, src=0, group=self.info.group)
+                self._run_slot(slot)
+            else:
+                raise RuntimeError(f"unknown control op {op}")
+
+
+def serve_worker(model: TPInferenceLM, tokenizer, max_batch_size: int, max_seq_len: Optional[int] = None,
+                 page_size: int = 128) -> None:
+    """Entry point of ranks > 0: same KV pool geometry as rank 0's scheduler, then the worker loop."""
+    config = model.config
+    max_seq_len = max_seq_len or config.max_len
+    first = next(model.parameters())
+    n_pages = (max_batch_size * (max_seq_len + page_size) + page_size - 1) // page_size
+    cache = KVCache(config.n_layers, n_pages, page_size, model.kv_heads_local, config.dim // config.n_heads,
+                    first.device, first.dtype)
+    DistributedExecutor(model, tokenizer, cache, first.device, first.dtype, max_seq_len=max_seq_len).worker_loop()
