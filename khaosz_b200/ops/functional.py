@@ -139,11 +139,15 @@ def _adjacent(ws) -> Optional[torch.Tensor]:
     if not all(w.is_contiguous() and w.shape[1] == first.shape[1] and w.dtype == first.dtype for w in ws):
         return None
     expect = first.data_ptr()
+    base = first.untyped_storage().data_ptr()
     for w in ws:
-        if w.data_ptr() != expect:
+        # consecutive addresses inside ONE storage (separate allocations can touch by accident)
+        if w.data_ptr() != expect or w.untyped_storage().data_ptr() != base:
             return None
         expect += w.numel() * w.element_size()
     rows = sum(w.shape[0] for w in ws)
+    if (first.storage_offset() + rows * first.shape[1]) * first.element_size() > first.untyped_storage().nbytes():
+        return None
     return first.as_strided((rows, first.shape[1]), (first.shape[1], 1), first.storage_offset())
 
 
