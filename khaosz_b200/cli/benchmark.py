@@ -126,7 +126,8 @@ def bench_serve(model, cfg, requests: int, rate: float, min_prompt: int, max_pro
     engine.shutdown()
     return {"benchmark": "serve", "requests": requests, "arrival_rate_per_s": rate, "generated_per_request": gen,
             "output_tokens_per_s_wall": requests * gen / wall, "decode_tokens_per_s_busy": stats["decode_tokens_per_s"],
-            "ttft_p50_s": stats["ttft_p50_s"], "ttft_p99_s": stats["ttft_p99_s"], "wall_s": wall}
+            "ttft_p50_s": stats["ttft_p50_s"], "ttft_p99_s": stats["ttft_p99_s"], "wall_s": wall,
+            "decode_graphs": stats.get("decode_graphs", 0)}
 
 
 def parse_args(argv=None):

@@ -69,7 +69,8 @@ class InferenceScheduler:
         stats.update(self._task_mgr.latency_stats())
         stats.update({"decode_steps": self._steps, "decode_tokens": self._decode_tokens,
                       "decode_tokens_per_s": self._decode_tokens / self._busy_s if self._busy_s > 0 else 0.0,
-                      "free_pages": self._page_cache.free_pages()})
+                      "free_pages": self._page_cache.free_pages(),
+                      "decode_graphs": sum(1 for s in getattr(self._executor, "_slots", {}).values() if s.graph is not None)})
         return stats
 
     def start(self) -> None:

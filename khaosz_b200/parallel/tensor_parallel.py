@@ -42,6 +42,7 @@ class TPContext:
         self._pool: Dict[Tuple[str, int], SymmetricBuffer] = {}
         self._images: Dict[Tuple[str, int, int, int], list] = {}
         self._turns: Dict[Tuple[str, int, int], int] = {}
+        self._retired: list = []
         if self.use_kernels:
             self.ctrl = PeerControl(self.device, self.group)
             self.grid_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
@@ -61,8 +62,22 @@ class TPContext:
     def reset(cls) -> None:
         cls._current = None
 
-    def buffer(self, tag: str, numel: int) -> SymmetricBuffer:
-        """Symmetric bf16 buffer of at least ``numel`` elements (collective on first use per tag/size)."""
+    def buffer(self, tag: str, numel: int, grow: bool = False) -> SymmetricBuffer:
+        """Symmetric bf16 buffer of at least ``numel`` elements (collective on first use per tag/size).
+        ``grow=True`` keeps one buffer per tag and replaces it by a larger one (next power of two)
+        only when needed: for scratch whose size follows the batch (staging of the reduced output),
+        so that a new batch size does not cost a new symmetric allocation."""
+        if grow:
+            buf = self._pool.get((tag, -1))
+            if buf is None or buf.tensor.numel() < numel:
+                if buf is not None:
+                    self._retired.append(buf)  # recorded CUDA graphs may still point at it
+                cap = 1 << max(int(numel - 1).bit_length(), 16)
+                buf = SymmetricBuffer(cap, torch.bfloat16, self.device, self.group, zero=True)
+                torch.cuda.synchronize(self.device)
+                dist.barrier(group=self.group)
+                self._pool[(tag, -1)] = buf
+            return buf
         key = (tag, numel)
         buf = self._pool.get(key)
         if buf is None:
@@ -159,7 +174,7 @@ def _comm_gemm(ctx: TPContext, a, b, *, a_mn=False, b_mn=False, a_gather=False, 
     else:
         rows = M // ws if c_mode == 1 else M
         slot_rows = (rows + 127) // 128 * 128
-        stage = ctx.buffer(tag + ".stage", ws * slot_rows * N)
+        stage = ctx.buffer(tag + ".stage", ws * slot_rows * N, grow=True)
         stage_ptrs = stage.ptrs
         out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
         ldc, ldo = N, N
