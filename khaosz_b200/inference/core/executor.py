@@ -59,12 +59,16 @@ class Executor:
         return sample(logits, temperature, top_k, top_p).tolist()
 
     # -- tensor-level bodies (what a tensor-parallel worker rank replays) ------------------------------
-    def _prefill_body(self, ids: torch.Tensor, table: torch.Tensor, start_pos: int, prompt_len: int) -> torch.Tensor:
-        """Logits ``[B, vocab]`` of the last prompt position."""
+    def _prefill_body(self, ids: torch.Tensor, table: torch.Tensor, start_pos: int, prompt_len: int,
+                      last: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Logits ``[B, vocab]`` of the last prompt position.  ``last`` (``[B]``, only with
+        ``start_pos == 0``): index of each sequence's last real token when shorter prompts were
+        right-padded to ``prompt_len`` - causal attention keeps the padding invisible to the real
+        tokens, and padded positions beyond a sequence's pages are not written."""
         B, T = ids.shape
         positions = torch.arange(start_pos, prompt_len, device=ids.device).unsqueeze(0).expand(B, T)
         view = self.page_cache.bind(table, total_len=prompt_len)
-        rows = torch.arange(B, device=ids.device) * T + (T - 1)
+        rows = torch.arange(B, device=ids.device) * T + (last if last is not None else T - 1)
         out = self.model(ids, paged_cache=view, position_ids=positions if start_pos else None, logits_rows=rows)
         return out["logits"].reshape(B, -1)
 
@@ -74,7 +78,8 @@ class Executor:
         return sample(out["logits"].reshape(ids.shape[0], -1), temperature, top_k, top_p)
 
     # -- hooks of the multi-rank executor (single process: nothing to do) ------------------------------
-    def _announce_prefill(self, ids: torch.Tensor, table: torch.Tensor, start_pos: int, prompt_len: int) -> None:
+    def _announce_prefill(self, ids: torch.Tensor, table: torch.Tensor, start_pos: int, prompt_len: int,
+                          last: Optional[torch.Tensor] = None) -> None:
         pass
 
     def _announce_decode(self, ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor) -> None:
@@ -91,6 +96,19 @@ class Executor:
         table = self.page_cache.make_table_tensor([t.task_id for t in tasks], self.device)
         self._announce_prefill(ids, table, start_pos, prompt_len)
         return self._sample(self._prefill_body(ids, table, start_pos, prompt_len), tasks)
+
+    @torch.inference_mode()
+    def execute_prefill_padded(self, tasks: List[Task]) -> List[int]:
+        """Prefill prompts of different lengths (none served from the prefix cache) in one batch:
+        right-padded to the longest, first generated token taken at each prompt's own last position."""
+        lens = [len(t.prompt_ids) for t in tasks]
+        width = max(lens)
+        ids = torch.tensor([t.prompt_ids + [0] * (width - n) for t, n in zip(tasks, lens)], dtype=torch.long,
+                           device=self.device)
+        last = torch.tensor([n - 1 for n in lens], dtype=torch.long, device=self.device)
+        table = self.page_cache.make_table_tensor([t.task_id for t in tasks], self.device)
+        self._announce_prefill(ids, table, 0, width, last)
+        return self._sample(self._prefill_body(ids, table, 0, width, last), tasks)
 
     def _slot(self, bucket: int) -> "_DecodeSlot":
         slot = self._slots.get(bucket)

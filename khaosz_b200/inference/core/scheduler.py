@@ -126,22 +126,41 @@ class InferenceScheduler:
         if task.is_finished(stop_ids):
             self._emit(task, STOP)
 
+    PAD_BUCKET = 256          # prompts whose lengths fall into the same bucket are prefilled together
+    PAD_BATCH_TOKENS = 32768  # padded tokens per prefill batch at most
+
     def _prefill(self, stop_ids: List[int]) -> None:
         page = self._page_cache.page_size
         groups: Dict[Tuple[int, int], List[Task]] = {}
+        padded: Dict[int, List[Task]] = {}
         for t in self._task_mgr.get_active_tasks():
             if getattr(t, "prefilled", False) or t.status != TaskStatus.RUNNING:
                 continue
             n = len(t.prompt_ids)
             cached = min(self._page_cache.task_cached(t.task_id), ((n - 1) // page) * page)
             t.input_tokens = n
-            groups.setdefault((n, cached), []).append(t)
-        for (n, cached), group in groups.items():
-            first = self._executor.execute_prefill(group, n, cached)
+            if cached == 0:   # nothing from the prefix cache: can share a right-padded batch
+                padded.setdefault((n + self.PAD_BUCKET - 1) // self.PAD_BUCKET, []).append(t)
+            else:
+                groups.setdefault((n, cached), []).append(t)
+
+        def done(group, first, cached):
             for t, tok in zip(group, first):
                 t.prefilled = True
                 self._page_cache.task_record_hashes(t.task_id, t.prompt_ids, start_logical_page=cached // page)
                 self._accept(t, tok, stop_ids)
+
+        for (n, cached), group in groups.items():
+            done(group, self._executor.execute_prefill(group, n, cached), cached)
+        for bucket, tasks in padded.items():
+            per_batch = max(1, self.PAD_BATCH_TOKENS // (bucket * self.PAD_BUCKET))
+            for i in range(0, len(tasks), per_batch):
+                group = tasks[i:i + per_batch]
+                if len({len(t.prompt_ids) for t in group}) == 1:
+                    first = self._executor.execute_prefill(group, len(group[0].prompt_ids), 0)
+                else:
+                    first = self._executor.execute_prefill_padded(group)
+                done(group, first, 0)
 
     def _decode(self, stop_ids: List[int]) -> None:
         ready: List[Task] = []

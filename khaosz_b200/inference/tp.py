@@ -200,9 +200,13 @@ class DistributedExecutor(Executor):
         return t
 
     # -- rank 0 ------------------------------------------------------------------------------------
-    def _announce_prefill(self, ids, table, start_pos, prompt_len) -> None:
-        self._header([OP_PREFILL, ids.shape[0], ids.shape[1], table.shape[1], start_pos, prompt_len])
+    def _announce_prefill(self, ids, table, start_pos, prompt_len, last=None) -> None:
+        # start_pos < 0 marks a right-padded batch whose per-sequence last positions follow
+        self._header([OP_PREFILL, ids.shape[0], ids.shape[1], table.shape[1], -1 if last is not None else start_pos,
+                      prompt_len])
         self._send(ids, table)
+        if last is not None:
+            self._send(last)
 
     def _announce_decode(self, ids, positions, table) -> None:
         self._header([OP_DECODE, ids.shape[0], 1, table.shape[1]])
@@ -229,7 +233,8 @@ class DistributedExecutor(Executor):
                 return
             if op == OP_PREFILL:
                 ids, table = self._recv((a, b), torch.long), self._recv((a, c), torch.long)
-                self._prefill_body(ids, table, d, e)
+                last = self._recv((a,), torch.long) if d < 0 else None
+                self._prefill_body(ids, table, max(d, 0), e, last)
             elif op == OP_DECODE:
                 ids, pos, table = self._recv((a, 1), torch.long), self._recv((a, 1), torch.long), self._recv((a, c), torch.long)
                 view = self.page_cache.bind(table, seq_lens=pos.squeeze(1) + 1)
