@@ -10,6 +10,7 @@ blocking ``.item()``; ``context.loss`` waits for that copy only when somebody re
 
 from __future__ import annotations
 
+import logging
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, Optional
@@ -25,6 +26,8 @@ from ..parallel.executor import BaseExecutor, ExecutorFactory
 from ..parallel.setup import get_current_device, get_rank, get_world_size
 from ..serialization import CONFIG_FILE, META_FILE, Checkpoint, load_json, load_model_weights
 from .strategy import BaseStrategy, StrategyFactory
+
+log = logging.getLogger(__name__)
 
 
 class _AsyncScalar:
@@ -110,8 +113,10 @@ class TrainContextBuilder:
             # the position comes from the config (CLI flags), as in the reference
             ctx.epoch, ctx.iteration = self.config.start_epoch, self.config.start_batch
             ctx.checkpoint = ckpt
-        else:
+        elif any(root.glob("*.safetensors")):
             model.load_state_dict(load_model_weights(str(root)), strict=False)
+        else:  # a parameter directory with only config.json: train from the random initialisation
+            log.info("no weights in %s: starting from the random initialisation", root)
 
     def build(self) -> TrainContext:
         cfg = self.config
