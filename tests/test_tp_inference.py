@@ -82,3 +82,50 @@ def test_tensor_parallel_engine_matches_dense_greedy(tmp_path):
     spawn_parallel_fn(_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29641", out=out)
     r = torch.load(out)
     assert r["got"] == r["want"]
+
+
+def _server_glue_case(param_dir, out):
+    """The HTTP server's engine factory under a process group: rank 0 gets a tensor-parallel engine,
+    rank 1 runs the worker entry point; both load the same saved model."""
+    from khaosz_b200.inference.api.server import _create_engine, serve_worker_rank
+
+    kw = dict(param_path=param_dir, device="cpu", dtype=torch.float32, max_batch_size=2, page_size=4, max_seq_len=48)
+    if dist.get_rank() != 0:
+        serve_worker_rank(**kw)
+        return
+    engine = _create_engine(**kw)
+    try:
+        assert type(engine.model).__name__ == "TPInferenceLM"
+        text = engine.generate("hello world", max_tokens=5, temperature=1.0, top_k=1, top_p=1.0)
+    finally:
+        engine.shutdown()
+    torch.save({"text": text}, out)
+
+
+def test_server_engine_factory_goes_tensor_parallel(tmp_path, tokenizer_dir, tokenizer):
+    import shutil
+
+    from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
+
+    param_dir = tmp_path / "params"
+    shutil.copytree(tokenizer_dir, param_dir)
+    cfg = AutoRegressiveLMConfig(vocab_size=len(tokenizer), dim=64, n_layers=2, norm_eps=1e-5, dim_ffn=128, tie_weight=False,
+                                 max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2)
+    torch.manual_seed(3)
+    dense = AutoRegressiveLM(cfg).eval()
+    dense.save_pretrained(str(param_dir))
+    out = str(tmp_path / "srv.pt")
+    spawn_parallel_fn(_server_glue_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29643",
+                      param_dir=str(param_dir), out=out)
+    text = torch.load(out)["text"]
+    # dense greedy reference
+    ids = torch.tensor([tokenizer.encode("hello world")])
+    want = []
+    with torch.no_grad():
+        for _ in range(5):
+            nxt = int(dense(ids)["logits"][0, -1].argmax())
+            if nxt in tokenizer.stop_ids:
+                break
+            want.append(nxt)
+            ids = torch.cat([ids, torch.tensor([[nxt]])], dim=1)
+    assert text == "".join(tokenizer.decode([t]) for t in want)
