@@ -149,6 +149,27 @@ class TPBlock(nn.Module):
         return h + self.mlp(y)
 
 
+class _GatherTokens(torch.autograd.Function):
+    """All-gather of per-token values over the group (``[n_local] -> [n_local * ws]``); the gradient
+    of a rank's slice is the sum of the slices the ranks hold for it (every rank evaluates the
+    same loss on the gathered values, so the copies are averaged by the executor's 1/ws)."""
+
+    @staticmethod
+    def forward(ctx, x, info):
+        ctx.info = info
+        parts = [torch.empty_like(x) for _ in range(info.ws)]
+        dist.all_gather(parts, x.contiguous(), group=info.group)
+        return torch.cat(parts, dim=0)
+
+    @staticmethod
+    def backward(ctx, g):
+        info = ctx.info
+        g = g.contiguous()
+        dist.all_reduce(g, group=info.group)
+        n = g.shape[0] // info.ws
+        return g[info.rank * n:(info.rank + 1) * n], None
+
+
 class TensorParallelLM(nn.Module):
     """Training-time tensor-parallel decoder.  ``forward`` takes the full ``[B, S]`` batch (the
     same on every rank of the group) and returns the logits of this rank's token slice as
@@ -177,6 +198,14 @@ class TensorParallelLM(nn.Module):
         off, n = self._slice(flat.numel())
         return flat[off:off + n].unsqueeze(0)
 
+    def gather_tokens(self, local_values: Tensor, shape) -> Tensor:
+        """Per-token values of this rank's slice -> the values of all ``B*S`` tokens, reshaped to
+        ``shape`` (differentiable; used for sequence-level objectives such as DPO / GRPO)."""
+        flat = local_values.reshape(-1)
+        if self.info.ws > 1:
+            flat = _GatherTokens.apply(flat, self.info)
+        return flat.view(shape)
+
     def loss_weight(self, local_targets: Tensor, ignore_index: int = -100) -> Tensor:
         """Factor that turns this rank's mean loss into its share of the global mean:
         ``n_local * ws / n_global`` (the executor divides by ``ws``)."""
@@ -193,7 +222,8 @@ class TensorParallelLM(nn.Module):
 
     def forward(self, input_ids: Tensor, input_mask: Optional[Tensor] = None, paged_cache=None,
                 position_ids: Optional[Tensor] = None, logits_rows: Optional[Tensor] = None) -> Dict[str, Tensor]:
-        if paged_cache is not None or position_ids is not None or input_mask is not None or logits_rows is not None:
+        # like the dense model, a padding mask without explicit positions does not change attention
+        if paged_cache is not None or position_ids is not None or logits_rows is not None:
             raise NotImplementedError("the tensor-parallel training model runs plain causal batches only")
         B, S = input_ids.shape
         off, n = self._slice(B * S)

@@ -51,7 +51,11 @@ def get_logprobs(model, input_ids: Tensor, mask: Tensor, reduction: str) -> Tens
         raise ValueError(f"reduction must be one of ['mean', 'sum', 'none'], got '{reduction}'")
     targets, m = input_ids[:, 1:], mask[:, 1:].to(torch.float32)
     logits = model(input_ids[:, :-1].contiguous(), mask[:, :-1])["logits"]
-    lp = ops.token_logprobs(logits, targets.contiguous()) * m
+    if hasattr(model, "gather_tokens"):  # tensor parallel: logits of this rank's token slice only
+        local = ops.token_logprobs(logits, model.shard_targets(targets.contiguous()))
+        lp = model.gather_tokens(local, targets.shape) * m
+    else:
+        lp = ops.token_logprobs(logits, targets.contiguous()) * m
     if reduction == "none":
         return lp
     total = lp.sum(dim=-1)
