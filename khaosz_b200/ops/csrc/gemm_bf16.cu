@@ -491,6 +491,15 @@ static double tile_cost(int M, int N, int K, int bn, int sms) {
 }  // namespace gemm
 }  // namespace kb
 
+// The split workspace of this device for other GEMM kernels of the library (same stream discipline).
+extern "C" int kb_gemm_split_space(int dev, int sms, float** ws, unsigned int** counters) {
+  kb::gemm::SplitSpace* sp = kb::gemm::split_space(dev, sms);
+  if (!sp) return KB_STATUS_CUDA_ERROR;
+  *ws = sp->ws;
+  *counters = sp->counters;
+  return KB_STATUS_OK;
+}
+
 extern "C" int kb_gemm_bf16_bn(const void* A, const void* B, void* C, const void* R, int M, int N,
                                int K, long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn,
                                int epi, int bn, void* stream) {

@@ -13,6 +13,8 @@
 #include "common.cuh"
 #include "kb_api.h"
 
+extern "C" int kb_gemm_split_space(int dev, int sms, float** ws, unsigned int** counters);
+
 namespace kb {
 namespace w8 {
 
@@ -36,7 +38,22 @@ struct Params {
   const float* scale;  // [N]
   int M, N, K;
   int* err;
+  // split-K for problems with fewer tiles than SMs (decode): every tile is cut into `split` K
+  // slices; a slice parks its fp32 accumulator in the workspace and the last slice of a tile to
+  // arrive sums them in slice order and finishes the tile (same scheme as gemm_bf16.cu)
+  int split;
+  float* ws;
+  unsigned int* counters;
 };
+
+__device__ __forceinline__ void unit_of(const Params& p, int u, int num_k, int& tile, int& kb0, int& kb1, int& slice) {
+  if (p.split <= 1) { tile = u; kb0 = 0; kb1 = num_k; slice = 0; return; }
+  tile = u / p.split;
+  slice = u - tile * p.split;
+  const int per = (num_k + p.split - 1) / p.split;
+  kb0 = slice * per;
+  kb1 = min(num_k, kb0 + per);
+}
 
 // Four int8 -> four bf16 without integer-to-float conversions: each byte, biased by 128, becomes the
 // low mantissa byte of 2^23 (bit pattern 0x4B0000uu = 8388608 + u), and subtracting 8388736 leaves
@@ -72,7 +89,7 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN, num_k = (p.K + BK - 1) / BK;
-  const int total = num_m * num_n;
+  const int total = num_m * num_n * (p.split > 1 ? p.split : 1);  // work units
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -94,9 +111,11 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   if (warp == 0) {
     if (lane == 0) {
       int s = 0; uint32_t ph = 0; bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      for (int u = blockIdx.x; u < total && ok; u += gridDim.x) {
+        int t, kb0, kb1, slice;
+        unit_of(p, u, num_k, t, kb0, kb1, slice);
         const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;  // m fastest: CTAs of a wave share W tiles in L2
-        for (int kb = 0; kb < num_k; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(&raw_full[s], A_STAGE_BYTES + RAW_STAGE_BYTES);
           tma_load_2d(sA + s * A_STAGE_BYTES, &tmap_x, &raw_full[s], kb * BK, m0);
@@ -109,18 +128,20 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(BM, BN, false, false);
       int s = 0; uint32_t ph = 0; int acc = 0; uint32_t aph = 0; bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      for (int u = blockIdx.x; u < total && ok; u += gridDim.x) {
+        int t, kb0, kb1, slice;
+        unit_of(p, u, num_k, t, kb0, kb1, slice);
         if (!mbar_wait(&tempty[acc], aph ^ 1u, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_k; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&cvt_full[s], ph, abort_flag, p.err, KB_ERR_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES), b_addr = smem_u32(sB + s * B_STAGE_BYTES);
 #pragma unroll
           for (int j = 0; j < BK / UMMA_K; ++j)
             umma_f16(d_tmem, umma_desc_kmajor(a_addr, j * 32), umma_desc_kmajor(b_addr, j * 32), idesc,
-                     (kb | j) != 0 ? 1u : 0u);
+                     (kb > kb0 || j) ? 1u : 0u);
           umma_commit(&empty[s]);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
@@ -133,8 +154,10 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     // ------------------------------- converters -------------------------------
     const int ctid = threadIdx.x - 192;  // 0..127, two weight rows each
     int s = 0; uint32_t ph = 0; bool ok = true;
-    for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-      for (int kb = 0; kb < num_k; ++kb) {
+    for (int u = blockIdx.x; u < total && ok; u += gridDim.x) {
+      int t, kb0, kb1, slice;
+      unit_of(p, u, num_k, t, kb0, kb1, slice);
+      for (int kb = kb0; kb < kb1; ++kb) {
         // raw_full also covers the X tile; the bf16 W tile of this stage is free once `empty`
         // completed, which the producer waited for before refilling raw
         if (!mbar_wait(&raw_full[s], ph, abort_flag, p.err, KB_ERR_TIMEOUT_FULL)) { ok = false; break; }
@@ -166,19 +189,17 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     const int row_in_tile = q * 32 + lane;
     const int epi_tid = threadIdx.x - 64;
     int acc = 0; uint32_t aph = 0; int buf = 0; bool ok = true;
-    for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+    __shared__ int s_last;
+    for (int u = blockIdx.x; u < total && ok; u += gridDim.x) {
+      int t, kb0, kb1, slice;
+      unit_of(p, u, num_k, t, kb0, kb1, slice);
       const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;
       if (!mbar_wait(&tfull[acc], aph, abort_flag, p.err, KB_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / EPI_COLS; ++c) {
+      // one 64-column chunk of fp32 sums -> * scale[n] -> bf16 -> staging -> TMA store
+      auto emit_chunk = [&](int c, const uint32_t (&v)[EPI_COLS]) {
         const int col0 = n0 + c * EPI_COLS;
-        if (col0 >= p.N) break;
-        uint32_t v[EPI_COLS];
-        tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
-        tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
-        tmem_ld_wait();
         if (epi_tid == 0) tma_store_wait_read<NUM_EPI_BUFS - 1>();
         named_barrier_sync(1, 128);
         uint8_t* stage = sEpi + buf * EPI_BUF_BYTES;
@@ -199,6 +220,63 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         named_barrier_sync(1, 128);
         if (epi_tid == 0) { tma_store_2d(&tmap_c, stage, col0, m0); tma_store_commit(); }
         buf ^= 1;
+      };
+      if (p.split <= 1) {
+#pragma unroll 1
+        for (int c = 0; c < BN / EPI_COLS; ++c) {
+          if (n0 + c * EPI_COLS >= p.N) break;
+          uint32_t v[EPI_COLS];
+          tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
+          tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
+          tmem_ld_wait();
+          emit_chunk(c, v);
+        }
+      } else {
+        // workspace layout per slice: [chunk][16-byte group][row]: a warp's accesses are contiguous
+        uint4* mine = reinterpret_cast<uint4*>(p.ws + ((size_t)t * p.split + slice) * (BM * BN)) + row_in_tile;
+#pragma unroll 1
+        for (int c = 0; c < BN / EPI_COLS; ++c) {
+          if (n0 + c * EPI_COLS >= p.N) break;
+          uint32_t v[EPI_COLS];
+          tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
+          tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < EPI_COLS / 4; ++i)
+            __stcg(mine + (size_t)(c * (EPI_COLS / 4) + i) * BM, make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+        }
+        __threadfence();
+        named_barrier_sync(1, 128);
+        if (epi_tid == 0) {
+          const unsigned int prev = atomicAdd(&p.counters[t], 1u);
+          const int last = prev == (unsigned int)(p.split - 1);
+          if (last) p.counters[t] = 0u;  // re-armed for the next launch
+          s_last = last;
+          __threadfence();
+        }
+        named_barrier_sync(1, 128);
+        if (s_last) {
+          const uint4* base = reinterpret_cast<const uint4*>(p.ws + (size_t)t * p.split * (BM * BN)) + row_in_tile;
+#pragma unroll 1
+          for (int c = 0; c < BN / EPI_COLS; ++c) {
+            if (n0 + c * EPI_COLS >= p.N) break;
+            uint32_t v[EPI_COLS];
+#pragma unroll
+            for (int i = 0; i < EPI_COLS; ++i) v[i] = 0u;
+            for (int sl = 0; sl < p.split; ++sl) {
+              const uint4* src = base + (size_t)sl * (BM * BN / 4) + (size_t)c * (EPI_COLS / 4) * BM;
+#pragma unroll
+              for (int i = 0; i < EPI_COLS / 4; ++i) {
+                const uint4 w = __ldcg(src + (size_t)i * BM);
+                v[4 * i + 0] = __float_as_uint(__uint_as_float(v[4 * i + 0]) + __uint_as_float(w.x));
+                v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + __uint_as_float(w.y));
+                v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + __uint_as_float(w.z));
+                v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + __uint_as_float(w.w));
+              }
+            }
+            emit_chunk(c, v);
+          }
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -260,8 +338,18 @@ int kb_gemm_w8(const void* X, const void* Wq, const float* scale, void* C, int M
   if (kb::make_tmap_2d(&tc, C, 2, M, N, ldc * 2, BM, EPI_COLS, true)) return KB_STATUS_TMAP_ERROR;
   Params p;
   p.scale = scale; p.M = M; p.N = N; p.K = K; p.err = kb::error_word(dev);
+  p.split = 1; p.ws = nullptr; p.counters = nullptr;
   const int total = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  gemm_w8_kernel<<<total < sms ? total : sms, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(tx, tw, tc, p);
+  const int num_k = (K + BK - 1) / BK;
+  if (total < sms) {  // skinny problem (decode): K slices put the idle SMs to work on the weight stream
+    int split = sms / total;
+    if (split > 16) split = 16;
+    if (split > num_k / 8) split = num_k / 8;
+    while (split > 1 && (split - 1) * ((num_k + split - 1) / split) >= num_k) --split;  // no empty slice
+    if (split > 1 && kb_gemm_split_space(dev, sms, &p.ws, &p.counters) == KB_STATUS_OK) p.split = split;
+  }
+  const int units = total * p.split;
+  gemm_w8_kernel<<<units < sms ? units : sms, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(tx, tw, tc, p);
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 
