@@ -71,8 +71,12 @@ class GQA(nn.Module):
         projs = (self.q_proj, self.k_proj, self.v_proj)
         if all(type(p) is Linear and p.bias is None for p in projs):
             qkv = ops.multi_linear(x, tuple(p.weight for p in projs))
-        else:  # adapters (LoRA) or biases: keep each projection's own forward
-            qkv = torch.cat([p(x) for p in projs], dim=-1)
+        else:
+            from ...ops.quant import int8_multi_linear
+
+            qkv = int8_multi_linear(x, projs)   # int8 weight-only projections: one GEMM over the stacked rows
+            if qkv is None:  # adapters (LoRA) or biases: keep each projection's own forward
+                qkv = torch.cat([p(x) for p in projs], dim=-1)
         qkv = qkv.view(B, S, H + 2 * Hkv, D)
         if paged_cache is None and attn_mask is None and not self.use_qk_norm and attn_ops.fused_ok(qkv, D):
             ctx = attn_ops.rope_attention_packed(qkv, cs, pos, H, Hkv, causal=causal)

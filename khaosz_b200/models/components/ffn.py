@@ -38,8 +38,12 @@ class MLP(nn.Module):
     def forward(self, x: Tensor, residual: Optional[Tensor] = None) -> Tensor:
         if type(self.gate) is Linear and type(self.up) is Linear:
             gu = ops.multi_linear(x, (self.gate.weight, self.up.weight))
-        else:  # adapters (LoRA): keep each projection's own forward
-            gu = torch.cat([self.gate(x), self.up(x)], dim=-1)
+        else:
+            from ...ops.quant import int8_multi_linear
+
+            gu = int8_multi_linear(x, (self.gate, self.up))
+            if gu is None:  # adapters (LoRA): keep each projection's own forward
+                gu = torch.cat([self.gate(x), self.up(x)], dim=-1)
         return self.down(ops.swiglu(gu), residual)
 
 

@@ -152,7 +152,7 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     }
   } else if (warp >= 6) {
     // ------------------------------- converters -------------------------------
-    const int ctid = threadIdx.x - 192;  // 0..127, two weight rows each
+    const int ctid = threadIdx.x - 192;  // 0..127
     int s = 0; uint32_t ph = 0; bool ok = true;
     for (int u = blockIdx.x; u < total && ok; u += gridDim.x) {
       int t, kb0, kb1, slice;
@@ -163,19 +163,20 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         if (!mbar_wait(&raw_full[s], ph, abort_flag, p.err, KB_ERR_TIMEOUT_FULL)) { ok = false; break; }
         const uint8_t* raw = sRaw + s * RAW_STAGE_BYTES;
         uint8_t* dst = sB + s * B_STAGE_BYTES;
+        // consecutive threads take consecutive 16-byte groups of the raw tile (256 rows x 64 B): the
+        // shared-memory reads are conflict free (a thread-per-row mapping put all lanes of a warp on
+        // the same banks) and a warp writes whole 128-byte rows of the swizzled bf16 tile
 #pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-          const int row = ctid * 2 + rr;
+        for (int it = 0; it < (BN * BK / 16) / 128; ++it) {
+          const int idx = it * 128 + ctid;
+          const int row = idx >> 2, q16 = idx & 3;
+          const uint4 v = *reinterpret_cast<const uint4*>(raw + idx * 16);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+          uint32_t o[8];
 #pragma unroll
-          for (int q16 = 0; q16 < 4; ++q16) {  // 16 int8 -> two 16-byte bf16 chunks
-            const uint4 v = *reinterpret_cast<const uint4*>(raw + row * BK + q16 * 16);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-            uint32_t o[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) cvt4(w[i], o[2 * i], o[2 * i + 1]);
-            *reinterpret_cast<uint4*>(dst + sw128_offset(row, q16 * 2)) = make_uint4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<uint4*>(dst + sw128_offset(row, q16 * 2 + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
-          }
+          for (int i = 0; i < 4; ++i) cvt4(w[i], o[2 * i], o[2 * i + 1]);
+          *reinterpret_cast<uint4*>(dst + sw128_offset(row, q16 * 2)) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(dst + sw128_offset(row, q16 * 2 + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
         }
         fence_proxy_async_smem();
         __syncwarp();

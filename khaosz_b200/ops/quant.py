@@ -60,6 +60,22 @@ class Int8Linear(nn.Module):
         return y if residual is None else y + residual
 
 
+def int8_multi_linear(x: torch.Tensor, mods) -> Optional[torch.Tensor]:
+    """``cat([m(x) for m in mods], -1)`` as ONE int8 GEMM when every module is an ``Int8Linear`` of the
+    same input width (q/k/v, gate/up): the quantised rows and scales are stacked once and cached on
+    the first module.  Returns ``None`` when the modules do not qualify."""
+    mods = list(mods)
+    if not all(type(m) is Int8Linear for m in mods) or len({m.in_dim for m in mods}) != 1:
+        return None
+    first = mods[0]
+    packed = getattr(first, "_packed", None)
+    if packed is None or packed[2] != tuple(id(m) for m in mods):
+        q = torch.cat([m.qweight for m in mods], dim=0).contiguous()
+        sc = torch.cat([m.scale for m in mods], dim=0).contiguous()
+        packed = first._packed = (q, sc, tuple(id(m) for m in mods))
+    return linear_w8(x, packed[0], packed[1])
+
+
 def quantize_model_int8(model: nn.Module, skip=("lm_head",)) -> int:
     """Replace every bias-free ``Linear`` (except ``skip``) by :class:`Int8Linear`; returns the
     number of layers converted."""

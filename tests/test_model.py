@@ -222,3 +222,18 @@ def test_int8_weight_only_model_close_to_full_precision():
     assert n == 2 * 7 and isinstance(model.layers[0].attention.q_proj, Int8Linear)
     got = model(ids)["logits"]
     assert (got - ref).abs().max().item() < 0.05 * ref.abs().max().item() + 0.02
+
+
+def test_int8_packed_projections_match_separate_ones():
+    from khaosz_b200.ops.quant import Int8Linear, int8_multi_linear, quantize_model_int8
+
+    torch.manual_seed(0)
+    model = AutoRegressiveLM(tiny_config()).eval()
+    ids = torch.randint(0, 300, (2, 9))
+    quantize_model_int8(model)
+    att = model.layers[0].attention
+    x = torch.randn(2, 9, 32)
+    packed = int8_multi_linear(x, (att.q_proj, att.k_proj, att.v_proj))
+    assert packed is not None and isinstance(att.q_proj, Int8Linear)
+    assert torch.allclose(packed, torch.cat([att.q_proj(x), att.k_proj(x), att.v_proj(x)], -1), atol=1e-5)
+    assert torch.isfinite(model(ids)["logits"]).all()
