@@ -93,7 +93,9 @@ def train(args: argparse.Namespace) -> None:
     window = args.window_size or config.max_len
     dataset = DatasetFactory.load(train_type=args.train_type, load_path=args.data_root_path, window_size=window,
                                   stride=args.stride)
-    total = compute_total_steps(len(dataset), args.n_epoch, args.batch_per_device, args.nprocs, args.grad_accum_steps)
+    # data-parallel replicas: the ranks of one tensor-parallel group read the same samples
+    replicas = max(1, args.nprocs // (args.tp_size or args.nprocs)) if args.parallel_mode == "tp" else args.nprocs
+    total = compute_total_steps(len(dataset), args.n_epoch, args.batch_per_device, replicas, args.grad_accum_steps)
     warmup = min(int(args.warmup_ratio * total), total)
     executor_kwargs = {"gradient_as_bucket_view": True, "broadcast_buffers": False}
     if args.fp8:

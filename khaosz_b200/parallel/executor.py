@@ -462,9 +462,29 @@ class FSDPExecutor(BaseExecutor):
         return sq
 
 
+def _hybrid_groups(tp_size: int):
+    """Process groups of a ``dp x tp`` layout: tensor-parallel groups are runs of ``tp_size``
+    consecutive ranks (same NVLink island), data-parallel groups take one rank of every run.
+    Collective: every rank creates every group, in the same order."""
+    ws, rank = get_world_size(), get_rank()
+    if ws % tp_size:
+        raise ValueError(f"world size {ws} is not a multiple of tp_size {tp_size}")
+    tp_group = dp_group = None
+    for start in range(0, ws, tp_size):
+        g = dist.new_group(list(range(start, start + tp_size)))
+        if start <= rank < start + tp_size:
+            tp_group = g
+    for offset in range(tp_size):
+        g = dist.new_group(list(range(offset, ws, tp_size)))
+        if rank % tp_size == offset:
+            dp_group = g
+    return tp_group, dp_group
+
+
 @ExecutorFactory.register("tp")
 class TPExecutor(BaseExecutor):
-    """Tensor parallelism with sequence-sharded activations over the whole process group.
+    """Tensor parallelism with sequence-sharded activations, optionally combined with data
+    parallelism (``tp_size`` < world size: ``world / tp_size`` replicas of a ``tp_size``-way model).
 
     ``prepare`` rewrites the model into its tensor-parallel form (``khaosz_b200.parallel.tp_model``),
     points the optimizer at the sharded parameters, and makes every rank read the same batches
@@ -482,16 +502,22 @@ class TPExecutor(BaseExecutor):
         super().__init__(grad_accum_steps, fp8, cuda_graph)
         self.tp_size = tp_size
         self.init_sync = init_sync
+        self.tp_group = self.dp_group = None   # None: the tensor-parallel group is the whole world
+        self.dp_size, self.dp_rank = 1, 0
+
+    def _tp_ranks(self) -> int:
+        return self.tp_size if self.tp_group is not None else get_world_size()
 
     def _prepare_model(self, model: nn.Module) -> nn.Module:
         from .tp_model import tensorize
 
         ws = get_world_size()
-        if self.tp_size not in (None, ws):
-            raise NotImplementedError(f"tp_size={self.tp_size}: the tensor-parallel group is the whole world ({ws} ranks)")
+        if self.tp_size not in (None, ws) and ws > 1:
+            self.tp_group, self.dp_group = _hybrid_groups(int(self.tp_size))
+            self.dp_size, self.dp_rank = ws // self.tp_size, get_rank() // self.tp_size
         if self.init_sync:
             _broadcast_parameters(model, None)
-        tp = tensorize(model) if ws > 1 or dist.is_initialized() else model
+        tp = tensorize(model, self.tp_group) if ws > 1 or dist.is_initialized() else model
         if self.flatten_on_cuda and _wants_flat(tp):
             self.flat = FlatParameters(tp, with_grad=True)
         self._model = tp
@@ -501,7 +527,7 @@ class TPExecutor(BaseExecutor):
         model = self._prepare_model(model)
         sampler = getattr(dataloader, "sampler", None)
         if hasattr(sampler, "set_replicas"):
-            sampler.set_replicas(1, 0)
+            sampler.set_replicas(self.dp_size, self.dp_rank)   # the ranks of one model replica read the same data
         if optimizer is not None:
             if len(optimizer.param_groups) != 1:
                 raise NotImplementedError("tp: optimizers with several parameter groups are not re-pointed")
@@ -522,13 +548,22 @@ class TPExecutor(BaseExecutor):
         return model, optimizer, dataloader, scheduler
 
     def _backward_only(self, loss: torch.Tensor) -> None:
-        ws = get_world_size()
-        (loss / ws if ws > 1 else loss).backward()
+        n = self._tp_ranks()
+        (loss / n if n > 1 else loss).backward()
 
     def _sync_gradients(self) -> None:
         reduce = getattr(self._model, "reduce_replicated_grads", None)
         if reduce is not None:
             reduce()
+        if self.dp_group is not None and self.dp_size > 1:   # average over the model replicas
+            if self.flat is not None and self.flat.grad is not None:
+                dist.all_reduce(self.flat.grad, group=self.dp_group)
+                self.flat.grad.div_(self.dp_size)
+            else:
+                for p in self._model.parameters():
+                    if p.grad is not None:
+                        dist.all_reduce(p.grad, group=self.dp_group)
+                        p.grad.div_(self.dp_size)
 
     def unwrap_model(self, model: nn.Module) -> Dict[str, torch.Tensor]:
         full = getattr(model, "full_state_dict", None)

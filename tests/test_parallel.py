@@ -66,14 +66,14 @@ def _make_model():
     return m
 
 
-def _run_steps(mode, world, rank, steps=10, accum=1, fused=True):
+def _run_steps(mode, world, rank, steps=10, accum=1, fused=True, tp_size=None):
     from khaosz_b200.trainer import FusedAdamW, StrategyFactory
 
     g = torch.Generator().manual_seed(3407)
     # global batch = 2 per data-parallel rank; tensor-parallel ranks all read the same 4 sequences
     data = torch.randint(0, 1000, (steps * accum, 4 if mode == "tp" else 2 * world, 129), generator=g)
     model = _make_model()
-    ex = ExecutorFactory.create(mode, grad_accum_steps=accum)
+    ex = ExecutorFactory.create(mode, grad_accum_steps=accum, **({"tp_size": tp_size} if tp_size else {}))
     if fused:
         opt = FusedAdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.01)
     else:
@@ -82,7 +82,11 @@ def _run_steps(mode, world, rank, steps=10, accum=1, fused=True):
     strat = StrategyFactory.create("seq", model, "cpu", label_smoothing=0.05)
     losses = []
     for i in range(steps * accum):
-        mine = data[i] if mode == "tp" else data[i, 2 * rank:2 * rank + 2]
+        if mode == "tp" and tp_size:   # dp x tp: the ranks of one replica share 2 of the 4 sequences
+            replica = rank // tp_size
+            mine = data[i, 2 * replica:2 * replica + 2]
+        else:
+            mine = data[i] if mode == "tp" else data[i, 2 * rank:2 * rank + 2]
         with ex.accumulate(model):
             loss = strat({"input_ids": mine[:, :-1], "target_ids": mine[:, 1:]})
             ex.backward(loss / accum)
@@ -101,8 +105,8 @@ def _run_steps(mode, world, rank, steps=10, accum=1, fused=True):
     return losses, {k: v.detach().clone() for k, v in ex.unwrap_model(model).items()}
 
 
-def _distributed_case(mode, out):
-    losses, sd = _run_steps(mode, dist.get_world_size(), dist.get_rank())
+def _distributed_case(mode, out, tp_size=None):
+    losses, sd = _run_steps(mode, dist.get_world_size(), dist.get_rank(), tp_size=tp_size)
     if dist.get_rank() == 0:
         torch.save({"losses": losses, "sd": sd}, out)
 
@@ -137,6 +141,18 @@ def test_executor_matches_single_process(mode, port, world, tmp_path):
     ref_losses, ref_sd = _single_reference()
     assert got["losses"] == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
     assert got["losses"][-1] < got["losses"][0]
+    for k, v in ref_sd.items():
+        assert torch.allclose(got["sd"][k], v, rtol=1e-3, atol=2e-5), k
+
+
+def test_tensor_parallel_times_data_parallel_matches_single_process(tmp_path):
+    """4 ranks as 2 replicas of a 2-way tensor-parallel model."""
+    out = str(tmp_path / "hybrid.pt")
+    spawn_parallel_fn(_distributed_case, world_size=4, backend="gloo", master_addr="127.0.0.1", master_port="29638",
+                      mode="tp", out=out, tp_size=2)
+    got = torch.load(out)
+    ref_losses, ref_sd = _single_reference()
+    assert got["losses"] == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
     for k, v in ref_sd.items():
         assert torch.allclose(got["sd"][k], v, rtol=1e-3, atol=2e-5), k
 
