@@ -1,12 +1,14 @@
 """Tensor parallelism with sequence-sharded activations (Megatron style) on fused kernels.
 
 Between tensor-parallel regions activations are sharded over the token dimension.  A
-column-parallel layer consumes them through **all-gather -> GEMM** (every rank's TMA producer
-reads the peers' token shards directly over NVLink), a row-parallel layer hands its partial
-sums back through **GEMM -> reduce-scatter** (training / prefill) or **GEMM -> all-reduce**
-(decode); both directions of the backward pass run on the same kernel with MN-major operands.
-On CPU (gloo) the same modules fall back to ``torch.distributed`` collectives, which is also the
-numerical reference in the tests.
+column-parallel layer consumes them through **all-gather -> GEMM** (a copier warp in every CTA
+pulls the peers' token shards once over NVLink into a local image while the tiles of the local
+shard are already being multiplied; the image is kept for the weight gradient), a row-parallel
+layer hands its partial sums back through **GEMM -> reduce-scatter** (training) or
+**GEMM -> all-reduce** (decode); the backward pass runs on the same kernel with MN-major
+operands.  The kernels take their barrier epoch from device memory, so a step that contains
+them can be recorded into a CUDA graph.  On CPU (gloo) the same modules fall back to
+``torch.distributed`` collectives, which is also the numerical reference in the tests.
 
 The reference only ships forward-only ``ColumnParallelLinear`` / ``RowParallelLinear``
 primitives (``astrai/parallel/module.py:18-115``); the class names, weight shapes and the
