@@ -91,6 +91,39 @@ class AccumOptimizer:
         return getattr(self.optimizer, name)
 
 
+class RankStateOptimizer(AccumOptimizer):
+    """Facade for executors whose parameters differ from rank to rank (tensor parallel, fully
+    sharded): ``state_dict`` is collective and returns one optimizer state per rank of the group, so
+    that the single checkpoint rank 0 writes can restore every rank; ``load_state_dict`` picks this
+    rank's entry (a plain state dict is loaded as is)."""
+
+    def __init__(self, optimizer, gradient_state, flat=None, after_step=None, group=None):
+        super().__init__(optimizer, gradient_state, flat, after_step)
+        self.group = group
+
+    def _layout(self):
+        if not (dist.is_available() and dist.is_initialized()):
+            return 0, 1
+        return dist.get_rank(self.group), dist.get_world_size(self.group)
+
+    def state_dict(self):
+        mine = self.optimizer.state_dict()
+        rank, ws = self._layout()
+        if ws == 1:
+            return mine
+        states = [None] * ws
+        dist.all_gather_object(states, mine, group=self.group)
+        return {"per_rank": states}
+
+    def load_state_dict(self, state):
+        if isinstance(state, dict) and "per_rank" in state:
+            rank, ws = self._layout()
+            if len(state["per_rank"]) != ws:
+                raise ValueError(f"checkpoint holds optimizer states of {len(state['per_rank'])} ranks, this group has {ws}")
+            state = state["per_rank"][rank]
+        self.optimizer.load_state_dict(state)
+
+
 class AccumScheduler:
     def __init__(self, scheduler, gradient_state: GradientState):
         self.scheduler = scheduler
@@ -542,7 +575,8 @@ class TPExecutor(BaseExecutor):
                 optimizer.attach_flat(self.flat)
             if hasattr(optimizer, "set_norm_fn") and hasattr(model, "grad_norm_sq"):
                 optimizer.set_norm_fn(model.grad_norm_sq)
-            optimizer = AccumOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step)
+            optimizer = RankStateOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step,
+                                           group=self.tp_group)
         if scheduler is not None:
             scheduler = AccumScheduler(scheduler, self.gradient_state)
         return model, optimizer, dataloader, scheduler

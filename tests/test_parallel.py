@@ -278,3 +278,47 @@ def test_dpo_under_tensor_parallel_matches_single_process(tmp_path):
     # differences of the gradients are amplified: three steps of lr 1e-3 move a weight by up to 3e-3
     for k, v in model.state_dict().items():
         assert torch.allclose(got["sd"][k], v, rtol=1e-3, atol=3e-4), k
+
+
+# ---- optimizer state of a tensor-parallel run survives a checkpoint written by rank 0 ----
+def _tp_opt_state_case(out):
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    def fresh():
+        model = _make_model()
+        ex = ExecutorFactory.create("tp", grad_accum_steps=1)
+        opt = FusedAdamW(model.parameters(), lr=1e-3)
+        model, opt, _, _ = ex.prepare(model, opt, None, None)
+        return model, ex, opt
+
+    model, ex, opt = fresh()
+    strat = StrategyFactory.create("seq", model, "cpu")
+    data = torch.randint(0, 1000, (2, 4, 65), generator=torch.Generator().manual_seed(1))
+    for i in range(2):
+        with ex.accumulate(model):
+            ex.micro_step(strat, {"input_ids": data[i, :, :-1], "target_ids": data[i, :, 1:]})
+            opt.step()
+            opt.zero_grad()
+    state = opt.state_dict()                      # collective: one entry per rank
+    assert len(state["per_rank"]) == dist.get_world_size()
+    saved = [None]
+    if dist.get_rank() == 0:
+        torch.save(state, out)                    # only rank 0 writes, as the checkpoint callback does
+    dist.barrier()
+    state = torch.load(out, weights_only=False)
+    model2, ex2, opt2 = fresh()
+    opt2.load_state_dict(state)
+    a, b = opt.optimizer.state_dict(), opt2.optimizer.state_dict()
+    for i in a["state"]:
+        assert torch.equal(a["state"][i]["exp_avg"], b["state"][i]["exp_avg"]), i
+        assert torch.equal(a["state"][i]["exp_avg_sq"], b["state"][i]["exp_avg_sq"]), i
+    # the two ranks really hold different moments for the sharded weights
+    mine = sum(st["exp_avg"].double().abs().sum() for st in a["state"].values()).float()
+    both = [torch.zeros(()) for _ in range(2)]
+    dist.all_gather(both, mine)
+    assert not torch.equal(both[0], both[1])
+
+
+def test_tensor_parallel_optimizer_state_roundtrip(tmp_path):
+    spawn_parallel_fn(_tp_opt_state_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29639",
+                      out=str(tmp_path / "opt.pt"))
