@@ -20,6 +20,7 @@ import torch
 from .cache import KVCache
 from .executor import Executor
 from .task import STOP, Task, TaskManager, TaskStatus
+from ...utils.trace import trace_range
 
 log = logging.getLogger(__name__)
 
@@ -126,6 +127,16 @@ class InferenceScheduler:
         if task.is_finished(stop_ids):
             self._emit(task, STOP)
 
+    HEALTH_EVERY = 64         # decode steps between two reads of the kernels' error word
+
+    def _check_device(self) -> None:
+        """A bounded wait that ran out inside a kernel leaves a code in the device's error word;
+        surface it as an exception (the loop's fatal-error path then releases every request)."""
+        if torch.device(self.device).type == "cuda":
+            from ...ops import raise_on_device_error
+
+            raise_on_device_error()
+
     PAD_BUCKET = 256          # prompts whose lengths fall into the same bucket are prefilled together
     PAD_BATCH_TOKENS = 32768  # padded tokens per prefill batch at most
 
@@ -151,7 +162,9 @@ class InferenceScheduler:
                 self._accept(t, tok, stop_ids)
 
         for (n, cached), group in groups.items():
-            done(group, self._executor.execute_prefill(group, n, cached), cached)
+            with trace_range("prefill"):
+                first = self._executor.execute_prefill(group, n, cached)
+            done(group, first, cached)
         for bucket, tasks in padded.items():
             per_batch = max(1, self.PAD_BATCH_TOKENS // (bucket * self.PAD_BUCKET))
             for i in range(0, len(tasks), per_batch):
@@ -175,9 +188,12 @@ class InferenceScheduler:
         if not ready:
             return
         t0 = time.perf_counter()
-        tokens = self._executor.execute_decode(ready)
+        with trace_range("decode_step"):
+            tokens = self._executor.execute_decode(ready)
         self._busy_s += time.perf_counter() - t0
         self._steps += 1
+        if self._steps % self.HEALTH_EVERY == 0:
+            self._check_device()
         self._decode_tokens += len(ready)
         for t, tok in zip(ready, tokens):
             self._accept(t, tok, stop_ids)

@@ -63,6 +63,31 @@ class GradientClippingCallback:
             clip_grad_norm_(context.model.parameters(), self.max_grad_norm)
 
 
+@CallbackFactory.register("device_health")
+class DeviceHealthCallback:
+    """Turns a device-side failure into a Python exception at the next optimizer step.
+
+    Every wait inside the kernels is bounded; a wait that runs out (a peer rank that never
+    arrives, a copy that never completes) records a code in a per-device error word and the kernel
+    returns instead of hanging.  This callback reads the word (one 4-byte device-to-host copy per
+    optimizer step) and raises ``KernelError``, which the trainer's error path turns into an
+    emergency checkpoint like any other failure."""
+
+    def __init__(self, check=None):
+        self._check = check
+
+    def on_optimizer_step(self, context):
+        if self._check is None:
+            import torch
+
+            if not torch.cuda.is_available():
+                return
+            from ..ops import raise_on_device_error
+
+            self._check = raise_on_device_error
+        self._check()
+
+
 @CallbackFactory.register("gradient_checkpointing")
 class GradientCheckpointingCallback:
     """Recompute the forward of the listed module types during backward."""

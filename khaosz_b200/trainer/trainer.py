@@ -13,6 +13,7 @@ from typing import List, Optional
 
 from ..config.train_config import TrainConfig
 from ..parallel.setup import spawn_parallel_fn
+from ..utils.trace import trace_range
 from .callbacks import CallbackFactory, TrainCallback
 from .context import TrainContext, TrainContextBuilder
 
@@ -35,6 +36,7 @@ class Trainer:
             make("progress_bar", cfg.n_epoch, log_interval=cfg.log_interval),
             make("gradient_clipping", cfg.max_grad_norm),
             make("validation"),
+            make("device_health"),
         ]
 
     def _call_callbacks(self, hook: str, context: TrainContext) -> None:
@@ -47,7 +49,8 @@ class Trainer:
         executor = context.executor
         with executor.accumulate(context.model):
             if hasattr(executor, "micro_step"):   # forward + backward, optionally as a replayed CUDA graph
-                context.loss = executor.micro_step(context.strategy, batch)
+                with trace_range("micro_step"):
+                    context.loss = executor.micro_step(context.strategy, batch)
             else:
                 loss = context.strategy(batch)
                 context.loss = loss.detach()
@@ -56,8 +59,9 @@ class Trainer:
             self._call_callbacks("on_batch_end", context)
             if executor.sync_gradients:
                 self._call_callbacks("on_optimizer_step", context)
-                context.optimizer.step()
-                context.optimizer.zero_grad()
+                with trace_range("optimizer_step"):
+                    context.optimizer.step()
+                    context.optimizer.zero_grad()
                 if context.scheduler:
                     context.scheduler.step()
 

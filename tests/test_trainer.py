@@ -228,3 +228,33 @@ def test_muon_and_metrics(tiny_model):
     assert set(grad_nan_num(tiny_model).values()) == {0}
     assert set(CallbackFactory.list_registered()) >= {"gradient_clipping", "gradient_checkpointing", "checkpoint",
                                                       "progress_bar", "metric_logger", "validation"}
+
+
+def test_device_health_callback_raises_into_the_error_path():
+    """A device-side error code surfaces at the optimizer step as an exception (fake error word)."""
+    from khaosz_b200.trainer.callbacks import CallbackFactory
+
+    calls = []
+
+    def check():
+        calls.append(1)
+        if len(calls) == 2:
+            raise RuntimeError("device-side kernel error: timeout waiting for a peer flag")
+
+    cb = CallbackFactory.create("device_health", check=check)
+    cb.on_optimizer_step(None)
+    with pytest.raises(RuntimeError, match="peer flag"):
+        cb.on_optimizer_step(None)
+
+
+def test_trace_ranges_are_noops_without_cuda():
+    from khaosz_b200.utils import enable_tracing, trace_range
+
+    enable_tracing(True)
+    try:
+        with trace_range("x"):
+            pass
+    finally:
+        enable_tracing(False)
+    with trace_range("y"):
+        pass
