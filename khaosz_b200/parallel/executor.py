@@ -97,25 +97,63 @@ class RankStateOptimizer(AccumOptimizer):
     that the single checkpoint rank 0 writes can restore every rank; ``load_state_dict`` picks this
     rank's entry (a plain state dict is loaded as is)."""
 
-    def __init__(self, optimizer, gradient_state, flat=None, after_step=None, group=None):
+    def __init__(self, optimizer, gradient_state, flat=None, after_step=None, group=None, model=None):
         super().__init__(optimizer, gradient_state, flat, after_step)
         self.group = group
+        self.model = model   # a model with gather_named / scatter_named makes the state portable
 
     def _layout(self):
         if not (dist.is_available() and dist.is_initialized()):
             return 0, 1
         return dist.get_rank(self.group), dist.get_world_size(self.group)
 
+    def _local_params(self):
+        return [p for g in self.optimizer.param_groups for p in g["params"]]
+
+    def _portable(self, mine) -> bool:
+        st = mine.get("state", {})
+        return (self.model is not None and hasattr(self.model, "gather_named") and len(st) == len(self._local_params())
+                and all(isinstance(v, dict) and set(v) >= {"step", "exp_avg", "exp_avg_sq"} for v in st.values()))
+
     def state_dict(self):
         mine = self.optimizer.state_dict()
         rank, ws = self._layout()
         if ws == 1:
             return mine
+        if self._portable(mine):
+            # Adam-style moments: assemble them to the dense model's parameter order, i.e. the same
+            # optimizer.pt layout a single-process or data-parallel run writes
+            params = self._local_params()
+            by_id = {id(p): mine["state"][i] for i, p in enumerate(params)}
+            full = {}
+            for key in ("exp_avg", "exp_avg_sq"):
+                full[key] = self.model.gather_named(lambda p, k=key: by_id[id(p)][k].to(p.device))
+            step = next(iter(mine["state"].values()))["step"]
+            state = {i: {"step": step, "exp_avg": full["exp_avg"][n].cpu(), "exp_avg_sq": full["exp_avg_sq"][n].cpu()}
+                     for i, n in enumerate(self.model.dense_names)}
+            group = {k: v for k, v in mine["param_groups"][0].items() if k != "params"}
+            group["params"] = list(range(len(self.model.dense_names)))
+            return {"state": state, "param_groups": [group]}
         states = [None] * ws
         dist.all_gather_object(states, mine, group=self.group)
         return {"per_rank": states}
 
     def load_state_dict(self, state):
+        if (isinstance(state, dict) and "per_rank" not in state and self.model is not None
+                and hasattr(self.model, "scatter_named") and self._layout()[1] > 1
+                and len(state.get("state", {})) == len(getattr(self.model, "dense_names", ()))):
+            names = self.model.dense_names
+            get = lambda i: state["state"].get(i) or state["state"].get(str(i))
+            params = self._local_params()
+            local = {}
+            for key in ("exp_avg", "exp_avg_sq"):
+                sliced = self.model.scatter_named({n: get(i)[key] for i, n in enumerate(names)})
+                for j, p in enumerate(params):
+                    local.setdefault(j, {"step": get(0)["step"]})[key] = sliced[id(p)].contiguous()
+            group = dict(state["param_groups"][0])
+            group["params"] = list(range(len(params)))
+            self.optimizer.load_state_dict({"state": local, "param_groups": [group]})
+            return
         if isinstance(state, dict) and "per_rank" in state:
             rank, ws = self._layout()
             if len(state["per_rank"]) != ws:
@@ -576,7 +614,7 @@ class TPExecutor(BaseExecutor):
             if hasattr(optimizer, "set_norm_fn") and hasattr(model, "grad_norm_sq"):
                 optimizer.set_norm_fn(model.grad_norm_sq)
             optimizer = RankStateOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step,
-                                           group=self.tp_group)
+                                           group=self.tp_group, model=model)
         if scheduler is not None:
             scheduler = AccumScheduler(scheduler, self.gradient_state)
         return model, optimizer, dataloader, scheduler

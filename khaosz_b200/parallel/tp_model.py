@@ -179,6 +179,8 @@ class TensorParallelLM(nn.Module):
         super().__init__()
         self.info = TPInfo(group)
         self.config = model.config
+        # parameter names of the dense model in optimizer order (checkpoint layout of the moments)
+        self.dense_names = [n for n, _ in model.named_parameters()]
         self.rotary_embedding = model.rotary_embedding
         self.embed_tokens = model.embed_tokens
         self.layers = nn.ModuleList(TPBlock(b, self.info) for b in model.layers)
@@ -318,10 +320,38 @@ class TensorParallelLM(nn.Module):
     def full_state_dict(self, grads: bool = False) -> Dict[str, Tensor]:
         """State dict with the reference's names and full shapes, identical on every rank
         (collective).  ``grads=True`` assembles the gradients the same way (tests)."""
+        return self.gather_named(lambda p: (p.grad if grads else p.data).detach())
 
-        def val(p):
-            return (p.grad if grads else p.data).detach()
+    @torch.no_grad()
+    def scatter_named(self, full: Dict[str, Tensor]) -> Dict[int, Tensor]:
+        """Inverse of ``gather_named``: this rank's slices of full, dense-named tensors, keyed by
+        ``id`` of the local parameter they belong to (optimizer moments from a dense checkpoint)."""
+        r = self.info.rank
+        out: Dict[int, Tensor] = {id(self.embed_tokens.weight): full["embed_tokens.weight"]}
+        for i, layer in enumerate(self.layers):
+            att, mlp = layer.attention, layer.mlp
+            pre = f"layers.{i}."
+            D, hl, kl, kv0 = att.head_dim, att.h_local, att.kv_local, att.kv_first
+            out[id(att.qkv_weight)] = torch.cat([
+                full[pre + "attention.q_proj.weight"][r * hl * D:(r + 1) * hl * D],
+                full[pre + "attention.k_proj.weight"][kv0 * D:(kv0 + kl) * D],
+                full[pre + "attention.v_proj.weight"][kv0 * D:(kv0 + kl) * D]], dim=0)
+            out[id(att.o_weight)] = full[pre + "attention.o_proj.weight"][:, r * hl * D:(r + 1) * hl * D]
+            fl = mlp.ffn_local
+            out[id(mlp.gate_up_weight)] = torch.cat([full[pre + "mlp.gate.weight"][r * fl:(r + 1) * fl],
+                                                     full[pre + "mlp.up.weight"][r * fl:(r + 1) * fl]], dim=0)
+            out[id(mlp.down_weight)] = full[pre + "mlp.down.weight"][:, r * fl:(r + 1) * fl]
+            out[id(layer.input_norm.weight)] = full[pre + "input_norm.weight"]
+            out[id(layer.post_attention_norm.weight)] = full[pre + "post_attention_norm.weight"]
+        out[id(self.norm.weight)] = full["norm.weight"]
+        if not getattr(self.config, "tie_weight", False):
+            out[id(self.lm_head.weight)] = full["lm_head.weight"]
+        return out
 
+    @torch.no_grad()
+    def gather_named(self, val) -> Dict[str, Tensor]:
+        """``val(param)`` (a tensor shaped like the local parameter: its data, gradient, an
+        optimizer moment) assembled to the dense model's names and shapes on every rank."""
         sd: Dict[str, Tensor] = {"embed_tokens.weight": val(self.embed_tokens.weight).clone()}
         for i, layer in enumerate(self.layers):
             att, mlp = layer.attention, layer.mlp

@@ -299,9 +299,9 @@ def _tp_opt_state_case(out):
             ex.micro_step(strat, {"input_ids": data[i, :, :-1], "target_ids": data[i, :, 1:]})
             opt.step()
             opt.zero_grad()
-    state = opt.state_dict()                      # collective: one entry per rank
-    assert len(state["per_rank"]) == dist.get_world_size()
-    saved = [None]
+    state = opt.state_dict()                      # collective: the dense model's optimizer.pt layout
+    dense_shapes = [tuple(p.shape) for p in _make_model().parameters()]
+    assert [tuple(state["state"][i]["exp_avg"].shape) for i in range(len(dense_shapes))] == dense_shapes
     if dist.get_rank() == 0:
         torch.save(state, out)                    # only rank 0 writes, as the checkpoint callback does
     dist.barrier()
