@@ -107,6 +107,8 @@ class FullShardLM(nn.Module):
         super().__init__()
         self.info = TPInfo(group)
         self.config = model.config
+        # parameter names of the dense model in optimizer order (checkpoint layout of the moments)
+        self.dense_names = [n for n, _ in model.named_parameters()]
         self.rotary_embedding = model.rotary_embedding
         self.embed_tokens = model.embed_tokens
         self.layers = nn.ModuleList(ShardedBlock(b, self.info) for b in model.layers)
@@ -173,26 +175,59 @@ class FullShardLM(nn.Module):
     @torch.no_grad()
     def full_state_dict(self) -> Dict[str, Tensor]:
         """Unsharded state dict with the reference's names, identical on every rank (collective)."""
-        sd: Dict[str, Tensor] = {"embed_tokens.weight": self.embed_tokens.weight.detach().clone()}
+        return self.gather_named(lambda p: p.detach())
+
+    @torch.no_grad()
+    def gather_named(self, val) -> Dict[str, Tensor]:
+        """``val(param)`` (shaped like the local parameter: data, gradient, optimizer moment)
+        assembled to the dense model's names and shapes on every rank."""
+        sd: Dict[str, Tensor] = {"embed_tokens.weight": val(self.embed_tokens.weight).clone()}
         for i, layer in enumerate(self.layers):
             att, mlp = layer.attention, layer.mlp
             pre = f"layers.{i}."
             D, H, Hkv = att.head_dim, att.n_heads, att.n_kv_heads
-            qkv = self._gather_rows(att.qkv_shard.detach())
+            qkv = self._gather_rows(val(att.qkv_shard))
             sd[pre + "attention.q_proj.weight"] = qkv[: H * D].clone()
             sd[pre + "attention.k_proj.weight"] = qkv[H * D:(H + Hkv) * D].clone()
             sd[pre + "attention.v_proj.weight"] = qkv[(H + Hkv) * D:].clone()
-            sd[pre + "attention.o_proj.weight"] = self._gather_rows(att.o_shard.detach())
-            gu = self._gather_rows(mlp.gate_up_shard.detach())
+            sd[pre + "attention.o_proj.weight"] = self._gather_rows(val(att.o_shard))
+            gu = self._gather_rows(val(mlp.gate_up_shard))
             sd[pre + "mlp.gate.weight"] = gu[: mlp.ffn].clone()
             sd[pre + "mlp.up.weight"] = gu[mlp.ffn:].clone()
-            sd[pre + "mlp.down.weight"] = self._gather_rows(mlp.down_shard.detach())
-            sd[pre + "input_norm.weight"] = layer.input_norm.weight.detach().clone()
-            sd[pre + "post_attention_norm.weight"] = layer.post_attention_norm.weight.detach().clone()
-        sd["norm.weight"] = self.norm.weight.detach().clone()
+            sd[pre + "mlp.down.weight"] = self._gather_rows(val(mlp.down_shard))
+            sd[pre + "input_norm.weight"] = val(layer.input_norm.weight).clone()
+            sd[pre + "post_attention_norm.weight"] = val(layer.post_attention_norm.weight).clone()
+        sd["norm.weight"] = val(self.norm.weight).clone()
         if not getattr(self.config, "tie_weight", False):
-            sd["lm_head.weight"] = self.lm_head.weight.detach().clone()
+            sd["lm_head.weight"] = val(self.lm_head.weight).clone()
         return sd
+
+    @torch.no_grad()
+    def scatter_named(self, full: Dict[str, Tensor]) -> Dict[int, Tensor]:
+        """Inverse of ``gather_named``: this rank's row shards of full, dense-named tensors, keyed by
+        ``id`` of the local parameter (optimizer moments from a dense checkpoint)."""
+        r, ws = self.info.rank, self.info.ws
+
+        def rows(t: Tensor) -> Tensor:
+            per = t.shape[0] // ws
+            return t[r * per:(r + 1) * per]
+
+        out: Dict[int, Tensor] = {id(self.embed_tokens.weight): full["embed_tokens.weight"]}
+        for i, layer in enumerate(self.layers):
+            att, mlp = layer.attention, layer.mlp
+            pre = f"layers.{i}."
+            out[id(att.qkv_shard)] = rows(torch.cat([full[pre + "attention.q_proj.weight"],
+                                                     full[pre + "attention.k_proj.weight"],
+                                                     full[pre + "attention.v_proj.weight"]], dim=0))
+            out[id(att.o_shard)] = rows(full[pre + "attention.o_proj.weight"])
+            out[id(mlp.gate_up_shard)] = rows(torch.cat([full[pre + "mlp.gate.weight"], full[pre + "mlp.up.weight"]], dim=0))
+            out[id(mlp.down_shard)] = rows(full[pre + "mlp.down.weight"])
+            out[id(layer.input_norm.weight)] = full[pre + "input_norm.weight"]
+            out[id(layer.post_attention_norm.weight)] = full[pre + "post_attention_norm.weight"]
+        out[id(self.norm.weight)] = full["norm.weight"]
+        if not getattr(self.config, "tie_weight", False):
+            out[id(self.lm_head.weight)] = full["lm_head.weight"]
+        return out
 
 
 def full_shard(model, group=None) -> FullShardLM:

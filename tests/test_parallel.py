@@ -281,12 +281,12 @@ def test_dpo_under_tensor_parallel_matches_single_process(tmp_path):
 
 
 # ---- optimizer state of a tensor-parallel run survives a checkpoint written by rank 0 ----
-def _tp_opt_state_case(out):
+def _tp_opt_state_case(out, mode="tp"):
     from khaosz_b200.trainer import FusedAdamW, StrategyFactory
 
     def fresh():
         model = _make_model()
-        ex = ExecutorFactory.create("tp", grad_accum_steps=1)
+        ex = ExecutorFactory.create(mode, grad_accum_steps=1)
         opt = FusedAdamW(model.parameters(), lr=1e-3)
         model, opt, _, _ = ex.prepare(model, opt, None, None)
         return model, ex, opt
@@ -295,8 +295,9 @@ def _tp_opt_state_case(out):
     strat = StrategyFactory.create("seq", model, "cpu")
     data = torch.randint(0, 1000, (2, 4, 65), generator=torch.Generator().manual_seed(1))
     for i in range(2):
+        mine = data[i] if mode == "tp" else data[i, 2 * dist.get_rank():2 * dist.get_rank() + 2]
         with ex.accumulate(model):
-            ex.micro_step(strat, {"input_ids": data[i, :, :-1], "target_ids": data[i, :, 1:]})
+            ex.micro_step(strat, {"input_ids": mine[:, :-1], "target_ids": mine[:, 1:]})
             opt.step()
             opt.zero_grad()
     state = opt.state_dict()                      # collective: the dense model's optimizer.pt layout
@@ -319,6 +320,7 @@ def _tp_opt_state_case(out):
     assert not torch.equal(both[0], both[1])
 
 
-def test_tensor_parallel_optimizer_state_roundtrip(tmp_path):
-    spawn_parallel_fn(_tp_opt_state_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29639",
-                      out=str(tmp_path / "opt.pt"))
+@pytest.mark.parametrize("mode,port", [("tp", "29639"), ("fsdp_full", "29640")])
+def test_sharded_optimizer_state_roundtrip(mode, port, tmp_path):
+    spawn_parallel_fn(_tp_opt_state_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port=port,
+                      out=str(tmp_path / "opt.pt"), mode=mode)
