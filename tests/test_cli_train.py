@@ -54,3 +54,21 @@ def test_cli_trains_fully_sharded_on_two_cpu_ranks(tmp_path):
 def test_cli_trains_single_process(tmp_path):
     ck = _run(tmp_path, "none", 1, 29654)
     assert "lm_head.weight" in ck.state_dict
+
+
+def test_checkpoint_of_a_tensor_parallel_run_resumes_in_a_single_process(tmp_path):
+    """Weights and optimizer state written by a 2-rank tensor-parallel run load into a dense run."""
+    _run(tmp_path, "tp", 2, 29655)
+    first = tmp_path / "ckpt_tp"
+    ckpt_dir = first / sorted(os.listdir(first))[-1]
+    assert (ckpt_dir / "optimizer.pt").exists()
+    state = torch.load(ckpt_dir / "optimizer.pt", weights_only=False)
+    assert state["state"][1]["exp_avg"].shape == (64, 64)       # layers.0.attention.q_proj: full shape
+    out = tmp_path / "ckpt_resumed"
+    args = train_cli.parse_args([
+        "--train_type", "seq", "--data_root_path", str(tmp_path / "data"), "--param_path", str(ckpt_dir),
+        "--ckpt_dir", str(out), "--batch_per_device", "2", "--grad_accum_steps", "2", "--window_size", "32",
+        "--num_workers", "0", "--no_pin_memory", "--nprocs", "1", "--parallel_mode", "none", "--backend", "gloo",
+        "--device_type", "cpu", "--master_addr", "127.0.0.1", "--master_port", "29656", "--ckpt_interval", "1000000"])
+    train_cli.train(args)
+    assert os.listdir(out)
