@@ -57,6 +57,7 @@ class TaskManager:
         self._total_tokens = 0
         self._ttft: List[float] = []
         self._latency: List[float] = []
+        self._itl: List[float] = []   # mean inter-token latency of each finished request
 
     def add_task(self, prompt, max_tokens: Optional[int] = None, temperature: float = 1.0, top_p: float = 1.0,
                  top_k: int = 50, stream_callback: Optional[Callable] = None) -> str:
@@ -98,6 +99,7 @@ class TaskManager:
 
         with self._lock:
             return {"ttft_p50_s": pct(self._ttft, 0.5), "ttft_p99_s": pct(self._ttft, 0.99),
+                    "itl_p50_s": pct(self._itl, 0.5), "itl_p99_s": pct(self._itl, 0.99),
                     "latency_p50_s": pct(self._latency, 0.5), "finished": len(self._latency)}
 
     def remove_finished_tasks(self, stop_ids: List[int]) -> List[Task]:
@@ -114,6 +116,8 @@ class TaskManager:
                     self._latency.append(now - t.arrival_time)
                     if t.first_token_time is not None:
                         self._ttft.append(t.first_token_time - t.arrival_time)
+                        if t.output_tokens > 1:
+                            self._itl.append((now - t.first_token_time) / (t.output_tokens - 1))
                     done.append(t)
             self.active_tasks = [t for t in self.active_tasks
                                  if t.status not in (TaskStatus.FINISHED, TaskStatus.ABORTED)]
