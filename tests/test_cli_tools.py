@@ -1,0 +1,45 @@
+"""Smoke tests of the command-line tools on CPU with a tiny saved model and tokenizer."""
+import json
+import shutil
+
+import pytest
+import torch
+
+from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
+
+
+@pytest.fixture
+def param_dir(tmp_path, tokenizer_dir, tokenizer):
+    d = tmp_path / "params"
+    shutil.copytree(tokenizer_dir, d)
+    cfg = AutoRegressiveLMConfig(vocab_size=len(tokenizer), dim=32, n_layers=2, norm_eps=1e-5, dim_ffn=64, tie_weight=False,
+                                 max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2)
+    torch.manual_seed(0)
+    AutoRegressiveLM(cfg).save_pretrained(str(d))
+    return d
+
+
+def test_generate_cli_writes_one_response_per_question(param_dir, tmp_path):
+    from khaosz_b200.cli import generate
+
+    src, dst = tmp_path / "q.jsonl", tmp_path / "a.jsonl"
+    src.write_text("\n".join(json.dumps({"question": q}) for q in ("hello world", "the quick brown fox")) + "\n")
+    a = generate.parse_args(["--param_path", str(param_dir), "--input_json_file", str(src), "--output_json_file", str(dst),
+                             "--max_tokens", "4", "--batch_size", "2", "--device", "cpu", "--top_k", "1"])
+    generate.run(a)
+    rows = [json.loads(l) for l in dst.read_text().splitlines() if l.strip()]
+    assert len(rows) == 2 and all("response" in r and "question" in r for r in rows)
+
+
+def test_perplexity_cli_reports_finite_values(param_dir, tmp_path):
+    from khaosz_b200.cli import perplexity
+
+    src, dst = tmp_path / "t.jsonl", tmp_path / "p.jsonl"
+    src.write_text("\n".join(json.dumps({"text": t}) for t in ("hello world this is a test", "the lazy dog")) + "\n")
+    a = perplexity.parse_args(["--param_path", str(param_dir), "--input_file", str(src), "--output_file", str(dst),
+                               "--batch_size", "2", "--device", "cpu"])
+    perplexity.run(a)
+    rows = [json.loads(l) for l in dst.read_text().splitlines() if l.strip()]
+    assert len(rows) == 2
+    vals = [v for r in rows for v in r.values() if isinstance(v, float)]
+    assert vals and all(v == v and v > 0 for v in vals)
