@@ -1,5 +1,6 @@
-from .callbacks import (CallbackFactory, CheckpointCallback, GradientCheckpointingCallback, GradientClippingCallback,
-                        MetricLoggerCallback, ProgressBarCallback, TrainCallback, ValidationCallback)
+from .callbacks import (CallbackFactory, CheckpointCallback, DeviceHealthCallback, GradientCheckpointingCallback,
+                        GradientClippingCallback, MetricLoggerCallback, ProgressBarCallback, ThroughputCallback,
+                        TrainCallback, ValidationCallback)
 from .context import TrainContext, TrainContextBuilder
 from .optim import FusedAdamW, Muon
 from .schedule import BaseScheduler, CosineScheduler, SchedulerFactory, SGDRScheduler
@@ -7,7 +8,7 @@ from .strategy import (BaseStrategy, DPOStrategy, GRPOStrategy, SEQStrategy, SFT
                        create_ref_model, get_logprobs)
 from .trainer import Trainer
 
-__all__ = ["CallbackFactory", "CheckpointCallback", "GradientCheckpointingCallback", "GradientClippingCallback",
+__all__ = ["CallbackFactory", "CheckpointCallback", "DeviceHealthCallback", "ThroughputCallback", "GradientCheckpointingCallback", "GradientClippingCallback",
            "MetricLoggerCallback", "ProgressBarCallback", "TrainCallback", "ValidationCallback", "TrainContext",
            "TrainContextBuilder", "FusedAdamW", "Muon", "BaseScheduler", "CosineScheduler", "SchedulerFactory",
            "SGDRScheduler", "BaseStrategy", "DPOStrategy", "GRPOStrategy", "SEQStrategy", "SFTStrategy",

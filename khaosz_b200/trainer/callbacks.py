@@ -88,6 +88,71 @@ class DeviceHealthCallback:
         self._check()
 
 
+_TOKEN_KEYS = ("input_ids", "chosen", "rejected", "prompts", "responses")
+
+
+def batch_tokens(batch) -> int:
+    """Tokens in one micro-batch of any of the dataset layouts (seq / sft / dpo / grpo)."""
+    if torch.is_tensor(batch):
+        return batch.numel()
+    if isinstance(batch, dict):
+        return sum(v.numel() for k, v in batch.items() if k in _TOKEN_KEYS and torch.is_tensor(v))
+    return 0
+
+
+@CallbackFactory.register("throughput")
+class ThroughputCallback:
+    """Step time and whole-job tokens per second, published as ``context.kwargs["step_ms"]`` and
+    ``context.kwargs["tokens_per_s"]`` (the ``step_ms`` / ``tokens_per_s`` metrics read them).
+
+    On a GPU the step is timed on the device: one CUDA event per optimizer step on the current
+    stream, and the interval between two consecutive events is read once both have completed
+    (``Event.query``), so the host never waits for the device; the published figure therefore lags
+    the running step by one or two steps.  On CPU the host clock is used.  The reference records
+    no throughput (``astrai/trainer/metric_util.py:18-75`` has loss, lr and gradient statistics only)."""
+
+    def __init__(self, clock: Callable[[], float] = time.perf_counter, use_cuda: Optional[bool] = None):
+        self._clock = clock
+        self._use_cuda = use_cuda
+        self._tokens = 0
+        self._marks: List[tuple] = []    # (event or host time, tokens since the previous mark)
+
+    def on_batch_end(self, context):
+        self._tokens += context.kwargs.get("batch_tokens", 0)
+
+    def _replicas(self, context) -> int:
+        sampler = getattr(context.dataloader, "sampler", None)
+        return int(getattr(sampler, "num_replicas", None) or context.world_size or 1)
+
+    def _publish(self, context, seconds: float, tokens: int) -> None:
+        if seconds > 0:
+            context.kwargs["step_ms"] = seconds * 1e3
+            context.kwargs["tokens_per_s"] = tokens * self._replicas(context) / seconds
+
+    def on_optimizer_step(self, context):
+        if self._use_cuda is None:
+            self._use_cuda = torch.cuda.is_available() and get_current_device().type == "cuda"
+        tokens, self._tokens = self._tokens, 0
+        if not self._use_cuda:
+            now = self._clock()
+            if self._marks:
+                self._publish(context, now - self._marks[-1][0], tokens)
+            self._marks = [(now, tokens)]
+            return
+        event = torch.cuda.Event(enable_timing=True)
+        event.record()
+        self._marks.append((event, tokens))
+        # the newest pair of consecutive marks that the device has already passed
+        done = [i for i, (ev, _) in enumerate(self._marks) if ev.query()]
+        if len(done) >= 2:
+            last = done[-1]
+            self._publish(context, self._marks[last - 1][0].elapsed_time(self._marks[last][0]) * 1e-3,
+                          self._marks[last][1])
+            self._marks = self._marks[last:]
+        elif len(self._marks) > 64:          # a device that never catches up: do not grow without bound
+            self._marks = self._marks[-2:]
+
+
 @CallbackFactory.register("gradient_checkpointing")
 class GradientCheckpointingCallback:
     """Recompute the forward of the listed module types during backward."""

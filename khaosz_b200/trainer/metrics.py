@@ -60,5 +60,6 @@ METRICS: Dict[str, Callable] = {
     "grad_min": lambda ctx: grad_min(ctx.model),
     "grad_mean": lambda ctx: grad_mean(ctx.model),
     "grad_nan_num": lambda ctx: grad_nan_num(ctx.model),
-    "tokens_per_s": lambda ctx: ctx.kwargs.get("tokens_per_s", 0.0),
+    "tokens_per_s": lambda ctx: ctx.kwargs.get("tokens_per_s", 0.0),   # set by the throughput callback
+    "step_ms": lambda ctx: ctx.kwargs.get("step_ms", 0.0),
 }

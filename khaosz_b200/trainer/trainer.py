@@ -1,9 +1,9 @@
 """The training loop (reference: ``astrai/trainer/trainer.py:15-109``).
 
 Default callbacks, in order: gradient_checkpointing, checkpoint, metric_logger, progress_bar,
-gradient_clipping, validation; user callbacks run after them.  Any exception triggers the
-``on_error`` hooks (emergency checkpoint, metric flush) and is re-raised; ``on_train_end``
-always runs.
+gradient_clipping, validation, device_health, throughput; user callbacks run after them.  Any
+exception triggers the ``on_error`` hooks (emergency checkpoint, metric flush) and is re-raised;
+``on_train_end`` always runs.
 """
 
 from __future__ import annotations
@@ -14,7 +14,7 @@ from typing import List, Optional
 from ..config.train_config import TrainConfig
 from ..parallel.setup import spawn_parallel_fn
 from ..utils.trace import trace_range
-from .callbacks import CallbackFactory, TrainCallback
+from .callbacks import CallbackFactory, TrainCallback, batch_tokens
 from .context import TrainContext, TrainContextBuilder
 
 log = logging.getLogger(__name__)
@@ -37,6 +37,7 @@ class Trainer:
             make("gradient_clipping", cfg.max_grad_norm),
             make("validation"),
             make("device_health"),
+            make("throughput"),
         ]
 
     def _call_callbacks(self, hook: str, context: TrainContext) -> None:
@@ -47,6 +48,7 @@ class Trainer:
 
     def _micro_step(self, context: TrainContext, batch) -> None:
         executor = context.executor
+        context.kwargs["batch_tokens"] = batch_tokens(batch)
         with executor.accumulate(context.model):
             if hasattr(executor, "micro_step"):   # forward + backward, optionally as a replayed CUDA graph
                 with trace_range("micro_step"):

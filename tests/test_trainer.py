@@ -258,3 +258,28 @@ def test_trace_ranges_are_noops_without_cuda():
         enable_tracing(False)
     with trace_range("y"):
         pass
+
+
+def test_throughput_callback_reports_step_time_and_tokens_per_second(tmp_path):
+    from types import SimpleNamespace
+
+    from khaosz_b200.trainer.callbacks import batch_tokens
+
+    assert batch_tokens({"input_ids": torch.zeros(4, 16), "target_ids": torch.zeros(4, 16)}) == 64
+    assert batch_tokens({"chosen": torch.zeros(2, 8), "rejected": torch.zeros(2, 8), "chosen_mask": torch.zeros(2, 8)}) == 32
+    ticks = iter([10.0, 10.5, 11.5])
+    cb = CallbackFactory.create("throughput", clock=lambda: next(ticks), use_cuda=False)
+    ctx = SimpleNamespace(kwargs={"batch_tokens": 100}, world_size=2,
+                          dataloader=SimpleNamespace(sampler=SimpleNamespace(num_replicas=2)))
+    for _ in range(3):          # three optimizer steps of two micro-batches each
+        cb.on_batch_end(ctx)
+        cb.on_batch_end(ctx)
+        cb.on_optimizer_step(ctx)
+    assert ctx.kwargs["step_ms"] == pytest.approx(1000.0)
+    assert ctx.kwargs["tokens_per_s"] == pytest.approx(200 * 2 / 1.0)
+
+    # through the trainer: the metric log carries both figures
+    Trainer(_config(tmp_path, metrics=["loss", "tokens_per_s", "step_ms"])).train()
+    files = os.listdir(tmp_path / "logs")
+    rows = [json.loads(l) for l in open(tmp_path / "logs" / files[0])]
+    assert rows[-1]["tokens_per_s"] > 0 and rows[-1]["step_ms"] > 0
