@@ -131,7 +131,7 @@ class ThroughputCallback:
 
     def on_optimizer_step(self, context):
         if self._use_cuda is None:
-            self._use_cuda = torch.cuda.is_available() and get_current_device().type == "cuda"
+            self._use_cuda = torch.cuda.is_available() and torch.device(get_current_device()).type == "cuda"
         tokens, self._tokens = self._tokens, 0
         if not self._use_cuda:
             now = self._clock()

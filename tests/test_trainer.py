@@ -283,3 +283,17 @@ def test_throughput_callback_reports_step_time_and_tokens_per_second(tmp_path):
     files = os.listdir(tmp_path / "logs")
     rows = [json.loads(l) for l in open(tmp_path / "logs" / files[0])]
     assert rows[-1]["tokens_per_s"] > 0 and rows[-1]["step_ms"] > 0
+
+
+def test_throughput_callback_device_detection(monkeypatch):
+    from types import SimpleNamespace
+
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setenv("LOCAL_DEVICE", "cpu")       # a CPU rank on a box that has GPUs
+    cb = CallbackFactory.create("throughput")
+    ctx = SimpleNamespace(kwargs={"batch_tokens": 8}, world_size=1, dataloader=None)
+    cb.on_batch_end(ctx)
+    cb.on_optimizer_step(ctx)
+    cb.on_batch_end(ctx)
+    cb.on_optimizer_step(ctx)
+    assert cb._use_cuda is False and ctx.kwargs["tokens_per_s"] > 0
