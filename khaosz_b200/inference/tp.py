@@ -77,12 +77,15 @@ class _Attention(nn.Module):
         super().__init__()
         self.inner = TPAttention(attn, info)   # weight slicing shared with tensor-parallel training
         self.info = info
-        self.qkv8 = self.o8 = None
+        self.qkv8 = self.o8 = self.gate8 = None
 
     def quantize(self) -> None:
         """Weight-only int8 (per output channel of this rank's slices); the bf16 copies are dropped."""
         self.qkv8, self.o8 = _quantize(self.inner.qkv_weight), _quantize(self.inner.o_weight)
         self.inner.qkv_weight = self.inner.o_weight = None
+        if self.inner.use_gate:
+            self.gate8 = _quantize(self.inner.gate_weight)
+            self.inner.gate_weight = None
 
     def forward(self, x: Tensor, rotary, paged_cache, residual: Tensor) -> Tensor:
         a = self.inner
@@ -92,11 +95,16 @@ class _Attention(nn.Module):
         qkv = _local_linear(x, a.qkv_weight, self.qkv8).view(B, S, hl + 2 * kl, D)
         qk = ops.rope(qkv[:, :, : hl + kl], cs, pos)
         q, k, v = qk[:, :, :hl], qk[:, :, hl:], qkv[:, :, hl + kl:]
+        if a.use_qk_norm:
+            q, k = a.q_norm(q), a.k_norm(k)
         if paged_cache is not None:
             ctx = paged_cache.attention(a.layer_id, q, k, v)
         else:
             ctx = attn_ops.attention(q, k, v, causal=True)
-        out = _row_linear(ctx.reshape(B * S, hl * D), a.o_weight, self.o8, self.info)
+        ctx = ctx.reshape(B * S, hl * D)
+        if a.use_gate:
+            ctx = ctx * torch.sigmoid(_local_linear(x, a.gate_weight, self.gate8).view(B * S, hl * D))
+        out = _row_linear(ctx, a.o_weight, self.o8, self.info)
         return out.view(B, S, -1) + residual
 
 

@@ -43,9 +43,15 @@ def _row_shard(w: Tensor, info: TPInfo) -> nn.Parameter:
 class ShardedAttention(nn.Module):
     def __init__(self, attn, info: TPInfo):
         super().__init__()
-        if getattr(attn, "use_qk_norm", False) or getattr(attn, "use_gated_attention", False) or not hasattr(attn, "k_proj"):
-            raise NotImplementedError("full sharding covers plain GQA attention (no qk-norm, gate or MLA)")
+        if not hasattr(attn, "k_proj"):
+            raise NotImplementedError("full sharding covers grouped-query attention (not MLA)")
         self.info = info
+        self.use_qk_norm = bool(getattr(attn, "use_qk_norm", False))
+        self.use_gate = bool(getattr(attn, "use_gated_attention", False))
+        if self.use_qk_norm:          # per-head norm weights: replicated, like the block norms
+            self.q_norm, self.k_norm = attn.q_norm, attn.k_norm
+        if self.use_gate:
+            self.gate_shard = _row_shard(attn.gate.weight, info)
         self.n_heads, self.n_kv_heads, self.head_dim = attn.n_heads, attn.n_kv_heads, attn.head_dim
         self.layer_id = attn.layer_id
         with torch.no_grad():
@@ -59,12 +65,18 @@ class ShardedAttention(nn.Module):
         cs, pos = rotary
         tp = self.info.ctx()
         qkv = sharded_weight_linear(x, self.qkv_shard, tp).view(B, S, H + 2 * Hkv, D)
-        if attn_ops.fused_ok(qkv, D):
+        if not self.use_qk_norm and attn_ops.fused_ok(qkv, D):
             ctx = attn_ops.rope_attention_packed(qkv, cs, pos, H, Hkv, causal=True)
         else:
             qk = ops.rope(qkv[:, :, : H + Hkv], cs, pos)
-            ctx = attn_ops.attention(qk[:, :, :H], qk[:, :, H:], qkv[:, :, H + Hkv:], causal=True)
-        return sharded_weight_linear(ctx.reshape(B, S, H * D), self.o_shard, tp)
+            q, k = qk[:, :, :H], qk[:, :, H:]
+            if self.use_qk_norm:       # after RoPE, as in the dense layer
+                q, k = self.q_norm(q), self.k_norm(k)
+            ctx = attn_ops.attention(q, k, qkv[:, :, H + Hkv:], causal=True)
+        ctx = ctx.reshape(B, S, H * D)
+        if self.use_gate:
+            ctx = ctx * torch.sigmoid(sharded_weight_linear(x, self.gate_shard, tp))
+        return sharded_weight_linear(ctx, self.o_shard, tp)
 
 
 class ShardedMLP(nn.Module):
@@ -191,6 +203,11 @@ class FullShardLM(nn.Module):
             sd[pre + "attention.k_proj.weight"] = qkv[H * D:(H + Hkv) * D].clone()
             sd[pre + "attention.v_proj.weight"] = qkv[(H + Hkv) * D:].clone()
             sd[pre + "attention.o_proj.weight"] = self._gather_rows(val(att.o_shard))
+            if att.use_gate:
+                sd[pre + "attention.gate.weight"] = self._gather_rows(val(att.gate_shard))
+            if att.use_qk_norm:
+                sd[pre + "attention.q_norm.weight"] = val(att.q_norm.weight).clone()
+                sd[pre + "attention.k_norm.weight"] = val(att.k_norm.weight).clone()
             gu = self._gather_rows(val(mlp.gate_up_shard))
             sd[pre + "mlp.gate.weight"] = gu[: mlp.ffn].clone()
             sd[pre + "mlp.up.weight"] = gu[mlp.ffn:].clone()
@@ -220,6 +237,11 @@ class FullShardLM(nn.Module):
                                                      full[pre + "attention.k_proj.weight"],
                                                      full[pre + "attention.v_proj.weight"]], dim=0))
             out[id(att.o_shard)] = rows(full[pre + "attention.o_proj.weight"])
+            if att.use_gate:
+                out[id(att.gate_shard)] = rows(full[pre + "attention.gate.weight"])
+            if att.use_qk_norm:
+                out[id(att.q_norm.weight)] = full[pre + "attention.q_norm.weight"]
+                out[id(att.k_norm.weight)] = full[pre + "attention.k_norm.weight"]
             out[id(mlp.gate_up_shard)] = rows(torch.cat([full[pre + "mlp.gate.weight"], full[pre + "mlp.up.weight"]], dim=0))
             out[id(mlp.down_shard)] = rows(full[pre + "mlp.down.weight"])
             out[id(layer.input_norm.weight)] = full[pre + "input_norm.weight"]

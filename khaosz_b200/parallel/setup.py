@@ -87,6 +87,12 @@ def setup_parallel(rank: int, world_size: int, local_rank: int, backend: str = "
         # A rank that is unwinding an exception must not wait for its peers in a collective
         # tear-down: it has to exit so that the launcher sees the failure and stops the others.
         if not failed and dist.is_initialized():
+            try:
+                # leave together: a rank that closes its transport while a peer still has traffic
+                # in flight (gloo) aborts that peer
+                dist.barrier()
+            except Exception:  # a peer that is already gone must not turn a finished run into a failure
+                pass
             dist.destroy_process_group()
 
 

@@ -75,13 +75,20 @@ def head_partition(n_heads: int, n_kv_heads: int, ws: int, rank: int) -> Tuple[i
 
 
 class TPAttention(nn.Module):
-    """This rank's heads of a grouped-query attention layer."""
+    """This rank's heads of a grouped-query attention layer.
+
+    QK-RMSNorm weights act per head, so they are replicated and their gradients summed over the
+    group like any replicated parameter; the sigmoid output gate (``astrai/model/components/
+    attention.py:32-120``: ``ctx * sigmoid(gate(x))`` before ``o_proj``) is column-parallel with
+    the rows of this rank's query heads."""
 
     def __init__(self, attn, info: TPInfo):
         super().__init__()
-        if getattr(attn, "use_qk_norm", False) or getattr(attn, "use_gated_attention", False) or not hasattr(attn, "k_proj"):
-            raise NotImplementedError("tensor parallelism covers plain GQA attention (no qk-norm, gate or MLA)")
+        if not hasattr(attn, "k_proj"):
+            raise NotImplementedError("tensor parallelism covers grouped-query attention (not MLA)")
         self.info = info
+        self.use_qk_norm = bool(getattr(attn, "use_qk_norm", False))
+        self.use_gate = bool(getattr(attn, "use_gated_attention", False))
         self.layer_id = attn.layer_id
         H, Hkv, D = attn.n_heads, attn.n_kv_heads, attn.head_dim
         self.n_heads, self.n_kv_heads, self.head_dim, self.dim = H, Hkv, D, attn.dim
@@ -94,6 +101,12 @@ class TPAttention(nn.Module):
             v = attn.v_proj.weight[kv0 * D:(kv0 + kl) * D]
             self.qkv_weight = nn.Parameter(torch.cat([q, k, v], dim=0).contiguous())
             self.o_weight = nn.Parameter(attn.o_proj.weight[:, r * hl * D:(r + 1) * hl * D].contiguous())
+            self.gate_weight = None
+            if self.use_gate:
+                self.gate_weight = nn.Parameter(attn.gate.weight[r * hl * D:(r + 1) * hl * D].contiguous())
+                self.gate_weight.tp_sharded = True
+        if self.use_qk_norm:
+            self.q_norm, self.k_norm = attn.q_norm, attn.k_norm
         self.qkv_weight.tp_kv_rows = (hl * D, rep)   # rows from here on are shared by `rep` ranks
         self.qkv_weight.tp_sharded = True
         self.o_weight.tp_sharded = True
@@ -102,12 +115,18 @@ class TPAttention(nn.Module):
         hl, kl, D = self.h_local, self.kv_local, self.head_dim
         cs, pos = rotary
         qkv = _column(x_shard, self.qkv_weight, self.info).view(batch, seq, hl + 2 * kl, D)
-        if attn_ops.fused_ok(qkv, D):
+        if not self.use_qk_norm and attn_ops.fused_ok(qkv, D):
             ctx = attn_ops.rope_attention_packed(qkv, cs, pos, hl, kl, causal=True)
         else:
             qk = ops.rope(qkv[:, :, : hl + kl], cs, pos)
-            ctx = attn_ops.attention(qk[:, :, :hl], qk[:, :, hl:], qkv[:, :, hl + kl:], causal=True)
-        return _row(ctx.reshape(batch * seq, hl * D), self.o_weight, self.info)
+            q, k = qk[:, :, :hl], qk[:, :, hl:]
+            if self.use_qk_norm:       # after RoPE, as in the dense layer
+                q, k = self.q_norm(q), self.k_norm(k)
+            ctx = attn_ops.attention(q, k, qkv[:, :, hl + kl:], causal=True)
+        ctx = ctx.reshape(batch * seq, hl * D)
+        if self.use_gate:
+            ctx = ctx * torch.sigmoid(_column(x_shard, self.gate_weight, self.info))
+        return _row(ctx, self.o_weight, self.info)
 
 
 class TPMLP(nn.Module):
@@ -337,6 +356,11 @@ class TensorParallelLM(nn.Module):
                 full[pre + "attention.k_proj.weight"][kv0 * D:(kv0 + kl) * D],
                 full[pre + "attention.v_proj.weight"][kv0 * D:(kv0 + kl) * D]], dim=0)
             out[id(att.o_weight)] = full[pre + "attention.o_proj.weight"][:, r * hl * D:(r + 1) * hl * D]
+            if att.use_gate:
+                out[id(att.gate_weight)] = full[pre + "attention.gate.weight"][r * hl * D:(r + 1) * hl * D]
+            if att.use_qk_norm:
+                out[id(att.q_norm.weight)] = full[pre + "attention.q_norm.weight"]
+                out[id(att.k_norm.weight)] = full[pre + "attention.k_norm.weight"]
             fl = mlp.ffn_local
             out[id(mlp.gate_up_weight)] = torch.cat([full[pre + "mlp.gate.weight"][r * fl:(r + 1) * fl],
                                                      full[pre + "mlp.up.weight"][r * fl:(r + 1) * fl]], dim=0)
@@ -363,6 +387,11 @@ class TensorParallelLM(nn.Module):
             sd[pre + "attention.k_proj.weight"] = torch.cat([w[hl * D:(hl + kl) * D] for w in owners], dim=0)
             sd[pre + "attention.v_proj.weight"] = torch.cat([w[(hl + kl) * D:] for w in owners], dim=0)
             sd[pre + "attention.o_proj.weight"] = torch.cat(self._gather(val(att.o_weight)), dim=1)
+            if att.use_gate:
+                sd[pre + "attention.gate.weight"] = torch.cat(self._gather(val(att.gate_weight)), dim=0)
+            if att.use_qk_norm:
+                sd[pre + "attention.q_norm.weight"] = val(att.q_norm.weight).clone()
+                sd[pre + "attention.k_norm.weight"] = val(att.k_norm.weight).clone()
             gu = self._gather(val(mlp.gate_up_weight))
             fl = mlp.ffn_local
             sd[pre + "mlp.gate.weight"] = torch.cat([w[:fl] for w in gu], dim=0)

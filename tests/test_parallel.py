@@ -324,3 +324,87 @@ def _tp_opt_state_case(out, mode="tp"):
 def test_sharded_optimizer_state_roundtrip(mode, port, tmp_path):
     spawn_parallel_fn(_tp_opt_state_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port=port,
                       out=str(tmp_path / "opt.pt"), mode=mode)
+
+
+# ---- tensor parallelism with QK-RMSNorm and the sigmoid output gate ----
+def _tp_variant_case(out):
+    from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
+    from khaosz_b200.parallel.tp_model import tensorize
+    from khaosz_b200.trainer import StrategyFactory
+
+    cfg = AutoRegressiveLMConfig(vocab_size=200, dim=64, n_layers=2, norm_eps=1e-5, dim_ffn=128, tie_weight=False,
+                                 max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, use_qk_norm=True,
+                                 use_gated_attention=True)
+    torch.manual_seed(21)
+    dense = AutoRegressiveLM(cfg)
+    with torch.no_grad():   # norm weights away from one, so that their gradients are not trivially alike
+        for name, p in dense.named_parameters():
+            if "norm" in name:
+                p.add_(0.1 * torch.randn_like(p))
+    data = torch.randint(0, 200, (4, 33), generator=torch.Generator().manual_seed(2))
+    batch = {"input_ids": data[:, :-1], "target_ids": data[:, 1:]}
+    ref_loss = StrategyFactory.create("seq", dense, "cpu")(batch)
+    ref_loss.backward()
+    ref = {n: p.grad.clone() for n, p in dense.named_parameters()}
+    dense.zero_grad()
+
+    tp = tensorize(dense)
+    loss = StrategyFactory.create("seq", tp, "cpu")(batch)
+    (loss / dist.get_world_size()).backward()
+    tp.reduce_replicated_grads()
+    got = tp.full_state_dict(grads=True)
+    total = loss.detach().clone()
+    dist.all_reduce(total)
+    weights = tp.full_state_dict()
+    if dist.get_rank() == 0:
+        torch.save({"loss": total.item() / dist.get_world_size(), "ref_loss": ref_loss.item(), "got": got, "ref": ref,
+                    "names": sorted(weights), "dense_names": sorted(n for n, _ in dense.named_parameters())}, out)
+    dist.barrier()
+
+
+@pytest.mark.parametrize("world,port", [(2, "29644"), (4, "29645")])   # 4 ranks: each KV head shared by two ranks
+def test_tensor_parallel_qk_norm_and_gate_match_the_dense_model(world, port, tmp_path):
+    out = str(tmp_path / "variant.pt")
+    spawn_parallel_fn(_tp_variant_case, world_size=world, backend="gloo", master_addr="127.0.0.1", master_port=port, out=out)
+    r = torch.load(out)
+    assert r["loss"] == pytest.approx(r["ref_loss"], rel=1e-4)
+    assert r["names"] == r["dense_names"]
+    for k, v in r["ref"].items():
+        assert torch.allclose(r["got"][k], v, rtol=1e-3, atol=1e-6), k
+
+
+def _fs_variant_case(out):
+    from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
+    from khaosz_b200.parallel.fsdp_model import full_shard
+    from khaosz_b200.trainer import StrategyFactory
+
+    cfg = AutoRegressiveLMConfig(vocab_size=200, dim=64, n_layers=2, norm_eps=1e-5, dim_ffn=128, tie_weight=False,
+                                 max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, use_qk_norm=True,
+                                 use_gated_attention=True)
+    torch.manual_seed(21)
+    dense = AutoRegressiveLM(cfg)
+    data = torch.randint(0, 200, (4, 33), generator=torch.Generator().manual_seed(2))
+    ref_loss = StrategyFactory.create("seq", dense, "cpu")({"input_ids": data[:, :-1], "target_ids": data[:, 1:]})
+    ref_loss.backward()
+    ref = {n: p.grad.clone() for n, p in dense.named_parameters()}
+    dense.zero_grad()
+
+    fs = full_shard(dense)
+    ws, r = dist.get_world_size(), dist.get_rank()
+    mine = data[2 * r:2 * r + 2]                     # data parallel: every rank its own two sequences
+    loss = StrategyFactory.create("seq", fs, "cpu")({"input_ids": mine[:, :-1], "target_ids": mine[:, 1:]})
+    (loss / ws).backward()
+    fs.reduce_replicated_grads()
+    got = fs.gather_named(lambda p: p.grad.detach())
+    if r == 0:
+        torch.save({"got": got, "ref": ref}, out)
+    dist.barrier()   # leave together: a rank that tears gloo down while its peer still writes aborts the peer
+
+
+def test_full_shard_qk_norm_and_gate_match_the_dense_model(tmp_path):
+    out = str(tmp_path / "fs_variant.pt")
+    spawn_parallel_fn(_fs_variant_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29647", out=out)
+    r = torch.load(out)
+    assert sorted(r["got"]) == sorted(r["ref"])
+    for k, v in r["ref"].items():
+        assert torch.allclose(r["got"][k], v, rtol=1e-3, atol=1e-6), k

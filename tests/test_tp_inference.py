@@ -129,3 +129,30 @@ def test_server_engine_factory_goes_tensor_parallel(tmp_path, tokenizer_dir, tok
             want.append(nxt)
             ids = torch.cat([ids, torch.tensor([[nxt]])], dim=1)
     assert text == "".join(tokenizer.decode([t]) for t in want)
+
+
+def _variant_case(out):
+    """QK-RMSNorm + sigmoid output gate under tensor-parallel serving: same logits as the dense model."""
+    from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
+    from khaosz_b200.inference.tp import TPInferenceLM
+
+    cfg = AutoRegressiveLMConfig(vocab_size=128, dim=64, n_layers=2, norm_eps=1e-5, dim_ffn=128, tie_weight=False,
+                                 max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, use_qk_norm=True,
+                                 use_gated_attention=True)
+    torch.manual_seed(13)
+    dense = AutoRegressiveLM(cfg).eval()
+    ids = torch.randint(0, 128, (2, 12), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = dense(ids)["logits"]
+        got = TPInferenceLM(dense).eval()(ids)["logits"]
+        got8 = TPInferenceLM(dense, int8=True).eval()(ids)["logits"]
+    if dist.get_rank() == 0:
+        torch.save({"err": (got - ref).abs().max().item(),
+                    "err8": (got8 - ref).abs().max().item() / ref.abs().max().item()}, out)
+
+
+def test_tensor_parallel_serving_with_qk_norm_and_gate(tmp_path):
+    out = str(tmp_path / "tp_variant.pt")
+    spawn_parallel_fn(_variant_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29646", out=out)
+    r = torch.load(out)
+    assert r["err"] < 1e-4 and r["err8"] < 0.05
