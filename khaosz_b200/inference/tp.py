@@ -132,7 +132,9 @@ class _Block(nn.Module):
         super().__init__()
         self.input_norm, self.post_attention_norm = block.input_norm, block.post_attention_norm
         self.attention = _Attention(block.attention, info)
-        self.mlp = _MLP(block.mlp, info)
+        # a mixture-of-experts feed-forward stays whole on every rank (activations are replicated)
+        dense = hasattr(block.mlp, "gate") and hasattr(block.mlp, "up") and hasattr(block.mlp, "down")
+        self.mlp = _MLP(block.mlp, info) if dense else block.mlp
 
     def forward(self, x: Tensor, rotary, paged_cache) -> Tensor:
         h = self.attention(self.input_norm(x), rotary, paged_cache, x)
@@ -154,12 +156,14 @@ class TPInferenceLM(nn.Module):
         if int8:
             for layer in self.layers:
                 layer.attention.quantize()
-                layer.mlp.quantize()
+                if hasattr(layer.mlp, "quantize"):
+                    layer.mlp.quantize()
         self.kv_heads_local = self.layers[0].attention.inner.kv_local
         self.executor_cls = DistributedExecutor
         # the decode step is recorded as a CUDA graph only when it contains no library collective
-        # (the int8 row-parallel layers sum their partial results with torch.distributed)
-        self.graph_safe = not int8
+        # (the int8 row-parallel layers sum their partial results with torch.distributed) and no
+        # host read-back (the expert dispatch of a mixture-of-experts layer sizes its groups on the host)
+        self.graph_safe = not int8 and all(isinstance(layer.mlp, _MLP) for layer in self.layers)
         # host-side control channel (collective: every rank builds the model at the same point)
         self.control = None
         if self.info.ws > 1:

@@ -159,7 +159,11 @@ class TPBlock(nn.Module):
         self.input_norm = block.input_norm
         self.post_attention_norm = block.post_attention_norm
         self.attention = TPAttention(block.attention, info)
-        self.mlp = TPMLP(block.mlp, info)
+        # A mixture-of-experts feed-forward acts per token, so it runs unchanged on this rank's token
+        # slice with replicated expert weights (their gradients are summed over the group like the
+        # norm weights'); only the dense SwiGLU MLP is cut into column / row slices.
+        self.dense_mlp = hasattr(block.mlp, "gate") and hasattr(block.mlp, "up") and hasattr(block.mlp, "down")
+        self.mlp = TPMLP(block.mlp, info) if self.dense_mlp else block.mlp
 
     def forward(self, x: Tensor, rotary, batch: int, seq: int) -> Tensor:
         y, x = self.input_norm.fork(x)
@@ -275,9 +279,10 @@ class TensorParallelLM(nn.Module):
         pieces: List[Tensor] = []
         targets: List[Tuple[Tensor, Optional[Tuple[int, int]]]] = []
         for p in self._replicated():
-            if p.grad is not None:
-                pieces.append(p.grad.reshape(-1))
-                targets.append((p.grad, None))
+            if p.grad is None:     # e.g. an expert none of this rank's tokens chose: the peers may hold a gradient
+                p.grad = torch.zeros_like(p)
+            pieces.append(p.grad.reshape(-1))
+            targets.append((p.grad, None))
         for layer in self.layers:
             att = layer.attention
             g = att.qkv_weight.grad
@@ -361,10 +366,14 @@ class TensorParallelLM(nn.Module):
             if att.use_qk_norm:
                 out[id(att.q_norm.weight)] = full[pre + "attention.q_norm.weight"]
                 out[id(att.k_norm.weight)] = full[pre + "attention.k_norm.weight"]
-            fl = mlp.ffn_local
-            out[id(mlp.gate_up_weight)] = torch.cat([full[pre + "mlp.gate.weight"][r * fl:(r + 1) * fl],
-                                                     full[pre + "mlp.up.weight"][r * fl:(r + 1) * fl]], dim=0)
-            out[id(mlp.down_weight)] = full[pre + "mlp.down.weight"][:, r * fl:(r + 1) * fl]
+            if layer.dense_mlp:
+                fl = mlp.ffn_local
+                out[id(mlp.gate_up_weight)] = torch.cat([full[pre + "mlp.gate.weight"][r * fl:(r + 1) * fl],
+                                                         full[pre + "mlp.up.weight"][r * fl:(r + 1) * fl]], dim=0)
+                out[id(mlp.down_weight)] = full[pre + "mlp.down.weight"][:, r * fl:(r + 1) * fl]
+            else:
+                for n, p in mlp.named_parameters():
+                    out[id(p)] = full[pre + "mlp." + n]
             out[id(layer.input_norm.weight)] = full[pre + "input_norm.weight"]
             out[id(layer.post_attention_norm.weight)] = full[pre + "post_attention_norm.weight"]
         out[id(self.norm.weight)] = full["norm.weight"]
@@ -392,11 +401,15 @@ class TensorParallelLM(nn.Module):
             if att.use_qk_norm:
                 sd[pre + "attention.q_norm.weight"] = val(att.q_norm.weight).clone()
                 sd[pre + "attention.k_norm.weight"] = val(att.k_norm.weight).clone()
-            gu = self._gather(val(mlp.gate_up_weight))
-            fl = mlp.ffn_local
-            sd[pre + "mlp.gate.weight"] = torch.cat([w[:fl] for w in gu], dim=0)
-            sd[pre + "mlp.up.weight"] = torch.cat([w[fl:] for w in gu], dim=0)
-            sd[pre + "mlp.down.weight"] = torch.cat(self._gather(val(mlp.down_weight)), dim=1)
+            if layer.dense_mlp:
+                gu = self._gather(val(mlp.gate_up_weight))
+                fl = mlp.ffn_local
+                sd[pre + "mlp.gate.weight"] = torch.cat([w[:fl] for w in gu], dim=0)
+                sd[pre + "mlp.up.weight"] = torch.cat([w[fl:] for w in gu], dim=0)
+                sd[pre + "mlp.down.weight"] = torch.cat(self._gather(val(mlp.down_weight)), dim=1)
+            else:
+                for n, p in mlp.named_parameters():
+                    sd[pre + "mlp." + n] = val(p).clone()
             sd[pre + "input_norm.weight"] = val(layer.input_norm.weight).clone()
             sd[pre + "post_attention_norm.weight"] = val(layer.post_attention_norm.weight).clone()
         sd["norm.weight"] = val(self.norm.weight).clone()

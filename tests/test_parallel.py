@@ -327,14 +327,15 @@ def test_sharded_optimizer_state_roundtrip(mode, port, tmp_path):
 
 
 # ---- tensor parallelism with QK-RMSNorm and the sigmoid output gate ----
-def _tp_variant_case(out):
+def _tp_variant_case(out, moe=False):
     from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
     from khaosz_b200.parallel.tp_model import tensorize
     from khaosz_b200.trainer import StrategyFactory
 
+    ffn = dict(ffn_type="moe", n_routed_experts=4, n_shared_experts=1, n_activated_experts=2) if moe else {}
     cfg = AutoRegressiveLMConfig(vocab_size=200, dim=64, n_layers=2, norm_eps=1e-5, dim_ffn=128, tie_weight=False,
                                  max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, use_qk_norm=True,
-                                 use_gated_attention=True)
+                                 use_gated_attention=True, **ffn)
     torch.manual_seed(21)
     dense = AutoRegressiveLM(cfg)
     with torch.no_grad():   # norm weights away from one, so that their gradients are not trivially alike
@@ -362,10 +363,12 @@ def _tp_variant_case(out):
     dist.barrier()
 
 
-@pytest.mark.parametrize("world,port", [(2, "29644"), (4, "29645")])   # 4 ranks: each KV head shared by two ranks
-def test_tensor_parallel_qk_norm_and_gate_match_the_dense_model(world, port, tmp_path):
+@pytest.mark.parametrize("world,port,moe", [(2, "29644", False), (4, "29645", False),   # 4 ranks: KV heads shared by rank pairs
+                                            (2, "29648", True)])   # mixture of experts: replicated experts on token slices
+def test_tensor_parallel_qk_norm_and_gate_match_the_dense_model(world, port, moe, tmp_path):
     out = str(tmp_path / "variant.pt")
-    spawn_parallel_fn(_tp_variant_case, world_size=world, backend="gloo", master_addr="127.0.0.1", master_port=port, out=out)
+    spawn_parallel_fn(_tp_variant_case, world_size=world, backend="gloo", master_addr="127.0.0.1", master_port=port, out=out,
+                      moe=moe)
     r = torch.load(out)
     assert r["loss"] == pytest.approx(r["ref_loss"], rel=1e-4)
     assert r["names"] == r["dense_names"]

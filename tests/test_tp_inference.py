@@ -146,8 +146,15 @@ def _variant_case(out):
         ref = dense(ids)["logits"]
         got = TPInferenceLM(dense).eval()(ids)["logits"]
         got8 = TPInferenceLM(dense, int8=True).eval()(ids)["logits"]
+    # a mixture-of-experts feed-forward stays whole on every rank; attention is still sliced
+    moe_cfg = AutoRegressiveLMConfig(vocab_size=128, dim=64, n_layers=2, norm_eps=1e-5, dim_ffn=128, tie_weight=False,
+                                     max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, ffn_type="moe",
+                                     n_routed_experts=4, n_shared_experts=1, n_activated_experts=2)
+    moe = AutoRegressiveLM(moe_cfg).eval()
+    with torch.no_grad():
+        err_moe = (TPInferenceLM(moe).eval()(ids)["logits"] - moe(ids)["logits"]).abs().max().item()
     if dist.get_rank() == 0:
-        torch.save({"err": (got - ref).abs().max().item(),
+        torch.save({"err": (got - ref).abs().max().item(), "err_moe": err_moe,
                     "err8": (got8 - ref).abs().max().item() / ref.abs().max().item()}, out)
 
 
@@ -155,4 +162,4 @@ def test_tensor_parallel_serving_with_qk_norm_and_gate(tmp_path):
     out = str(tmp_path / "tp_variant.pt")
     spawn_parallel_fn(_variant_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29646", out=out)
     r = torch.load(out)
-    assert r["err"] < 1e-4 and r["err8"] < 0.05
+    assert r["err"] < 1e-4 and r["err8"] < 0.05 and r["err_moe"] < 1e-4
