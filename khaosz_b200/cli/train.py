@@ -52,6 +52,10 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--gradient_checkpointing", action="store_true", default=False)
     p.add_argument("--ckpt_interval", type=int, default=5000)
     p.add_argument("--ckpt_dir", type=str, default="checkpoint")
+    p.add_argument("--log_dir", type=str, default=None, help="Metric log directory (default: <ckpt_dir>/logs).")
+    p.add_argument("--log_interval", type=int, default=10, help="Record the metrics every this many micro-batches.")
+    p.add_argument("--metrics", type=str, nargs="+", default=["loss", "lr", "tokens_per_s", "step_ms"],
+                   help="Metrics written to the JSONL log (see khaosz_b200.trainer.metrics.METRICS).")
     p.add_argument("--start_epoch", type=int, default=0)
     p.add_argument("--start_batch", type=int, default=0)
     p.add_argument("--master_addr", type=str, default="localhost")
@@ -110,7 +114,8 @@ def train(args: argparse.Namespace) -> None:
                              betas=(args.adamw_beta1, args.adamw_beta2), weight_decay=args.adamw_weight_decay),
         scheduler_fn=partial(SchedulerFactory.create, schedule_type="cosine", warmup_steps=warmup,
                              lr_decay_steps=max(total - warmup, 1)),
-        ckpt_dir=args.ckpt_dir, n_epoch=args.n_epoch, batch_per_device=args.batch_per_device,
+        ckpt_dir=args.ckpt_dir, log_dir=args.log_dir or os.path.join(args.ckpt_dir, "logs"),
+        log_interval=args.log_interval, metrics=args.metrics, n_epoch=args.n_epoch, batch_per_device=args.batch_per_device,
         start_epoch=args.start_epoch, start_batch=args.start_batch, ckpt_interval=args.ckpt_interval,
         grad_accum_steps=args.grad_accum_steps, max_grad_norm=args.max_grad_norm, random_seed=args.random_seed,
         num_workers=args.num_workers, pin_memory=args.pin_memory, nprocs=args.nprocs, backend=args.backend,

@@ -31,8 +31,10 @@ def _run(tmp_path, mode, nprocs, port):
         "--no_pin_memory", "--nprocs", str(nprocs), "--parallel_mode", mode, "--backend", "gloo", "--device_type", "cpu",
         "--master_addr", "127.0.0.1", "--master_port", str(port), "--ckpt_interval", "1000000"])
     train_cli.train(args)
-    dirs = sorted(os.listdir(ckpt))
+    dirs = sorted(d for d in os.listdir(ckpt) if d.startswith("epoch_"))
     assert dirs, "no checkpoint written"
+    rows = [json.loads(line) for f in sorted(os.listdir(ckpt / "logs")) for line in open(ckpt / "logs" / f)]
+    assert rows and {"loss", "lr", "tokens_per_s", "step_ms"} <= set(rows[-1])   # the metric log sits beside the checkpoints
     loaded = Checkpoint.load(str(ckpt / dirs[-1]))
     model = AutoRegressiveLM(cfg)
     model.load_state_dict(loaded.state_dict)      # full names and shapes
@@ -60,7 +62,7 @@ def test_checkpoint_of_a_tensor_parallel_run_resumes_in_a_single_process(tmp_pat
     """Weights and optimizer state written by a 2-rank tensor-parallel run load into a dense run."""
     _run(tmp_path, "tp", 2, 29655)
     first = tmp_path / "ckpt_tp"
-    ckpt_dir = first / sorted(os.listdir(first))[-1]
+    ckpt_dir = first / sorted(d for d in os.listdir(first) if d.startswith("epoch_"))[-1]
     assert (ckpt_dir / "optimizer.pt").exists()
     state = torch.load(ckpt_dir / "optimizer.pt", weights_only=False)
     assert state["state"][1]["exp_avg"].shape == (64, 64)       # layers.0.attention.q_proj: full shape
