@@ -297,3 +297,11 @@ def test_throughput_callback_device_detection(monkeypatch):
     cb.on_batch_end(ctx)
     cb.on_optimizer_step(ctx)
     assert cb._use_cuda is False and ctx.kwargs["tokens_per_s"] > 0
+
+
+def test_iteration_counter_runs_across_epochs(tmp_path):
+    """Two epochs of five micro-batches: the final checkpoint is ``epoch_1_iter_10`` (the counter is
+    global, not per epoch; pinned by the reference's tests/trainer/test_early_stopping.py:46-57)."""
+    Trainer(_config(tmp_path, dataset=RandomTokens(n=20), n_epoch=2, grad_accum_steps=2)).train()
+    final = tmp_path / "ck" / "epoch_1_iter_10"
+    assert json.loads((final / "meta.json").read_text())["iteration"] == 10
