@@ -12,12 +12,13 @@ from typing import Any, Dict, List, Optional, Union
 
 import torch
 import uvicorn
-from fastapi import FastAPI, HTTPException
+from fastapi import FastAPI, HTTPException, Response
 from pydantic import BaseModel, Field
 
 from ...models import AutoModel
 from ...tokenize import AutoTokenizer
 from ..engine import InferenceEngine
+from . import metrics
 from .anthropic import AnthropicResponseBuilder
 from .openai import OpenAIResponseBuilder
 from .protocol import ProtocolHandler
@@ -142,6 +143,13 @@ async def health():
 @app.get("/stats")
 async def get_stats():
     return _get_engine().get_stats()
+
+
+@app.get("/metrics")
+async def get_metrics():
+    """Counters, gauges and the TTFT / inter-token / total latency histograms for a Prometheus scrape."""
+    engine = _get_engine()
+    return Response(content=metrics.render(engine.get_stats(), engine.get_histograms()), media_type=metrics.CONTENT_TYPE)
 
 
 @app.post("/v1/chat/completions")

@@ -74,6 +74,9 @@ class InferenceScheduler:
                       "decode_graphs": sum(1 for s in getattr(self._executor, "_slots", {}).values() if s.graph is not None)})
         return stats
 
+    def get_histograms(self) -> Dict[str, Dict[str, Any]]:
+        return self._task_mgr.histograms()
+
     def start(self) -> None:
         if self._running:
             return

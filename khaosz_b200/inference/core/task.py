@@ -4,6 +4,7 @@ time-to-first-token and finish time so the engine can report latency statistics.
 
 from __future__ import annotations
 
+import bisect
 import threading
 import time
 import uuid
@@ -12,6 +13,31 @@ from enum import Enum
 from typing import Any, Callable, Deque, Dict, List, Optional
 
 STOP = object()  # sentinel pushed through stream callbacks when a task ends
+
+LATENCY_BUCKETS_S = (0.005, 0.01, 0.025, 0.05, 0.1, 0.25, 0.5, 1.0, 2.5, 5.0, 10.0, 30.0, 60.0, 120.0, 300.0)
+RECENT = 65536   # finished requests kept for the percentile figures
+
+
+class Histogram:
+    """Cumulative histogram over fixed upper bounds (the shape a Prometheus scrape expects)."""
+
+    def __init__(self, bounds=LATENCY_BUCKETS_S):
+        self.bounds = tuple(bounds)
+        self.counts = [0] * (len(self.bounds) + 1)   # last slot: above every bound
+        self.total = 0.0
+        self.n = 0
+
+    def observe(self, value: float) -> None:
+        self.counts[bisect.bisect_left(self.bounds, value)] += 1
+        self.total += value
+        self.n += 1
+
+    def snapshot(self) -> Dict[str, Any]:
+        running, cumulative = 0, []
+        for c in self.counts[:-1]:
+            running += c
+            cumulative.append(running)
+        return {"bounds": list(self.bounds), "cumulative": cumulative, "count": self.n, "sum": self.total}
 
 
 class TaskStatus(Enum):
@@ -55,9 +81,10 @@ class TaskManager:
         self._lock = threading.Lock()
         self._total_tasks = 0
         self._total_tokens = 0
-        self._ttft: List[float] = []
-        self._latency: List[float] = []
-        self._itl: List[float] = []   # mean inter-token latency of each finished request
+        self._ttft: Deque[float] = deque(maxlen=RECENT)
+        self._latency: Deque[float] = deque(maxlen=RECENT)
+        self._itl: Deque[float] = deque(maxlen=RECENT)   # mean inter-token latency of each finished request
+        self._hist = {"ttft_seconds": Histogram(), "itl_seconds": Histogram(), "latency_seconds": Histogram()}
 
     def add_task(self, prompt, max_tokens: Optional[int] = None, temperature: float = 1.0, top_p: float = 1.0,
                  top_k: int = 50, stream_callback: Optional[Callable] = None) -> str:
@@ -102,6 +129,12 @@ class TaskManager:
                     "itl_p50_s": pct(self._itl, 0.5), "itl_p99_s": pct(self._itl, 0.99),
                     "latency_p50_s": pct(self._latency, 0.5), "finished": len(self._latency)}
 
+    def histograms(self) -> Dict[str, Dict[str, Any]]:
+        """Time to first token, mean inter-token latency and total latency of every finished request
+        since start, as cumulative histograms."""
+        with self._lock:
+            return {name: h.snapshot() for name, h in self._hist.items()}
+
     def remove_finished_tasks(self, stop_ids: List[int]) -> List[Task]:
         now = time.time()
         with self._lock:
@@ -114,10 +147,14 @@ class TaskManager:
                     t.status, t.finish_time = TaskStatus.FINISHED, now
                     self._total_tokens += t.output_tokens
                     self._latency.append(now - t.arrival_time)
+                    self._hist["latency_seconds"].observe(now - t.arrival_time)
                     if t.first_token_time is not None:
                         self._ttft.append(t.first_token_time - t.arrival_time)
+                        self._hist["ttft_seconds"].observe(t.first_token_time - t.arrival_time)
                         if t.output_tokens > 1:
-                            self._itl.append((now - t.first_token_time) / (t.output_tokens - 1))
+                            itl = (now - t.first_token_time) / (t.output_tokens - 1)
+                            self._itl.append(itl)
+                            self._hist["itl_seconds"].observe(itl)
                     done.append(t)
             self.active_tasks = [t for t in self.active_tasks
                                  if t.status not in (TaskStatus.FINISHED, TaskStatus.ABORTED)]

@@ -173,5 +173,9 @@ class InferenceEngine:
     def get_stats(self) -> Dict[str, Any]:
         return self.scheduler.get_stats()
 
+    def get_histograms(self) -> Dict[str, Dict[str, Any]]:
+        """Latency histograms of the finished requests (``/metrics`` renders them)."""
+        return self.scheduler.get_histograms()
+
     def shutdown(self) -> None:
         self.scheduler.stop()

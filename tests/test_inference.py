@@ -209,6 +209,9 @@ def test_engine_ragged_batch_matches_dense_greedy(engine, tokenizer):
     assert isinstance(engine.generate("hello", max_tokens=3, top_k=1), str)
     stats = engine.get_stats()
     assert stats["total_tasks"] == 6 and stats["active_tasks"] == 0 and stats["ttft_p50_s"] is not None
+    hist = engine.get_histograms()
+    assert hist["latency_seconds"]["count"] == 6 and hist["ttft_seconds"]["count"] == 6
+    assert hist["latency_seconds"]["sum"] >= hist["ttft_seconds"]["sum"] > 0
 
 
 def test_engine_streaming_async_and_request(engine, tokenizer):

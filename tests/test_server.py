@@ -123,3 +123,22 @@ def test_protocol_helpers():
     o = OpenAIResponseBuilder()
     o._resp_id, o._model = "r", "m"
     assert json.loads(o.format_chunk("t")[6:])["created"] == 0
+
+
+def test_metrics_endpoint_serves_prometheus_text(client):
+    from khaosz_b200.inference.core.task import Histogram
+
+    h = Histogram()
+    for v in (0.004, 0.02, 0.02, 7.0, 1000.0):
+        h.observe(v)
+    snap = h.snapshot()
+    assert snap["count"] == 5 and snap["cumulative"][0] == 1 and snap["cumulative"][-1] == 4   # 1000 s is above every bound
+    app.state.engine.get_histograms = lambda: {"ttft_seconds": snap}
+    r = client.get("/metrics")
+    assert r.status_code == 200 and r.headers["content-type"].startswith("text/plain")
+    lines = r.text.splitlines()
+    assert "khaosz_b200_requests_total 1" in lines and "# TYPE khaosz_b200_ttft_seconds histogram" in lines
+    assert 'khaosz_b200_ttft_seconds_bucket{le="0.025"} 3' in lines
+    assert 'khaosz_b200_ttft_seconds_bucket{le="+Inf"} 5' in lines and "khaosz_b200_ttft_seconds_count 5" in lines
+    buckets = [int(l.rsplit(" ", 1)[1]) for l in lines if l.startswith("khaosz_b200_ttft_seconds_bucket")]
+    assert buckets == sorted(buckets)     # cumulative
