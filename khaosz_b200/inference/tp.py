@@ -29,7 +29,7 @@ from torch import Tensor
 from .. import ops
 from ..ops import attention as attn_ops
 from ..parallel.tensor_parallel import TPContext, _RowParallelFn
-from ..parallel.tp_model import TPAttention, TPInfo, TPMLP
+from ..parallel.tp_model import TPAttention, TPInfo, TPMLP, reject_adapters
 from .core.cache import KVCache
 from .core.executor import Executor
 
@@ -147,6 +147,7 @@ class TPInferenceLM(nn.Module):
 
     def __init__(self, model, group=None, int8: bool = False):
         super().__init__()
+        reject_adapters(model, "tensor-parallel serving")
         self.info = TPInfo(group)
         self.config = model.config
         self.rotary_embedding = model.rotary_embedding

@@ -27,7 +27,7 @@ from torch import Tensor
 from .. import ops
 from ..ops import attention as attn_ops
 from .tensor_parallel import sharded_weight_linear
-from .tp_model import TPInfo
+from .tp_model import TPInfo, reject_adapters
 
 
 def _row_shard(w: Tensor, info: TPInfo) -> nn.Parameter:
@@ -257,4 +257,5 @@ def full_shard(model, group=None) -> FullShardLM:
         return model
     if not (hasattr(model, "layers") and hasattr(model, "embed_tokens") and hasattr(model, "lm_head")):
         raise NotImplementedError(f"full sharding is implemented for decoder LMs, not {type(model).__name__}")
+    reject_adapters(model, "full sharding")
     return FullShardLM(model, group)

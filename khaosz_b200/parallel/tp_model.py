@@ -418,6 +418,17 @@ class TensorParallelLM(nn.Module):
         return sd
 
 
+def reject_adapters(model, what: str) -> None:
+    """The sliced / sharded layers are built from the projections' base weights; adapters wrapped
+    around them would be dropped without a trace, so they are refused instead."""
+    from ..models.components.lora import LoRALinear
+
+    wrapped = [name for name, mod in model.named_modules() if isinstance(mod, LoRALinear) and not mod._merged]
+    if wrapped:
+        raise NotImplementedError(f"{what} does not carry LoRA adapters ({len(wrapped)} wrapped layers, e.g. "
+                                  f"{wrapped[0]}): merge them first (merge_lora) or train with none / ddp / fsdp")
+
+
 def tensorize(model, group=None) -> TensorParallelLM:
     """Tensor-parallel form of an ``AutoRegressiveLM`` (weights are sliced from the full model,
     which must hold the same values on every rank)."""
@@ -425,4 +436,5 @@ def tensorize(model, group=None) -> TensorParallelLM:
         return model
     if not (hasattr(model, "layers") and hasattr(model, "embed_tokens") and hasattr(model, "lm_head")):
         raise NotImplementedError(f"tensor parallelism is implemented for decoder LMs, not {type(model).__name__}")
+    reject_adapters(model, "tensor parallelism")
     return TensorParallelLM(model, group)

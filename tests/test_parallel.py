@@ -411,3 +411,17 @@ def test_full_shard_qk_norm_and_gate_match_the_dense_model(tmp_path):
     assert sorted(r["got"]) == sorted(r["ref"])
     for k, v in r["ref"].items():
         assert torch.allclose(r["got"][k], v, rtol=1e-3, atol=1e-6), k
+
+
+def test_sliced_models_refuse_lora_adapters_instead_of_dropping_them():
+    from khaosz_b200 import AutoRegressiveLM
+    from khaosz_b200.models.components.lora import inject_lora, merge_lora
+    from khaosz_b200.parallel.tp_model import reject_adapters
+
+    model = AutoRegressiveLM(_tiny_cfg())
+    reject_adapters(model, "tensor parallelism")          # nothing wrapped: fine
+    inject_lora(model, r=4, alpha=8)
+    with pytest.raises(NotImplementedError, match="LoRA adapters"):
+        reject_adapters(model, "tensor parallelism")
+    merge_lora(model)                                      # merged adapters are plain weights again
+    reject_adapters(model, "tensor parallelism")
