@@ -29,7 +29,7 @@ from torch import Tensor
 from .. import ops
 from ..ops import attention as attn_ops
 from ..parallel.tensor_parallel import TPContext, _RowParallelFn
-from ..parallel.tp_model import TPAttention, TPInfo, TPMLP, reject_adapters
+from ..parallel.tp_model import TPAttention, TPInfo, TPMLAttention, TPMLP, reject_adapters
 from .core.cache import KVCache
 from .core.executor import Executor
 
@@ -108,6 +108,47 @@ class _Attention(nn.Module):
         return out.view(B, S, -1) + residual
 
 
+class _LatentAttention(nn.Module):
+    """Multi-head latent attention: local query heads, the full latent projection, local KV heads."""
+
+    def __init__(self, attn, info: TPInfo):
+        super().__init__()
+        self.inner = TPMLAttention(attn, info)
+        self.info = info
+        self.qa8 = self.kvb8 = self.o8 = self.gate8 = None
+
+    def quantize(self) -> None:
+        a = self.inner
+        self.qa8, self.kvb8, self.o8 = _quantize(a.qa_weight), _quantize(a.kv_b_weight), _quantize(a.o_weight)
+        a.qa_weight = a.kv_b_weight = a.o_weight = None
+        if a.use_gate:
+            self.gate8 = _quantize(a.gate_weight)
+            a.gate_weight = None
+
+    def forward(self, x: Tensor, rotary, paged_cache, residual: Tensor) -> Tensor:
+        a = self.inner
+        B, S, _ = x.shape
+        hl, kl, hd, nope = a.h_local, a.kv_local, a.head_dim, a.nope
+        cs, pos = rotary
+        y = _local_linear(x, a.qa_weight, self.qa8)
+        q = y[..., : hl * hd].reshape(B, S, hl, hd)
+        kv = _local_linear(a.kv_norm(y[..., hl * hd:].contiguous()), a.kv_b_weight, self.kvb8).view(B, S, kl, 2 * hd)
+        q = torch.cat([q[..., :nope], ops.rope(q[..., nope:].contiguous(), cs, pos)], dim=-1)
+        k = torch.cat([kv[..., :nope], ops.rope(kv[..., nope:hd].contiguous(), cs, pos)], dim=-1)
+        v = kv[..., hd:]
+        if a.use_qk_norm:
+            q, k = a.q_norm(q), a.k_norm(k)
+        if paged_cache is not None:
+            ctx = paged_cache.attention(a.layer_id, q, k, v)
+        else:
+            ctx = attn_ops.attention(q, k, v, causal=True)
+        ctx = ctx.reshape(B * S, hl * hd)
+        if a.use_gate:
+            ctx = ctx * torch.sigmoid(_local_linear(x, a.gate_weight, self.gate8).view(B * S, hl * hd))
+        out = _row_linear(ctx, a.o_weight, self.o8, self.info)
+        return out.view(B, S, -1) + residual
+
+
 class _MLP(nn.Module):
     def __init__(self, mlp, info: TPInfo):
         super().__init__()
@@ -131,7 +172,8 @@ class _Block(nn.Module):
     def __init__(self, block, info: TPInfo):
         super().__init__()
         self.input_norm, self.post_attention_norm = block.input_norm, block.post_attention_norm
-        self.attention = _Attention(block.attention, info)
+        latent = hasattr(block.attention, "kv_a_proj")
+        self.attention = (_LatentAttention if latent else _Attention)(block.attention, info)
         # a mixture-of-experts feed-forward stays whole on every rank (activations are replicated)
         dense = hasattr(block.mlp, "gate") and hasattr(block.mlp, "up") and hasattr(block.mlp, "down")
         self.mlp = _MLP(block.mlp, info) if dense else block.mlp

@@ -129,6 +129,65 @@ class TPAttention(nn.Module):
         return _row(ctx, self.o_weight, self.info)
 
 
+class TPMLAttention(nn.Module):
+    """This rank's heads of a multi-head latent attention layer
+    (``astrai/model/components/attention.py:123-212``).
+
+    The rows of ``q_proj`` for the local heads and the whole (narrow) ``kv_a_proj`` form one
+    column-parallel weight, so the latent of every token comes out of the same gathered GEMM on
+    every rank; ``kv_norm`` is replicated and ``kv_b_proj`` keeps the rows of the local KV heads.
+    A rank back-propagates into the latent through its own KV heads only, so the gradient of the
+    ``kv_a_proj`` rows is partial per rank and is summed over the group with the replicated
+    parameters' gradients."""
+
+    def __init__(self, attn, info: TPInfo):
+        super().__init__()
+        self.info = info
+        self.layer_id = attn.layer_id
+        H, Hkv, hd = attn.n_heads, attn.n_kv_heads, attn.head_dim
+        if H % info.ws or Hkv % info.ws:
+            raise ValueError(f"n_heads={H} and n_kv_heads={Hkv} must divide by the tensor-parallel size {info.ws}")
+        self.n_heads, self.n_kv_heads, self.head_dim = H, Hkv, hd
+        self.nope, self.rank_lat = attn.qk_nope_head_dim, attn.kv_lora_rank
+        hl, kl, r = H // info.ws, Hkv // info.ws, info.rank
+        self.h_local, self.kv_local = hl, kl
+        self.use_qk_norm = bool(getattr(attn, "use_qk_norm", False))
+        self.use_gate = bool(getattr(attn, "use_gated_attention", False))
+        with torch.no_grad():
+            self.qa_weight = nn.Parameter(torch.cat([attn.q_proj.weight[r * hl * hd:(r + 1) * hl * hd],
+                                                     attn.kv_a_proj.weight], dim=0).contiguous())
+            self.kv_b_weight = nn.Parameter(attn.kv_b_proj.weight[r * kl * 2 * hd:(r + 1) * kl * 2 * hd].contiguous())
+            self.o_weight = nn.Parameter(attn.o_proj.weight[:, r * hl * hd:(r + 1) * hl * hd].contiguous())
+            self.gate_weight = None
+            if self.use_gate:
+                self.gate_weight = nn.Parameter(attn.gate.weight[r * hl * hd:(r + 1) * hl * hd].contiguous())
+                self.gate_weight.tp_sharded = True
+        self.kv_norm = attn.kv_norm
+        if self.use_qk_norm:
+            self.q_norm, self.k_norm = attn.q_norm, attn.k_norm
+        self.qa_weight.tp_sharded = True
+        self.qa_weight.tp_shared_rows = hl * hd     # rows from here on: the same on every rank, partial gradients
+        self.kv_b_weight.tp_sharded = True
+        self.o_weight.tp_sharded = True
+
+    def forward(self, x_shard: Tensor, rotary, batch: int, seq: int) -> Tensor:
+        hl, kl, hd, nope = self.h_local, self.kv_local, self.head_dim, self.nope
+        cs, pos = rotary
+        y = _column(x_shard, self.qa_weight, self.info)
+        q = y[:, : hl * hd].reshape(batch, seq, hl, hd)
+        latent = self.kv_norm(y[:, hl * hd:].contiguous())
+        kv = ops.linear(latent, self.kv_b_weight).view(batch, seq, kl, 2 * hd)
+        q = torch.cat([q[..., :nope], ops.rope(q[..., nope:].contiguous(), cs, pos)], dim=-1)
+        k = torch.cat([kv[..., :nope], ops.rope(kv[..., nope:hd].contiguous(), cs, pos)], dim=-1)
+        v = kv[..., hd:]
+        if self.use_qk_norm:
+            q, k = self.q_norm(q), self.k_norm(k)
+        ctx = attn_ops.attention(q, k, v, causal=True).reshape(batch * seq, hl * hd)
+        if self.use_gate:
+            ctx = ctx * torch.sigmoid(_column(x_shard, self.gate_weight, self.info))
+        return _row(ctx, self.o_weight, self.info)
+
+
 class TPMLP(nn.Module):
     def __init__(self, mlp, info: TPInfo):
         super().__init__()
@@ -158,7 +217,8 @@ class TPBlock(nn.Module):
         self.layer_id = block.layer_id
         self.input_norm = block.input_norm
         self.post_attention_norm = block.post_attention_norm
-        self.attention = TPAttention(block.attention, info)
+        self.latent_attention = hasattr(block.attention, "kv_a_proj")
+        self.attention = (TPMLAttention if self.latent_attention else TPAttention)(block.attention, info)
         # A mixture-of-experts feed-forward acts per token, so it runs unchanged on this rank's token
         # slice with replicated expert weights (their gradients are summed over the group like the
         # norm weights'); only the dense SwiGLU MLP is cut into column / row slices.
@@ -285,6 +345,13 @@ class TensorParallelLM(nn.Module):
             targets.append((p.grad, None))
         for layer in self.layers:
             att = layer.attention
+            if layer.latent_attention:
+                g = att.qa_weight.grad
+                if g is not None:                                       # kv_a_proj rows: partial on every rank
+                    shared = g[att.qa_weight.tp_shared_rows:]
+                    pieces.append(shared.reshape(-1))
+                    targets.append((shared, None))
+                continue
             g = att.qkv_weight.grad
             if att.kv_rep > 1 and g is not None:
                 row0 = att.h_local * att.head_dim
@@ -323,6 +390,8 @@ class TensorParallelLM(nn.Module):
             g = p.grad.float()
             if not getattr(p, "tp_sharded", False):
                 total += g.pow(2).sum() / info.ws
+            elif hasattr(p, "tp_shared_rows"):
+                total += g[:p.tp_shared_rows].pow(2).sum() + g[p.tp_shared_rows:].pow(2).sum() / info.ws
             elif hasattr(p, "tp_kv_rows") and p.tp_kv_rows[1] > 1:
                 row0, rep = p.tp_kv_rows
                 total += g[:row0].pow(2).sum() + g[row0:].pow(2).sum() / rep
@@ -355,11 +424,18 @@ class TensorParallelLM(nn.Module):
         for i, layer in enumerate(self.layers):
             att, mlp = layer.attention, layer.mlp
             pre = f"layers.{i}."
-            D, hl, kl, kv0 = att.head_dim, att.h_local, att.kv_local, att.kv_first
-            out[id(att.qkv_weight)] = torch.cat([
-                full[pre + "attention.q_proj.weight"][r * hl * D:(r + 1) * hl * D],
-                full[pre + "attention.k_proj.weight"][kv0 * D:(kv0 + kl) * D],
-                full[pre + "attention.v_proj.weight"][kv0 * D:(kv0 + kl) * D]], dim=0)
+            D, hl, kl = att.head_dim, att.h_local, att.kv_local
+            if layer.latent_attention:
+                out[id(att.qa_weight)] = torch.cat([full[pre + "attention.q_proj.weight"][r * hl * D:(r + 1) * hl * D],
+                                                    full[pre + "attention.kv_a_proj.weight"]], dim=0)
+                out[id(att.kv_b_weight)] = full[pre + "attention.kv_b_proj.weight"][r * kl * 2 * D:(r + 1) * kl * 2 * D]
+                out[id(att.kv_norm.weight)] = full[pre + "attention.kv_norm.weight"]
+            else:
+                kv0 = att.kv_first
+                out[id(att.qkv_weight)] = torch.cat([
+                    full[pre + "attention.q_proj.weight"][r * hl * D:(r + 1) * hl * D],
+                    full[pre + "attention.k_proj.weight"][kv0 * D:(kv0 + kl) * D],
+                    full[pre + "attention.v_proj.weight"][kv0 * D:(kv0 + kl) * D]], dim=0)
             out[id(att.o_weight)] = full[pre + "attention.o_proj.weight"][:, r * hl * D:(r + 1) * hl * D]
             if att.use_gate:
                 out[id(att.gate_weight)] = full[pre + "attention.gate.weight"][r * hl * D:(r + 1) * hl * D]
@@ -389,12 +465,20 @@ class TensorParallelLM(nn.Module):
         for i, layer in enumerate(self.layers):
             att, mlp = layer.attention, layer.mlp
             pre = f"layers.{i}."
-            D, hl, kl, rep = att.head_dim, att.h_local, att.kv_local, att.kv_rep
-            qkv = self._gather(val(att.qkv_weight))
-            sd[pre + "attention.q_proj.weight"] = torch.cat([w[: hl * D] for w in qkv], dim=0)
-            owners = qkv[::rep]  # one rank per KV head group
-            sd[pre + "attention.k_proj.weight"] = torch.cat([w[hl * D:(hl + kl) * D] for w in owners], dim=0)
-            sd[pre + "attention.v_proj.weight"] = torch.cat([w[(hl + kl) * D:] for w in owners], dim=0)
+            D, hl, kl = att.head_dim, att.h_local, att.kv_local
+            if layer.latent_attention:
+                qa = val(att.qa_weight)
+                sd[pre + "attention.q_proj.weight"] = torch.cat([w[: hl * D] for w in self._gather(qa[: hl * D])], dim=0)
+                sd[pre + "attention.kv_a_proj.weight"] = qa[hl * D:].clone()     # the same on every rank
+                sd[pre + "attention.kv_norm.weight"] = val(att.kv_norm.weight).clone()
+                sd[pre + "attention.kv_b_proj.weight"] = torch.cat(self._gather(val(att.kv_b_weight)), dim=0)
+            else:
+                rep = att.kv_rep
+                qkv = self._gather(val(att.qkv_weight))
+                sd[pre + "attention.q_proj.weight"] = torch.cat([w[: hl * D] for w in qkv], dim=0)
+                owners = qkv[::rep]  # one rank per KV head group
+                sd[pre + "attention.k_proj.weight"] = torch.cat([w[hl * D:(hl + kl) * D] for w in owners], dim=0)
+                sd[pre + "attention.v_proj.weight"] = torch.cat([w[(hl + kl) * D:] for w in owners], dim=0)
             sd[pre + "attention.o_proj.weight"] = torch.cat(self._gather(val(att.o_weight)), dim=1)
             if att.use_gate:
                 sd[pre + "attention.gate.weight"] = torch.cat(self._gather(val(att.gate_weight)), dim=0)

@@ -327,7 +327,7 @@ def test_sharded_optimizer_state_roundtrip(mode, port, tmp_path):
 
 
 # ---- tensor parallelism with QK-RMSNorm and the sigmoid output gate ----
-def _tp_variant_case(out, moe=False):
+def _tp_variant_case(out, moe=False, mla=False):
     from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
     from khaosz_b200.parallel.tp_model import tensorize
     from khaosz_b200.trainer import StrategyFactory
@@ -335,7 +335,8 @@ def _tp_variant_case(out, moe=False):
     ffn = dict(ffn_type="moe", n_routed_experts=4, n_shared_experts=1, n_activated_experts=2) if moe else {}
     cfg = AutoRegressiveLMConfig(vocab_size=200, dim=64, n_layers=2, norm_eps=1e-5, dim_ffn=128, tie_weight=False,
                                  max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, use_qk_norm=True,
-                                 use_gated_attention=True, **ffn)
+                                 use_gated_attention=True, **ffn,
+                                 **(dict(attn_type="mla", kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=8) if mla else {}))
     torch.manual_seed(21)
     dense = AutoRegressiveLM(cfg)
     with torch.no_grad():   # norm weights away from one, so that their gradients are not trivially alike
@@ -357,18 +358,23 @@ def _tp_variant_case(out, moe=False):
     total = loss.detach().clone()
     dist.all_reduce(total)
     weights = tp.full_state_dict()
+    back = tp.scatter_named(weights)             # the inverse: every local parameter from the dense-named tensors
+    for prm in tp.parameters():
+        assert torch.equal(back[id(prm)], prm), "scatter_named does not invert gather_named"
     if dist.get_rank() == 0:
         torch.save({"loss": total.item() / dist.get_world_size(), "ref_loss": ref_loss.item(), "got": got, "ref": ref,
                     "names": sorted(weights), "dense_names": sorted(n for n, _ in dense.named_parameters())}, out)
     dist.barrier()
 
 
-@pytest.mark.parametrize("world,port,moe", [(2, "29644", False), (4, "29645", False),   # 4 ranks: KV heads shared by rank pairs
-                                            (2, "29648", True)])   # mixture of experts: replicated experts on token slices
-def test_tensor_parallel_qk_norm_and_gate_match_the_dense_model(world, port, moe, tmp_path):
+@pytest.mark.parametrize("world,port,moe,mla", [
+    (2, "29644", False, False), (4, "29645", False, False),   # 4 ranks: KV heads shared by rank pairs
+    (2, "29648", True, False),                                # mixture of experts: replicated experts on token slices
+    (2, "29649", False, True)])                               # multi-head latent attention
+def test_tensor_parallel_qk_norm_and_gate_match_the_dense_model(world, port, moe, mla, tmp_path):
     out = str(tmp_path / "variant.pt")
     spawn_parallel_fn(_tp_variant_case, world_size=world, backend="gloo", master_addr="127.0.0.1", master_port=port, out=out,
-                      moe=moe)
+                      moe=moe, mla=mla)
     r = torch.load(out)
     assert r["loss"] == pytest.approx(r["ref_loss"], rel=1e-4)
     assert r["names"] == r["dense_names"]

@@ -1,5 +1,6 @@
 """Tensor-parallel serving on CPU (gloo, 2 ranks): rank 0 drives the engine, rank 1 replays the
 announced steps; greedy outputs must equal the dense single-process model's."""
+import pytest
 import torch
 import torch.distributed as dist
 
@@ -29,13 +30,14 @@ def _dense_greedy(model, prompt, n):
     return out
 
 
-def _case(out):
+def _case(out, mla=False):
     from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
     from khaosz_b200.inference import InferenceEngine
     from khaosz_b200.inference.tp import TPInferenceLM, serve_worker
 
+    extra = dict(attn_type="mla", kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=8, use_qk_norm=True) if mla else {}
     cfg = AutoRegressiveLMConfig(vocab_size=128, dim=64, n_layers=2, norm_eps=1e-5, dim_ffn=128, tie_weight=False,
-                                 max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2)
+                                 max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, **extra)
     torch.manual_seed(11)
     dense = AutoRegressiveLM(cfg).eval()
     tp = TPInferenceLM(dense).eval()
@@ -77,9 +79,10 @@ def test_tensor_parallel_int8_slices_track_the_dense_model(tmp_path):
     assert torch.load(out)["err"] < 0.05
 
 
-def test_tensor_parallel_engine_matches_dense_greedy(tmp_path):
+@pytest.mark.parametrize("mla,port", [(False, "29641"), (True, "29650")])
+def test_tensor_parallel_engine_matches_dense_greedy(mla, port, tmp_path):
     out = str(tmp_path / "tp_inf.pt")
-    spawn_parallel_fn(_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29641", out=out)
+    spawn_parallel_fn(_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port=port, out=out, mla=mla)
     r = torch.load(out)
     assert r["got"] == r["want"]
 
@@ -153,8 +156,17 @@ def _variant_case(out):
     moe = AutoRegressiveLM(moe_cfg).eval()
     with torch.no_grad():
         err_moe = (TPInferenceLM(moe).eval()(ids)["logits"] - moe(ids)["logits"]).abs().max().item()
+    # multi-head latent attention, through the engine (paged KV of the local latent-expanded heads)
+    mla_cfg = AutoRegressiveLMConfig(vocab_size=128, dim=64, n_layers=2, norm_eps=1e-5, dim_ffn=128, tie_weight=False,
+                                     max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, attn_type="mla",
+                                     kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=8, use_gated_attention=True)
+    mla = AutoRegressiveLM(mla_cfg).eval()
+    with torch.no_grad():
+        err_mla = (TPInferenceLM(mla).eval()(ids)["logits"] - mla(ids)["logits"]).abs().max().item()
+        err_mla8 = (TPInferenceLM(mla, int8=True).eval()(ids)["logits"] - mla(ids)["logits"]).abs().max().item()
     if dist.get_rank() == 0:
-        torch.save({"err": (got - ref).abs().max().item(), "err_moe": err_moe,
+        torch.save({"err": (got - ref).abs().max().item(), "err_moe": err_moe, "err_mla": err_mla,
+                    "err_mla8": err_mla8 / mla(ids)["logits"].abs().max().item(),
                     "err8": (got8 - ref).abs().max().item() / ref.abs().max().item()}, out)
 
 
@@ -163,3 +175,4 @@ def test_tensor_parallel_serving_with_qk_norm_and_gate(tmp_path):
     spawn_parallel_fn(_variant_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29646", out=out)
     r = torch.load(out)
     assert r["err"] < 1e-4 and r["err8"] < 0.05 and r["err_moe"] < 1e-4
+    assert r["err_mla"] < 1e-4 and r["err_mla8"] < 0.05
