@@ -79,6 +79,47 @@ class ShardedAttention(nn.Module):
         return sharded_weight_linear(ctx, self.o_shard, tp)
 
 
+class ShardedMLAttention(nn.Module):
+    """Multi-head latent attention (``astrai/model/components/attention.py:123-212``) with every
+    projection stored as a row shard and gathered inside its GEMM."""
+
+    def __init__(self, attn, info: TPInfo):
+        super().__init__()
+        self.info = info
+        self.n_heads, self.n_kv_heads, self.head_dim = attn.n_heads, attn.n_kv_heads, attn.head_dim
+        self.nope = attn.qk_nope_head_dim
+        self.layer_id = attn.layer_id
+        self.use_qk_norm = bool(getattr(attn, "use_qk_norm", False))
+        self.use_gate = bool(getattr(attn, "use_gated_attention", False))
+        self.q_shard = _row_shard(attn.q_proj.weight, info)
+        self.kv_a_shard = _row_shard(attn.kv_a_proj.weight, info)
+        self.kv_b_shard = _row_shard(attn.kv_b_proj.weight, info)
+        self.o_shard = _row_shard(attn.o_proj.weight, info)
+        self.kv_norm = attn.kv_norm
+        if self.use_qk_norm:
+            self.q_norm, self.k_norm = attn.q_norm, attn.k_norm
+        if self.use_gate:
+            self.gate_shard = _row_shard(attn.gate.weight, info)
+
+    def forward(self, x: Tensor, rotary) -> Tensor:
+        B, S, _ = x.shape
+        H, Hkv, hd, nope = self.n_heads, self.n_kv_heads, self.head_dim, self.nope
+        cs, pos = rotary
+        tp = self.info.ctx()
+        q = sharded_weight_linear(x, self.q_shard, tp).view(B, S, H, hd)
+        latent = self.kv_norm(sharded_weight_linear(x, self.kv_a_shard, tp))
+        kv = sharded_weight_linear(latent, self.kv_b_shard, tp).view(B, S, Hkv, 2 * hd)
+        q = torch.cat([q[..., :nope], ops.rope(q[..., nope:].contiguous(), cs, pos)], dim=-1)
+        k = torch.cat([kv[..., :nope], ops.rope(kv[..., nope:hd].contiguous(), cs, pos)], dim=-1)
+        v = kv[..., hd:]
+        if self.use_qk_norm:
+            q, k = self.q_norm(q), self.k_norm(k)
+        ctx = attn_ops.attention(q, k, v, causal=True).reshape(B, S, H * hd)
+        if self.use_gate:
+            ctx = ctx * torch.sigmoid(sharded_weight_linear(x, self.gate_shard, tp))
+        return sharded_weight_linear(ctx, self.o_shard, tp)
+
+
 class ShardedMLP(nn.Module):
     def __init__(self, mlp, info: TPInfo):
         super().__init__()
@@ -102,8 +143,12 @@ class ShardedBlock(nn.Module):
         self.layer_id = block.layer_id
         self.input_norm = block.input_norm
         self.post_attention_norm = block.post_attention_norm
-        self.attention = ShardedAttention(block.attention, info)
-        self.mlp = ShardedMLP(block.mlp, info)
+        self.latent_attention = hasattr(block.attention, "kv_a_proj")
+        self.attention = (ShardedMLAttention if self.latent_attention else ShardedAttention)(block.attention, info)
+        # a mixture-of-experts feed-forward stays replicated (data parallel): its expert loop issues a
+        # different number of GEMMs on every rank, which in-GEMM weight gathering cannot follow
+        self.dense_mlp = hasattr(block.mlp, "gate") and hasattr(block.mlp, "up") and hasattr(block.mlp, "down")
+        self.mlp = ShardedMLP(block.mlp, info) if self.dense_mlp else block.mlp
 
     def forward(self, x: Tensor, rotary) -> Tensor:
         y, x = self.input_norm.fork(x)
@@ -151,7 +196,11 @@ class FullShardLM(nn.Module):
         """Sum the replicated parameters' gradients over the group (the loss carries the 1/ws)."""
         if self.info.ws <= 1:
             return
-        grads = [p.grad for p in self._replicated() if p.grad is not None]
+        grads = []
+        for p in self._replicated():
+            if p.grad is None:      # e.g. an expert none of this rank's tokens chose: the peers may hold a gradient
+                p.grad = torch.zeros_like(p)
+            grads.append(p.grad)
         if not grads:
             return
         flat = torch.cat([g.reshape(-1) for g in grads])
@@ -198,20 +247,30 @@ class FullShardLM(nn.Module):
             att, mlp = layer.attention, layer.mlp
             pre = f"layers.{i}."
             D, H, Hkv = att.head_dim, att.n_heads, att.n_kv_heads
-            qkv = self._gather_rows(val(att.qkv_shard))
-            sd[pre + "attention.q_proj.weight"] = qkv[: H * D].clone()
-            sd[pre + "attention.k_proj.weight"] = qkv[H * D:(H + Hkv) * D].clone()
-            sd[pre + "attention.v_proj.weight"] = qkv[(H + Hkv) * D:].clone()
+            if layer.latent_attention:
+                sd[pre + "attention.q_proj.weight"] = self._gather_rows(val(att.q_shard))
+                sd[pre + "attention.kv_a_proj.weight"] = self._gather_rows(val(att.kv_a_shard))
+                sd[pre + "attention.kv_norm.weight"] = val(att.kv_norm.weight).clone()
+                sd[pre + "attention.kv_b_proj.weight"] = self._gather_rows(val(att.kv_b_shard))
+            else:
+                qkv = self._gather_rows(val(att.qkv_shard))
+                sd[pre + "attention.q_proj.weight"] = qkv[: H * D].clone()
+                sd[pre + "attention.k_proj.weight"] = qkv[H * D:(H + Hkv) * D].clone()
+                sd[pre + "attention.v_proj.weight"] = qkv[(H + Hkv) * D:].clone()
             sd[pre + "attention.o_proj.weight"] = self._gather_rows(val(att.o_shard))
             if att.use_gate:
                 sd[pre + "attention.gate.weight"] = self._gather_rows(val(att.gate_shard))
             if att.use_qk_norm:
                 sd[pre + "attention.q_norm.weight"] = val(att.q_norm.weight).clone()
                 sd[pre + "attention.k_norm.weight"] = val(att.k_norm.weight).clone()
-            gu = self._gather_rows(val(mlp.gate_up_shard))
-            sd[pre + "mlp.gate.weight"] = gu[: mlp.ffn].clone()
-            sd[pre + "mlp.up.weight"] = gu[mlp.ffn:].clone()
-            sd[pre + "mlp.down.weight"] = self._gather_rows(val(mlp.down_shard))
+            if layer.dense_mlp:
+                gu = self._gather_rows(val(mlp.gate_up_shard))
+                sd[pre + "mlp.gate.weight"] = gu[: mlp.ffn].clone()
+                sd[pre + "mlp.up.weight"] = gu[mlp.ffn:].clone()
+                sd[pre + "mlp.down.weight"] = self._gather_rows(val(mlp.down_shard))
+            else:
+                for n, p in mlp.named_parameters():
+                    sd[pre + "mlp." + n] = val(p).clone()
             sd[pre + "input_norm.weight"] = val(layer.input_norm.weight).clone()
             sd[pre + "post_attention_norm.weight"] = val(layer.post_attention_norm.weight).clone()
         sd["norm.weight"] = val(self.norm.weight).clone()
@@ -233,17 +292,27 @@ class FullShardLM(nn.Module):
         for i, layer in enumerate(self.layers):
             att, mlp = layer.attention, layer.mlp
             pre = f"layers.{i}."
-            out[id(att.qkv_shard)] = rows(torch.cat([full[pre + "attention.q_proj.weight"],
-                                                     full[pre + "attention.k_proj.weight"],
-                                                     full[pre + "attention.v_proj.weight"]], dim=0))
+            if layer.latent_attention:
+                out[id(att.q_shard)] = rows(full[pre + "attention.q_proj.weight"])
+                out[id(att.kv_a_shard)] = rows(full[pre + "attention.kv_a_proj.weight"])
+                out[id(att.kv_b_shard)] = rows(full[pre + "attention.kv_b_proj.weight"])
+                out[id(att.kv_norm.weight)] = full[pre + "attention.kv_norm.weight"]
+            else:
+                out[id(att.qkv_shard)] = rows(torch.cat([full[pre + "attention.q_proj.weight"],
+                                                         full[pre + "attention.k_proj.weight"],
+                                                         full[pre + "attention.v_proj.weight"]], dim=0))
             out[id(att.o_shard)] = rows(full[pre + "attention.o_proj.weight"])
             if att.use_gate:
                 out[id(att.gate_shard)] = rows(full[pre + "attention.gate.weight"])
             if att.use_qk_norm:
                 out[id(att.q_norm.weight)] = full[pre + "attention.q_norm.weight"]
                 out[id(att.k_norm.weight)] = full[pre + "attention.k_norm.weight"]
-            out[id(mlp.gate_up_shard)] = rows(torch.cat([full[pre + "mlp.gate.weight"], full[pre + "mlp.up.weight"]], dim=0))
-            out[id(mlp.down_shard)] = rows(full[pre + "mlp.down.weight"])
+            if layer.dense_mlp:
+                out[id(mlp.gate_up_shard)] = rows(torch.cat([full[pre + "mlp.gate.weight"], full[pre + "mlp.up.weight"]], dim=0))
+                out[id(mlp.down_shard)] = rows(full[pre + "mlp.down.weight"])
+            else:
+                for n, p in mlp.named_parameters():
+                    out[id(p)] = full[pre + "mlp." + n]
             out[id(layer.input_norm.weight)] = full[pre + "input_norm.weight"]
             out[id(layer.post_attention_norm.weight)] = full[pre + "post_attention_norm.weight"]
         out[id(self.norm.weight)] = full["norm.weight"]

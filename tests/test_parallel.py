@@ -382,14 +382,18 @@ def test_tensor_parallel_qk_norm_and_gate_match_the_dense_model(world, port, moe
         assert torch.allclose(r["got"][k], v, rtol=1e-3, atol=1e-6), k
 
 
-def _fs_variant_case(out):
+def _fs_variant_case(out, variant="gqa"):
     from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
     from khaosz_b200.parallel.fsdp_model import full_shard
     from khaosz_b200.trainer import StrategyFactory
 
+    extra = {}
+    if variant == "mla_moe":
+        extra = dict(attn_type="mla", kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=8, ffn_type="moe",
+                     n_routed_experts=4, n_shared_experts=1, n_activated_experts=2)
     cfg = AutoRegressiveLMConfig(vocab_size=200, dim=64, n_layers=2, norm_eps=1e-5, dim_ffn=128, tie_weight=False,
                                  max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, use_qk_norm=True,
-                                 use_gated_attention=True)
+                                 use_gated_attention=True, **extra)
     torch.manual_seed(21)
     dense = AutoRegressiveLM(cfg)
     data = torch.randint(0, 200, (4, 33), generator=torch.Generator().manual_seed(2))
@@ -405,14 +409,19 @@ def _fs_variant_case(out):
     (loss / ws).backward()
     fs.reduce_replicated_grads()
     got = fs.gather_named(lambda p: p.grad.detach())
+    back = fs.scatter_named(fs.full_state_dict())
+    for prm in fs.parameters():
+        assert torch.equal(back[id(prm)], prm), "scatter_named does not invert gather_named"
     if r == 0:
         torch.save({"got": got, "ref": ref}, out)
     dist.barrier()   # leave together: a rank that tears gloo down while its peer still writes aborts the peer
 
 
-def test_full_shard_qk_norm_and_gate_match_the_dense_model(tmp_path):
+@pytest.mark.parametrize("variant,port", [("gqa", "29647"), ("mla_moe", "29651")])
+def test_full_shard_qk_norm_and_gate_match_the_dense_model(variant, port, tmp_path):
     out = str(tmp_path / "fs_variant.pt")
-    spawn_parallel_fn(_fs_variant_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29647", out=out)
+    spawn_parallel_fn(_fs_variant_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port=port, out=out,
+                      variant=variant)
     r = torch.load(out)
     assert sorted(r["got"]) == sorted(r["ref"])
     for k, v in r["ref"].items():
