@@ -9,6 +9,8 @@ cosine over the number of optimizer steps.
 from __future__ import annotations
 
 import argparse
+import json
+import logging
 import os
 from functools import partial
 
@@ -21,6 +23,8 @@ from ..models.components.block import DecoderBlock
 from ..parallel.fsdp_model import ShardedBlock
 from ..parallel.tp_model import TPBlock
 from ..trainer import FusedAdamW, Muon, SchedulerFactory, Trainer
+
+log = logging.getLogger(__name__)
 
 
 def parse_args(argv=None) -> argparse.Namespace:
@@ -56,6 +60,9 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--log_interval", type=int, default=10, help="Record the metrics every this many micro-batches.")
     p.add_argument("--metrics", type=str, nargs="+", default=["loss", "lr", "tokens_per_s", "step_ms"],
                    help="Metrics written to the JSONL log (see khaosz_b200.trainer.metrics.METRICS).")
+    p.add_argument("--auto_resume", action="store_true", default=False,
+                   help="Continue from the newest checkpoint under --ckpt_dir (weights, optimizer, scheduler and the "
+                        "position in the data), if there is one; --param_path is used otherwise.")
     p.add_argument("--start_epoch", type=int, default=0)
     p.add_argument("--start_batch", type=int, default=0)
     p.add_argument("--master_addr", type=str, default="localhost")
@@ -88,7 +95,32 @@ def compute_total_steps(dataset_len: int, n_epoch: int, batch_per_device: int, n
     return (batches // grad_accum_steps) * n_epoch
 
 
+def find_latest_checkpoint(ckpt_dir: str):
+    """``(directory, meta)`` of the newest complete checkpoint under ``ckpt_dir`` (ordered by epoch, then
+    iteration), or ``None``.  The reference resumes only from a directory and a position given by hand
+    (``scripts/tools/train.py:144-149``); an emergency checkpoint written by the error path counts too."""
+    best = None
+    if not os.path.isdir(ckpt_dir):
+        return None
+    for name in os.listdir(ckpt_dir):
+        root = os.path.join(ckpt_dir, name)
+        if not (os.path.isfile(os.path.join(root, "meta.json")) and os.path.isfile(os.path.join(root, "model.safetensors"))):
+            continue
+        try:
+            with open(os.path.join(root, "meta.json")) as fh:
+                meta = json.load(fh)
+        except (OSError, ValueError):       # a checkpoint that was being written when the job died
+            continue
+        key = (int(meta.get("epoch", 0)), int(meta.get("iteration", 0)))
+        if best is None or key > best[0]:
+            best = (key, root, meta)
+    return None if best is None else (best[1], best[2])
+
+
 def train(args: argparse.Namespace) -> None:
+    latest = find_latest_checkpoint(args.ckpt_dir) if getattr(args, "auto_resume", False) else None
+    if latest is not None:
+        args.param_path = latest[0]
     if not os.path.exists(args.param_path):
         raise FileNotFoundError(args.param_path)
     if args.nprocs > 1 and args.parallel_mode == "none":
@@ -100,6 +132,17 @@ def train(args: argparse.Namespace) -> None:
     # data-parallel replicas: the ranks of one tensor-parallel group read the same samples
     replicas = max(1, args.nprocs // (args.tp_size or args.nprocs)) if args.parallel_mode == "tp" else args.nprocs
     total = compute_total_steps(len(dataset), args.n_epoch, args.batch_per_device, replicas, args.grad_accum_steps)
+    if latest is not None:
+        # the iteration counter runs across epochs; the sampler wants the position inside the epoch
+        per_epoch = -(-(-(-len(dataset) // replicas)) // args.batch_per_device)
+        meta = latest[1]
+        epoch = int(meta.get("epoch", 0))
+        # continue after the last micro-batch whose gradient reached the weights (a periodic checkpoint is
+        # taken before the optimizer step of its own iteration)
+        iteration = int(meta.get("completed_iteration", meta.get("iteration", 0)))
+        args.start_epoch = epoch
+        args.start_batch = max(iteration - epoch * per_epoch, 0)
+        log.info("resuming from %s (epoch %d, batch %d)", latest[0], args.start_epoch, args.start_batch)
     warmup = min(int(args.warmup_ratio * total), total)
     executor_kwargs = {"gradient_as_bucket_view": True, "broadcast_buffers": False}
     if args.fp8:

@@ -199,10 +199,15 @@ class CheckpointCallback:
         state = context.executor.unwrap_model(context.model)  # collective under sharded executors
         extra = {} if self.weight_only else self.save_extra_fn(context)  # may gather optimizer shards
         self.last_ckpt_iter = context.iteration
+        # micro-batches whose gradients are already in the weights: a periodic checkpoint is taken before the
+        # optimizer step of its own iteration, so a run that continues from it has to start from here
+        applied = (context.kwargs.get("start_iteration", 0)
+                   + context.kwargs.get("optimizer_steps", 0) * context.executor.grad_accum_steps)
         if get_rank() == 0:
             path = os.path.join(self.save_dir, f"epoch_{context.epoch}_iter_{context.iteration}")
             context.checkpoint = Checkpoint(state_dict=state, epoch=context.epoch, iteration=context.iteration,
-                                            extra=extra, config=context.model_config)
+                                            extra=extra, config=context.model_config,
+                                            meta={"completed_iteration": min(applied, context.iteration)})
             context.checkpoint.save(path)
 
     def on_batch_end(self, context):

@@ -191,7 +191,19 @@ class FusedAdamW(Optimizer):
 
     def load_state_dict(self, state_dict: Dict[str, Any]) -> None:
         if self._flat is None:
-            return super().load_state_dict(state_dict)
+            super().load_state_dict(state_dict)
+            # torch casts loaded state to the parameter's dtype (bf16); the moments live in fp32, and a
+            # resumed run has to continue with exactly the values that were saved
+            params = [p for g in self.param_groups for p in g["params"]]
+            keys = [i for g in state_dict["param_groups"] for i in g["params"]]
+            for key, p in zip(keys, params):
+                saved = state_dict["state"].get(key)
+                if saved is None:
+                    continue
+                for name in ("exp_avg", "exp_avg_sq"):
+                    if name in saved:
+                        self.state[p][name] = saved[name].detach().to(device=p.device, dtype=torch.float32).clone()
+            return
         for k, val in state_dict["param_groups"][0].items():
             if k != "params":
                 self.param_groups[0][k] = val

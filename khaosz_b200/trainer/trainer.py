@@ -64,11 +64,13 @@ class Trainer:
                 with trace_range("optimizer_step"):
                     context.optimizer.step()
                     context.optimizer.zero_grad()
+                context.kwargs["optimizer_steps"] = context.kwargs.get("optimizer_steps", 0) + 1
                 if context.scheduler:
                     context.scheduler.step()
 
     def _trainer_loop(self, resume_dir: Optional[str] = None) -> None:
         context = TrainContextBuilder(self.train_config).with_resume_dir(resume_dir).build()
+        context.kwargs["start_iteration"] = context.iteration
         self._call_callbacks("on_train_begin", context)
         try:
             context.model.train()

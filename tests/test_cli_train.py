@@ -3,6 +3,8 @@ checkpoint with the reference's full (unsharded) parameter names, which the dens
 import json
 import os
 
+import pytest
+
 import torch
 
 from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
@@ -74,3 +76,41 @@ def test_checkpoint_of_a_tensor_parallel_run_resumes_in_a_single_process(tmp_pat
         "--device_type", "cpu", "--master_addr", "127.0.0.1", "--master_port", "29656", "--ckpt_interval", "1000000"])
     train_cli.train(args)
     assert os.listdir(out)
+
+
+@pytest.mark.parametrize("accum", [1, 2])
+def test_cli_auto_resume_continues_from_the_newest_checkpoint(accum, tmp_path):
+    """A run that dies and is restarted with --auto_resume ends with exactly the weights of the uninterrupted run."""
+    import shutil
+
+    cfg, params, data = _setup(tmp_path)
+    ckpt = tmp_path / "ckpt"
+    base = ["--train_type", "seq", "--data_root_path", str(data), "--param_path", str(params), "--ckpt_dir", str(ckpt),
+            "--batch_per_device", "2", "--window_size", "32", "--num_workers", "0", "--no_pin_memory", "--nprocs", "1",
+            "--parallel_mode", "none", "--device_type", "cpu", "--ckpt_interval", "6", "--log_interval", "1",
+            "--grad_accum_steps", str(accum), "--warmup_ratio", "0.2"]
+    torch.manual_seed(0)
+    AutoRegressiveLM(cfg).to(torch.bfloat16).save_pretrained(str(params))     # both runs start from these weights
+    assert train_cli.find_latest_checkpoint(str(ckpt)) is None
+    train_cli.train(train_cli.parse_args(base + ["--auto_resume"]))        # nothing to resume: starts from --param_path
+    names = sorted(d for d in os.listdir(ckpt) if d.startswith("epoch_"))
+    assert names == ["epoch_0_iter_12", "epoch_0_iter_18", "epoch_0_iter_20", "epoch_0_iter_6"]
+    assert train_cli.find_latest_checkpoint(str(ckpt))[0].endswith("epoch_0_iter_20")
+    whole = Checkpoint.load(str(ckpt / "epoch_0_iter_20"))
+    # the job "died" after iteration 6; one later checkpoint was cut off while being written
+    for gone in ("epoch_0_iter_12", "epoch_0_iter_20"):
+        shutil.rmtree(ckpt / gone)
+    os.remove(ckpt / "epoch_0_iter_18" / "model.safetensors")
+    shutil.rmtree(ckpt / "logs")
+    path, meta = train_cli.find_latest_checkpoint(str(ckpt))
+    # the checkpoint of iteration 6 precedes that iteration's optimizer step
+    assert path.endswith("epoch_0_iter_6") and meta["iteration"] == 6 and meta["completed_iteration"] == 6 - accum
+    train_cli.train(train_cli.parse_args(base + ["--auto_resume"]))
+    final = Checkpoint.load(str(ckpt / "epoch_0_iter_20"))
+    assert final.iteration == 20
+    rows = [json.loads(line) for f in sorted(os.listdir(ckpt / "logs")) for line in open(ckpt / "logs" / f)]
+    assert min(r["iter"] for r in rows) == 6 - accum + 1 and max(r["iter"] for r in rows) == 20
+    for k, v in whole.state_dict.items():
+        assert torch.equal(final.state_dict[k], v), k
+    opt = torch.load(ckpt / "epoch_0_iter_20" / "optimizer.pt", weights_only=False)
+    assert {int(st["step"]) for st in opt["state"].values()} == {20 // accum}
