@@ -43,3 +43,30 @@ def test_perplexity_cli_reports_finite_values(param_dir, tmp_path):
     assert len(rows) == 2
     vals = [v for r in rows for v in r.values() if isinstance(v, float)]
     assert vals and all(v == v and v > 0 for v in vals)
+
+
+def test_cli_reference_lists_every_flag():
+    """docs/cli.md is generated from the parsers; a flag added to a tool has to show up there."""
+    import contextlib
+    import importlib
+    import io
+    import re
+    from pathlib import Path
+
+    text = (Path(__file__).resolve().parent.parent / "docs" / "cli.md").read_text()
+    sections = {m.group(1): m.end() for m in re.finditer(r"^## `python -m khaosz_b200\.cli\.(\w+)`", text, re.M)}
+    assert {"train", "server", "generate", "perplexity", "evaluate_mmlu", "preprocess", "benchmark", "demo",
+            "kernel_bench", "comm_bench"} <= set(sections)
+    order = sorted(sections.values()) + [len(text)]
+    for tool, start in sections.items():
+        body = text[start:order[order.index(start) + 1]]
+        mod = importlib.import_module(f"khaosz_b200.cli.{tool}")
+        buf = io.StringIO()
+        with contextlib.redirect_stdout(buf), contextlib.redirect_stderr(buf):
+            try:
+                (getattr(mod, "parse_args", None) or mod.main)(["--help"])
+            except SystemExit:
+                pass
+        flags = set(re.findall(r"(?<![\w-])--[a-z][\w-]*", buf.getvalue()))
+        missing = sorted(f for f in flags if f not in body)
+        assert not missing, f"docs/cli.md section of {tool} lacks {missing}"
