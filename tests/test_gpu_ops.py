@@ -199,3 +199,22 @@ def test_rms_norm_fork_fuses_the_residual_gradient():
     assert torch.equal(xr, x)
     assert (gx.float() - rx).abs().max().item() < 3e-2 * rx.abs().max().item() + 2e-2
     assert (gw.float() - rw).abs().max().item() < 3e-2 * rw.abs().max().item() + 0.5
+
+
+def test_throughput_callback_times_steps_on_the_device():
+    """The trainer's throughput callback brackets optimizer steps with CUDA events and reads an interval
+    only once both of its events have completed."""
+    from types import SimpleNamespace
+
+    from khaosz_b200.trainer import CallbackFactory
+
+    cb = CallbackFactory.create("throughput")
+    ctx = SimpleNamespace(kwargs={"batch_tokens": 1024}, world_size=1, dataloader=None)
+    x = torch.randn(2048, 2048, device="cuda")
+    for _ in range(4):
+        cb.on_batch_end(ctx)
+        (x @ x).sum()
+        cb.on_optimizer_step(ctx)
+        torch.cuda.synchronize()
+    assert cb._use_cuda and len(cb._marks) <= 2
+    assert 0 < ctx.kwargs["step_ms"] < 1000 and ctx.kwargs["tokens_per_s"] > 0
