@@ -242,6 +242,8 @@ class ProgressBarCallback:
             postfix = {"loss": f"{context.loss:.4f}", "lr": f"{context.optimizer.param_groups[-1]['lr']:.2e}"}
             if context.val_loss > 0:
                 postfix["val_loss"] = f"{context.val_loss:.4f}"
+            if context.kwargs.get("tokens_per_s"):       # published by the throughput callback
+                postfix["tok/s"] = f"{context.kwargs['tokens_per_s']:,.0f}"
             self.progress_bar.set_postfix(postfix, refresh=False)
         self.progress_bar.update(1)
 
