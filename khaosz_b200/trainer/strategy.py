@@ -31,12 +31,22 @@ def move_to_device(batch: Dict[str, Tensor], device) -> Dict[str, Tensor]:
 
 
 def create_ref_model(model_fn: Callable[[], nn.Module], state_dict: dict, like: nn.Module = None) -> nn.Module:
-    """Frozen copy of the policy built from ``model_fn`` and a full state dict."""
+    """Frozen copy of the policy built from ``model_fn`` and a full state dict.  When the policy is
+    sliced (tensor parallel) or sharded (fully sharded) the copy is cut the same way, so it costs
+    ``1 / world`` of the memory and runs through the same fused GEMM + collective kernels."""
     ref = model_fn()
     if like is not None:
         p = next(like.parameters())
         ref = ref.to(device=p.device, dtype=p.dtype)
     ref.load_state_dict(state_dict)
+    if like is not None and hasattr(like, "info"):
+        from ..parallel.fsdp_model import FullShardLM, full_shard
+        from ..parallel.tp_model import TensorParallelLM, tensorize
+
+        if isinstance(like, TensorParallelLM):
+            ref = tensorize(ref, like.info.group)
+        elif isinstance(like, FullShardLM):
+            ref = full_shard(ref, like.info.group)
     ref.requires_grad_(False)
     ref.eval()
     if like is not None and next(ref.parameters()).is_cuda and hasattr(ref, "pack_parameters"):

@@ -440,3 +440,36 @@ def test_sliced_models_refuse_lora_adapters_instead_of_dropping_them():
         reject_adapters(model, "tensor parallelism")
     merge_lora(model)                                      # merged adapters are plain weights again
     reject_adapters(model, "tensor parallelism")
+
+
+# ---- the frozen reference copy of DPO / GRPO is cut like the policy ----
+def _sharded_ref_case(mode):
+    from khaosz_b200.parallel.fsdp_model import FullShardLM
+    from khaosz_b200.parallel.tp_model import TensorParallelLM
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    model = _make_model()
+    ex = ExecutorFactory.create(mode, grad_accum_steps=1)
+    opt = FusedAdamW(model.parameters(), lr=1e-3)
+    model, opt, _, _ = ex.prepare(model, opt, None, None)
+    strat = StrategyFactory.create("dpo", model, "cpu", executor=ex, model_fn=_make_model, beta=0.1)
+    seed = 5 if mode == "tp" else 5 + dist.get_rank()       # data parallel: every rank its own pairs
+    g = torch.Generator().manual_seed(seed)
+    batch = {"chosen": torch.randint(0, 1000, (2, 33), generator=g), "rejected": torch.randint(0, 1000, (2, 33), generator=g),
+             "chosen_mask": torch.ones(2, 33, dtype=torch.bool), "rejected_mask": torch.ones(2, 33, dtype=torch.bool)}
+    with ex.accumulate(model):
+        loss = ex.micro_step(strat, batch)
+        opt.step()
+    ref = strat.ref_model
+    assert isinstance(ref, TensorParallelLM if mode == "tp" else FullShardLM)
+    assert not any(p.requires_grad for p in ref.parameters())
+    dense = sum(p.numel() for p in _make_model().layers.parameters())
+    held = sum(p.numel() for p in ref.layers.parameters())
+    assert held < 0.6 * dense                                # two ranks: about half of every block
+    # policy == reference before the first update: the DPO loss is log 2
+    assert loss.item() == pytest.approx(0.6931, abs=2e-3)
+
+
+@pytest.mark.parametrize("mode,port", [("tp", "29652"), ("fsdp_full", "29653")])
+def test_frozen_reference_model_is_sharded_like_the_policy(mode, port):
+    spawn_parallel_fn(_sharded_ref_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port=port, mode=mode)
