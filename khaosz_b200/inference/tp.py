@@ -28,7 +28,7 @@ from torch import Tensor
 
 from .. import ops
 from ..ops import attention as attn_ops
-from ..parallel.tensor_parallel import TPContext, _RowParallelFn
+from ..parallel.tensor_parallel import _RowParallelFn
 from ..parallel.tp_model import TPAttention, TPInfo, TPMLAttention, TPMLP, reject_adapters
 from .core.cache import KVCache
 from .core.executor import Executor

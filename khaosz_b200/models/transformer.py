@@ -14,7 +14,6 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
-from .. import ops
 from ..config.model_config import AutoRegressiveLMConfig
 from .automodel import AutoModel
 from .components.block import DecoderBlock

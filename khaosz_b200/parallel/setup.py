@@ -19,7 +19,7 @@ from __future__ import annotations
 import contextlib
 import functools
 import os
-from typing import Callable, Optional
+from typing import Callable
 
 import torch
 import torch.distributed as dist

@@ -14,7 +14,7 @@ script (``scripts/tools/train.py:197-198``, ``astrai/trainer/train_callback.py:7
 from __future__ import annotations
 
 import math
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, Optional, Tuple
 
 import torch
 import torch.distributed as dist

@@ -1,7 +1,5 @@
 """Inference kernels vs PyTorch references: paged KV write, paged decode attention, fused
 sampling, and the engine end to end on the GPU."""
-import math
-
 import pytest
 import torch
 

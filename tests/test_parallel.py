@@ -1,6 +1,5 @@
 """Process launch and executor parity on CPU (gloo, world size 2)."""
 import os
-import tempfile
 
 import pytest
 import torch
