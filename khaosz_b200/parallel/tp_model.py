@@ -291,18 +291,22 @@ class TensorParallelLM(nn.Module):
             flat = _GatherTokens.apply(flat, self.info)
         return flat.view(shape)
 
-    def loss_weight(self, local_targets: Tensor, ignore_index: int = -100) -> Tensor:
+    def loss_weight(self, local_targets: Tensor, ignore_index: int = -100,
+                    full_targets: Optional[Tensor] = None) -> Tensor:
         """Factor that turns this rank's mean loss into its share of the global mean:
-        ``n_local * ws / n_global`` (the executor divides by ``ws``)."""
+        ``n_local * ws / n_global`` (the executor divides by ``ws``).  Every rank of the group reads
+        the same batch, so the global count comes from ``full_targets`` without a collective (and the
+        step stays recordable as a CUDA graph)."""
         n_local = (local_targets != ignore_index).sum().to(torch.float32)
         if self.info.ws == 1:
             return torch.ones_like(n_local)
-        if local_targets.is_cuda and torch.cuda.is_current_stream_capturing():
-            # no library collective inside a captured micro-step: the ranks' valid-token counts
-            # are taken as equal (exact for next-token training, where every target counts)
-            return torch.ones_like(n_local)
-        n_global = n_local.clone()
-        dist.all_reduce(n_global, group=self.info.group)
+        if full_targets is not None:
+            n_global = (full_targets != ignore_index).sum().to(torch.float32)
+        else:
+            if local_targets.is_cuda and torch.cuda.is_current_stream_capturing():
+                return torch.ones_like(n_local)   # no library collective inside a recorded step
+            n_global = n_local.clone()
+            dist.all_reduce(n_global, group=self.info.group)
         return n_local * self.info.ws / n_global.clamp_min(1.0)
 
     def forward(self, input_ids: Tensor, input_mask: Optional[Tensor] = None, paged_cache=None,

@@ -80,7 +80,7 @@ def local_loss(model, logits: Tensor, targets: Tensor, label_smoothing: float) -
     if shard is None:
         return ops.cross_entropy(logits, targets, label_smoothing, IGNORE_INDEX)
     local = shard(targets)
-    return ops.cross_entropy(logits, local, label_smoothing, IGNORE_INDEX) * model.loss_weight(local, IGNORE_INDEX)
+    return ops.cross_entropy(logits, local, label_smoothing, IGNORE_INDEX) * model.loss_weight(local, IGNORE_INDEX, targets)
 
 
 class BaseStrategy(ABC):

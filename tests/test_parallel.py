@@ -472,3 +472,34 @@ def _sharded_ref_case(mode):
 @pytest.mark.parametrize("mode,port", [("tp", "29652"), ("fsdp_full", "29653")])
 def test_frozen_reference_model_is_sharded_like_the_policy(mode, port):
     spawn_parallel_fn(_sharded_ref_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port=port, mode=mode)
+
+
+# ---- SFT under tensor parallelism: the masked positions fall unevenly on the ranks' token slices ----
+def _sft_tp_case():
+    from khaosz_b200.parallel.tp_model import tensorize
+    from khaosz_b200.trainer import StrategyFactory
+
+    dense = _make_model()
+    data = torch.randint(0, 1000, (4, 65), generator=torch.Generator().manual_seed(9))
+    mask = torch.ones(4, 64, dtype=torch.bool)
+    mask[:2] = False                      # the first rank's token slice is all context ...
+    mask[0, 60:] = True                   # ... except four positions
+    batch = {"input_ids": data[:, :-1], "target_ids": data[:, 1:], "loss_mask": mask}
+    ref = StrategyFactory.create("sft", dense, "cpu")(batch)
+    ref.backward()
+    want = dense.layers[0].mlp.down.weight.grad.clone()
+    dense.zero_grad()
+    tp = tensorize(dense)
+    loss = StrategyFactory.create("sft", tp, "cpu")(batch)
+    (loss / dist.get_world_size()).backward()
+    tp.reduce_replicated_grads()
+    got = tp.full_state_dict(grads=True)["layers.0.mlp.down.weight"]
+    total = loss.detach().clone()
+    dist.all_reduce(total)
+    assert total.item() / dist.get_world_size() == pytest.approx(ref.item(), rel=1e-5)
+    assert torch.allclose(got, want, rtol=1e-3, atol=1e-7)
+    dist.barrier()
+
+
+def test_sft_under_tensor_parallel_weights_uneven_masks_exactly():
+    spawn_parallel_fn(_sft_tp_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29654")
