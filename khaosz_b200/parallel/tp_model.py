@@ -239,6 +239,10 @@ class _GatherTokens(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, info):
+        if x.is_cuda and torch.cuda.is_current_stream_capturing():
+            # every rank reaches this point in the same micro-step, so all of them give up the
+            # recording together and keep running the step with plain launches
+            raise RuntimeError("a library collective cannot be part of a recorded micro-step")
         ctx.info = info
         parts = [torch.empty_like(x) for _ in range(info.ws)]
         dist.all_gather(parts, x.contiguous(), group=info.group)
