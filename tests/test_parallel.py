@@ -503,3 +503,55 @@ def _sft_tp_case():
 
 def test_sft_under_tensor_parallel_weights_uneven_masks_exactly():
     spawn_parallel_fn(_sft_tp_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29654")
+
+
+# ---- GRPO under tensor parallelism ----
+def _grpo_batch():
+    g = torch.Generator().manual_seed(3)
+    return {"prompts": torch.randint(0, 1000, (2, 6), generator=g), "responses": torch.randint(0, 1000, (2, 4, 11), generator=g),
+            "masks": torch.rand(2, 4, 11, generator=g) > 0.2, "rewards": torch.rand(2, 4, generator=g)}
+
+
+def _grpo_tp_case(out):
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    model = _make_model()
+    ex = ExecutorFactory.create("tp", grad_accum_steps=1)
+    opt = FusedAdamW(model.parameters(), lr=1e-3)
+    model, opt, _, _ = ex.prepare(model, opt, None, None)
+    strat = StrategyFactory.create("grpo", model, "cpu", executor=ex, model_fn=_make_model, group_size=4, kl_coef=0.1,
+                                   sync_interval=100)
+    losses = []
+    for _ in range(3):
+        with ex.accumulate(model):
+            losses.append(ex.micro_step(strat, _grpo_batch()).item())
+            opt.step()
+            opt.zero_grad()
+    sd = ex.unwrap_model(model)
+    if dist.get_rank() == 0:
+        torch.save({"losses": losses, "sd": sd}, out)
+
+
+def test_grpo_under_tensor_parallel_matches_single_process(tmp_path):
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    out = str(tmp_path / "grpo_tp.pt")
+    spawn_parallel_fn(_grpo_tp_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29655", out=out)
+    got = torch.load(out)
+    model = _make_model()
+    opt = FusedAdamW(model.parameters(), lr=1e-3)
+    ex = ExecutorFactory.create("none")
+    model, opt, _, _ = ex.prepare(model, opt, None, None)
+    strat = StrategyFactory.create("grpo", model, "cpu", executor=ex, model_fn=_make_model, group_size=4, kl_coef=0.1,
+                                   sync_interval=100)
+    ref = []
+    for _ in range(3):
+        loss = strat(_grpo_batch())
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        ref.append(loss.item())
+    assert got["losses"] == pytest.approx(ref, rel=1e-3, abs=1e-5)
+    assert abs(ref[-1]) > 1e-6          # the policy has moved away from the reference copy
+    for k, v in model.state_dict().items():
+        assert torch.allclose(got["sd"][k], v, rtol=1e-3, atol=3e-4), k
