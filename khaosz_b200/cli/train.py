@@ -20,9 +20,10 @@ from ..config import AutoRegressiveLMConfig, TrainConfig
 from ..data import DatasetFactory
 from ..models import AutoRegressiveLM
 from ..models.components.block import DecoderBlock
+from ..models.components.lora import LoRAConfig
 from ..parallel.fsdp_model import ShardedBlock
 from ..parallel.tp_model import TPBlock
-from ..trainer import FusedAdamW, Muon, SchedulerFactory, Trainer
+from ..trainer import CallbackFactory, FusedAdamW, Muon, SchedulerFactory, Trainer
 
 log = logging.getLogger(__name__)
 
@@ -54,6 +55,10 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--grpo_sync_interval", type=int, default=200)
     p.add_argument("--label_smoothing", type=float, default=0.05)
     p.add_argument("--gradient_checkpointing", action="store_true", default=False)
+    p.add_argument("--lora_r", type=int, default=0, help="Rank of the LoRA adapters (0 = train the full model).")
+    p.add_argument("--lora_alpha", type=int, default=32)
+    p.add_argument("--lora_target_modules", type=str, nargs="+", default=["q_proj", "v_proj"],
+                   help="Names of the Linear layers that get adapters (q_proj k_proj v_proj o_proj gate up down).")
     p.add_argument("--ckpt_interval", type=int, default=5000)
     p.add_argument("--ckpt_dir", type=str, default="checkpoint")
     p.add_argument("--log_dir", type=str, default=None, help="Metric log directory (default: <ckpt_dir>/logs).")
@@ -151,8 +156,13 @@ def train(args: argparse.Namespace) -> None:
         executor_kwargs["cuda_graph"] = True
     if args.parallel_mode == "tp":
         executor_kwargs["tp_size"] = args.tp_size or args.nprocs
+    lora = None
+    if args.lora_r > 0:
+        if args.parallel_mode in ("tp", "fsdp_full"):
+            raise ValueError("LoRA adapters train under --parallel_mode none, ddp or fsdp")
+        lora = LoRAConfig(r=args.lora_r, alpha=args.lora_alpha, target_modules=tuple(args.lora_target_modules))
     cfg = TrainConfig(
-        model_fn=partial(create_model, config), strategy=args.train_type, dataset=dataset,
+        model_fn=partial(create_model, config), lora=lora, strategy=args.train_type, dataset=dataset,
         optimizer_fn=partial(create_optimizer, kind=args.optimizer, lr=args.max_lr,
                              betas=(args.adamw_beta1, args.adamw_beta2), weight_decay=args.adamw_weight_decay),
         scheduler_fn=partial(SchedulerFactory.create, schedule_type="cosine", warmup_steps=warmup,
@@ -169,7 +179,10 @@ def train(args: argparse.Namespace) -> None:
         extra_kwargs={"beta": args.dpo_beta, "label_smoothing": args.label_smoothing, "clip_eps": args.grpo_clip_eps,
                       "kl_coef": args.grpo_kl_coef, "group_size": args.group_size,
                       "sync_interval": args.grpo_sync_interval})
-    Trainer(cfg).train(resume_dir=args.param_path)
+    callbacks = []
+    if lora is not None:   # the adapters alone, beside the full checkpoints
+        callbacks.append(CallbackFactory.create("lora_adapter", os.path.join(args.ckpt_dir, "lora_adapter"), lora))
+    Trainer(cfg, callbacks=callbacks).train(resume_dir=args.param_path)
 
 
 if __name__ == "__main__":

@@ -222,6 +222,25 @@ class CheckpointCallback:
         self._save(context)
 
 
+@CallbackFactory.register("lora_adapter")
+class LoRAAdapterCallback:
+    """Writes the adapters of a LoRA run (``adapter_model.safetensors`` + ``adapter_config.json``,
+    the layout of ``astrai/model/components/lora.py:121-137``) to ``save_dir`` when training ends -
+    after an error too, since ``on_train_end`` always runs."""
+
+    def __init__(self, save_dir: str, config):
+        self.save_dir, self.config = save_dir, config
+
+    def _save(self, context) -> None:
+        from ..models.components.lora import save_lora
+
+        if get_rank() == 0:
+            save_lora(context.model, self.save_dir, self.config)
+
+    def on_train_end(self, context):
+        self._save(context)
+
+
 @CallbackFactory.register("progress_bar")
 class ProgressBarCallback:
     def __init__(self, num_epoch: int, log_interval: int = 100, file: Optional[IO[str]] = None):

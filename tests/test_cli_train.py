@@ -114,3 +114,35 @@ def test_cli_auto_resume_continues_from_the_newest_checkpoint(accum, tmp_path):
         assert torch.equal(final.state_dict[k], v), k
     opt = torch.load(ckpt / "epoch_0_iter_20" / "optimizer.pt", weights_only=False)
     assert {int(st["step"]) for st in opt["state"].values()} == {20 // accum}
+
+
+def test_cli_lora_run_trains_adapters_only_and_saves_them(tmp_path):
+    from khaosz_b200.models.components.lora import load_lora
+    from khaosz_b200.serialization import load_state_dict
+
+    cfg, params, data = _setup(tmp_path)
+    torch.manual_seed(0)
+    start = AutoRegressiveLM(cfg).to(torch.bfloat16)
+    start.save_pretrained(str(params))
+    ckpt = tmp_path / "ckpt"
+    train_cli.train(train_cli.parse_args([
+        "--train_type", "seq", "--data_root_path", str(data), "--param_path", str(params), "--ckpt_dir", str(ckpt),
+        "--batch_per_device", "2", "--window_size", "32", "--num_workers", "0", "--no_pin_memory", "--nprocs", "1",
+        "--parallel_mode", "none", "--device_type", "cpu", "--ckpt_interval", "1000", "--max_lr", "1e-2",
+        "--lora_r", "4", "--lora_alpha", "8", "--lora_target_modules", "q_proj", "v_proj"]))
+    adapter = ckpt / "lora_adapter"
+    assert json.loads((adapter / "adapter_config.json").read_text())["r"] == 4
+    weights = load_state_dict(adapter / "adapter_model.safetensors")
+    assert set(k.rsplit(".", 1)[1] for k in weights) == {"lora_A", "lora_B"} and len(weights) == 2 * 2 * cfg.n_layers
+    assert weights["layers.0.attention.q_proj.lora_B"].float().abs().sum() > 0        # B starts at zero: it has trained
+    final = Checkpoint.load(str(ckpt / "epoch_0_iter_20")).state_dict
+    base = start.state_dict()
+    assert torch.equal(final["layers.0.attention.q_proj.weight"], base["layers.0.attention.q_proj.weight"])   # frozen
+    assert not torch.equal(final["layers.0.attention.k_proj.weight"], base["layers.0.attention.k_proj.weight"])
+    fresh = AutoRegressiveLM(cfg).to(torch.bfloat16)
+    fresh.load_state_dict(base)
+    assert load_lora(fresh, str(adapter)).r == 4                                      # the adapters load onto the base model
+    with pytest.raises(ValueError, match="LoRA"):
+        train_cli.train(train_cli.parse_args([
+            "--train_type", "seq", "--data_root_path", str(data), "--param_path", str(params), "--ckpt_dir", str(ckpt),
+            "--nprocs", "2", "--parallel_mode", "tp", "--lora_r", "4"]))
