@@ -21,6 +21,7 @@ def parse_args(argv=None):
     p.add_argument("--top_p", type=float, default=0.95)
     p.add_argument("--batch_size", type=int, default=1)
     p.add_argument("--max_tokens", type=int, default=2048)
+    p.add_argument("--adapter_path", type=str, default=None, help="LoRA adapter directory, merged into the weights at load")
     p.add_argument("--device", type=str, default="cuda" if torch.cuda.is_available() else "cpu")
     return p.parse_args(argv)
 
@@ -33,6 +34,11 @@ def run(a) -> int:
     tokenizer = AutoTokenizer.from_pretrained(a.param_path)
     dtype = torch.bfloat16 if a.device.startswith("cuda") else torch.float32
     model = AutoModel.from_pretrained(a.param_path).to(device=a.device, dtype=dtype).eval()
+    if a.adapter_path:
+        from ..models.components.lora import load_lora, merge_lora
+
+        load_lora(model, a.adapter_path)
+        merge_lora(model, unwrap=True)
     if a.device.startswith("cuda"):
         model.pack_parameters(with_grad=False)
     with open(a.input_json_file, "r", encoding="utf-8") as fh:

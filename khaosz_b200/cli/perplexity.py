@@ -19,6 +19,7 @@ def parse_args(argv=None):
     p.add_argument("--output_file", type=str, required=True)
     p.add_argument("--batch_size", type=int, default=4)
     p.add_argument("--text_key", type=str, default="text")
+    p.add_argument("--adapter_path", type=str, default=None, help="LoRA adapter directory, merged into the weights at load")
     p.add_argument("--device", type=str, default="cuda" if torch.cuda.is_available() else "cpu")
     return p.parse_args(argv)
 
@@ -46,6 +47,11 @@ def run(a):
     tokenizer = AutoTokenizer.from_pretrained(a.param_path)
     dtype = torch.bfloat16 if a.device.startswith("cuda") else torch.float32
     model = AutoModel.from_pretrained(a.param_path).to(device=a.device, dtype=dtype).eval()
+    if a.adapter_path:
+        from ..models.components.lora import load_lora, merge_lora
+
+        load_lora(model, a.adapter_path)
+        merge_lora(model, unwrap=True)
     with open(a.input_file, "r", encoding="utf-8") as fh:
         items = [json.loads(line) for line in fh if line.strip()]
     with open(a.output_file, "w", encoding="utf-8") as out:

@@ -24,6 +24,8 @@ def parse_args(argv=None):
     p.add_argument("--page_size", type=int, default=16, help="KV-cache page size in tokens")
     p.add_argument("--max_seq_len", type=int, default=None)
     p.add_argument("--int8", action="store_true", help="int8 weight-only linears (per-channel scales)")
+    p.add_argument("--adapter_path", type=Path, default=None,
+                   help="LoRA adapter directory (adapter_model.safetensors + adapter_config.json), merged at load")
     p.add_argument("--tp_size", type=int, default=1, help="tensor-parallel ranks (GPUs) of one server")
     p.add_argument("--master_addr", default="127.0.0.1")
     p.add_argument("--master_port", default="29560")
@@ -40,7 +42,7 @@ def _rank_main(a) -> None:
 
     device = get_current_device() if a.device == "cuda" else a.device
     common = dict(device=device, dtype=DTYPES[a.dtype], param_path=a.param_path, max_batch_size=a.max_batch_size,
-                  page_size=a.page_size, max_seq_len=a.max_seq_len, int8=a.int8)
+                  page_size=a.page_size, max_seq_len=a.max_seq_len, int8=a.int8, adapter_path=a.adapter_path)
     if dist.get_rank() == 0:
         run_server(host=a.host, port=a.port, reload=False, **common)
     else:
@@ -60,7 +62,7 @@ def main(argv=None):
         return
     run_server(host=a.host, port=a.port, reload=a.reload, device=a.device, dtype=DTYPES[a.dtype],
                param_path=a.param_path, max_batch_size=a.max_batch_size, page_size=a.page_size,
-               max_seq_len=a.max_seq_len, int8=a.int8)
+               max_seq_len=a.max_seq_len, int8=a.int8, adapter_path=a.adapter_path)
 
 
 if __name__ == "__main__":

@@ -65,12 +65,18 @@ class MessagesRequest(BaseModel):
     stop_sequences: Optional[List[str]] = None
 
 
-def _load(param_path: Optional[Path], device: str, dtype: torch.dtype, int8: bool = False, tp: bool = False):
+def _load(param_path: Optional[Path], device: str, dtype: torch.dtype, int8: bool = False, tp: bool = False,
+          adapter_path: Optional[Path] = None):
     root = Path(param_path) if param_path is not None else DEFAULT_PARAM_DIR
     if not root.exists():
         raise FileNotFoundError(f"Parameter directory not found: {root}")
     tokenizer = AutoTokenizer.from_pretrained(root)
     model = AutoModel.from_pretrained(root).to(device=device, dtype=dtype).eval()
+    if adapter_path is not None:   # LoRA adapters are folded into the base weights before serving
+        from ...models.components.lora import load_lora, merge_lora
+
+        load_lora(model, str(adapter_path))
+        merge_lora(model, unwrap=True)
     if tp:
         from ..tp import TPInferenceLM
 
@@ -84,13 +90,13 @@ def _load(param_path: Optional[Path], device: str, dtype: torch.dtype, int8: boo
 
 def _create_engine(param_path: Optional[Path] = None, device: str = "cuda", dtype: torch.dtype = torch.bfloat16,
                    max_batch_size: int = 16, page_size: int = 16, max_seq_len: Optional[int] = None,
-                   int8: bool = False) -> InferenceEngine:
+                   int8: bool = False, adapter_path: Optional[Path] = None) -> InferenceEngine:
     """Single-process engine, or rank 0 of a tensor-parallel group when a process group is up (the
     other ranks run ``serve_worker_rank``)."""
     import torch.distributed as dist
 
     tp = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
-    model, tokenizer = _load(param_path, device, dtype, int8, tp)
+    model, tokenizer = _load(param_path, device, dtype, int8, tp, adapter_path)
     if not tp and next(model.parameters()).is_cuda and hasattr(model, "pack_parameters") and not int8:
         model.pack_parameters(with_grad=False)  # adjacent q/k/v and gate/up weights -> single GEMMs
     log.info("Model loaded on %s with dtype %s", device, dtype)
@@ -100,12 +106,12 @@ def _create_engine(param_path: Optional[Path] = None, device: str = "cuda", dtyp
 
 def serve_worker_rank(param_path: Optional[Path] = None, device: str = "cuda", dtype: torch.dtype = torch.bfloat16,
                       max_batch_size: int = 16, page_size: int = 16, max_seq_len: Optional[int] = None,
-                      int8: bool = False) -> None:
+                      int8: bool = False, adapter_path: Optional[Path] = None) -> None:
     """Ranks > 0 of a tensor-parallel server: load the same weights, keep this rank's slice, replay
     the steps rank 0 announces until it shuts down."""
     from ..tp import serve_worker
 
-    model, tokenizer = _load(param_path, device, dtype, int8, tp=True)
+    model, tokenizer = _load(param_path, device, dtype, int8, tp=True, adapter_path=adapter_path)
     serve_worker(model, tokenizer, max_batch_size=max_batch_size, max_seq_len=max_seq_len, page_size=page_size)
 
 
@@ -164,8 +170,9 @@ async def create_message(request: MessagesRequest):
 
 def run_server(host: str = "0.0.0.0", port: int = 8000, reload: bool = False, device: str = "cuda",
                dtype: torch.dtype = torch.bfloat16, param_path: Optional[Path] = None, max_batch_size: int = 16,
-               page_size: int = 16, max_seq_len: Optional[int] = None, int8: bool = False) -> None:
+               page_size: int = 16, max_seq_len: Optional[int] = None, int8: bool = False,
+               adapter_path: Optional[Path] = None) -> None:
     app.state.server_config = {"device": device, "dtype": dtype, "param_path": param_path,
                                "max_batch_size": max_batch_size, "page_size": page_size, "max_seq_len": max_seq_len,
-                               "int8": int8}
+                               "int8": int8, "adapter_path": adapter_path}
     uvicorn.run(app, host=host, port=port, reload=reload)

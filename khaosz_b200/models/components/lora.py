@@ -100,7 +100,10 @@ def inject_lora(model: nn.Module, r: int = 16, alpha: int = 32, target_modules: 
     return LoRAConfig(r=r, alpha=alpha, target_modules=tuple(targets))
 
 
-def merge_lora(model: nn.Module) -> None:
+def merge_lora(model: nn.Module, unwrap: bool = False) -> None:
+    """Fold every adapter into its base weight.  ``unwrap=True`` also puts plain ``Linear`` layers
+    (sharing the merged weights) back in place of the wrappers, so the model is again the
+    architecture the packed-projection and tensor-parallel paths expect."""
     layers = _adapters(model)
     for layer in layers:
         layer.merge()
@@ -108,6 +111,15 @@ def merge_lora(model: nn.Module) -> None:
         log.info("Merged %d LoRA layers", len(layers))
     else:
         log.warning("No LoRA layers to merge.")
+    if unwrap:
+        for path, mod in list(model.named_modules()):
+            if isinstance(mod, LoRALinear):
+                plain = Linear.__new__(Linear)
+                nn.Module.__init__(plain)
+                plain.out_dim, plain.in_dim = mod.weight.shape
+                plain.weight, plain.bias = mod.weight, mod.bias
+                parent_path, _, leaf = path.rpartition(".")
+                setattr(model.get_submodule(parent_path) if parent_path else model, leaf, plain)
 
 
 def save_lora(model: nn.Module, save_dir: str, config: LoRAConfig) -> None:

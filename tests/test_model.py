@@ -1,4 +1,5 @@
 import logging
+import os
 
 import pytest
 import torch
@@ -237,3 +238,35 @@ def test_int8_packed_projections_match_separate_ones():
     assert packed is not None and isinstance(att.q_proj, Int8Linear)
     assert torch.allclose(packed, torch.cat([att.q_proj(x), att.k_proj(x), att.v_proj(x)], -1), atol=1e-5)
     assert torch.isfinite(model(ids)["logits"]).all()
+
+
+def test_server_loader_merges_lora_adapters(tmp_path, tokenizer_dir):
+    """Adapters given to the server are folded into the base weights; the wrappers are gone afterwards."""
+    import shutil
+
+    from khaosz_b200.inference.api.server import _load
+    from khaosz_b200.models.components.layers import Linear
+    from khaosz_b200.models.components.lora import LoRAConfig, LoRALinear, inject_lora, save_lora
+
+    torch.manual_seed(0)
+    model = AutoRegressiveLM(tiny_config()).eval()
+    params, adapter = tmp_path / "params", tmp_path / "adapter"
+    model.save_pretrained(str(params))
+    for name in os.listdir(tokenizer_dir):
+        shutil.copy(os.path.join(tokenizer_dir, name), params / name)
+    inject_lora(model, r=4, alpha=8, target_modules={"q_proj", "o_proj", "down"})
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, LoRALinear):
+                m.lora_B.normal_(0, 0.05)
+    save_lora(model, str(adapter), LoRAConfig(r=4, alpha=8, target_modules=("q_proj", "o_proj", "down")))
+    ids = torch.randint(0, 300, (2, 9))
+    with torch.no_grad():
+        want = model(ids)["logits"]
+    served, _ = _load(params, "cpu", torch.float32, adapter_path=adapter)
+    assert not any(isinstance(m, LoRALinear) for m in served.modules())
+    assert type(served.layers[0].attention.q_proj) is Linear
+    with torch.no_grad():
+        got = served(ids)["logits"]
+        plain = _load(params, "cpu", torch.float32)[0](ids)["logits"]
+    assert torch.allclose(got, want, atol=1e-5) and not torch.allclose(plain, want, atol=1e-3)
