@@ -8,6 +8,7 @@ Default dtype is int32, overridable per key through ``output.dtype``.
 from __future__ import annotations
 
 import json
+import logging
 import os
 from typing import Dict, Iterator, List, Optional
 
@@ -18,6 +19,8 @@ from ..config.pipeline_config import PipelineConfig
 from ..data.storage import save_bin, save_h5
 from ..tokenize import AutoTokenizer
 from .builder import DEFAULT_DOMAIN, SectionedMaskBuilder
+
+log = logging.getLogger(__name__)
 
 DTYPES = {name: getattr(torch, name) for name in
           ("bool", "uint8", "int8", "int16", "int32", "int64", "float16", "float32", "float64")}
@@ -55,6 +58,7 @@ class Pipeline:
         self.output_dir, self.tokenizer_path = output_dir, tokenizer_path
         self.mask_builder = SectionedMaskBuilder()
         self._tokenizer = None
+        self.skipped_lines = 0      # input lines that were not valid JSON
 
     def transform(self, item: dict) -> Optional[dict]:
         return self.mask_builder.build(item, self.config, self._tokenizer)
@@ -62,9 +66,14 @@ class Pipeline:
     def _iter_items(self) -> Iterator[dict]:
         for path in self.paths:
             with open(path, "r", encoding="utf-8") as fh:
-                for line in fh:
-                    if line.strip():
+                for number, line in enumerate(fh, 1):
+                    if not line.strip():
+                        continue
+                    try:
                         yield json.loads(line)
+                    except ValueError:       # one damaged record must not cost the whole corpus
+                        self.skipped_lines += 1
+                        log.warning("%s:%d is not valid JSON; skipped", path, number)
 
     def _dtype(self, key: str) -> torch.dtype:
         return DTYPES.get((self.config.output.dtype or {}).get(key, "int32"), torch.int32)
