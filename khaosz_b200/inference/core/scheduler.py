@@ -59,11 +59,20 @@ class InferenceScheduler:
 
     # -- public ---------------------------------------------------------------------------------
     def add_task(self, prompt, **kwargs) -> str:
+        if self._fatal_error is not None:
+            # the loop is gone: close the stream at once instead of queueing a request nobody will serve
+            callback = kwargs.get("stream_callback")
+            if callback:
+                callback(STOP)
+            return "task_rejected"
         return self._task_mgr.add_task(prompt, **kwargs)
 
     def remove_task(self, task_id: str) -> None:
-        for task in self._task_mgr.remove_task(task_id):
-            self._page_cache.task_free(task.task_id)
+        """Withdraw a request (any thread): its stream is closed here, its pages are released by the
+        scheduler thread."""
+        task = self._task_mgr.cancel(task_id)
+        if task is not None and task.status == TaskStatus.ABORTED:
+            self._emit(task, STOP)
 
     def get_stats(self) -> Dict[str, Any]:
         stats = self._task_mgr.get_stats()

@@ -81,6 +81,7 @@ class TaskManager:
         self._lock = threading.Lock()
         self._total_tasks = 0
         self._total_tokens = 0
+        self._cancelled: Dict[str, None] = {}   # ids cancelled while their task was between the queue and the batch
         self._ttft: Deque[float] = deque(maxlen=RECENT)
         self._latency: Deque[float] = deque(maxlen=RECENT)
         self._itl: Deque[float] = deque(maxlen=RECENT)   # mean inter-token latency of each finished request
@@ -112,6 +113,35 @@ class TaskManager:
             self.waiting_queue = deque(t for t in self.waiting_queue if t.task_id != task_id)
             self.active_tasks = [t for t in self.active_tasks if t.task_id != task_id]
         return removed
+
+    def cancel(self, task_id: str) -> Optional[Task]:
+        """Withdraw a task from any thread and return it (``None`` if it is unknown or already done).
+        A waiting task leaves the queue; a running one is only marked ``ABORTED`` - the scheduler
+        thread, which owns the KV pages, collects it at its next clean-up, so no page is freed under a
+        step that is still using it."""
+        found: Optional[Task] = None
+        with self._lock:
+            for t in self.waiting_queue:
+                if t.task_id == task_id:
+                    found = t
+                    break
+            if found is not None:
+                self.waiting_queue = deque(t for t in self.waiting_queue if t.task_id != task_id)
+                found.status = TaskStatus.ABORTED
+            else:
+                for t in self.active_tasks:
+                    if t.task_id == task_id:
+                        if t.status == TaskStatus.RUNNING:
+                            t.status = TaskStatus.ABORTED
+                        found = t
+                        break
+            if found is None:
+                # between the queue and the batch right now, or finished long ago: remember the id for a while
+                self._cancelled[task_id] = None
+                while len(self._cancelled) > 1024:
+                    self._cancelled.pop(next(iter(self._cancelled)))
+        self._task_event.set()
+        return found
 
     def get_stats(self) -> Dict[str, Any]:
         return {"total_tasks": self._total_tasks, "total_tokens": self._total_tokens,
@@ -165,8 +195,9 @@ class TaskManager:
             return [self.waiting_queue.popleft() for _ in range(min(max(n, 0), len(self.waiting_queue)))]
 
     def activate(self, task: Task) -> None:
-        task.status = TaskStatus.RUNNING
         with self._lock:
+            cancelled = self._cancelled.pop(task.task_id, 0) is None
+            task.status = TaskStatus.ABORTED if cancelled else TaskStatus.RUNNING
             self.active_tasks.append(task)
 
     def return_to_waiting(self, tasks: List[Task]) -> None:

@@ -272,3 +272,39 @@ def test_shutdown_stops_the_loop_and_is_repeatable(tokenizer):
     thread.join(timeout=10)
     assert not thread.is_alive()
     eng.shutdown()
+
+
+def test_requests_after_a_crashed_loop_are_closed_at_once(tokenizer):
+    class Broken(AutoRegressiveLM):
+        def forward(self, *a, **k):
+            raise RuntimeError("boom")
+
+    eng = InferenceEngine(Broken(tiny_config(vocab_size=len(tokenizer))), tokenizer, max_batch_size=2, max_seq_len=32,
+                          page_size=4)
+    assert eng.generate("hello", max_tokens=4) == ""                  # the crash closes the first request
+    start = time.time()
+    assert eng.generate("hello again", max_tokens=4) == ""            # later ones do not wait for a dead loop
+    assert eng.generate(["a", "b"], max_tokens=4) == ["", ""] and time.time() - start < 5
+    eng.shutdown()
+
+
+def test_cancelling_a_running_request_closes_its_stream_and_frees_its_pages(engine):
+    sched = engine.scheduler
+    events, started = [], threading.Event()
+
+    def cb(token):
+        events.append(token)
+        started.set()
+
+    tid = sched.add_task("the quick brown fox", max_tokens=50, top_k=1, stream_callback=cb)
+    assert started.wait(timeout=30)
+    sched.remove_task(tid)
+    assert events[-1] is STOP
+    deadline = time.time() + 10
+    while sched.get_stats()["active_tasks"] and time.time() < deadline:
+        time.sleep(0.02)
+    time.sleep(0.05)
+    cache = sched._page_cache
+    assert sched.get_stats()["active_tasks"] == 0 and cache.free_pages() == cache._storage.n_pages
+    sched.remove_task(tid)                                            # cancelling again is harmless
+    sched.remove_task("task_never_existed")

@@ -330,3 +330,37 @@ def test_sample_with_per_row_parameters():
     k = torch.tensor([1, 2] * 50)
     out = sample(logits, temperature=torch.tensor([1.0, 0.5] * 50), top_k=k, top_p=torch.tensor([1.0, 0.9] * 50))
     assert set(out[0::2].tolist()) == {1} and set(out[1::2].tolist()) <= {2, 3}
+
+
+def test_cancel_withdraws_waiting_tasks_and_only_marks_running_ones():
+    tm = _manager()
+    a, b = tm.add_task([1]), tm.add_task([2])
+    running = tm.pull_candidates(1)[0]
+    tm.activate(running)
+    gone = tm.cancel(b)
+    assert gone.task_id == b and gone.status == TaskStatus.ABORTED and tm.get_waiting_tasks() == []
+    marked = tm.cancel(a)
+    assert marked is running and running.status == TaskStatus.ABORTED
+    assert tm.get_active_tasks() == [running]           # still listed: the scheduler thread frees its pages
+    assert tm.remove_finished_tasks([]) == [running] and tm.get_active_tasks() == []
+    assert tm.cancel(a) is None and tm.cancel("task_unknown") is None
+
+
+def test_cancel_reaches_a_task_that_is_being_admitted():
+    tm = _manager()
+    tid = tm.add_task([1])
+    pulled = tm.pull_candidates(1)[0]                   # neither waiting nor active at this moment
+    assert tm.cancel(tid) is None
+    tm.activate(pulled)
+    assert pulled.status == TaskStatus.ABORTED and tm.remove_finished_tasks([]) == [pulled]
+    other = tm.add_task([2])
+    fresh = tm.pull_candidates(1)[0]
+    tm.activate(fresh)
+    assert fresh.status == TaskStatus.RUNNING and other == fresh.task_id
+
+
+def test_cancelled_ids_do_not_pile_up():
+    tm = _manager()
+    for i in range(5000):
+        tm.cancel(f"task_gone_{i}")
+    assert len(tm._cancelled) <= 1024
