@@ -184,7 +184,7 @@ def test_loading_onto_an_already_wrapped_model_reuses_its_layers(tmp_path, caplo
     layer = b.layers[0].attention.q_proj
     with caplog.at_level(logging.WARNING):
         load_lora(b, str(tmp_path / "ad"))
-    assert b.layers[0].attention.q_proj is layer and float(layer.lora_B.mean()) == 0.5
+    assert b.layers[0].attention.q_proj is layer and float(layer.lora_B.detach().mean()) == 0.5
     assert "already has LoRA layers" in caplog.text
 
 
