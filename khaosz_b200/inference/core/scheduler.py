@@ -137,6 +137,9 @@ class InferenceScheduler:
             task.first_token_time = time.time()
         self._emit(task, self._task_mgr.tokenizer.decode([token]))
         if task.is_finished(stop_ids):
+            # finished before the stream closes: the client's release of the task (which may arrive the moment
+            # it sees STOP) must not turn a completed request into an aborted one in the statistics
+            task.status = TaskStatus.FINISHED
             self._emit(task, STOP)
 
     HEALTH_EVERY = 64         # decode steps between two reads of the kernels' error word

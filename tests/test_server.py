@@ -142,3 +142,75 @@ def test_metrics_endpoint_serves_prometheus_text(client):
     assert 'khaosz_b200_ttft_seconds_bucket{le="+Inf"} 5' in lines and "khaosz_b200_ttft_seconds_count 5" in lines
     buckets = [int(l.rsplit(" ", 1)[1]) for l in lines if l.startswith("khaosz_b200_ttft_seconds_bucket")]
     assert buckets == sorted(buckets)     # cumulative
+
+
+# ---- the real engine behind the HTTP routes ----
+@pytest.fixture
+def live_client(tokenizer):
+    import torch
+
+    from conftest import tiny_config
+    from khaosz_b200 import AutoRegressiveLM, InferenceEngine
+
+    torch.manual_seed(0)
+    model = AutoRegressiveLM(tiny_config(vocab_size=len(tokenizer))).eval()
+    engine = InferenceEngine(model, tokenizer, max_batch_size=4, max_seq_len=64, page_size=4)
+    app.state.server_config = {"_test": True}
+    app.state.engine = engine
+    with TestClient(app) as c:
+        yield c, engine
+    app.state.engine = None            # the app's shutdown hook has already stopped the engine
+
+
+def test_http_routes_with_a_real_engine_agree_with_direct_generation(live_client, tokenizer):
+    client, engine = live_client
+    messages = [{"role": "user", "content": "hello world"}]
+    prompt = tokenizer.apply_chat_template(messages, tokenize=False)
+    want = engine.generate(prompt, max_tokens=6, top_k=1)
+    body = client.post("/v1/chat/completions", json={"messages": messages, "max_tokens": 6, "top_k": 1}).json()
+    assert body["choices"][0]["message"]["content"] == want
+    assert body["usage"]["prompt_tokens"] == len(tokenizer.encode(prompt)) and 0 < body["usage"]["completion_tokens"] <= 6
+    streamed = client.post("/v1/chat/completions", json={"messages": messages, "max_tokens": 6, "top_k": 1, "stream": True})
+    text = "".join(e["choices"][0]["delta"].get("content", "") for e in _events(streamed.text) if "choices" in e)
+    assert text == want
+    msg = client.post("/v1/messages", json={"messages": messages, "max_tokens": 6, "top_k": 1}).json()
+    assert msg["content"][0]["text"] == want and msg["usage"]["output_tokens"] == body["usage"]["completion_tokens"]
+    import time
+
+    deadline = time.time() + 5                      # the scheduler collects a finished request at its next pass
+    while client.get("/stats").json()["active_tasks"] and time.time() < deadline:
+        time.sleep(0.02)
+    stats = client.get("/stats").json()
+    assert stats["total_tasks"] == 4 and stats["active_tasks"] == 0 and stats["ttft_p50_s"] is not None
+    assert stats["finished"] == 4 and stats["total_tokens"] == 4 * body["usage"]["completion_tokens"]
+    assert "khaosz_b200_ttft_seconds_count 4" in client.get("/metrics").text
+
+
+def test_http_requests_in_parallel_share_the_batch(live_client, tokenizer):
+    import threading
+
+    client, engine = live_client
+    prompts = ["hello world", "the quick brown fox", "this is a test", "the lazy dog", "hello", "world"]
+    want = {p: engine.generate(tokenizer.apply_chat_template([{"role": "user", "content": p}], tokenize=False),
+                               max_tokens=5, top_k=1) for p in prompts}
+    got, errors = {}, []
+
+    def call(p):
+        try:
+            r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": p}], "max_tokens": 5,
+                                                          "top_k": 1})
+            got[p] = r.json()["choices"][0]["message"]["content"]
+        except Exception as exc:  # pragma: no cover
+            errors.append(exc)
+
+    threads = [threading.Thread(target=call, args=(p,)) for p in prompts]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not errors and got == want
+    cache = engine.scheduler._page_cache
+    import time
+
+    time.sleep(0.1)
+    assert cache.free_pages() == cache._storage.n_pages
