@@ -105,8 +105,17 @@ class InferenceScheduler:
 
     # -- loop -----------------------------------------------------------------------------------
     def _emit(self, task: Task, item) -> None:
-        if task.stream_callback:
+        """Hand a token (or STOP) to the request's consumer.  A consumer that raises - an event loop
+        that was closed, a broken pipe - costs that request only: it is aborted, the loop goes on."""
+        if task.stream_callback is None:
+            return
+        try:
             task.stream_callback(item)
+        except Exception as exc:
+            log.warning("stream callback of %s failed (%s); the request is dropped", task.task_id, exc)
+            task.stream_callback = None
+            if task.status == TaskStatus.RUNNING:
+                task.status = TaskStatus.ABORTED
 
     def _drain(self) -> None:
         for task in self._task_mgr.get_active_tasks():

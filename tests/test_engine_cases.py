@@ -308,3 +308,43 @@ def test_cancelling_a_running_request_closes_its_stream_and_frees_its_pages(engi
     assert sched.get_stats()["active_tasks"] == 0 and cache.free_pages() == cache._storage.n_pages
     sched.remove_task(tid)                                            # cancelling again is harmless
     sched.remove_task("task_never_existed")
+
+
+def test_closing_a_stream_early_cancels_the_request(engine):
+    gen = engine.generate("the quick brown fox", stream=True, max_tokens=50, top_k=1)
+    first = next(gen)
+    assert isinstance(first, str)
+    gen.close()                                         # the consumer walks away
+    deadline = time.time() + 10
+    while engine.get_stats()["active_tasks"] and time.time() < deadline:
+        time.sleep(0.02)
+    time.sleep(0.05)
+    cache = engine.scheduler._page_cache
+    assert engine.get_stats()["active_tasks"] == 0 and cache.free_pages() == cache._storage.n_pages
+    assert engine.get_stats()["total_tokens"] < 50      # it did not run to the end
+
+
+def test_an_abandoned_async_stream_does_not_hurt_the_engine(engine):
+    async def take_one():
+        agen = engine.generate_async("the quick brown fox", max_tokens=50, top_k=1)
+        token = await agen.__anext__()
+        await agen.aclose()
+        return token
+
+    for _ in range(3):                                  # each run closes its event loop behind it
+        assert isinstance(asyncio.run(take_one()), str)
+    assert engine.scheduler._fatal_error is None
+    assert isinstance(engine.generate("hello", max_tokens=3, top_k=1), str)
+
+
+def test_a_failing_stream_callback_only_costs_its_own_request(engine):
+    def bad(token):
+        raise RuntimeError("consumer went away")
+
+    engine.scheduler.add_task("hello world", max_tokens=5, top_k=1, stream_callback=bad)
+    out = engine.generate("the lazy dog", max_tokens=4, top_k=1)
+    assert isinstance(out, str) and out and engine.scheduler._fatal_error is None
+    deadline = time.time() + 10
+    while engine.get_stats()["active_tasks"] and time.time() < deadline:
+        time.sleep(0.02)
+    assert engine.get_stats()["active_tasks"] == 0
