@@ -212,3 +212,13 @@ def test_sampler_set_replicas_changes_the_share():
     assert len(s) == 4
     s.set_replicas(2, 0)
     assert len(s) == 8 and list(s) == list(ResumableDistributedSampler(range(16), seed=1, num_replicas=2, rank=0))
+
+
+@pytest.mark.parametrize("method", ["fork", "spawn"])
+def test_memory_mapped_dataset_works_in_dataloader_workers(tmp_path, method):
+    _ramp(tmp_path / "d", 1000)
+    ds = DatasetFactory.load("seq", str(tmp_path / "d"), 16)
+    sampler = ResumableDistributedSampler(ds, seed=1, num_replicas=1, rank=0)
+    loader = DataLoader(ds, batch_size=4, sampler=sampler, num_workers=2, multiprocessing_context=method, prefetch_factor=2)
+    firsts = sorted(int(x) for batch in loader for x in batch["input_ids"][:, 0])
+    assert firsts == [i * 16 for i in range(len(ds))]                  # every window exactly once
