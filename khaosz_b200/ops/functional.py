@@ -426,10 +426,8 @@ def cross_entropy_rows(logits: torch.Tensor, targets: torch.Tensor, label_smooth
 def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, label_smoothing: float = 0.0,
                   ignore_index: int = -100) -> torch.Tensor:
     """Mean label-smoothed cross entropy over the non-ignored targets (``F.cross_entropy``
-    semantics, fp32 math, no fp32 copy of the logits)."""
-    if not use_kernels(logits):
-        return F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), targets.reshape(-1),
-                               label_smoothing=label_smoothing, ignore_index=ignore_index)
+    semantics, fp32 math, no fp32 copy of the logits).  A batch whose targets are all ignored gives
+    0 (``F.cross_entropy`` gives NaN there), so a fully masked micro-batch cannot poison a run."""
     rows = cross_entropy_rows(logits, targets, label_smoothing, ignore_index)
     count = (targets.reshape(-1) != ignore_index).sum().clamp_min(1)
     return rows.sum() / count

@@ -305,3 +305,18 @@ def test_iteration_counter_runs_across_epochs(tmp_path):
     Trainer(_config(tmp_path, dataset=RandomTokens(n=20), n_epoch=2, grad_accum_steps=2)).train()
     final = tmp_path / "ck" / "epoch_1_iter_10"
     assert json.loads((final / "meta.json").read_text())["iteration"] == 10
+
+
+def test_fully_masked_batches_give_zero_loss_and_zero_gradients(tiny_model):
+    ids = torch.randint(0, 300, (2, 9))
+    strat = StrategyFactory.create("sft", tiny_model, "cpu")
+    loss = strat({"input_ids": ids[:, :-1], "target_ids": ids[:, 1:], "loss_mask": torch.zeros(2, 8, dtype=torch.bool)})
+    assert loss.item() == 0.0
+    loss.backward()
+    assert all(p.grad is None or float(p.grad.abs().sum()) == 0.0 for p in tiny_model.parameters())
+    partly = torch.zeros(2, 8, dtype=torch.bool)
+    partly[0, 3:] = True
+    loss = strat({"input_ids": ids[:, :-1], "target_ids": ids[:, 1:], "loss_mask": partly})
+    logits = tiny_model(ids[:, :-1])["logits"]
+    want = F.cross_entropy(logits[0, 3:].float(), ids[0, 4:])
+    assert loss.item() == pytest.approx(want.item(), rel=1e-5)
