@@ -15,6 +15,7 @@ process group (objects with ``broadcast_object_list``, tensors one by one).
 from __future__ import annotations
 
 import json
+import os
 import time
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -44,9 +45,22 @@ def _share(read, broadcast: bool):
 
 
 # -- primitives ---------------------------------------------------------------------------
+def _atomically(path: PathLike, write) -> None:
+    """``write(tmp_path)`` then rename over ``path``: a reader (or a job restarted after a crash)
+    sees either the old file or the complete new one, never a torn write."""
+    target = Path(path)
+    tmp = target.with_name(target.name + ".tmp")
+    try:
+        write(tmp)
+        os.replace(tmp, target)
+    finally:
+        if tmp.exists():
+            tmp.unlink()
+
+
 def save_safetensors(state_dict: Dict[str, torch.Tensor], path: PathLike) -> None:
     tensors = {k: v.detach().contiguous().cpu() for k, v in state_dict.items()}
-    save_file(tensors, str(path))
+    _atomically(path, lambda tmp: save_file(tensors, str(tmp)))
 
 
 def load_safetensors(path: PathLike, broadcast: bool = False) -> Dict[str, torch.Tensor]:
@@ -54,7 +68,8 @@ def load_safetensors(path: PathLike, broadcast: bool = False) -> Dict[str, torch
 
 
 def save_json(data: dict, path: PathLike) -> None:
-    Path(path).write_text(json.dumps(data, indent=2, ensure_ascii=False), encoding="utf-8")
+    text = json.dumps(data, indent=2, ensure_ascii=False)
+    _atomically(path, lambda tmp: tmp.write_text(text, encoding="utf-8"))
 
 
 def load_json(path: PathLike, broadcast: bool = False) -> dict:
@@ -62,7 +77,7 @@ def load_json(path: PathLike, broadcast: bool = False) -> dict:
 
 
 def save_torch(obj: Any, path: PathLike) -> None:
-    torch.save(obj, str(path))
+    _atomically(path, lambda tmp: torch.save(obj, str(tmp)))
 
 
 def load_torch(path: PathLike, broadcast: bool = False) -> Any:
@@ -116,11 +131,12 @@ class Checkpoint:
         if _rank() != 0:
             return
         stamp = {"epoch": self.epoch, "iteration": self.iteration, "timestamp": time.strftime("%Y-%m-%dT%H:%M:%S")}
-        save_json({**stamp, **self.meta}, root / META_FILE)
         save_json(self.config, root / CONFIG_FILE)
         save_safetensors(self.state_dict, root / WEIGHTS_FILE)
         for name, payload in self.extra.items():
             save_torch(payload, root / f"{name}.pt")
+        # last: its presence says that everything else is complete (what an automatic resume looks for)
+        save_json({**stamp, **self.meta}, root / META_FILE)
 
     @classmethod
     def load(cls, save_dir: str, broadcast: bool = False) -> "Checkpoint":

@@ -140,3 +140,34 @@ def _two_rank_ckpt(path):
 def test_checkpoint_two_ranks(tmp_path):
     spawn_parallel_fn(_two_rank_ckpt, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29611",
                       path=str(tmp_path / "ck2"))
+
+
+def test_checkpoint_files_are_written_atomically_and_meta_comes_last(tmp_path, monkeypatch):
+    import khaosz_b200.serialization as ser
+
+    order = []
+    real_replace = os.replace
+
+    def spy(src, dst):
+        order.append(os.path.basename(str(dst)))
+        assert str(src).endswith(".tmp") and os.path.exists(src)
+        real_replace(src, dst)
+
+    monkeypatch.setattr(ser.os, "replace", spy)
+    ck = Checkpoint(state_dict={"w": torch.ones(3)}, epoch=1, iteration=7, extra={"optimizer": {"lr": 0.1}},
+                    config={"dim": 8}, meta={"completed_iteration": 6})
+    ck.save(str(tmp_path / "ck"))
+    assert order[-1] == "meta.json" and set(order) == {"config.json", "model.safetensors", "optimizer.pt", "meta.json"}
+    assert not [p for p in os.listdir(tmp_path / "ck") if p.endswith(".tmp")]
+    meta = json.loads((tmp_path / "ck" / "meta.json").read_text())
+    assert meta["epoch"] == 1 and meta["iteration"] == 7 and meta["completed_iteration"] == 6 and "timestamp" in meta
+
+    # a write that dies half-way leaves the previous file intact and no debris
+    def boom(tmp):
+        tmp.write_text("partial")
+        raise OSError("disk full")
+
+    with pytest.raises(OSError):
+        ser._atomically(tmp_path / "ck" / "meta.json", boom)
+    assert json.loads((tmp_path / "ck" / "meta.json").read_text())["iteration"] == 7
+    assert not [p for p in os.listdir(tmp_path / "ck") if p.endswith(".tmp")]
