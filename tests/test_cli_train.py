@@ -146,3 +146,51 @@ def test_cli_lora_run_trains_adapters_only_and_saves_them(tmp_path):
         train_cli.train(train_cli.parse_args([
             "--train_type", "seq", "--data_root_path", str(data), "--param_path", str(params), "--ckpt_dir", str(ckpt),
             "--nprocs", "2", "--parallel_mode", "tp", "--lora_r", "4"]))
+
+
+def _two_rank_config(tmp_path, mode):
+    from conftest import RandomTokens, tiny_config
+    from khaosz_b200 import TrainConfig
+
+    cfg = tiny_config(n_heads=4, n_kv_heads=2)
+    return TrainConfig(model_fn=_TinyFactory(cfg), strategy="seq", dataset=RandomTokens(n=48),
+                       optimizer_fn=_adamw, scheduler_fn=_cosine, batch_per_device=4, grad_accum_steps=2,
+                       ckpt_dir=str(tmp_path / "ck"), log_dir=str(tmp_path / "logs"), ckpt_interval=1000, log_interval=1,
+                       device_type="cpu", backend="gloo", nprocs=2, parallel_mode=mode, master_addr="127.0.0.1",
+                       master_port="29662" if mode == "ddp" else "29663", val_split=0.25, val_step=1,
+                       metrics=["loss", "lr", "val_loss", "tokens_per_s"])
+
+
+class _TinyFactory:
+    """Picklable model factory (the trainer spawns its ranks)."""
+
+    def __init__(self, cfg):
+        self.cfg = cfg
+
+    def __call__(self):
+        torch.manual_seed(0)
+        return AutoRegressiveLM(self.cfg)
+
+
+def _adamw(model):
+    from khaosz_b200.trainer import FusedAdamW
+
+    return FusedAdamW(model.parameters(), lr=1e-3)
+
+
+def _cosine(opt):
+    from khaosz_b200.trainer import SchedulerFactory
+
+    return SchedulerFactory.create(opt, "cosine", warmup_steps=2, lr_decay_steps=20)
+
+
+@pytest.mark.parametrize("mode", ["ddp", "fsdp"])
+def test_trainer_with_validation_on_two_ranks(tmp_path, mode):
+    from khaosz_b200.trainer import Trainer
+
+    Trainer(_two_rank_config(tmp_path, mode)).train()
+    rows = [json.loads(line) for f in sorted(os.listdir(tmp_path / "logs")) for line in open(tmp_path / "logs" / f)]
+    assert rows and rows[-1]["val_loss"] > 0 and rows[-1]["tokens_per_s"] > 0
+    # 36 training samples over two ranks, four per micro-batch: five iterations each (the last one padded)
+    final = sorted(d for d in os.listdir(tmp_path / "ck") if d.startswith("epoch_"))[-1]
+    assert (tmp_path / "ck" / final / "optimizer.pt").exists()
