@@ -70,3 +70,56 @@ def test_cli_reference_lists_every_flag():
         flags = set(re.findall(r"(?<![\w-])--[a-z][\w-]*", buf.getvalue()))
         missing = sorted(f for f in flags if f not in body)
         assert not missing, f"docs/cli.md section of {tool} lacks {missing}"
+
+
+def _mmlu_dir(tmp_path):
+    root = tmp_path / "mmlu"
+    rows = [["the quick brown fox is", "A) lazy", "B) quick", "C) a dog", "D) hello", "B"],
+            ["hello world is a", "test", "corpus", "question", "answer", "A"],
+            ["this is a small", "world", "dog", "test", "fox", "C"]]
+    for split, subset in (("dev", rows[:2]), ("test", rows)):
+        (root / split).mkdir(parents=True)
+        for subject in ("toy_logic", "toy_words"):
+            with open(root / split / f"{subject}_{split}.csv", "w", encoding="utf-8") as fh:
+                fh.write("question,A,B,C,D,answer\n")            # a header line is tolerated
+                for r in subset:
+                    fh.write(",".join(r) + "\n")
+    return root
+
+
+def test_mmlu_tool_scores_every_question_and_writes_a_summary(param_dir, tmp_path):
+    from khaosz_b200.cli import evaluate_mmlu as tool
+
+    data = _mmlu_dir(tmp_path)
+    rows = tool.load_csv(str(data / "test" / "toy_logic_test.csv"))
+    assert len(rows) == 3 and rows[0]["B"] == "quick" and rows[0]["answer"] == "B" and rows[1]["A"] == "test"
+    prompt = tool.build_prompt(rows[2]["question"], rows[2], "toy logic", 1, rows[:2])
+    assert prompt.startswith("The following are multiple choice questions (with answers) about toy logic.")
+    assert prompt.count("Answer:") == 2 and prompt.endswith("Answer:") and "Answer: B\n" in prompt
+    assert tool.build_prompt(rows[2]["question"], rows[2], "toy logic", 0, rows[:2]).count("Question:") == 1
+    out = tmp_path / "mmlu.json"
+    summary = tool.run(tool.parse_args(["--param_path", str(param_dir), "--data_dir", str(data), "--n_shot", "2",
+                                        "--device", "cpu", "--dtype", "float32", "--output", str(out)]))
+    assert summary["total"] == 6 and set(summary["subjects"]) == {"toy_logic", "toy_words"}
+    assert 0.0 <= summary["average"] <= 1.0 and summary["correct"] == sum(s["correct"] for s in summary["subjects"].values())
+    assert json.loads(out.read_text()) == summary
+    one = tool.run(tool.parse_args(["--param_path", str(param_dir), "--data_dir", str(data), "--subjects", "toy_words",
+                                    "--split", "test", "--device", "cpu", "--dtype", "float32", "--n_shot", "0"]))
+    assert one["total"] == 3 and list(one["subjects"]) == ["toy_words"]
+
+
+def test_mmlu_choice_scores_are_the_log_likelihoods_of_the_letters(param_dir, tokenizer):
+    from khaosz_b200 import AutoModel
+    from khaosz_b200.cli.evaluate_mmlu import choice_logprobs
+
+    model = AutoModel.from_pretrained(str(param_dir)).eval()
+    context = tokenizer.encode("hello world this is a test")
+    scores = choice_logprobs(model, tokenizer, context, "cpu")
+    assert set(scores) == {"A", "B", "C", "D"}
+    for letter in "AD":
+        cont = tokenizer.encode(f" {letter}", add_special_tokens=False)
+        ids = torch.tensor([context + cont])
+        with torch.no_grad():
+            lp = torch.log_softmax(model(ids[:, :-1])["logits"][0].float(), dim=-1)
+        want = sum(float(lp[len(context) - 1 + j, tok]) for j, tok in enumerate(cont))
+        assert scores[letter] == pytest.approx(want, abs=1e-4)
