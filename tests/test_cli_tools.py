@@ -123,3 +123,23 @@ def test_mmlu_choice_scores_are_the_log_likelihoods_of_the_letters(param_dir, to
             lp = torch.log_softmax(model(ids[:, :-1])["logits"][0].float(), dim=-1)
         want = sum(float(lp[len(context) - 1 + j, tok]) for j, tok in enumerate(cont))
         assert scores[letter] == pytest.approx(want, abs=1e-4)
+
+
+def test_perplexity_of_a_padded_batch_equals_the_per_text_value(param_dir, tokenizer):
+    import math
+
+    from khaosz_b200 import AutoModel
+    from khaosz_b200.cli.perplexity import batch_perplexity
+
+    model = AutoModel.from_pretrained(str(param_dir)).eval()
+    texts = ["hello world this is a small test corpus", "the lazy dog", "hello"]
+    got = batch_perplexity(model, tokenizer, texts, "cpu")
+    for text, ppl in zip(texts, got):
+        ids = torch.tensor([tokenizer.encode(text)])
+        if ids.shape[1] < 2:
+            assert ppl == 1.0                           # nothing to predict
+            continue
+        with torch.no_grad():
+            lp = torch.log_softmax(model(ids[:, :-1])["logits"][0].float(), dim=-1)
+        nll = -lp.gather(-1, ids[0, 1:, None]).mean()
+        assert ppl == pytest.approx(math.exp(float(nll)), rel=1e-4)
