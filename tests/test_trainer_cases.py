@@ -279,3 +279,20 @@ def test_only_on_rank_without_a_process_group_runs_on_the_single_rank():
         calls.append("never")
 
     assert f(21) == 42 and g() is None and calls == [21]
+
+
+def test_accumulation_groups_run_across_the_epoch_boundary(tmp_path):
+    """Five micro-batches per epoch with two per optimizer step: the fifth of the first epoch is
+    grouped with the first of the second (the micro-step counter is global), five steps in total."""
+    steps = []
+
+    class Count:
+        def on_optimizer_step(self, ctx):
+            steps.append((ctx.epoch, ctx.iteration))
+
+    Trainer(_config(tmp_path, dataset=RandomTokens(n=20), n_epoch=2, grad_accum_steps=2), callbacks=[Count()]).train()
+    assert steps == [(0, 2), (0, 4), (1, 6), (1, 8), (1, 10)]
+    from khaosz_b200.serialization import Checkpoint
+
+    opt = Checkpoint.load(str(tmp_path / "ck" / "epoch_1_iter_10")).extra["optimizer"]
+    assert {int(st["step"]) for st in opt["state"].values()} == {5}
