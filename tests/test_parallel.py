@@ -555,3 +555,41 @@ def test_grpo_under_tensor_parallel_matches_single_process(tmp_path):
     assert abs(ref[-1]) > 1e-6          # the policy has moved away from the reference copy
     for k, v in model.state_dict().items():
         assert torch.allclose(got["sd"][k], v, rtol=1e-3, atol=3e-4), k
+
+
+# ---- the optimizer state of a single-process run loads into tensor-parallel / fully sharded runs ----
+def _dense_state_into_sharded_case(path, mode):
+    from khaosz_b200.trainer import FusedAdamW
+
+    dense = torch.load(path, weights_only=False)
+    model = _make_model()
+    ex = ExecutorFactory.create(mode, grad_accum_steps=1)
+    opt = FusedAdamW(model.parameters(), lr=1e-3)
+    model, opt, _, _ = ex.prepare(model, opt, None, None)
+    opt.load_state_dict(dense)                           # every rank takes its slices
+    back = opt.state_dict()                              # collective: reassembled to the dense layout
+    assert len(back["state"]) == len(dense["state"])
+    for i, st in dense["state"].items():
+        assert torch.equal(back["state"][i]["exp_avg"], st["exp_avg"]), i
+        assert torch.equal(back["state"][i]["exp_avg_sq"], st["exp_avg_sq"]), i
+        assert int(back["state"][i]["step"]) == int(st["step"])
+    assert back["param_groups"][0]["lr"] == dense["param_groups"][0]["lr"]
+    dist.barrier()
+
+
+@pytest.mark.parametrize("mode,port", [("tp", "29656"), ("fsdp_full", "29657")])
+def test_dense_optimizer_state_loads_into_sharded_runs(mode, port, tmp_path):
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    model = _make_model()
+    opt = FusedAdamW(model.parameters(), lr=1e-3)
+    strat = StrategyFactory.create("seq", model, "cpu")
+    data = torch.randint(0, 1000, (2, 4, 65), generator=torch.Generator().manual_seed(1))
+    for i in range(2):
+        strat({"input_ids": data[i, :, :-1], "target_ids": data[i, :, 1:]}).backward()
+        opt.step()
+        opt.zero_grad()
+    path = str(tmp_path / "dense_opt.pt")
+    torch.save(opt.state_dict(), path)
+    spawn_parallel_fn(_dense_state_into_sharded_case, world_size=2, backend="gloo", master_addr="127.0.0.1",
+                      master_port=port, path=path, mode=mode)
