@@ -9,7 +9,6 @@ cosine over the number of optimizer steps.
 from __future__ import annotations
 
 import argparse
-import json
 import logging
 import os
 from functools import partial
@@ -23,6 +22,7 @@ from ..models.components.block import DecoderBlock
 from ..models.components.lora import LoRAConfig
 from ..parallel.fsdp_model import ShardedBlock
 from ..parallel.tp_model import TPBlock
+from ..serialization import find_latest_checkpoint
 from ..trainer import CallbackFactory, FusedAdamW, Muon, SchedulerFactory, Trainer
 
 log = logging.getLogger(__name__)
@@ -98,28 +98,6 @@ def compute_total_steps(dataset_len: int, n_epoch: int, batch_per_device: int, n
     per_rank = -(-dataset_len // nprocs)
     batches = -(-per_rank // batch_per_device)
     return (batches // grad_accum_steps) * n_epoch
-
-
-def find_latest_checkpoint(ckpt_dir: str):
-    """``(directory, meta)`` of the newest complete checkpoint under ``ckpt_dir`` (ordered by epoch, then
-    iteration), or ``None``.  The reference resumes only from a directory and a position given by hand
-    (``scripts/tools/train.py:144-149``); an emergency checkpoint written by the error path counts too."""
-    best = None
-    if not os.path.isdir(ckpt_dir):
-        return None
-    for name in os.listdir(ckpt_dir):
-        root = os.path.join(ckpt_dir, name)
-        if not (os.path.isfile(os.path.join(root, "meta.json")) and os.path.isfile(os.path.join(root, "model.safetensors"))):
-            continue
-        try:
-            with open(os.path.join(root, "meta.json")) as fh:
-                meta = json.load(fh)
-        except (OSError, ValueError):       # a checkpoint that was being written when the job died
-            continue
-        key = (int(meta.get("epoch", 0)), int(meta.get("iteration", 0)))
-        if best is None or key > best[0]:
-            best = (key, root, meta)
-    return None if best is None else (best[1], best[2])
 
 
 def train(args: argparse.Namespace) -> None:

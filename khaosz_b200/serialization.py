@@ -145,3 +145,25 @@ class Checkpoint:
         extra = {p.stem: load_torch(p, broadcast) for p in sorted(root.glob("*.pt"))}
         return cls(state_dict=load_state_dict(root / WEIGHTS_FILE, broadcast=broadcast), epoch=meta.get("epoch", 0),
                    iteration=meta.get("iteration", 0), extra=extra, config=load_json(root / CONFIG_FILE, broadcast))
+
+
+def find_latest_checkpoint(ckpt_dir: str):
+    """``(directory, meta)`` of the newest complete checkpoint under ``ckpt_dir`` (ordered by epoch, then
+    iteration), or ``None``.  The reference resumes only from a directory and a position given by hand
+    (``scripts/tools/train.py:144-149``); an emergency checkpoint written by the error path counts too."""
+    best = None
+    if not os.path.isdir(ckpt_dir):
+        return None
+    for name in os.listdir(ckpt_dir):
+        root = os.path.join(ckpt_dir, name)
+        if not (os.path.isfile(os.path.join(root, META_FILE)) and os.path.isfile(os.path.join(root, WEIGHTS_FILE))):
+            continue
+        try:
+            with open(os.path.join(root, META_FILE)) as fh:
+                meta = json.load(fh)
+        except (OSError, ValueError):       # a checkpoint that was being written when the job died
+            continue
+        key = (int(meta.get("epoch", 0)), int(meta.get("iteration", 0)))
+        if best is None or key > best[0]:
+            best = (key, root, meta)
+    return None if best is None else (best[1], best[2])
