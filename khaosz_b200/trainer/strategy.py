@@ -179,7 +179,13 @@ class GRPOStrategy(BaseStrategy):
 
     def sync_ref_model(self) -> None:
         state = self.executor.unwrap_model(self.model) if self.executor is not None else self.model.state_dict()
-        self.ref_model.load_state_dict(state)
+        if hasattr(self.ref_model, "scatter_named"):     # sliced / sharded copy: every rank takes its own pieces
+            pieces = self.ref_model.scatter_named(state)
+            with torch.no_grad():
+                for p in self.ref_model.parameters():
+                    p.copy_(pieces[id(p)])
+        else:
+            self.ref_model.load_state_dict(state)
 
     def _fold(self, batch):
         prompts, responses, masks, rewards = batch["prompts"], batch["responses"], batch["masks"], batch["rewards"]
