@@ -467,6 +467,17 @@ def _sharded_ref_case(mode):
     assert held < 0.6 * dense                                # two ranks: about half of every block
     # policy == reference before the first update: the DPO loss is log 2
     assert loss.item() == pytest.approx(0.6931, abs=2e-3)
+    # GRPO refreshes its old-policy copy in place: after a refresh it holds the updated weights, piece by piece
+    grpo = StrategyFactory.create("grpo", model, "cpu", executor=ex, model_fn=_make_model, group_size=4, sync_interval=1)
+    before = [p.detach().clone() for p in grpo.ref_model.parameters()]
+    with torch.no_grad():
+        for prm in model.parameters():                                       # the policy moves on
+            prm.add_(0.01)
+    grpo.sync_ref_model()
+    after = list(grpo.ref_model.parameters())
+    assert all(not torch.equal(a, b) for a, b in zip(after, before))
+    for mine, pol in zip(grpo.ref_model.layers.parameters(), model.layers.parameters()):
+        assert torch.equal(mine, pol)
 
 
 @pytest.mark.parametrize("mode,port", [("tp", "29652"), ("fsdp_full", "29653")])
