@@ -416,7 +416,7 @@ def _fs_variant_case(out, variant="gqa"):
     dist.barrier()   # leave together: a rank that tears gloo down while its peer still writes aborts the peer
 
 
-@pytest.mark.parametrize("variant,port", [("gqa", "29647"), ("mla_moe", "29651")])
+@pytest.mark.parametrize("variant,port", [("gqa", "29647"), ("mla_moe", "29681")])
 def test_full_shard_qk_norm_and_gate_match_the_dense_model(variant, port, tmp_path):
     out = str(tmp_path / "fs_variant.pt")
     spawn_parallel_fn(_fs_variant_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port=port, out=out,
@@ -480,7 +480,7 @@ def _sharded_ref_case(mode):
         assert torch.equal(mine, pol)
 
 
-@pytest.mark.parametrize("mode,port", [("tp", "29652"), ("fsdp_full", "29653")])
+@pytest.mark.parametrize("mode,port", [("tp", "29682"), ("fsdp_full", "29683")])
 def test_frozen_reference_model_is_sharded_like_the_policy(mode, port):
     spawn_parallel_fn(_sharded_ref_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port=port, mode=mode)
 
@@ -513,7 +513,7 @@ def _sft_tp_case():
 
 
 def test_sft_under_tensor_parallel_weights_uneven_masks_exactly():
-    spawn_parallel_fn(_sft_tp_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29654")
+    spawn_parallel_fn(_sft_tp_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29684")
 
 
 # ---- GRPO under tensor parallelism ----
@@ -543,7 +543,7 @@ def _grpo_tp_case(out, sync_interval=100):
         torch.save({"losses": losses, "sd": sd}, out)
 
 
-@pytest.mark.parametrize("sync_interval,port", [(100, "29655"), (2, "29658")])   # 2: the old-policy copy is refreshed mid-run
+@pytest.mark.parametrize("sync_interval,port", [(100, "29685"), (2, "29688")])   # 2: the old-policy copy is refreshed mid-run
 def test_grpo_under_tensor_parallel_matches_single_process(sync_interval, port, tmp_path):
     from khaosz_b200.trainer import FusedAdamW, StrategyFactory
 
@@ -590,7 +590,7 @@ def _dense_state_into_sharded_case(path, mode):
     dist.barrier()
 
 
-@pytest.mark.parametrize("mode,port", [("tp", "29656"), ("fsdp_full", "29657")])
+@pytest.mark.parametrize("mode,port", [("tp", "29686"), ("fsdp_full", "29687")])
 def test_dense_optimizer_state_loads_into_sharded_runs(mode, port, tmp_path):
     from khaosz_b200.trainer import FusedAdamW, StrategyFactory
 
