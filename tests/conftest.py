@@ -11,7 +11,14 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
 
 
+TEST_TIMEOUT_S = 900   # no single test may hold a run longer than this (needs the pytest-timeout plugin)
+
+
 def pytest_collection_modifyitems(config, items):
+    if config.pluginmanager.hasplugin("timeout"):
+        for item in items:
+            if item.get_closest_marker("timeout") is None:
+                item.add_marker(pytest.mark.timeout(TEST_TIMEOUT_S))
     if torch.cuda.is_available():
         return
     skip = pytest.mark.skip(reason="no CUDA device")
