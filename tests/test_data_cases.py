@@ -214,8 +214,7 @@ def test_sampler_set_replicas_changes_the_share():
     assert len(s) == 8 and list(s) == list(ResumableDistributedSampler(range(16), seed=1, num_replicas=2, rank=0))
 
 
-@pytest.mark.parametrize("method", ["fork", "spawn"])
-def test_memory_mapped_dataset_works_in_dataloader_workers(tmp_path, method):
+def test_memory_mapped_dataset_works_in_dataloader_workers(tmp_path, method="spawn"):
     _ramp(tmp_path / "d", 1000)
     ds = DatasetFactory.load("seq", str(tmp_path / "d"), 16)
     sampler = ResumableDistributedSampler(ds, seed=1, num_replicas=1, rank=0)
