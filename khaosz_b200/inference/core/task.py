@@ -95,7 +95,8 @@ class TaskManager:
         if len(ids) > self.max_prompt_len:
             ids = ids[-self.max_prompt_len:]
         room = self.max_seq_len - len(ids)
-        if room <= 0:
+        if room <= 0 or not ids or (max_tokens is not None and max_tokens <= 0):
+            # nothing can be generated: no room left, nothing to condition on, or nothing asked for
             if stream_callback:
                 stream_callback(STOP)
             return task_id

@@ -348,3 +348,12 @@ def test_a_failing_stream_callback_only_costs_its_own_request(engine):
     while engine.get_stats()["active_tasks"] and time.time() < deadline:
         time.sleep(0.02)
     assert engine.get_stats()["active_tasks"] == 0
+
+
+def test_requests_with_nothing_to_do_return_at_once_and_do_not_hurt_the_loop(engine):
+    assert engine.generate([], max_tokens=3) == []
+    assert engine.generate("", max_tokens=3, top_k=1) == ""              # an empty prompt: nothing to condition on
+    assert engine.generate("hello", max_tokens=0, top_k=1) == ""
+    assert engine.generate(["", "hello world"], max_tokens=3, top_k=1)[0] == ""
+    assert engine.scheduler._fatal_error is None
+    assert engine.generate("hello world", max_tokens=3, top_k=1) != ""

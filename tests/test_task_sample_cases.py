@@ -364,3 +364,12 @@ def test_cancelled_ids_do_not_pile_up():
     for i in range(5000):
         tm.cancel(f"task_gone_{i}")
     assert len(tm._cancelled) <= 1024
+
+
+def test_empty_prompts_and_zero_budgets_are_closed_without_queueing():
+    tm = _manager()
+    seen = []
+    tm.add_task([], stream_callback=seen.append)
+    tm.add_task("", stream_callback=seen.append)
+    tm.add_task([1, 2], max_tokens=0, stream_callback=seen.append)
+    assert seen == [STOP, STOP, STOP] and tm.get_waiting_tasks() == [] and tm.get_stats()["total_tasks"] == 0
