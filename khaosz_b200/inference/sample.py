@@ -105,7 +105,15 @@ class SamplingPipeline(BaseSamplingStrategy):
 
     @torch.no_grad()
     def sample(self, logits: Tensor, filter_value: float = NEG_INF) -> Tensor:
-        probs = torch.softmax(self.apply(logits, filter_value), dim=-1)
+        filtered = self.apply(logits, filter_value)
+        probs = torch.softmax(filtered, dim=-1)
+        broken = ~torch.isfinite(probs).all(dim=-1)
+        if bool(broken.any()):
+            # a row with NaN or +inf logits has no distribution to draw from: take its largest finite-or-inf
+            # entry instead of failing the whole batch (``multinomial`` raises on such rows)
+            safe = torch.nan_to_num(filtered[broken], nan=float("-inf"))
+            probs = probs.clone()
+            probs[broken] = torch.nn.functional.one_hot(safe.argmax(dim=-1), probs.shape[-1]).to(probs.dtype)
         return torch.multinomial(probs, num_samples=1).squeeze(-1)
 
 

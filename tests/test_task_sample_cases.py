@@ -373,3 +373,12 @@ def test_empty_prompts_and_zero_budgets_are_closed_without_queueing():
     tm.add_task("", stream_callback=seen.append)
     tm.add_task([1, 2], max_tokens=0, stream_callback=seen.append)
     assert seen == [STOP, STOP, STOP] and tm.get_waiting_tasks() == [] and tm.get_stats()["total_tasks"] == 0
+
+
+def test_rows_with_nan_or_infinite_logits_do_not_fail_the_batch():
+    torch.manual_seed(0)
+    logits = torch.randn(3, 20)
+    logits[0, 7] = float("inf")
+    logits[1, 2] = float("nan")
+    out = sample(logits)
+    assert out[0] == 7 and out[1] == logits[1].nan_to_num(nan=float("-inf")).argmax() and 0 <= int(out[2]) < 20
