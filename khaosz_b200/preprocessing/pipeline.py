@@ -70,10 +70,14 @@ class Pipeline:
                     if not line.strip():
                         continue
                     try:
-                        yield json.loads(line)
+                        item = json.loads(line)
                     except ValueError:       # one damaged record must not cost the whole corpus
+                        item = None
+                    if isinstance(item, dict):
+                        yield item
+                    else:
                         self.skipped_lines += 1
-                        log.warning("%s:%d is not valid JSON; skipped", path, number)
+                        log.warning("%s:%d is not a JSON object; skipped", path, number)
 
     def _dtype(self, key: str) -> torch.dtype:
         return DTYPES.get((self.config.output.dtype or {}).get(key, "int32"), torch.int32)

@@ -255,6 +255,7 @@ def test_pipeline_starts_a_new_shard_at_the_token_limit(tokenizer_dir, tokenizer
 def test_pipeline_reads_several_files_and_skips_bad_lines(tokenizer_dir, tmp_path):
     a = _write(tmp_path / "a.jsonl", [{"text": "the quick brown fox jumps"}])
     b = tmp_path / "b.jsonl"
-    b.write_text(json.dumps({"text": "hello world this is a test"}) + "\n\nnot json at all\n" + json.dumps({"text": "the lazy dog"}) + "\n")
+    b.write_text(json.dumps({"text": "hello world this is a test"}) + "\n\nnot json at all\n[1, 2, 3]\n42\n"
+                 + json.dumps({"text": "the lazy dog"}) + "\n")
     job = Pipeline(_cfg(TEXT), [a, str(b)], str(tmp_path / "out"), tokenizer_dir)
-    assert job.run() == 3 and job.skipped_lines == 1
+    assert job.run() == 3 and job.skipped_lines == 3          # damaged text, a list and a number are not records
