@@ -52,6 +52,8 @@ class SectionedMaskBuilder(BaseMaskBuilder):
     def _chat_section(self, messages, action: str, config, tokenizer) -> List[Tuple[List[int], int]]:
         pieces = []
         for msg in messages:
+            if not isinstance(msg, dict):        # a malformed turn is dropped, the rest of the dialogue kept
+                continue
             text = tokenizer.apply_chat_template([msg], tokenize=False, add_generation_prompt=False)
             ids = tokenizer.encode(text, add_special_tokens=False)
             pieces.append((ids, int(resolve_action(action, msg.get("role", ""), config) == "train")))

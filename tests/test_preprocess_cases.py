@@ -259,3 +259,11 @@ def test_pipeline_reads_several_files_and_skips_bad_lines(tokenizer_dir, tmp_pat
                  + json.dumps({"text": "the lazy dog"}) + "\n")
     job = Pipeline(_cfg(TEXT), [a, str(b)], str(tmp_path / "out"), tokenizer_dir)
     assert job.run() == 3 and job.skipped_lines == 3          # damaged text, a list and a number are not records
+
+
+def test_malformed_turns_are_dropped_and_the_dialogue_kept(tokenizer):
+    good = SectionedMaskBuilder().build(TALK, _cfg(CHAT), tokenizer)
+    noisy = {"messages": [TALK["messages"][0], "not a turn", None, *TALK["messages"][1:]]}
+    assert SectionedMaskBuilder().build(noisy, _cfg(CHAT), tokenizer) == good
+    assert SectionedMaskBuilder().build({"messages": ["only junk", 7]}, _cfg(CHAT), tokenizer) is None
+    assert SectionedMaskBuilder().build({"text": 12345}, _cfg(TEXT), tokenizer)["sequence"] == tokenizer.encode("12345")
