@@ -214,3 +214,26 @@ def test_http_requests_in_parallel_share_the_batch(live_client, tokenizer):
 
     time.sleep(0.1)
     assert cache.free_pages() == cache._storage.n_pages
+
+
+def test_odd_requests_get_an_answer_and_leave_the_engine_alive(live_client):
+    client, engine = live_client
+    ok = {"messages": [{"role": "user", "content": "hello world"}], "max_tokens": 3, "top_k": 1}
+    odd = [
+        {"messages": [], "max_tokens": 3},                                          # nothing to condition on
+        {"messages": [{"role": "user", "content": ""}], "max_tokens": 3},
+        {"messages": [{"role": "user", "content": "hello " * 400}], "max_tokens": 5},  # longer than the engine's window
+        {**ok, "max_tokens": 100000},                                               # clamped to the room that is left
+        {**ok, "stop": ""}, {**ok, "stop": ["", "zzz"]},                            # empty stop strings never match
+        {**ok, "temperature": 0.0},                                                 # allowed by the schema: clamped
+        {**ok, "top_p": 0.0},
+    ]
+    for body in odd:
+        r = client.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200, (body, r.text)
+        assert isinstance(r.json()["choices"][0]["message"]["content"], str)
+        s = client.post("/v1/chat/completions", json={**body, "stream": True})
+        assert s.status_code == 200 and s.text.rstrip().endswith("data: [DONE]")
+    assert client.post("/v1/messages", json={"messages": [{"role": "user", "content": []}], "max_tokens": 3}).status_code == 200
+    assert engine.scheduler._fatal_error is None
+    assert client.post("/v1/chat/completions", json=ok).json()["choices"][0]["message"]["content"] != ""
