@@ -135,6 +135,11 @@ class TrainContextBuilder:
             self._resume(ctx, model)
         if cfg.lora is not None:
             inject_lora(model, r=cfg.lora.r, alpha=cfg.lora.alpha, target_modules=set(cfg.lora.target_modules))
+            if ctx.checkpoint is not None:
+                # the adapters did not exist yet when the checkpoint's weights were loaded above
+                adapters = {k: v for k, v in ctx.checkpoint.state_dict.items() if k.rpartition(".")[2] in ("lora_A", "lora_B")}
+                if adapters:
+                    model.load_state_dict(adapters, strict=False)
         ctx.optimizer = cfg.optimizer_fn(model)
         ctx.scheduler = cfg.scheduler_fn(ctx.optimizer)
 

@@ -194,3 +194,26 @@ def test_trainer_with_validation_on_two_ranks(tmp_path, mode):
     # 36 training samples over two ranks, four per micro-batch: five iterations each (the last one padded)
     final = sorted(d for d in os.listdir(tmp_path / "ck") if d.startswith("epoch_"))[-1]
     assert (tmp_path / "ck" / final / "optimizer.pt").exists()
+
+
+def test_resuming_a_lora_run_keeps_the_adapters(tmp_path):
+    cfg, params, data = _setup(tmp_path)
+    torch.manual_seed(0)
+    AutoRegressiveLM(cfg).to(torch.bfloat16).save_pretrained(str(params))
+    ckpt = tmp_path / "ckpt"
+    base = ["--train_type", "seq", "--data_root_path", str(data), "--param_path", str(params), "--ckpt_dir", str(ckpt),
+            "--batch_per_device", "2", "--window_size", "32", "--num_workers", "0", "--no_pin_memory", "--nprocs", "1",
+            "--parallel_mode", "none", "--device_type", "cpu", "--ckpt_interval", "6", "--max_lr", "1e-2",
+            "--lora_r", "4", "--lora_alpha", "8", "--warmup_ratio", "0.2"]
+    train_cli.train(train_cli.parse_args(base))
+    whole = Checkpoint.load(str(ckpt / "epoch_0_iter_20")).state_dict
+    import shutil
+
+    for gone in ("epoch_0_iter_12", "epoch_0_iter_18", "epoch_0_iter_20", "lora_adapter"):
+        shutil.rmtree(ckpt / gone)
+    train_cli.train(train_cli.parse_args(base + ["--auto_resume"]))
+    resumed = Checkpoint.load(str(ckpt / "epoch_0_iter_20")).state_dict
+    key = "layers.0.attention.q_proj.lora_B"
+    assert float(whole[key].float().abs().sum()) > 0
+    for k, v in whole.items():                        # adapters included: the restart continued, it did not start them over
+        assert torch.equal(resumed[k], v), k
