@@ -218,3 +218,30 @@ def test_resuming_a_lora_run_keeps_the_adapters(tmp_path):
     assert float(whole[key].float().abs().sum()) > 0
     for k, v in whole.items():                        # adapters included: the restart continued, it did not start them over
         assert torch.equal(resumed[k], v), k
+
+
+@pytest.mark.parametrize("mode,port", [("ddp", 29692), ("fsdp", 29693), ("tp", 29694)])
+def test_auto_resume_is_exact_on_two_ranks(mode, port, tmp_path):
+    """A killed and restarted two-rank run (data parallel, sharded optimizer, tensor parallel) ends with the
+    weights of the uninterrupted one."""
+    import shutil
+
+    cfg, params, data = _setup(tmp_path)
+    torch.manual_seed(0)
+    AutoRegressiveLM(cfg).to(torch.bfloat16).save_pretrained(str(params))
+    ckpt = tmp_path / "ckpt"
+    base = ["--train_type", "seq", "--data_root_path", str(data), "--param_path", str(params), "--ckpt_dir", str(ckpt),
+            "--batch_per_device", "2", "--window_size", "32", "--num_workers", "0", "--no_pin_memory", "--nprocs", "2",
+            "--parallel_mode", mode, "--backend", "gloo", "--device_type", "cpu", "--master_addr", "127.0.0.1",
+            "--master_port", str(port), "--ckpt_interval", "6", "--warmup_ratio", "0.2"]
+    train_cli.train(train_cli.parse_args(base))
+    dirs = sorted((d for d in os.listdir(ckpt) if d.startswith("epoch_")), key=lambda d: int(d.rsplit("_", 1)[1]))
+    final = dirs[-1]
+    whole = Checkpoint.load(str(ckpt / final)).state_dict
+    for gone in dirs[1:]:
+        shutil.rmtree(ckpt / gone)
+    assert dirs[0] == "epoch_0_iter_6"
+    train_cli.train(train_cli.parse_args(base + ["--auto_resume"]))
+    resumed = Checkpoint.load(str(ckpt / final)).state_dict
+    for k, v in whole.items():
+        assert torch.equal(resumed[k], v), k
