@@ -52,6 +52,7 @@ class InferenceScheduler:
                                       max_seq_len=max_seq_len)
         self._running = False
         self._fatal_error: Optional[Exception] = None
+        self._stopped = False          # set by stop(): requests that arrive afterwards are closed at once
         self._loop_thread: Optional[threading.Thread] = None
         self._steps = 0
         self._decode_tokens = 0
@@ -59,7 +60,7 @@ class InferenceScheduler:
 
     # -- public ---------------------------------------------------------------------------------
     def add_task(self, prompt, **kwargs) -> str:
-        if self._fatal_error is not None:
+        if self._fatal_error is not None or self._stopped:
             # the loop is gone: close the stream at once instead of queueing a request nobody will serve
             callback = kwargs.get("stream_callback")
             if callback:
@@ -89,11 +90,13 @@ class InferenceScheduler:
     def start(self) -> None:
         if self._running:
             return
+        self._stopped = False
         self._running = True
         self._loop_thread = threading.Thread(target=self._run_generation_loop, daemon=True, name="kb200-scheduler")
         self._loop_thread.start()
 
     def stop(self) -> None:
+        self._stopped = True
         self._running = False
         self._task_mgr.wake()
         if self._loop_thread is not None:

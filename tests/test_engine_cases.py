@@ -357,3 +357,12 @@ def test_requests_with_nothing_to_do_return_at_once_and_do_not_hurt_the_loop(eng
     assert engine.generate(["", "hello world"], max_tokens=3, top_k=1)[0] == ""
     assert engine.scheduler._fatal_error is None
     assert engine.generate("hello world", max_tokens=3, top_k=1) != ""
+
+
+def test_requests_after_shutdown_are_closed_at_once(tokenizer):
+    model = AutoRegressiveLM(tiny_config(vocab_size=len(tokenizer))).eval()
+    eng = InferenceEngine(model, tokenizer, max_batch_size=2, max_seq_len=32, page_size=4)
+    assert eng.generate("hello world", max_tokens=3, top_k=1) != ""
+    eng.shutdown()
+    start = time.time()
+    assert eng.generate("hello world", max_tokens=3, top_k=1) == "" and time.time() - start < 5
