@@ -245,3 +245,9 @@ def test_auto_resume_is_exact_on_two_ranks(mode, port, tmp_path):
     resumed = Checkpoint.load(str(ckpt / final)).state_dict
     for k, v in whole.items():
         assert torch.equal(resumed[k], v), k
+
+
+@pytest.mark.parametrize("mode", ["ddp", "fsdp", "fsdp_full", "tp"])
+def test_parallel_modes_degrade_to_a_single_process(mode, tmp_path):
+    ck = _run(tmp_path, mode, 1, 29695)
+    assert ck.iteration == 20 and "layers.1.mlp.down.weight" in ck.state_dict
