@@ -125,6 +125,7 @@ def train(args: argparse.Namespace) -> None:
         iteration = int(meta.get("completed_iteration", meta.get("iteration", 0)))
         args.start_epoch = epoch
         args.start_batch = max(iteration - epoch * per_epoch, 0)
+        args.start_iteration = iteration   # the counter keeps running across epochs and restarts
         log.info("resuming from %s (epoch %d, batch %d)", latest[0], args.start_epoch, args.start_batch)
     warmup = min(int(args.warmup_ratio * total), total)
     executor_kwargs = {"gradient_as_bucket_view": True, "broadcast_buffers": False}
@@ -147,7 +148,8 @@ def train(args: argparse.Namespace) -> None:
                              lr_decay_steps=max(total - warmup, 1)),
         ckpt_dir=args.ckpt_dir, log_dir=args.log_dir or os.path.join(args.ckpt_dir, "logs"),
         log_interval=args.log_interval, metrics=args.metrics, n_epoch=args.n_epoch, batch_per_device=args.batch_per_device,
-        start_epoch=args.start_epoch, start_batch=args.start_batch, ckpt_interval=args.ckpt_interval,
+        start_epoch=args.start_epoch, start_batch=args.start_batch,
+        start_iteration=getattr(args, "start_iteration", None), ckpt_interval=args.ckpt_interval,
         grad_accum_steps=args.grad_accum_steps, max_grad_norm=args.max_grad_norm, random_seed=args.random_seed,
         num_workers=args.num_workers, pin_memory=args.pin_memory, nprocs=args.nprocs, backend=args.backend,
         master_addr=args.master_addr, master_port=args.master_port, parallel_mode=args.parallel_mode,

@@ -38,6 +38,9 @@ class TrainConfig(BaseConfig):
     # -- checkpoints --------------------------------------------------------------------
     start_epoch: int = field(default=0, metadata=_opt("Epoch to resume from."))
     start_batch: int = field(default=0, metadata=_opt("Batch iteration to resume from."))
+    start_iteration: Optional[int] = field(default=None, metadata=_opt(
+        "Value of the run-wide iteration counter to continue from (it runs across epochs); "
+        "None: start_batch, as in the reference."))
     ckpt_dir: str = field(default="./checkpoint", metadata=_opt("Checkpoint directory."))
     ckpt_interval: int = field(default=5000, metadata=_opt("Iterations between checkpoints."))
     # -- LoRA ---------------------------------------------------------------------------

@@ -2,8 +2,8 @@
 
 Reference behaviour: ``astrai/model/components/mlp.py:16-93`` (``down(up(x) * silu(gate(x)))``,
 router softmax in fp32 -> top-k -> renormalise, shared experts averaged).  The MLP runs
-gate and up as one GEMM over adjacent weights, a fused SwiGLU kernel, and the down projection
-with the residual add in its epilogue.  The MoE dispatch is sort-based (one ``argsort``, no
+gate and up as one GEMM over adjacent weights with the SwiGLU in that GEMM's epilogue, and the
+down projection with the residual add in its epilogue.  The MoE dispatch is sort-based (one ``argsort``, no
 per-expert ``nonzero`` round trips to the host).
 """
 
@@ -37,7 +37,8 @@ class MLP(nn.Module):
 
     def forward(self, x: Tensor, residual: Optional[Tensor] = None) -> Tensor:
         if type(self.gate) is Linear and type(self.up) is Linear:
-            gu = ops.multi_linear(x, (self.gate.weight, self.up.weight))
+            # one kernel: gate|up GEMM with the SwiGLU in its epilogue (CUDA bf16, adjacent weights)
+            return self.down(ops.linear_swiglu(x, self.gate.weight, self.up.weight), residual)
         else:
             from ...ops.quant import int8_multi_linear
 

@@ -9,6 +9,7 @@ from .functional import (
     fp8_linear_enabled,
     gemm,
     linear,
+    linear_swiglu,
     multi_linear,
     rms_norm,
     rms_norm_fork,
@@ -23,5 +24,5 @@ from .functional import (
 __all__ = [
     "KernelError", "available", "launch_count", "raise_on_device_error", "add_rms_norm", "cross_entropy",
     "cross_entropy_rows", "embedding", "gemm", "linear", "multi_linear", "rms_norm", "rope", "rope_table",
-    "sdpa_reference", "swiglu", "token_logprobs", "set_fp8_linear", "fp8_linear_enabled", "rms_norm_fork",
+    "sdpa_reference", "swiglu", "linear_swiglu", "token_logprobs", "set_fp8_linear", "fp8_linear_enabled", "rms_norm_fork",
 ]

@@ -39,10 +39,14 @@ def _declare(lib):
     sigs = {
         "kb_last_error": ([], I),
         "kb_sm_count": ([], I),
+        "kb_error_probe": ([P, P], I),
+        "kb_store_f32x2": ([P, F, F, P], I),
         "kb_last_tmap_error": ([], I),
         "kb_gemm_bf16": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, P], I),
         "kb_gemm_bf16_bn": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P], I),
         "kb_gemm_bf16_pair": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, P], I),
+        "kb_gemm_bf16_pair_bn": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P], I),
+        "kb_gemm_swiglu_bf16": ([P, P, P, P, I, I, I, L, L, L, L, I, P], I),
         "kb_rmsnorm_fwd": ([P, P, P, P, P, P, I, I, F, P], I),
         "kb_rmsnorm_bwd_partials": ([I], I),
         "kb_rmsnorm_bwd": ([P, P, P, P, P, P, P, P, I, I, P], I),
@@ -143,6 +147,52 @@ def launch_count() -> int:
 def add_launches(n: int):
     global _LAUNCHES
     _LAUNCHES += n
+
+
+class ErrorProbe:
+    """Non-blocking reads of the device error word.
+
+    ``post()`` enqueues a 4-byte copy of the word into page-locked host memory plus an event on the
+    current stream; ``poll()`` looks at the probes whose event has completed and raises for the first
+    non-zero code.  Neither call waits for the device."""
+
+    def __init__(self, slots: int = 8):
+        self._host = torch.zeros(slots, dtype=torch.int32).pin_memory()
+        self._pending = []      # (slot, event)
+        self._free = list(range(slots))
+
+    def post(self) -> None:
+        if not self._free:
+            return              # enough probes in flight; the next poll frees some
+        slot = self._free.pop()
+        dst = c_void_p(self._host.data_ptr() + 4 * slot)
+        if lib().kb_error_probe(dst, stream()) != 0:
+            self._free.append(slot)
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        self._pending.append((slot, ev))
+
+    def poll(self, wait: bool = False) -> None:
+        keep, code = [], 0
+        for slot, ev in self._pending:
+            if wait:
+                ev.synchronize()
+            if wait or ev.query():
+                code = code or int(self._host[slot])
+                self._free.append(slot)
+            else:
+                keep.append((slot, ev))
+        self._pending = keep
+        if code:
+            lib().kb_last_error()   # clears the word
+            raise KernelError(f"device-side kernel error: {DEVICE_ERR.get(code, code)}")
+
+
+def set_device_floats(dst: torch.Tensor, a: float, b: float) -> None:
+    """``dst[0], dst[1] = a, b`` on the current stream, the values carried as launch arguments."""
+    check(lib().kb_store_f32x2(ptr(dst), float(a), float(b), stream()), "store_f32x2")
+    add_launches(-1)
 
 
 def raise_on_device_error():

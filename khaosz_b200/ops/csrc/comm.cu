@@ -21,6 +21,8 @@
 namespace kb {
 namespace comm {
 
+constexpr int UNROLL = 4;  // 16-byte remote loads each thread keeps in flight
+
 __device__ __forceinline__ void acc8(float* acc, uint4 v) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -56,27 +58,53 @@ reduce_slice_kernel(Peers grads, const void* grad_mc, Peers ctrl, int rank, int 
   __nv_bfloat16* mine = static_cast<__nv_bfloat16*>(grads.p[rank]) + slice_off;
   const long long nchunks = slice_n >> 3;
   float sq = 0.f;
-  for (long long c = blockIdx.x * (long long)THREADS + threadIdx.x; c < nchunks; c += (long long)gridDim.x * THREADS) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  // UNROLL chunks per thread per trip: the remote loads of a trip are all issued before the
+  // first one is consumed, which is what hides the NVLink / NVSwitch round trip
+  const long long stride = (long long)gridDim.x * THREADS;
+  for (long long c0 = blockIdx.x * (long long)THREADS + threadIdx.x; c0 < nchunks; c0 += stride * UNROLL) {
+    uint4 raw[UNROLL];
+    float acc[UNROLL][8];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long c = c0 + u * stride;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (grad_mc != nullptr && c < nchunks)
+        raw[u] = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(grad_mc) + slice_off + c * 8);
+    }
     if (grad_mc != nullptr) {
-      acc8(acc, multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(grad_mc) + slice_off + c * 8));
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) acc8(acc[u], raw[u]);
     } else {
 #pragma unroll
       for (int r = 0; r < MAX_RANKS; ++r) {
         if (r < ws) {
           const int peer = (rank + r) % ws;  // spread the traffic: every rank starts with itself
-          acc8(acc, *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[peer]) + slice_off + c * 8));
+          const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(grads.p[peer]) + slice_off;
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const long long c = c0 + u * stride;
+            raw[u] = c < nchunks ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) acc8(acc[u], raw[u]);
         }
       }
     }
-    uint4 o;
-    o.x = pack_bf16x2(acc[0] * scale, acc[1] * scale);
-    o.y = pack_bf16x2(acc[2] * scale, acc[3] * scale);
-    o.z = pack_bf16x2(acc[4] * scale, acc[5] * scale);
-    o.w = pack_bf16x2(acc[6] * scale, acc[7] * scale);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) sq += (acc[e] * scale) * (acc[e] * scale);
-    *reinterpret_cast<uint4*>(mine + c * 8) = o;
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long c = c0 + u * stride;
+      if (c >= nchunks) break;
+      uint4 o;
+      o.x = pack_bf16x2(acc[u][0] * scale, acc[u][1] * scale);
+      o.y = pack_bf16x2(acc[u][2] * scale, acc[u][3] * scale);
+      o.z = pack_bf16x2(acc[u][4] * scale, acc[u][5] * scale);
+      o.w = pack_bf16x2(acc[u][6] * scale, acc[u][7] * scale);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq += (acc[u][e] * scale) * (acc[u][e] * scale);
+      *reinterpret_cast<uint4*>(mine + c * 8) = o;
+    }
   }
   sq = warp_sum(sq);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
@@ -91,6 +119,9 @@ reduce_slice_kernel(Peers grads, const void* grad_mc, Peers ctrl, int rank, int 
 // Phase 2 (one CTA): publish my partial squared norm to every peer, barrier, total.
 __global__ void exchange_norm_kernel(Peers norms, Peers ctrl, int rank, int ws, const float* norm_sq_local,
                                      float* norm_sq_total, int slot, uint32_t epoch, int* err) {
+  // a failed reduction (or any earlier failure on this device) leaves the total unset and the
+  // update below refuses to run; the peers' waits run out and they refuse as well
+  if (*reinterpret_cast<volatile int*>(err) != 0) return;
   if (threadIdx.x < ws)
     static_cast<float*>(norms.p[threadIdx.x])[rank] = *norm_sq_local;
   if (!cta_peer_barrier(ctrl, rank, ws, slot, epoch, err, KB_WAIT_BUDGET_NS)) return;
@@ -108,6 +139,9 @@ adamw_allgather_kernel(Peers params, void* param_mc, Peers grads, Peers ctrl, in
                        long long slice_off, long long slice_n, float* m, float* v, const float* lr_step, float beta1,
                        float beta2, float eps, float wd, const float* norm_sq_total, float max_norm, uint32_t epoch,
                        int* err) {
+  // Never update from gradients that were not reduced or a norm that was not exchanged: with the
+  // error word set the moments and the parameters of every rank stay exactly as they were.
+  if (*reinterpret_cast<volatile int*>(err) != 0) return;
   const float lr = lr_step[0], step = lr_step[1];
   float gs = 1.f;
   if (max_norm > 0.f) gs = fminf(1.f, max_norm / (sqrtf(*norm_sq_total) + 1e-6f));
@@ -161,25 +195,50 @@ allreduce_kernel(Peers bufs, void* mc, Peers ctrl, int rank, int ws, long long n
   const long long off = per * rank;
   const long long cnt = (rank == ws - 1) ? (n - off) : per;
   const long long nchunks = cnt >> 3;
-  for (long long c = blockIdx.x * (long long)THREADS + threadIdx.x; c < nchunks; c += (long long)gridDim.x * THREADS) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (mc != nullptr) {
-      acc8(acc, multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(mc) + off + c * 8));
-    } else {
+  const long long stride = (long long)gridDim.x * THREADS;
+  for (long long c0 = blockIdx.x * (long long)THREADS + threadIdx.x; c0 < nchunks; c0 += stride * UNROLL) {
+    uint4 raw[UNROLL];
+    float acc[UNROLL][8];
 #pragma unroll
-      for (int r = 0; r < MAX_RANKS; ++r)
-        if (r < ws)
-          acc8(acc, *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(bufs.p[(rank + r) % ws]) + off + c * 8));
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long c = c0 + u * stride;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (mc != nullptr && c < nchunks)
+        raw[u] = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(mc) + off + c * 8);
     }
-    uint4 o;
-    o.x = pack_bf16x2(acc[0] * scale, acc[1] * scale); o.y = pack_bf16x2(acc[2] * scale, acc[3] * scale);
-    o.z = pack_bf16x2(acc[4] * scale, acc[5] * scale); o.w = pack_bf16x2(acc[6] * scale, acc[7] * scale);
     if (mc != nullptr) {
-      multimem_st_bf16x8(static_cast<__nv_bfloat16*>(mc) + off + c * 8, o);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) acc8(acc[u], raw[u]);
     } else {
 #pragma unroll
       for (int r = 0; r < MAX_RANKS; ++r)
-        if (r < ws) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bufs.p[(rank + r) % ws]) + off + c * 8) = o;
+        if (r < ws) {
+          const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(bufs.p[(rank + r) % ws]) + off;
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const long long c = c0 + u * stride;
+            raw[u] = c < nchunks ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) acc8(acc[u], raw[u]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long c = c0 + u * stride;
+      if (c >= nchunks) break;
+      uint4 o;
+      o.x = pack_bf16x2(acc[u][0] * scale, acc[u][1] * scale); o.y = pack_bf16x2(acc[u][2] * scale, acc[u][3] * scale);
+      o.z = pack_bf16x2(acc[u][4] * scale, acc[u][5] * scale); o.w = pack_bf16x2(acc[u][6] * scale, acc[u][7] * scale);
+      if (mc != nullptr) {
+        multimem_st_bf16x8(static_cast<__nv_bfloat16*>(mc) + off + c * 8, o);
+      } else {
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < ws) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bufs.p[(rank + r) % ws]) + off + c * 8) = o;
+      }
     }
   }
   cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch + 1, err, KB_WAIT_BUDGET_NS);

@@ -139,7 +139,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jb = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  // 1-D grid, heaviest key blocks first over ALL (batch, KV head) pairs: under a causal mask key block
+  // jb meets (n_blocks - jb) query blocks per head, and CTAs are handed to SMs in index order, so the
+  // long ones start first and the short ones fill the gaps at the end
+  const int n_bh = p.Hkv * p.B;
+  const int jb = blockIdx.x / n_bh;
+  const int kvh = (blockIdx.x % n_bh) % p.Hkv, b = (blockIdx.x % n_bh) / p.Hkv;
   const int kv0 = jb * BLK;
   const int G = p.H / p.Hkv;
   const int i_start = p.causal ? jb : 0;
@@ -387,8 +392,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int ib = p.n_blocks - 1 - blockIdx.x;  // heavy (late) query blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // 1-D grid, heavy (late) query blocks first over all (batch, head) pairs
+  const int n_bh = p.H * p.B;
+  const int ib = p.n_blocks - 1 - blockIdx.x / n_bh;
+  const int h = (blockIdx.x % n_bh) % p.H, b = (blockIdx.x % n_bh) / p.H;
   const int q0 = ib * BLK;
   const int kvh = h / (p.H / p.Hkv);
   const int n_it = p.causal ? min(p.n_blocks, ib + 1) : p.n_blocks;
@@ -589,7 +596,10 @@ extern "C" int kb_flash_bwd(const void* q, const void* k, const void* v, const v
   if (bad(q, q_pitch) || bad(k, k_pitch) || bad(v, v_pitch) || bad(o, o_pitch) || bad(d_o, do_pitch) ||
       bad(dq, dq_pitch) || bad(dk, dk_pitch) || bad(dv, dv_pitch) || !lse || !delta)
     return KB_STATUS_BAD_ARG;
-  static bool attr_set = false;
+  static bool attr_set_dev[64] = {false};  // the attribute is per device
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_set_dev[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(flash_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
         cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_DQ) != cudaSuccess)
@@ -616,7 +626,7 @@ extern "C" int kb_flash_bwd(const void* q, const void* k, const void* v, const v
   const long pairs = (long)B * S * H;
   delta_kernel<<<(unsigned)((pairs * 16 + 255) / 256), 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, B, S, H, o_pitch, do_pitch);
-  flash_bwd_dkdv_kernel<<<dim3(p.n_blocks, Hkv, B), NUM_THREADS, SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdk, tdv, p);
-  flash_bwd_dq_kernel<<<dim3(p.n_blocks, H, B), NUM_THREADS, SMEM_BYTES_DQ, st>>>(tq, tk, tv, tdo, tdq, p);
+  flash_bwd_dkdv_kernel<<<dim3(p.n_blocks * Hkv * B), NUM_THREADS, SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdk, tdv, p);
+  flash_bwd_dq_kernel<<<dim3(p.n_blocks * H * B), NUM_THREADS, SMEM_BYTES_DQ, st>>>(tq, tk, tv, tdo, tdq, p);
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }

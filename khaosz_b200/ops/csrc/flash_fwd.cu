@@ -66,11 +66,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int lane = threadIdx.x & 31;
 
   // ---- which two tiles does this CTA own? (heavy causal tiles are scheduled first) ----
-  const int b = blockIdx.y;
+  // 1-D grid with the batch as the fast index: CTAs are handed to SMs in index order, so the heavy
+  // (late) query blocks of every batch entry start first and the light ones fill the end
+  const int b = blockIdx.x % p.B;
   int head[2], q0[2], nblk[2];
   {
     const int group = p.H / p.Hkv;
-    int slot = blockIdx.x;
+    int slot = blockIdx.x / p.B;
     if (p.pair_heads) {
       const int pairs = p.H / 2;
       const int qb = p.n_qblocks - 1 - slot / pairs;
@@ -325,7 +327,10 @@ extern "C" int kb_flash_fwd(const void* q, const void* k, const void* v, void* o
   if (Dh != D || B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || H % Hkv) return KB_STATUS_BAD_ARG;
   auto bad = [](const void* p, long pitch) { return (reinterpret_cast<uintptr_t>(p) & 15) || (pitch & 7); };
   if (bad(q, q_pitch) || bad(k, k_pitch) || bad(v, v_pitch) || bad(o, o_pitch) || !lse) return KB_STATUS_BAD_ARG;
-  static bool attr_set = false;
+  static bool attr_set_dev[64] = {false};  // the attribute is per device
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_set_dev[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return KB_STATUS_CUDA_ERROR;
@@ -347,7 +352,7 @@ extern "C" int kb_flash_fwd(const void* q, const void* k, const void* v, void* o
   p.pair_heads = (group % 2 == 0) ? 1 : 0;
   p.err = kb::error_word(dev);
   const int slots = p.pair_heads ? (H / 2) * p.n_qblocks : H * ((p.n_qblocks + 1) / 2);
-  dim3 grid(slots, B);
+  dim3 grid(slots * B);
   flash_fwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, to, p);
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }

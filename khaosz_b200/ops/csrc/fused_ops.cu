@@ -14,6 +14,15 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
          d = unpack_bf16x2(v.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
+__device__ __forceinline__ void unpack8(uint4 v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack_bf16x2(w[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
   uint4 v;
   v.x = pack_bf16x2(f[0], f[1]);
@@ -104,7 +113,9 @@ constexpr int RMS_BWD_THREADS = 256;
 constexpr int RMS_BWD_MAX_NCH = 4;  // dim <= 8 * 256 * 4 = 8192
 constexpr int RMS_BWD_ROWS = 4;
 
-template <int NCH>
+// KEEP: the dy / x chunks of the four rows stay in registers (as packed bf16) between the two
+// passes, so every input byte is read exactly once; used while that fits (NCH <= 2).
+template <int NCH, bool KEEP>
 __global__ void __launch_bounds__(RMS_BWD_THREADS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -125,9 +136,23 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   const float inv_dim = 1.f / (float)dim;
   for (int r0 = blockIdx.x * RMS_BWD_ROWS; r0 < rows; r0 += gridDim.x * RMS_BWD_ROWS) {
     float dot[RMS_BWD_ROWS];
+    uint4 keep_a[KEEP ? RMS_BWD_ROWS : 1][KEEP ? NCH : 1], keep_b[KEEP ? RMS_BWD_ROWS : 1][KEEP ? NCH : 1];
 #pragma unroll
     for (int j = 0; j < RMS_BWD_ROWS; ++j) dot[j] = 0.f;
-    // pass 1: dot_j = sum_k dy*w*x
+    // pass 1: dot_j = sum_k dy*w*x  (all loads of the four rows are issued before the first use)
+    if (KEEP) {
+#pragma unroll
+      for (int j = 0; j < RMS_BWD_ROWS; ++j) {
+        const int row = r0 + j;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+          const int c = tid + i * RMS_BWD_THREADS;
+          const bool live = row < rows && c < nchunks;
+          keep_a[j][i] = live ? *reinterpret_cast<const uint4*>(dy + (size_t)row * dim + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+          keep_b[j][i] = live ? *reinterpret_cast<const uint4*>(x + (size_t)row * dim + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    }
 #pragma unroll
     for (int j = 0; j < RMS_BWD_ROWS; ++j) {
       const int row = r0 + j;
@@ -137,8 +162,13 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
           const int c = tid + i * RMS_BWD_THREADS;
           if (c < nchunks) {
             float a[8], b[8];
-            load8(dy + (size_t)row * dim + c * 8, a);
-            load8(x + (size_t)row * dim + c * 8, b);
+            if (KEEP) {
+              unpack8(keep_a[j][i], a);
+              unpack8(keep_b[j][i], b);
+            } else {
+              load8(dy + (size_t)row * dim + c * 8, a);
+              load8(x + (size_t)row * dim + c * 8, b);
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) dot[j] += a[e] * wreg[i][e] * b[e];
           }
@@ -146,7 +176,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       }
     }
     block_sum<RMS_BWD_ROWS>(dot, red);
-    // pass 2 (re-reads hit L1/L2): dx and the weight-gradient accumulation
+    // pass 2 (without KEEP the re-reads hit L1/L2): dx and the weight-gradient accumulation
 #pragma unroll
     for (int j = 0; j < RMS_BWD_ROWS; ++j) {
       const int row = r0 + j;
@@ -158,8 +188,13 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
           const int c = tid + i * RMS_BWD_THREADS;
           if (c < nchunks) {
             float a[8], b[8], o[8];
-            load8(dy + (size_t)row * dim + c * 8, a);
-            load8(x + (size_t)row * dim + c * 8, b);
+            if (KEEP) {
+              unpack8(keep_a[j][i], a);
+              unpack8(keep_b[j][i], b);
+            } else {
+              load8(dy + (size_t)row * dim + c * 8, a);
+              load8(x + (size_t)row * dim + c * 8, b);
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
               o[e] = a[e] * wreg[i][e] * rs - b[e] * coef;
@@ -193,26 +228,32 @@ static void launch_rmsnorm_bwd(int blocks, cudaStream_t st, const __nv_bfloat16*
                                const __nv_bfloat16* w, const float* rstd, const __nv_bfloat16* dres,
                                __nv_bfloat16* dx, float* partial, int rows, int dim) {
   const int nch = ((dim >> 3) + RMS_BWD_THREADS - 1) / RMS_BWD_THREADS;
-  if (nch <= 1) rmsnorm_bwd_kernel<1><<<blocks, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, partial, rows, dim);
-  else if (nch <= 2) rmsnorm_bwd_kernel<2><<<blocks, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, partial, rows, dim);
-  else rmsnorm_bwd_kernel<4><<<blocks, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, partial, rows, dim);
+  if (nch <= 1) rmsnorm_bwd_kernel<1, true><<<blocks, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, partial, rows, dim);
+  else if (nch <= 2) rmsnorm_bwd_kernel<2, true><<<blocks, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, partial, rows, dim);
+  else rmsnorm_bwd_kernel<4, false><<<blocks, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, partial, rows, dim);
 }
 
-// out[col] = sum over rows of partial[row][col]; block = 32 columns x 32 row lanes.
-__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int nrows,
-                              int dim) {
-  __shared__ float tile[32][33];
-  const int col = blockIdx.x * 32 + threadIdx.x;
+// out[col] = sum over rows of partial[row][col], in a fixed order (deterministic).  A block owns 8
+// columns (one 32-byte sector per row) and walks the rows with 128 row lanes, so that a [~600, dim]
+// partial matrix is spread over dim / 8 blocks instead of a handful.
+constexpr int COLSUM_COLS = 8;
+constexpr int COLSUM_LANES = 128;
+__global__ void __launch_bounds__(COLSUM_COLS * COLSUM_LANES)
+colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int nrows, int dim) {
+  __shared__ float tile[COLSUM_LANES][COLSUM_COLS + 1];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int col = blockIdx.x * COLSUM_COLS + tx;
   float s = 0.f;
   if (col < dim)
-    for (int r = threadIdx.y; r < nrows; r += 32) s += partial[(size_t)r * dim + col];
-  tile[threadIdx.y][threadIdx.x] = s;
+    for (int r = ty; r < nrows; r += COLSUM_LANES) s += partial[(size_t)r * dim + col];
+  tile[ty][tx] = s;
   __syncthreads();
-  // transpose so that a warp reduces one column
-  float v = tile[threadIdx.x][threadIdx.y];
-  v = warp_sum(v);
-  const int ocol = blockIdx.x * 32 + threadIdx.y;
-  if (threadIdx.x == 0 && ocol < dim) out[ocol] = v;
+#pragma unroll
+  for (int off = COLSUM_LANES / 2; off > 0; off >>= 1) {
+    if (ty < off) tile[ty][tx] += tile[ty + off][tx];
+    __syncthreads();
+  }
+  if (ty == 0 && col < dim) out[col] = tile[0][tx];
 }
 
 // =======================================================================================
@@ -555,7 +596,7 @@ int kb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void*
 
 int kb_rmsnorm_bwd_partials(int rows) {
   int blocks = (rows + RMS_BWD_ROWS - 1) / RMS_BWD_ROWS;
-  const int cap = grid_for(1LL << 40, RMS_BWD_THREADS, 4);
+  const int cap = grid_for(1LL << 40, RMS_BWD_THREADS, 2);  // two CTAs are resident per SM (registers)
   return blocks < cap ? (blocks < 1 ? 1 : blocks) : cap;
 }
 
@@ -569,7 +610,7 @@ int kb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rs
   const int blocks = kb_rmsnorm_bwd_partials(rows);
   launch_rmsnorm_bwd(blocks, (cudaStream_t)stream, (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
                      (const bf16*)dres_in, (bf16*)dx, dw_partial, rows, dim);
-  colsum_kernel<<<(dim + 31) / 32, dim3(32, 32), 0, (cudaStream_t)stream>>>(dw_partial, dw, blocks, dim);
+  colsum_kernel<<<(dim + COLSUM_COLS - 1) / COLSUM_COLS, dim3(COLSUM_COLS, COLSUM_LANES), 0, (cudaStream_t)stream>>>(dw_partial, dw, blocks, dim);
   return launch_status();
 }
 
@@ -715,7 +756,7 @@ extern "C" int kb_rmsnorm_bwd_static(const void* dy, const void* x, const void* 
   if (blocks > KB_STATIC_RMS_MAX_PARTIALS) blocks = KB_STATIC_RMS_MAX_PARTIALS;  // the kernel strides over rows
   launch_rmsnorm_bwd(blocks, (cudaStream_t)stream, (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
                      (const bf16*)dres_in, (bf16*)dx, scratch, rows, dim);
-  colsum_kernel<<<(dim + 31) / 32, dim3(32, 32), 0, (cudaStream_t)stream>>>(scratch, dw, blocks, dim);
+  colsum_kernel<<<(dim + COLSUM_COLS - 1) / COLSUM_COLS, dim3(COLSUM_COLS, COLSUM_LANES), 0, (cudaStream_t)stream>>>(scratch, dw, blocks, dim);
   if (cudaGetLastError() != cudaSuccess)
     return rms_static_fail(KB_STATUS_CUDA_ERROR, "kb_rmsnorm_bwd_static: kernel launch failed", 0, 0);
   return KB_STATUS_OK;

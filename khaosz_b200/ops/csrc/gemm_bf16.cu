@@ -417,12 +417,14 @@ template <int BN>
 static int launch(const void* A, const void* B, void* C, const Params& p_in, long lda, long ldb, long ldc, int grid_cap,
                   cudaStream_t stream) {
   Params p = p_in;
-  static bool attr_set = false;
-  if (!attr_set) {
+  int cur = 0;
+  cudaGetDevice(&cur);
+  static bool attr_set[64] = {false};  // the attribute is per device
+  if (!attr_set[cur & 63]) {
     if (cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg<BN>::SMEM_BYTES) != cudaSuccess)
       return KB_STATUS_CUDA_ERROR;
-    attr_set = true;
+    attr_set[cur & 63] = true;
   }
   CUtensorMap ta, tb, tc;
   int rc;

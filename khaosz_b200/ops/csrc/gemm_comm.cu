@@ -518,7 +518,10 @@ int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_l
   if ((lda & 7) || (ldb & 7) || (N & 7)) return KB_STATUS_BAD_ARG;
   const bool copy = gather_copy && ws > 1 && (a_gather || b_gather);
   if (copy && ((a_gather && b_gather) || !ready)) return KB_STATUS_BAD_ARG;
-  static bool attr_set = false;
+  static bool attr_set_dev[64] = {false};  // the attribute is per device
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_set_dev[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_comm_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smem_bytes<4, false>()) != cudaSuccess ||

@@ -277,7 +277,10 @@ int kb_gemm_fp8(const void* A8, const void* B8, const void* sa, const void* sb, 
   if (M <= 0 || N <= 0 || K <= 0) return KB_STATUS_BAD_ARG;
   auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
   if (mis(A8) || mis(B8) || mis(C) || (K & 127) || (lda & 15) || (ldb & 15) || (ldc & 7)) return KB_STATUS_BAD_ARG;
-  static bool attr_set = false;
+  static bool attr_set_dev[64] = {false};  // the attribute is per device
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_set_dev[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return KB_STATUS_CUDA_ERROR;

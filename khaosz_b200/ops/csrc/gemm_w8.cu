@@ -323,7 +323,10 @@ int kb_gemm_w8(const void* X, const void* Wq, const float* scale, void* C, int M
   if (M <= 0 || N <= 0 || K <= 0) return KB_STATUS_BAD_ARG;
   auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
   if (mis(X) || mis(Wq) || mis(C) || (ldx & 7) || (ldw & 15) || (ldc & 7) || (K & 15) || !scale) return KB_STATUS_BAD_ARG;
-  static bool attr_set = false;
+  static bool attr_set_dev[64] = {false};  // the attribute is per device
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_set_dev[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_w8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return KB_STATUS_CUDA_ERROR;

@@ -355,7 +355,10 @@ int kb_sample(const void* logits, const void* temperature, const void* top_k, co
   using namespace kb::inf;
   if (rows <= 0) return KB_STATUS_OK;
   if (V <= 0 || (size_t)V * 4 > 200 * 1024 || !uniform) return KB_STATUS_TOO_LARGE;
-  static bool attr_set = false;
+  static bool attr_set_dev[64] = {false};  // the attribute is per device
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_set_dev[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
       return KB_STATUS_CUDA_ERROR;

@@ -20,6 +20,8 @@ enum {
 
 // ---- runtime ------------------------------------------------------------------------
 int kb_last_error(void);  // device-side status of bounded waits since the last call (0 = ok)
+int kb_error_probe(int* pinned_host, void* stream);  // async copy of the error word (no sync)
+int kb_store_f32x2(float* dst, float a, float b, void* stream);  // dst[0..1] = (a, b) on the stream
 int kb_sm_count(void);
 int kb_last_tmap_error(void);  // CUresult of the last failed tensor-map encode
 const char* kb_version(void);
@@ -103,9 +105,18 @@ int kb_flash_bwd(const void* q, const void* k, const void* v, const void* o, con
                  int causal, void* stream);
 
 // ---- more GEMMs ---------------------------------------------------------------------------
-// CTA-pair variant (cta_group::2, 256 x 256 output per pair of SMs); same contract as kb_gemm_bf16.
+// CTA-pair variant (cta_group::2, 256 x bn output per pair of SMs, bn in {256, 192, 128} chosen
+// per problem, K-sliced tail wave); same contract as kb_gemm_bf16.  The _bn form takes an
+// explicit tile width (0: automatic; 192 needs a K-major B).
 int kb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
                       long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn, int epi, void* stream);
+int kb_gemm_bf16_pair_bn(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                         long lda, long ldb, long ldc, long ldr, int a_mn, int b_mn, int epi, int bn,
+                         void* stream);
+// Gate/up projection with the SwiGLU in the epilogue: W is [2F, K] (gate rows, then up rows);
+// writes GU[M, 2F] = X W^T and H[M, F] = up * silu(gate).  bn as above.
+int kb_gemm_swiglu_bf16(const void* X, const void* W, void* GU, void* H, int M, int F, int K, long ldx,
+                        long ldw, long ldgu, long ldh, int bn, void* stream);
 // int8 weight-only: C[M,N] = A[M,K] (bf16) * dequant(Wq[N,K] int8, scale[N] fp32)^T.
 int kb_gemm_w8(const void* A, const void* Wq, const float* scale, void* C, int M, int N, int K,
                long lda, long ldw, long ldc, void* stream);

@@ -303,7 +303,10 @@ extern "C" int kb_paged_decode_tc(const void* q, const void* k_pool, const void*
   auto mis = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) != 0; };
   if (mis(q) || mis(k_pool) || mis(v_pool) || mis(out) || (q_pitch & 7) || (out_pitch & 7)) return KB_STATUS_BAD_ARG;
   if (n_splits > 1 && (!part_acc || !part_ml)) return KB_STATUS_BAD_ARG;
-  static bool attr_set = false;
+  static bool attr_set_dev[64] = {false};  // the attribute is per device
+  int attr_dev = 0;
+  cudaGetDevice(&attr_dev);
+  bool& attr_set = attr_set_dev[attr_dev & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(paged_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return KB_STATUS_CUDA_ERROR;

@@ -130,6 +130,36 @@ int kb_last_error(void) {
   return v;
 }
 
+// Enqueues a copy of the current device's error word into `pinned_host` (4 bytes of page-locked
+// host memory) on `stream`; the caller records an event behind it and reads the value once the
+// event has completed, so nobody waits for the device.
+int kb_error_probe(int* pinned_host, void* stream) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || pinned_host == nullptr) return KB_STATUS_BAD_ARG;
+  int* p = kb::error_word(dev);
+  if (!p) return KB_STATUS_CUDA_ERROR;
+  return cudaMemcpyAsync(pinned_host, p, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)) ==
+                 cudaSuccess
+             ? KB_STATUS_OK
+             : KB_STATUS_CUDA_ERROR;
+}
+
+namespace {
+__global__ void store_f32x2_kernel(float* dst, float a, float b) {
+  dst[0] = a;
+  dst[1] = b;
+}
+}  // namespace
+
+// dst[0] = a, dst[1] = b on `stream`: host scalars that kernels read from device memory (learning
+// rate and step of the optimizer kernels) travel as launch arguments, not through a staging buffer
+// that a later step could overwrite before the copy ran.
+int kb_store_f32x2(float* dst, float a, float b, void* stream) {
+  if (dst == nullptr) return KB_STATUS_BAD_ARG;
+  store_f32x2_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(dst, a, b);
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
 int kb_sm_count(void) {
   int dev = 0, n = 0;
   cudaGetDevice(&dev);

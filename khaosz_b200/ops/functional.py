@@ -366,6 +366,62 @@ class _SwiGLUFn(torch.autograd.Function):
         return dgu.view(ctx.shape)
 
 
+class _LinearSwiGLUFn(torch.autograd.Function):
+    """``h = up(x) * silu(gate(x))`` from ONE kernel: the gate|up GEMM over the adjacent weights with
+    the SwiGLU in its epilogue (``kb_gemm_swiglu_bf16``).  The epilogue also writes ``[gate | up]``,
+    which the backward pass needs; what disappears is the separate SwiGLU launch and its re-read of
+    the ``[tokens, 2F]`` projection."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_up):
+        x2 = _as2d(x)
+        wcat = _adjacent([w_gate.detach(), w_up.detach()])
+        assert wcat is not None
+        M, K = x2.shape
+        Fh = w_gate.shape[0]
+        gu = torch.empty((M, 2 * Fh), dtype=x2.dtype, device=x2.device)
+        h = torch.empty((M, Fh), dtype=x2.dtype, device=x2.device)
+        check(lib().kb_gemm_swiglu_bf16(ptr(x2), ptr(wcat), ptr(gu), ptr(h), M, Fh, K, x2.stride(0), wcat.stride(0),
+                                        gu.stride(0), h.stride(0), 0, stream()), "gemm_swiglu")
+        ctx.save_for_backward(x2, wcat, gu)
+        ctx.ws = (w_gate, w_up)
+        ctx.x_shape = x.shape
+        return h.view(*x.shape[:-1], Fh)
+
+    @staticmethod
+    def backward(ctx, dh):
+        x2, wcat, gu = ctx.saved_tensors
+        dh2 = dh.reshape(gu.shape[0], -1).contiguous()
+        dgu = torch.empty_like(gu)
+        check(lib().kb_swiglu_bwd(ptr(gu), ptr(dh2), ptr(dgu), gu.shape[0], gu.shape[1] // 2, stream()), "swiglu_bwd")
+        dx = gemm(dgu, wcat, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        grads = [None, None]
+        need = [ctx.needs_input_grad[1], ctx.needs_input_grad[2]]
+        if any(need):
+            mains = [getattr(w, "main_grad", None) for w in ctx.ws]
+            mcat = _adjacent(mains) if all(m is not None for m in mains) and all(need) else None
+            if mcat is not None:
+                gemm(dgu, x2, a_mn=True, b_mn=True, out=mcat, residual=mcat)
+                for w in ctx.ws:
+                    w.main_grad_dirty = True
+            else:
+                dw = gemm(dgu, x2, a_mn=True, b_mn=True)
+                Fh = ctx.ws[0].shape[0]
+                grads = [dw[:Fh] if need[0] else None, dw[Fh:] if need[1] else None]
+        return (dx, *grads)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """``(x @ w_up.T) * silu(x @ w_gate.T)``; one fused kernel when the two weights are adjacent in
+    memory (gate first), bf16, on CUDA (reference: ``astrai/model/components/mlp.py:25-26``)."""
+    Fh = w_gate.shape[0]
+    if (use_kernels(x) and w_gate.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and Fh % 8 == 0
+            and w_up.shape == w_gate.shape and not _FP8_FORWARD and _lib.has("kb_gemm_swiglu_bf16")
+            and _adjacent([w_gate.detach(), w_up.detach()]) is not None):
+        return _LinearSwiGLUFn.apply(x, w_gate, w_up)
+    return swiglu(multi_linear(x, (w_gate, w_up)))
+
+
 def swiglu(gu: torch.Tensor) -> torch.Tensor:
     """``up * silu(gate)`` for ``gu = [gate | up]`` concatenated on the last dimension."""
     Fh = gu.shape[-1] // 2

@@ -8,7 +8,9 @@ reduce-scatter + clip + sharded AdamW + all-gather kernels of ``csrc/comm.cu`` o
 optimizer step; NCCL is only used for bootstrap and as the comparison path.
 
 Environment: ``KHAOSZ_B200_NVLS=0`` forces plain peer loads/stores even where multicast is
-available (fault-tolerance tests require that).
+available, and keeps torch's symmetric memory from creating or binding a multicast object at
+all (``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` is set before the first rendezvous), so "NVLS off"
+means that no rank's memory is ever bound to one (fault-tolerance tests require that).
 """
 
 from __future__ import annotations
@@ -34,6 +36,8 @@ class SymmetricBuffer:
     """A tensor whose peers' copies are addressable from this rank's kernels."""
 
     def __init__(self, numel: int, dtype: torch.dtype, device, group=None, zero: bool = True):
+        if os.environ.get("KHAOSZ_B200_NVLS", "1") == "0":
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
 
         self.group = group if group is not None else dist.group.WORLD
@@ -114,7 +118,6 @@ class GradReducer:
         self._m = torch.zeros(self.slice_n, dtype=torch.float32, device=dev)
         self._v = torch.zeros(self.slice_n, dtype=torch.float32, device=dev)
         self._scratch = torch.zeros(2, dtype=torch.float32, device=dev)
-        self._lr_host = torch.zeros(2, dtype=torch.float32).pin_memory()
         self._lr_dev = torch.zeros(2, dtype=torch.float32, device=dev)
         self.use_multicast = bool(self.params.multicast_ptr and self.grads.multicast_ptr)
 
@@ -135,8 +138,7 @@ class GradReducer:
         allreduce_(self.grads, self.ctrl, 1.0 / self.ws, self.use_multicast)
 
     def fused_step(self, opt, lr, beta1, beta2, eps, wd, clip, step) -> None:
-        self._lr_host[0], self._lr_host[1] = lr, step
-        self._lr_dev.copy_(self._lr_host, non_blocking=True)
+        _lib.set_device_floats(self._lr_dev, lr, step)   # launch arguments: no staging buffer to overwrite
         mc_g = ctypes.c_void_p(self.grads.multicast_ptr) if self.use_multicast else None
         mc_p = ctypes.c_void_p(self.params.multicast_ptr) if self.use_multicast else None
         check(lib().kb_reduce_adamw(self.grads.ptrs, self.params.ptrs, self.ctrl.flags.ptrs, self.ctrl.norms.ptrs,

@@ -65,26 +65,55 @@ class GradientClippingCallback:
 
 @CallbackFactory.register("device_health")
 class DeviceHealthCallback:
-    """Turns a device-side failure into a Python exception at the next optimizer step.
+    """Turns a device-side failure into a Python exception.
 
     Every wait inside the kernels is bounded; a wait that runs out (a peer rank that never
     arrives, a copy that never completes) records a code in a per-device error word and the kernel
-    returns instead of hanging.  This callback reads the word (one 4-byte device-to-host copy per
-    optimizer step) and raises ``KernelError``, which the trainer's error path turns into an
-    emergency checkpoint like any other failure."""
+    returns instead of hanging.  The word is read
 
-    def __init__(self, check=None):
+    * before every optimizer step (one 4-byte synchronising copy per accumulation window), so that
+      gradients of a failed forward / backward never reach the weights;
+    * after every optimizer step through a non-blocking probe (an asynchronous copy plus an event
+      that the next batches poll), so that a failure inside the fused reduce + update kernels -
+      which refuse to touch moments and parameters once the word is set - surfaces within a batch
+      or two and not a whole accumulation window later;
+    * at the end of training, so that a failure in the last step is not lost.
+
+    The raised ``KernelError`` takes the trainer's error path; the checkpoint callback then writes
+    no resumable checkpoint (the ranks may disagree about what was applied)."""
+
+    def __init__(self, check=None, probe=None):
         self._check = check
+        self._probe = probe
+        self._step_pending = False
 
-    def on_optimizer_step(self, context):
+    def _ready(self) -> bool:
         if self._check is None:
-            import torch
-
             if not torch.cuda.is_available():
-                return
+                return False
             from ..ops import raise_on_device_error
+            from ..ops._lib import ErrorProbe
 
             self._check = raise_on_device_error
+            if self._probe is None:
+                self._probe = ErrorProbe()
+        return True
+
+    def on_optimizer_step(self, context):
+        if self._ready():
+            self._check()
+            self._step_pending = True
+
+    def on_batch_begin(self, context):
+        if self._probe is not None:
+            if self._step_pending:       # the optimizer step of the previous batch has been enqueued
+                self._step_pending = False
+                self._probe.post()
+            self._probe.poll()
+
+    def on_train_end(self, context):
+        if context.kwargs.get("error") is not None or not self._ready():
+            return
         self._check()
 
 
@@ -210,6 +239,10 @@ class CheckpointCallback:
                                             meta={"completed_iteration": min(applied, context.iteration)})
             context.checkpoint.save(path)
 
+    def on_train_begin(self, context):
+        # a resumed run counts its interval from where it continues, not from zero
+        self.last_ckpt_iter = context.iteration
+
     def on_batch_end(self, context):
         if context.iteration - self.last_ckpt_iter >= self.interval:
             self._save(context)
@@ -219,6 +252,13 @@ class CheckpointCallback:
             self._save(context)
 
     def on_error(self, context):
+        from ..ops._lib import KernelError
+
+        if isinstance(context.kwargs.get("error"), KernelError):
+            # a device-side failure (a collective that gave up): the ranks may hold different weights,
+            # and an automatic resume must not pick such a state up
+            log.error("device-side failure: no emergency checkpoint is written; resume from the last periodic one")
+            return
         self._save(context)
 
 

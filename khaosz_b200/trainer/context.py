@@ -110,8 +110,12 @@ class TrainContextBuilder:
             if ckpt.config:
                 ctx.model_config = ckpt.config
             model.load_state_dict(ckpt.state_dict, strict=False)
-            # the position comes from the config (CLI flags), as in the reference
-            ctx.epoch, ctx.iteration = self.config.start_epoch, self.config.start_batch
+            # the position comes from the config (CLI flags), as in the reference: start_batch is the
+            # position inside start_epoch (what the sampler skips); the iteration counter itself runs
+            # across epochs, so a resumed run continues it from start_iteration when that is given
+            ctx.epoch = self.config.start_epoch
+            ctx.iteration = self.config.start_batch if self.config.start_iteration is None else self.config.start_iteration
+            ctx.kwargs["epoch_start_batch"] = self.config.start_batch
             ctx.checkpoint = ckpt
         elif any(root.glob("*.safetensors")):
             model.load_state_dict(load_model_weights(str(root)), strict=False)
@@ -149,7 +153,8 @@ class TrainContextBuilder:
             gen = torch.Generator().manual_seed(cfg.random_seed)
             train_set, val_set = random_split(cfg.dataset, [len(cfg.dataset) - n_val, n_val], generator=gen)
         sampler = ResumableDistributedSampler(train_set, start_epoch=ctx.epoch,
-                                              start_iter=ctx.iteration * cfg.batch_per_device, seed=cfg.random_seed)
+                                              start_iter=ctx.kwargs.get("epoch_start_batch", 0) * cfg.batch_per_device,
+                                              seed=cfg.random_seed)
         ctx.dataloader = _loader(train_set, sampler, cfg)
         if val_set is not None:
             val_sampler = ResumableDistributedSampler(val_set, seed=cfg.random_seed, shuffle=False)

@@ -35,7 +35,6 @@ class FusedAdamW(Optimizer):
         self._step_count = 0
         self._m: Optional[torch.Tensor] = None
         self._v: Optional[torch.Tensor] = None
-        self._lr_step_host: Optional[torch.Tensor] = None
         self._lr_step_dev: Optional[torch.Tensor] = None
         self._gnorm_sq: Optional[torch.Tensor] = None
         self.last_grad_norm: Optional[torch.Tensor] = None
@@ -61,7 +60,6 @@ class FusedAdamW(Optimizer):
             self._v = torch.zeros(n, dtype=torch.float32, device=dev)
         self._gnorm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
         if dev.type == "cuda":
-            self._lr_step_host = torch.zeros(2, dtype=torch.float32).pin_memory()
             self._lr_step_dev = torch.zeros(2, dtype=torch.float32, device=dev)
 
     def attach_reducer(self, reducer) -> None:
@@ -118,9 +116,7 @@ class FusedAdamW(Optimizer):
         if gn is not None:
             self.last_grad_norm = gn.sqrt()
         if p.is_cuda and p.dtype == torch.bfloat16:
-            self._lr_step_host[0] = lr
-            self._lr_step_host[1] = self._step_count
-            self._lr_step_dev.copy_(self._lr_step_host, non_blocking=True)
+            _lib.set_device_floats(self._lr_step_dev, lr, self._step_count)
             check(lib().kb_adamw_bf16(ptr(p), ptr(g), ptr(self._m), ptr(self._v), n, ptr(self._lr_step_dev),
                                       beta1, beta2, eps, wd, 1.0, ptr(gn) if gn is not None else None,
                                       float(clip or 0.0), stream()), "adamw")

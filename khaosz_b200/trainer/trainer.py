@@ -83,6 +83,7 @@ class Trainer:
                 self._call_callbacks("on_epoch_end", context)
         except Exception as exc:
             log.error("Training failed: %s", exc, exc_info=True)
+            context.kwargs["error"] = exc
             self._call_callbacks("on_error", context)
             raise
         finally:

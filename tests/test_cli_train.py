@@ -117,6 +117,50 @@ def test_cli_auto_resume_continues_from_the_newest_checkpoint(accum, optimizer, 
         assert {int(st["step"]) for st in opt["state"].values()} == {20 // accum}
 
 
+def test_cli_auto_resume_twice_inside_the_second_epoch(tmp_path):
+    """The iteration counter runs across epochs and across restarts: a run killed twice inside epoch 1
+    picks the newest checkpoint each time (not an older one of the same epoch), continues at the right
+    batch of the epoch, and ends with exactly the weights of the uninterrupted two-epoch run."""
+    import shutil
+
+    cfg, params, data = _setup(tmp_path)
+    ckpt = tmp_path / "ckpt"
+    base = ["--train_type", "seq", "--data_root_path", str(data), "--param_path", str(params), "--ckpt_dir", str(ckpt),
+            "--batch_per_device", "2", "--window_size", "32", "--num_workers", "0", "--no_pin_memory", "--nprocs", "1",
+            "--parallel_mode", "none", "--device_type", "cpu", "--ckpt_interval", "6", "--log_interval", "1",
+            "--grad_accum_steps", "2", "--warmup_ratio", "0.2", "--n_epoch", "2", "--auto_resume"]
+    torch.manual_seed(0)
+    AutoRegressiveLM(cfg).to(torch.bfloat16).save_pretrained(str(params))
+    train_cli.train(train_cli.parse_args(base))
+    names = sorted((d for d in os.listdir(ckpt) if d.startswith("epoch_")), key=lambda d: int(d.rsplit("_", 1)[1]))
+    assert names == ["epoch_0_iter_6", "epoch_0_iter_12", "epoch_0_iter_18", "epoch_1_iter_24", "epoch_1_iter_30",
+                     "epoch_1_iter_36", "epoch_1_iter_40"]
+    whole = Checkpoint.load(str(ckpt / "epoch_1_iter_40"))
+
+    def kill_after(last_kept):
+        for d in os.listdir(ckpt):
+            if d.startswith("epoch_") and int(d.rsplit("_", 1)[1]) > last_kept:
+                shutil.rmtree(ckpt / d)
+
+    kill_after(24)                                   # first death: inside epoch 1, after iteration 24
+    path, meta = train_cli.find_latest_checkpoint(str(ckpt))
+    assert path.endswith("epoch_1_iter_24") and meta["epoch"] == 1 and meta["completed_iteration"] == 22
+    train_cli.train(train_cli.parse_args(base))
+    again = sorted(int(d.rsplit("_", 1)[1]) for d in os.listdir(ckpt) if d.startswith("epoch_1_"))
+    assert again == [24, 28, 34, 40], again          # the resumed run keeps counting where the first one stopped
+    assert Checkpoint.load(str(ckpt / "epoch_1_iter_34")).iteration == 34
+    kill_after(28)                                   # second death: the newest checkpoint was written by the resumed run
+    path, meta = train_cli.find_latest_checkpoint(str(ckpt))
+    assert path.endswith("epoch_1_iter_28") and meta["completed_iteration"] == 26
+    train_cli.train(train_cli.parse_args(base))
+    final = Checkpoint.load(str(ckpt / "epoch_1_iter_40"))
+    assert final.iteration == 40 and final.epoch == 1
+    for k, v in whole.state_dict.items():
+        assert torch.equal(final.state_dict[k], v), k
+    opt = torch.load(ckpt / "epoch_1_iter_40" / "optimizer.pt", weights_only=False)
+    assert {int(st["step"]) for st in opt["state"].values()} == {20}
+
+
 def test_cli_lora_run_trains_adapters_only_and_saves_them(tmp_path):
     from khaosz_b200.models.components.lora import load_lora
     from khaosz_b200.serialization import load_state_dict

@@ -1,6 +1,8 @@
 """Multi-GPU tests (2 ranks, one process per GPU): in-kernel NVLink collectives against NCCL,
 the fused data-parallel optimizer step against a single-GPU run, and the bounded peer wait.
-Plain peer loads/stores only (multicast off), as required for fault-handling tests."""
+Every case runs on plain peer loads/stores with no multicast object bound (what the
+fault-handling tests require); the collective and data-parallel parity cases run a second time
+through the NVSwitch multicast (multimem) data plane, which is what a default run uses."""
 import os
 
 import pytest
@@ -15,14 +17,31 @@ if torch.cuda.device_count() < 2:
 from khaosz_b200.parallel import ExecutorFactory, spawn_parallel_fn  # noqa: E402
 
 
-def _spawn(fn, port, **kw):
-    os.environ["KHAOSZ_B200_NVLS"] = "0"
-    os.environ["NCCL_NVLS_ENABLE"] = "0"
+_NVLS_OFF = {"KHAOSZ_B200_NVLS": "0", "NCCL_NVLS_ENABLE": "0", "TORCH_SYMM_MEM_DISABLE_MULTICAST": "1"}
+
+
+def _spawn(fn, port, nvls=False, **kw):
+    """Run ``fn`` on two ranks.  ``nvls=False``: no multicast object is created at all (not by
+    this package, not by torch's symmetric memory, not by NCCL), so a rank that ends early never
+    holds a multicast binding.  ``nvls=True``: the default data plane (multimem where available)."""
+    saved = {k: os.environ.get(k) for k in _NVLS_OFF}
+    for k, v in _NVLS_OFF.items():
+        if nvls:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
     os.environ["KHAOSZ_B200_PG_TIMEOUT_S"] = "90"  # a failing rank must not keep the others waiting
-    spawn_parallel_fn(fn, world_size=2, backend="nccl", master_addr="127.0.0.1", master_port=str(port), **kw)
+    try:
+        spawn_parallel_fn(fn, world_size=2, backend="nccl", master_addr="127.0.0.1", master_port=str(port), **kw)
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
 
 
-def _allreduce_case():
+def _allreduce_case(expect_multicast=False):
     from khaosz_b200.ops import raise_on_device_error
     from khaosz_b200.parallel.comm import PeerControl, SymmetricBuffer, allreduce_
 
@@ -30,6 +49,10 @@ def _allreduce_case():
     dev = torch.device("cuda", rank)
     n = 8 * 1000 * 1000 + 64
     buf = SymmetricBuffer(n, torch.bfloat16, dev)
+    if not expect_multicast:
+        assert buf.multicast_ptr == 0
+    elif not buf.multicast_ptr:
+        print("no multicast support on this box: the multimem path did not run")
     ctrl = PeerControl(dev)
     g = torch.Generator(device=dev).manual_seed(rank)
     src = torch.randn(n, device=dev, generator=g).to(torch.bfloat16)
@@ -59,8 +82,9 @@ def _allreduce_case():
         print(f"kernel all-reduce {n * 2 / 1e6:.0f} MB, 2 ranks: {t.item():.3f} ms (bus {n * 2 / t.item() / 1e6:.0f} GB/s)")
 
 
-def test_kernel_allreduce_matches_nccl():
-    _spawn(_allreduce_case, 29701)
+@pytest.mark.parametrize("nvls,port", [(False, 29701), (True, 29711)])
+def test_kernel_allreduce_matches_nccl(nvls, port):
+    _spawn(_allreduce_case, port, nvls=nvls, expect_multicast=nvls)
 
 
 def _timeout_case():
@@ -101,13 +125,14 @@ def _cfg():
                                   max_len=256, rope_theta=1e4, n_heads=4, n_kv_heads=2)
 
 
-def _train(mode, world, rank, device, steps=4, accum=2, cuda_graph=False):
+def _train(mode, world, rank, device, steps=4, accum=2, cuda_graph=False, overlap=False):
     from khaosz_b200 import AutoRegressiveLM
     from khaosz_b200.trainer import FusedAdamW, StrategyFactory
 
     torch.manual_seed(3407)
     model = AutoRegressiveLM(_cfg()).to(device=device, dtype=torch.bfloat16)
-    ex = ExecutorFactory.create(mode, grad_accum_steps=accum, cuda_graph=cuda_graph)
+    extra = {"bucket_cap_mb": 1} if overlap else {}   # ~1 MB buckets: several per step on this small model
+    ex = ExecutorFactory.create(mode, grad_accum_steps=accum, cuda_graph=cuda_graph, **extra)
     opt = FusedAdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.01)
     model, opt, _, _ = ex.prepare(model, opt, None, None)
     strat = StrategyFactory.create("seq", model, device, label_smoothing=0.05)
@@ -129,12 +154,12 @@ def _train(mode, world, rank, device, steps=4, accum=2, cuda_graph=False):
     return torch.stack(losses), model, ex, opt
 
 
-def _dp_case(mode, out):
+def _dp_case(mode, out, overlap=False):
     from khaosz_b200.ops import raise_on_device_error
 
     rank = dist.get_rank()
     dev = torch.device("cuda", rank)
-    losses, model, ex, opt = _train(mode, 2, rank, dev)
+    losses, model, ex, opt = _train(mode, 2, rank, dev, overlap=overlap)
     dist.all_reduce(losses)
     losses /= 2
     raise_on_device_error()
@@ -157,10 +182,10 @@ def _tp_train_case(out, mode="tp", cuda_graph=False):
 
     rank = dist.get_rank()
     dev = torch.device("cuda", rank)
-    if cuda_graph:  # a stuck rank reports where it is and leaves instead of holding the GPUs
+    if cuda_graph:  # a stuck rank reports where it is; the kernels' bounded waits and the error word end the run
         import faulthandler
 
-        faulthandler.dump_traceback_later(60, exit=True)
+        faulthandler.dump_traceback_later(60, exit=False)
     losses, model, ex, opt = _train(mode, 2, rank, dev, cuda_graph=cuda_graph)
     if cuda_graph:
         faulthandler.cancel_dump_traceback_later()
@@ -174,15 +199,19 @@ def _tp_train_case(out, mode="tp", cuda_graph=False):
 
 
 @pytest.mark.parametrize("mode,port", [("ddp", 29703), ("fsdp", 29704), ("tp", 29707), ("fsdp_full", 29708),
-                                       ("tp_graph", 29709)])
+                                       ("tp_graph", 29709), ("ddp_nvls", 29712), ("fsdp_nvls", 29713),
+                                       ("ddp_overlap", 29714)])
 def test_fused_data_parallel_step_matches_single_gpu(mode, port, tmp_path):
     out = str(tmp_path / "dp.pt")
+    nvls = mode.endswith("_nvls")
+    overlap = mode.endswith("_overlap")
+    mode = mode.split("_nvls")[0].split("_overlap")[0]
     if mode == "tp_graph":   # forward+backward of the tensor-parallel micro-step replayed as a CUDA graph
         _spawn(_tp_train_case, port, out=out, mode="tp", cuda_graph=True)
     elif mode in ("tp", "fsdp_full"):
         _spawn(_tp_train_case, port, out=out, mode=mode)
     else:
-        _spawn(_dp_case, port, mode=mode, out=out)
+        _spawn(_dp_case, port, nvls=nvls, mode=mode, out=out, overlap=overlap)
     got = torch.load(out)
     # single GPU over the global batch
     from khaosz_b200 import AutoRegressiveLM
@@ -191,6 +220,7 @@ def test_fused_data_parallel_step_matches_single_gpu(mode, port, tmp_path):
     torch.manual_seed(3407)
     dev = torch.device("cuda", 0)
     model = AutoRegressiveLM(_cfg()).to(device=dev, dtype=torch.bfloat16)
+    init = {k: v.detach().float().cpu().clone() for k, v in model.state_dict().items()}
     ex = ExecutorFactory.create("none", grad_accum_steps=2)
     opt = FusedAdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.01)
     model, opt, _, _ = ex.prepare(model, opt, None, None)
@@ -213,6 +243,16 @@ def test_fused_data_parallel_step_matches_single_gpu(mode, port, tmp_path):
     sd = model.state_dict()
     worst = max((got["sd"][k].float() - v.float().cpu()).abs().max().item() for k, v in sd.items())
     assert worst < 2e-2, worst
+    # the *updates* must agree, not only the weights: four AdamW steps at lr 1e-3 move a weight by a
+    # few 1e-3, so a rank that never applied an update would pass the absolute check above
+    for k, v in sd.items():
+        d_ref = v.float().cpu() - init[k]
+        d_got = got["sd"][k].float() - init[k]
+        assert d_ref.abs().max().item() > 5e-4, f"{k}: the single-GPU run did not move"
+        cos = torch.nn.functional.cosine_similarity(d_ref.flatten(), d_got.flatten(), dim=0).item()
+        assert cos > 0.9, f"{k}: update direction differs from the single-GPU run (cosine {cos:.3f})"
+        ratio = d_got.norm().item() / d_ref.norm().item()
+        assert 0.8 < ratio < 1.25, f"{k}: update size differs from the single-GPU run (ratio {ratio:.3f})"
     if "m0" in got:
         assert got["m0"].shape == sd["embed_tokens.weight"].shape
 

@@ -247,6 +247,60 @@ def test_device_health_callback_raises_into_the_error_path():
         cb.on_optimizer_step(None)
 
 
+def test_device_health_probes_after_the_step_and_at_the_end():
+    """After an optimizer step the error word is probed without blocking and polled on the following
+    batches; the end of training checks once more, so a failure in the last step is not lost."""
+    from types import SimpleNamespace
+
+    from khaosz_b200.trainer.callbacks import CallbackFactory
+
+    log_ = []
+
+    class FakeProbe:
+        def post(self):
+            log_.append("post")
+
+        def poll(self):
+            log_.append("poll")
+            if log_.count("poll") == 3:
+                raise RuntimeError("device-side kernel error: timeout waiting for a peer flag")
+
+    cb = CallbackFactory.create("device_health", check=lambda: log_.append("check"), probe=FakeProbe())
+    ctx = SimpleNamespace(kwargs={})
+    cb.on_batch_begin(ctx)                       # nothing stepped yet: poll only
+    cb.on_optimizer_step(ctx)                    # synchronous check before the update
+    cb.on_batch_begin(ctx)                       # the step is enqueued: probe behind it, then poll
+    assert log_ == ["poll", "check", "post", "poll"]
+    with pytest.raises(RuntimeError, match="peer flag"):
+        cb.on_batch_begin(ctx)
+    cb.on_train_end(ctx)
+    assert log_[-1] == "check"
+    ctx.kwargs["error"] = RuntimeError("x")      # already failing: the end-of-training check stays quiet
+    n = len(log_)
+    cb.on_train_end(ctx)
+    assert len(log_) == n
+
+
+def test_no_emergency_checkpoint_after_a_device_side_failure(tmp_path):
+    """A KernelError (a collective that gave up) must not leave a checkpoint that --auto_resume would pick."""
+    from types import SimpleNamespace
+
+    from khaosz_b200.ops._lib import KernelError
+    from khaosz_b200.serialization import find_latest_checkpoint
+    from khaosz_b200.trainer.callbacks import CallbackFactory
+
+    model = torch.nn.Linear(4, 4)
+    ex = SimpleNamespace(unwrap_model=lambda m: m.state_dict(), grad_accum_steps=1)
+    cb = CallbackFactory.create("checkpoint", str(tmp_path), 100, weight_only=True)
+    ctx = SimpleNamespace(kwargs={"error": KernelError("device-side kernel error: timeout waiting for a peer flag")},
+                          executor=ex, model=model, iteration=7, epoch=0, model_config={}, checkpoint=None)
+    cb.on_error(ctx)
+    assert find_latest_checkpoint(str(tmp_path)) is None
+    ctx.kwargs["error"] = ValueError("host-side failure")       # any other failure still writes the emergency checkpoint
+    cb.on_error(ctx)
+    assert find_latest_checkpoint(str(tmp_path))[0].endswith("epoch_0_iter_7")
+
+
 def test_trace_ranges_are_noops_without_cuda():
     from khaosz_b200.utils import enable_tracing, trace_range
 

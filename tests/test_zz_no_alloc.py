@@ -46,7 +46,10 @@ def _case(rows, dim, seed, with_res):
 def test_static_entry_matches_regular_entry_twice():
     handle, fn, msg = _setup_symbol()
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
-    for call, (rows, dim, with_res) in enumerate([(777, 2048, True), (64, 512, False)]):
+    # the last two cases reach what the small ones do not: more row blocks than the scratch has partial
+    # rows (the grid is clamped and each block strides over rows) and the widest supported rows (4096)
+    for call, (rows, dim, with_res) in enumerate([(777, 2048, True), (64, 512, False), (5000, 4096, True),
+                                                  (5000, 4096, False)]):
         dy, x, w, rstd, dres = _case(rows, dim, 100 + call, with_res)
         # regular entry point: scratch handed in by the caller
         nparts = handle.kb_rmsnorm_bwd_partials(rows)
