@@ -127,6 +127,8 @@ class Store(ABC):
         self._length = min(lengths) if lengths else 0
         self._loaded = True
 
+    _normalize = _install   # the reference's name for the same step (``astrai/dataset/storage.py:193``)
+
     @property
     def keys(self) -> List[str]:
         return list(self._segments)

@@ -67,7 +67,7 @@ class Allocator:
                 if keep_cached:
                     self._lru[idx] = None
                 else:
-                    self._free.append(idx)
+                    self._free.appendleft(idx)   # most recently freed first: its lines are the warmest
 
     def inc_ref(self, idx: int) -> None:
         with self._lock:
@@ -93,19 +93,19 @@ class PrefixCache:
 
     def __init__(self, page_size: int):
         self._page_size = page_size
-        self._hash_of: Dict[int, int] = {}
-        self._page_of: Dict[int, int] = {}
+        self._page_to_hash: Dict[int, int] = {}
+        self._hash_to_page: Dict[int, int] = {}
         self._lock = threading.Lock()
 
     def evict(self, idx: int) -> None:
         with self._lock:
-            h = self._hash_of.pop(idx, None)
-            if h is not None and self._page_of.get(h) == idx:
-                del self._page_of[h]
+            h = self._page_to_hash.pop(idx, None)
+            if h is not None and self._hash_to_page.get(h) == idx:
+                del self._hash_to_page[h]
 
     def has_page(self, idx: int) -> bool:
         with self._lock:
-            return idx in self._hash_of
+            return idx in self._page_to_hash
 
     def lookup(self, token_ids: List[int]) -> List[int]:
         hits: List[int] = []
@@ -114,7 +114,7 @@ class PrefixCache:
             for i in range(len(token_ids) // self._page_size):
                 for tok in token_ids[i * self._page_size:(i + 1) * self._page_size]:
                     h = (h * 31 + tok + 1) & _MASK64
-                page = self._page_of.get(h)
+                page = self._hash_to_page.get(h)
                 if page is None:
                     break
                 hits.append(page)
@@ -123,11 +123,11 @@ class PrefixCache:
     def record(self, page_idx: int, token_ids: List[int], logical_page_idx: int) -> None:
         h = page_hash(token_ids, logical_page_idx, self._page_size)
         with self._lock:
-            old = self._hash_of.pop(page_idx, None)
-            if old is not None and self._page_of.get(old) == page_idx:
-                del self._page_of[old]
-            self._hash_of[page_idx] = h
-            self._page_of[h] = page_idx
+            old = self._page_to_hash.pop(page_idx, None)
+            if old is not None and self._hash_to_page.get(old) == page_idx:
+                del self._hash_to_page[old]
+            self._page_to_hash[page_idx] = h
+            self._hash_to_page[h] = page_idx
 
 
 class PagePool:

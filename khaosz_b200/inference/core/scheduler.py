@@ -20,6 +20,8 @@ import torch
 from .cache import KVCache
 from .executor import Executor
 from .task import STOP, Task, TaskManager, TaskStatus
+from ...models.automodel import AutoModel  # noqa: F401  (the types of the constructor's arguments; callers patch them)
+from ...tokenize import AutoTokenizer  # noqa: F401
 from ...utils.trace import trace_range
 
 log = logging.getLogger(__name__)

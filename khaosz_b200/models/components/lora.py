@@ -76,8 +76,15 @@ def _linear_children(model: nn.Module) -> Dict[str, List[str]]:
     return found
 
 
+_collect_lora_info = _linear_children   # the reference's name (``astrai/model/components/lora.py:61``)
+
+
 def _adapters(model: nn.Module) -> List[LoRALinear]:
     return [m for m in model.modules() if isinstance(m, LoRALinear)]
+
+
+def _get_lora_count(model: nn.Module) -> int:
+    return len(_adapters(model))
 
 
 def inject_lora(model: nn.Module, r: int = 16, alpha: int = 32, target_modules: Optional[Iterable[str]] = None) -> LoRAConfig:
