@@ -12,6 +12,13 @@ random-init N(0, 0.02) weights.
         --master-port 29511 bench.py --gpus 8 --steps 5 --warmup 3
     python bench.py --impl reference ...   # the unmodified reference from baseline/_ref
 
+Other named configurations through the same two arms: ``--parallel fsdp`` (N > 1: the reference's
+FULL_SHARD wrapper against this package's sharded executor), ``--strategy dpo`` (a trainable policy
+plus a frozen copy, 8 chosen/rejected pairs per GPU sharing a 512-token prompt with 512-token
+responses, beta 0.1, one micro-batch per step), ``--serve 1`` (own arm, after the training
+numbers: decode tokens/s and median time to first token of the continuous-batching server on the
+same GPUs, tensor parallel when N > 1, reported under the ``serving`` key).
+
 Two numbers come out of the own arm: ``value`` — K steps timed on the device with CUDA
 events, inputs already resident; and ``e2e`` — the same K steps through the public
 ``Trainer`` API, where every micro-batch is copied from pinned host memory and every
@@ -37,8 +44,32 @@ METRIC = "train_tokens_per_s_1B"
 MODEL = dict(vocab_size=32000, dim=2048, n_layers=24, norm_eps=1e-5, dim_ffn=5632, tie_weight=True, max_len=2048,
              rope_theta=10000.0, n_heads=16, n_kv_heads=4)
 SEQ, BPD, ACCUM = 2048, 4, 8
+DPO_PROMPT, DPO_RESPONSE, DPO_PAIRS, DPO_BETA = 512, 512, 8, 0.1
 LR, BETAS, WD, SMOOTH, CLIP = 3e-4, (0.9, 0.95), 0.01, 0.05, 1.0
 SEED = 3407
+
+
+class Workload:
+    """Shape of one optimizer step for the chosen strategy (per GPU)."""
+
+    def __init__(self, strategy: str):
+        self.strategy = strategy
+        if strategy == "dpo":
+            self.seq, self.bpd, self.accum = DPO_PROMPT + DPO_RESPONSE, DPO_PAIRS, 1
+            self.tokens_per_sample = 2 * self.seq           # chosen + rejected
+            self.extra = {"beta": DPO_BETA}
+            self.h2d_per_micro = self.bpd * (2 * self.seq * 8 + 2 * self.seq)   # two id tensors (int64), two masks (bool)
+        else:
+            self.seq, self.bpd, self.accum = SEQ, BPD, ACCUM
+            self.tokens_per_sample = self.seq
+            self.extra = {"label_smoothing": SMOOTH}
+            self.h2d_per_micro = 2 * self.bpd * self.seq * 8                 # input and target ids (int64)
+
+    def tokens_per_step(self, replicas: int) -> int:
+        return self.accum * self.bpd * self.tokens_per_sample * replicas
+
+    def dataset(self, n_samples: int, vocab: int, seed: int):
+        return SyntheticPairs(n_samples, vocab, seed) if self.strategy == "dpo" else SyntheticTokens(n_samples, self.seq, vocab, seed)
 
 
 # ----------------------------------------------------------------------------------------
@@ -129,6 +160,23 @@ class SyntheticTokens(torch.utils.data.Dataset):
         return {"input_ids": row[:-1], "target_ids": row[1:]}
 
 
+class SyntheticPairs(torch.utils.data.Dataset):
+    """Chosen / rejected pairs sharing a prompt: uniform random ids, the loss covers the responses."""
+
+    def __init__(self, n_samples: int, vocab: int, seed: int):
+        g = torch.Generator().manual_seed(seed)
+        prompt = torch.randint(0, vocab, (n_samples, DPO_PROMPT), generator=g, dtype=torch.long)
+        self.chosen = torch.cat([prompt, torch.randint(0, vocab, (n_samples, DPO_RESPONSE), generator=g)], dim=1)
+        self.rejected = torch.cat([prompt, torch.randint(0, vocab, (n_samples, DPO_RESPONSE), generator=g)], dim=1)
+        self.mask = torch.cat([torch.zeros(DPO_PROMPT, dtype=torch.bool), torch.ones(DPO_RESPONSE, dtype=torch.bool)])
+
+    def __len__(self):
+        return self.chosen.shape[0]
+
+    def __getitem__(self, i):
+        return {"chosen": self.chosen[i], "rejected": self.rejected[i], "chosen_mask": self.mask, "rejected_mask": self.mask}
+
+
 class StepTimer:
     """Trainer callback (both arms): times exactly ``steps`` optimizer steps after ``warmup``
     ones with CUDA events bracketed by barrier + synchronize."""
@@ -142,6 +190,10 @@ class StepTimer:
         self.clocks = None
         self._count = count_launches
         self._sampler = ClockSampler(device_index)
+        self.final_loss = None
+
+    def on_batch_end(self, context):
+        self.final_loss = context.loss   # a float in the reference, a device scalar here; read after the run
 
     def on_batch_begin(self, context):
         if self.seen == self.first:
@@ -178,15 +230,26 @@ def emit(payload: dict):
         print(json.dumps(payload), flush=True)
 
 
-def base_payload(args, ws: int, impl: str) -> dict:
+def base_payload(args, ws: int, impl: str, wl: "Workload") -> dict:
+    par = args.parallel if ws > 1 else "single"
+    cfg = {"model": "1B decoder (24L, d2048, 16q/4kv heads, ffn5632, vocab32000, tied)",
+           "global_batch": wl.bpd * wl.accum * ws, "micro_batch_per_gpu": wl.bpd, "grad_accum": wl.accum,
+           "seq_len": wl.seq, "parallelism": (f"dp{ws}" if par == "ddp" else f"{par}{ws}") if ws > 1 else "single",
+           "strategy": wl.strategy,
+           "optimizer": "AdamW lr3e-4 betas(0.9,0.95) wd0.01 clip1.0" + (" label_smoothing0.05" if wl.strategy == "seq" else f" dpo beta{DPO_BETA}"),
+           "l2": "no flush: weights (2.3 GB) + activations exceed the 126 MB L2 every step"}
+    if wl.strategy == "dpo":
+        cfg["pairs_per_gpu"] = wl.bpd
+        cfg["prompt_len"], cfg["response_len"] = DPO_PROMPT, DPO_RESPONSE
     return {"metric": METRIC, "unit": "tokens/s", "n_gpus": ws, "steps": args.steps, "warmup": args.warmup,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "impl": impl,
-            "config": {"model": "1B decoder (24L, d2048, 16q/4kv heads, ffn5632, vocab32000, tied)",
-                       "global_batch": BPD * ACCUM * ws, "micro_batch_per_gpu": BPD, "grad_accum": ACCUM,
-                       "seq_len": SEQ, "parallelism": f"dp{ws}" if ws > 1 else "single",
-                       "optimizer": "AdamW lr3e-4 betas(0.9,0.95) wd0.01 clip1.0 label_smoothing0.05",
-                       "l2": "no flush: weights (2.3 GB) + activations exceed the 126 MB L2 every step"}}
+            "impl": impl, "config": cfg}
+
+
+def strip_untimed_callbacks(trainer) -> None:
+    """Both arms: the end-of-run checkpoint (2.3 GB of safetensors) and the progress bar are not part of a step."""
+    trainer.callbacks = [cb for cb in trainer.callbacks
+                         if type(cb).__name__ not in ("CheckpointCallback", "ProgressBarCallback")]
 
 
 # ----------------------------------------------------------------------------------------
@@ -206,10 +269,12 @@ def run_own(args):
     from khaosz_b200.trainer import FusedAdamW, SchedulerFactory, StrategyFactory, Trainer
 
     cfg = AutoRegressiveLMConfig(**MODEL)
+    wl = Workload(args.strategy)
     mode = args.parallel if ws > 1 else "none"
     replicas = 1 if mode == "tp" else ws  # data-parallel replicas
     args.cuda_graph = bool(args.cuda_graph) if args.cuda_graph >= 0 else mode == "tp"
     steps_total = args.warmup + args.steps
+    accum = wl.accum
 
     def model_fn():
         torch.manual_seed(SEED)
@@ -225,19 +290,24 @@ def run_own(args):
     def scheduler_fn(opt):
         return SchedulerFactory.create(opt, "cosine", warmup_steps=1, lr_decay_steps=10_000)
 
-    # ---- device-timed steps (inputs resident on the device) ----
+    # ---- device-timed steps (inputs resident on the device; every step sees data it has not seen) ----
     model = model_fn().to(device)
-    executor = ExecutorFactory.create(mode, grad_accum_steps=ACCUM, cuda_graph=args.cuda_graph)
+    executor = ExecutorFactory.create(mode, grad_accum_steps=accum, cuda_graph=args.cuda_graph)
     opt = optimizer_fn(model)
     model, opt, _, sched = executor.prepare(model, opt, None, scheduler_fn(opt))
-    strategy = StrategyFactory.create("seq", model, device, label_smoothing=SMOOTH)
-    g = torch.Generator(device="cpu").manual_seed(SEED + (rank if replicas > 1 else 0))
-    pool = torch.randint(0, MODEL["vocab_size"], (ACCUM, BPD, SEQ + 1), generator=g).to(device)
+    strategy = StrategyFactory.create(wl.strategy, model, device, executor=executor, model_fn=model_fn, **wl.extra)
+    data = wl.dataset(steps_total * accum * wl.bpd, MODEL["vocab_size"], SEED + (rank if replicas > 1 else 0))
+    micro = []
+    for i in range(steps_total * accum):
+        rows = [data[i * wl.bpd + j] for j in range(wl.bpd)]
+        micro.append({k: torch.stack([r[k] for r in rows]).to(device) for k in rows[0]})
     model.train()
+    cursor = [0]
 
     def one_step():
-        for mb in range(ACCUM):
-            batch = {"input_ids": pool[mb, :, :-1], "target_ids": pool[mb, :, 1:]}
+        for _ in range(accum):
+            batch = micro[cursor[0] % len(micro)]
+            cursor[0] += 1
             with executor.accumulate(model):
                 loss = executor.micro_step(strategy, batch)
                 if executor.sync_gradients:
@@ -264,50 +334,82 @@ def run_own(args):
     clocks = sampler.stop()
     final_loss = float(loss)
     raise_on_device_error()
-    tokens = args.steps * ACCUM * BPD * SEQ * replicas
+    tokens = args.steps * wl.tokens_per_step(replicas)
     value = tokens / (ms / 1e3)
-    del model, opt, sched, strategy, executor, pool
+    del model, opt, sched, strategy, executor, micro, data
     torch.cuda.empty_cache()
 
     # ---- end to end through the public Trainer API ----
     e2e = None
     if not args.no_e2e:
-        n_samples = steps_total * ACCUM * BPD * replicas
-        dataset = SyntheticTokens(n_samples, SEQ, MODEL["vocab_size"], SEED)
-        timer = StepTimer(args.warmup, args.steps, ACCUM, local_rank, _lib.launch_count)
+        n_samples = steps_total * accum * wl.bpd * replicas
+        dataset = wl.dataset(n_samples, MODEL["vocab_size"], SEED)
+        timer = StepTimer(args.warmup, args.steps, accum, local_rank, _lib.launch_count)
         tmp = tempfile.mkdtemp(prefix="kb200_bench_")
-        tc = TrainConfig(model_fn=model_fn, strategy="seq", dataset=dataset, optimizer_fn=optimizer_fn,
-                         scheduler_fn=scheduler_fn, n_epoch=1, batch_per_device=BPD, grad_accum_steps=ACCUM,
+        tc = TrainConfig(model_fn=model_fn, strategy=wl.strategy, dataset=dataset, optimizer_fn=optimizer_fn,
+                         scheduler_fn=scheduler_fn, n_epoch=1, batch_per_device=wl.bpd, grad_accum_steps=accum,
                          max_grad_norm=CLIP, ckpt_dir=tmp, ckpt_interval=10 ** 9, log_dir=os.path.join(tmp, "logs"),
-                         log_interval=ACCUM, random_seed=SEED, num_workers=0, pin_memory=True, nprocs=ws,
+                         log_interval=accum, random_seed=SEED, num_workers=0, pin_memory=True, nprocs=ws,
                          backend="nccl", parallel_mode=mode, device_type="cuda",
-                         executor_kwargs={"cuda_graph": args.cuda_graph},
-                         extra_kwargs={"label_smoothing": SMOOTH})
+                         executor_kwargs={"cuda_graph": args.cuda_graph}, extra_kwargs=dict(wl.extra))
 
         trainer = Trainer(tc, callbacks=[timer])
-        # the end-of-run checkpoint and the progress bar are not part of a training step
-        trainer.callbacks = [cb for cb in trainer.callbacks
-                             if type(cb).__name__ not in ("CheckpointCallback", "ProgressBarCallback")]
+        strip_untimed_callbacks(trainer)
         trainer.train()
         ms_e2e = timer.ms  # already the max over ranks
         e2e = {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-               "h2d_bytes_per_step": ACCUM * 2 * BPD * SEQ * 8, "d2h_bytes_per_step": ACCUM * 4,
+               "h2d_bytes_per_step": accum * wl.h2d_per_micro, "d2h_bytes_per_step": accum * 4,
+               "final_loss": float(timer.final_loss) if timer.final_loss is not None else None,
                "api": "khaosz_b200.trainer.Trainer.train (DataLoader pin_memory -> H2D per micro-batch, "
                       "loss read back per micro-batch)"}
 
-    payload = base_payload(args, ws, "khaosz_b200")
-    if mode in ("fsdp", "fsdp_full", "tp"):
-        payload["config"]["parallelism"] = f"{mode}{ws}"
+    payload = base_payload(args, ws, "khaosz_b200", wl)
     if mode == "tp":
         payload["scaling"] = "strong"
-        payload["config"]["global_batch"] = BPD * ACCUM
+        payload["config"]["global_batch"] = wl.bpd * accum
     payload.update({"value": value, "ms_per_step": ms / args.steps, "clocks": clocks, "gpu_launches": launches,
                     "final_loss": final_loss})
     if e2e is not None:
         payload["e2e"] = e2e
+    if args.serve:
+        payload["serving"] = run_serving(args, rank, local_rank, ws)
     emit(payload)
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+def run_serving(args, rank: int, local_rank: int, ws: int) -> dict:
+    """Decode tokens/s and median time to first token of the continuous-batching server on the same
+    GPUs (tensor parallel over all ranks when N > 1): 256 Poisson arrivals, prompts uniform in
+    [128, 2048] random ids, 256 greedy tokens each, 16-token KV pages, bf16.  Rank 0 owns the
+    scheduler; the other ranks serve their weight slices."""
+    from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
+    from khaosz_b200.cli.benchmark import PRESETS, _IdTokenizer, bench_serve
+
+    try:
+        device = f"cuda:{local_rank}"
+        torch.manual_seed(SEED)   # identical random weights on every rank
+        cfg = AutoRegressiveLMConfig(**PRESETS["1b"])
+        model = AutoRegressiveLM(cfg).to(device=device, dtype=torch.bfloat16).eval()
+        knobs = dict(requests=256, rate=64.0, min_prompt=128, max_prompt=2048, gen=256, max_batch=256, page_size=16, seed=SEED)
+        if ws > 1:
+            from khaosz_b200.inference.tp import TPInferenceLM, serve_worker
+
+            if not dist.is_initialized():
+                dist.init_process_group("nccl", device_id=torch.device(device))
+            model = TPInferenceLM(model).eval()
+            if rank != 0:
+                serve_worker(model, _IdTokenizer(), max_batch_size=knobs["max_batch"],
+                             max_seq_len=knobs["max_prompt"] + knobs["gen"] + 1, page_size=knobs["page_size"])
+                return {}
+        row = bench_serve(model, cfg, knobs["requests"], knobs["rate"], knobs["min_prompt"], knobs["max_prompt"],
+                          knobs["gen"], knobs["max_batch"], knobs["page_size"], knobs["seed"])
+        return {"decode_tokens_per_s": row["decode_tokens_per_s_busy"], "output_tokens_per_s_wall": row["output_tokens_per_s_wall"],
+                "ttft_p50_s": row["ttft_p50_s"], "ttft_p99_s": row["ttft_p99_s"], "tensor_parallel": ws, "weights": "bf16",
+                "requests": knobs["requests"], "arrival_rate_per_s": knobs["rate"], "generated_per_request": knobs["gen"],
+                "page_size": knobs["page_size"], "clock": "host wall clock around the trace (requests arrive over seconds)"}
+    except Exception as exc:   # the training numbers above stand on their own
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
 
 # ----------------------------------------------------------------------------------------
@@ -353,7 +455,13 @@ def run_reference(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     cfg = AutoRegressiveLMConfig(**MODEL)
+    wl = Workload(args.strategy)
     steps_total = args.warmup + args.steps
+    if ws > 1 and args.parallel not in ("ddp", "fsdp"):
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": f"the reference has no '{args.parallel}' executor "
+                              "(its parallel_mode choices are none, ddp and fsdp)"}), flush=True)
+        return
 
     def model_fn():
         torch.manual_seed(SEED)
@@ -369,19 +477,18 @@ def run_reference(args):
     def scheduler_fn(opt):
         return SchedulerFactory.create(opt, schedule_type="cosine", warmup_steps=1, lr_decay_steps=10_000)
 
-    dataset = SyntheticTokens(steps_total * ACCUM * BPD * ws, SEQ, MODEL["vocab_size"], SEED)
-    timer = StepTimer(args.warmup, args.steps, ACCUM, local_rank)
+    dataset = wl.dataset(steps_total * wl.accum * wl.bpd * ws, MODEL["vocab_size"], SEED)
+    timer = StepTimer(args.warmup, args.steps, wl.accum, local_rank)
     tmp = tempfile.mkdtemp(prefix="ref_bench_")
-    tc = TrainConfig(model_fn=model_fn, strategy="seq", dataset=dataset, optimizer_fn=optimizer_fn,
-                     scheduler_fn=scheduler_fn, n_epoch=1, batch_per_device=BPD, grad_accum_steps=ACCUM,
+    mode = args.parallel if ws > 1 else "none"
+    ex_kwargs = {"gradient_as_bucket_view": True, "broadcast_buffers": False} if mode == "ddp" else {}
+    tc = TrainConfig(model_fn=model_fn, strategy=wl.strategy, dataset=dataset, optimizer_fn=optimizer_fn,
+                     scheduler_fn=scheduler_fn, n_epoch=1, batch_per_device=wl.bpd, grad_accum_steps=wl.accum,
                      max_grad_norm=CLIP, ckpt_dir=tmp, ckpt_interval=10 ** 9, log_dir=os.path.join(tmp, "logs"),
-                     log_interval=ACCUM, random_seed=SEED, num_workers=0, pin_memory=True, nprocs=ws, backend="nccl",
-                     parallel_mode="ddp" if ws > 1 else "none", device_type="cuda",
-                     executor_kwargs={"gradient_as_bucket_view": True, "broadcast_buffers": False} if ws > 1 else {},
-                     extra_kwargs={"label_smoothing": SMOOTH})
+                     log_interval=wl.accum, random_seed=SEED, num_workers=0, pin_memory=True, nprocs=ws, backend="nccl",
+                     parallel_mode=mode, device_type="cuda", executor_kwargs=ex_kwargs, extra_kwargs=dict(wl.extra))
     trainer = Trainer(tc, callbacks=[timer])
-    # the final full checkpoint (2.3 GB safetensors) is outside the timed steps; skip writing it
-    trainer.callbacks = [cb for cb in trainer.callbacks if type(cb).__name__ != "CheckpointCallback"]
+    strip_untimed_callbacks(trainer)
     try:
         trainer.train()
     except Exception as exc:
@@ -390,12 +497,14 @@ def run_reference(args):
                   flush=True)
         return
     ms = timer.ms  # already the max over ranks
-    tokens = args.steps * ACCUM * BPD * SEQ * ws
-    payload = base_payload(args, ws, "reference")
+    tokens = args.steps * wl.tokens_per_step(ws)
+    payload = base_payload(args, ws, "reference", wl)
     val = tokens / (ms / 1e3)
     payload.update({"value": val, "ms_per_step": ms / args.steps, "clocks": timer.clocks, "gpu_launches": None,
-                    "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": ACCUM * 2 * BPD * SEQ * 8,
-                            "d2h_bytes_per_step": ACCUM * 4,
+                    "final_loss": float(timer.final_loss) if timer.final_loss is not None else None,
+                    "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": wl.accum * wl.h2d_per_micro,
+                            "d2h_bytes_per_step": wl.accum * 4,
+                            "final_loss": float(timer.final_loss) if timer.final_loss is not None else None,
                             "api": "astrai.trainer.Trainer.train (the reference's only training path: H2D per "
                                    "micro-batch and loss.item() per micro-batch are inside it)"}})
     emit(payload)
@@ -413,6 +522,10 @@ def main():
     ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp", "fsdp_full", "tp"],
                     help="own arm, N > 1: data parallel (default), sharded data parallel, or tensor parallel "
                          "(tp: every rank reads the same batches, total work is fixed -> strong scaling)")
+    ap.add_argument("--strategy", default="seq", choices=["seq", "dpo"],
+                    help="seq: next-token pre-training (the headline); dpo: policy + frozen copy on chosen/rejected pairs")
+    ap.add_argument("--serve", type=int, default=0,
+                    help="own arm: 1 appends decode tokens/s and median time to first token of the server on the same GPUs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     ws = env_rank()[2]

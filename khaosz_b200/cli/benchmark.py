@@ -97,21 +97,35 @@ def bench_decode(model, cfg, batch: int, prompt: int, gen: int, trials: int, pag
 
 
 def bench_serve(model, cfg, requests: int, rate: float, min_prompt: int, max_prompt: int, gen: int, max_batch: int,
-                page_size: int, seed: int):
+                page_size: int, seed: int, engine_cls=None, stop=None):
+    """Replays a Poisson arrival trace through an engine with the reference's public interface
+    (``engine.scheduler.add_task(prompt, max_tokens, temperature, top_p, top_k, stream_callback)``).
+    ``engine_cls`` / ``stop`` select the engine under test: this package's by default, or the unmodified
+    reference's ``InferenceEngine`` and its ``STOP`` sentinel.  Time to first token is taken here, from the
+    stream callbacks, so that both engines are measured by the same clock."""
+    from ..inference.core.task import STOP as OWN_STOP
+
     rng = random.Random(seed)
-    engine = InferenceEngine(model, _IdTokenizer(), max_batch_size=max_batch, max_seq_len=max_prompt + gen + 1,
-                             max_prompt_len=max_prompt, page_size=page_size)
+    engine_cls = engine_cls or InferenceEngine
+    stop = OWN_STOP if stop is None else stop
+    engine = engine_cls(model, _IdTokenizer(), max_batch_size=max_batch, max_seq_len=max_prompt + gen + 1,
+                        max_prompt_len=max_prompt, page_size=page_size)
     done = threading.Semaphore(0)
+    ttft, tokens_out = [], [0]
     t_start = time.time()
 
     def submit():
         prompt = [rng.randrange(cfg.vocab_size) for _ in range(rng.randint(min_prompt, max_prompt))]
+        state = {"t0": time.time(), "first": None}
 
         def cb(tok):
-            from ..inference.core.task import STOP
-
-            if tok is STOP:
+            if tok is stop:
                 done.release()
+                return
+            tokens_out[0] += 1
+            if state["first"] is None:
+                state["first"] = time.time() - state["t0"]
+                ttft.append(state["first"])
 
         engine.scheduler.add_task(prompt, max_tokens=gen, temperature=1.0, top_p=1.0, top_k=1, stream_callback=cb)
 
@@ -124,10 +138,44 @@ def bench_serve(model, cfg, requests: int, rate: float, min_prompt: int, max_pro
     wall = time.time() - t_start
     stats = engine.get_stats()
     engine.shutdown()
+    ttft.sort()
+    pick = lambda q: ttft[min(len(ttft) - 1, int(q * len(ttft)))] if ttft else None
     return {"benchmark": "serve", "requests": requests, "arrival_rate_per_s": rate, "generated_per_request": gen,
-            "output_tokens_per_s_wall": requests * gen / wall, "decode_tokens_per_s_busy": stats["decode_tokens_per_s"],
-            "ttft_p50_s": stats["ttft_p50_s"], "ttft_p99_s": stats["ttft_p99_s"], "wall_s": wall,
-            "decode_graphs": stats.get("decode_graphs", 0)}
+            "output_tokens_per_s_wall": tokens_out[0] / wall, "decode_tokens_per_s_busy": stats.get("decode_tokens_per_s"),
+            "ttft_p50_s": pick(0.50), "ttft_p99_s": pick(0.99), "wall_s": wall,
+            "engine_ttft_p50_s": stats.get("ttft_p50_s"), "decode_graphs": stats.get("decode_graphs", 0)}
+
+
+def reference_serve(a, dtype):
+    """The same trace through the unmodified reference (``astrai.inference.InferenceEngine`` of the
+    install under ``baseline/_ref``, its own model class, its own scheduler loop and kernels:
+    ``astrai/inference/engine.py:93-288``, ``astrai/inference/core/scheduler.py:86-176``)."""
+    import os
+    import sys
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "baseline", "_ref")
+    if not os.path.isdir(os.path.join(root, "astrai")):
+        return {"impl": "reference", "unavailable": "baseline/_ref/astrai is not installed"}
+    try:
+        import h5py  # noqa: F401
+    except ImportError:
+        import types
+
+        sys.modules["h5py"] = types.ModuleType("h5py")   # imported by the reference at module import, never used here
+    for name in [m for m in sys.modules if m == "astrai" or m.startswith("astrai.")]:
+        del sys.modules[name]
+    sys.path.insert(0, root)
+    from astrai.config import AutoRegressiveLMConfig as RefConfig
+    from astrai.inference import STOP as REF_STOP, InferenceEngine as RefEngine
+    from astrai.model import AutoRegressiveLM as RefLM
+
+    torch.manual_seed(a.seed)
+    cfg = RefConfig(**PRESETS[a.preset])
+    model = RefLM(cfg).to(device=a.device, dtype=dtype).eval()
+    row = bench_serve(model, cfg, a.requests, a.rate, a.min_prompt, a.max_prompt, a.gen_length, a.max_batch_size,
+                      a.page_size if a.page_size != 128 else 16, a.seed, engine_cls=RefEngine, stop=REF_STOP)
+    row["impl"] = "reference"
+    return row
 
 
 def parse_args(argv=None):
@@ -147,6 +195,8 @@ def parse_args(argv=None):
     p.add_argument("--seed", type=int, default=3407)
     p.add_argument("--device", default="cuda")
     p.add_argument("--int8", action="store_true", help="int8 weight-only linears (per-channel scales)")
+    p.add_argument("--impl", choices=["khaosz_b200", "reference"], default="khaosz_b200",
+                   help="serve mode: 'reference' drives the unmodified reference engine installed under baseline/_ref")
     return p.parse_args(argv)
 
 
@@ -188,6 +238,13 @@ def main(argv=None):
         if a.mode != "serve":
             raise SystemExit("tensor-parallel benchmarking covers the serve mode")
         return _tensor_parallel(a, dtype)
+    if a.impl == "reference":
+        if a.mode != "serve":
+            raise SystemExit("the reference arm covers the serve mode (its own scripts/tools/benchmark.py has the others)")
+        row = reference_serve(a, dtype)
+        row["weights"] = "bf16"
+        print(json.dumps(row))
+        return [row]
     cfg, model = build_model(a.preset, a.device, dtype)
     if a.int8:
         from ..ops.quant import quantize_model_int8

@@ -46,6 +46,7 @@ def main(argv=None) -> None:
     ap.add_argument("--gemm_peak_tflops", type=float, default=1399.5, help="measured sustained bf16 GEMM peak")
     ap.add_argument("--link_gbs", type=float, default=770.0, help="measured peer copy bandwidth per direction")
     ap.add_argument("--nvls", type=int, default=1)
+    ap.add_argument("--model_params", type=int, default=1_148_000_000, help="length of the optimizer-step buffer")
     args = ap.parse_args(argv)
 
     rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -144,6 +145,68 @@ def main(argv=None) -> None:
     dist.barrier()
     report("all_reduce 256 MiB (kernel vs NCCL)", _timed(lambda: allreduce_(buf, ctrl, scale=1.0 / ws), args.iters),
            _timed(lambda: dist.all_reduce(plain), args.iters), 0.0, 2 * (ws - 1) / ws * n * 2)
+
+    # ---- stand-alone reduce-scatter / all-gather / broadcast of the same buffer against NCCL
+    from ..parallel.comm import all_gather_, broadcast_, reduce_scatter
+
+    piece = torch.empty(n // ws, dtype=torch.bfloat16, device=dev)
+    report("reduce_scatter 256 MiB (kernel vs NCCL)", _timed(lambda: reduce_scatter(buf, ctrl, out=piece), args.iters),
+           _timed(lambda: dist.reduce_scatter_tensor(piece, plain), args.iters), 0.0, (ws - 1) / ws * n * 2)
+    report("all_gather 256 MiB (kernel vs NCCL)", _timed(lambda: all_gather_(buf, ctrl), args.iters),
+           _timed(lambda: dist.all_gather_into_tensor(plain, piece), args.iters), 0.0, (ws - 1) / ws * n * 2)
+    report("broadcast 256 MiB (kernel vs NCCL)", _timed(lambda: broadcast_(buf, ctrl, root=0), args.iters),
+           _timed(lambda: dist.broadcast(plain, src=0), args.iters), 0.0, n * 2)
+    del buf, plain, piece
+
+    # ---- the data-parallel optimizer step on a buffer of the 1B model's size (1.15 G parameters): gradient
+    # reduce-scatter + global clip + sharded AdamW + parameter all-gather, as one monolithic call and in
+    # 25 MB buckets, against NCCL all-reduce + this package's single-GPU AdamW kernel on the whole vector
+    from ..parallel.comm import GradReducer
+    from ..trainer.optim import FusedAdamW
+    from ..utils.flat_params import FlatParameters
+
+    n_model = args.model_params // (8 * ws) * (8 * ws)
+
+    class _One(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.zeros(n_model, dtype=torch.bfloat16, device=dev))
+
+    link = 2 * (ws - 1) / ws * n_model * 2
+    for label, cap in (("one launch", None), ("25 MB buckets", 25)):
+        mod = _One()
+        flat = FlatParameters(mod, with_grad=True, pad_to=8 * ws)
+        red = GradReducer.create(flat, bucket_cap_mb=cap, overlap=cap is not None)
+        opt = FusedAdamW(mod.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.01)
+        opt.attach_flat(flat, allocate=False)
+        opt.attach_reducer(red)
+        flat.grad.normal_(generator=gen)
+
+        def fused_step():
+            opt.fused_clip(1.0)
+            opt.step()
+
+        fused_ms = _timed(fused_step, max(3, args.iters // 4))
+        if cap is None:
+            m = torch.zeros(n_model, dtype=torch.float32, device=dev)
+            v = torch.zeros_like(m)
+            g2 = flat.grad.clone()
+            lr_step = torch.tensor([1e-4, 1.0], device=dev)
+            sq = torch.zeros(1, device=dev)
+            from ..ops._lib import check as _check, lib as _lib_, ptr as _ptr, stream as _stream
+
+            def lib_step():
+                dist.all_reduce(g2)
+                sq.zero_()
+                _check(_lib_().kb_sumsq_bf16(_ptr(g2), n_model, _ptr(sq), _stream()), "sumsq")
+                _check(_lib_().kb_adamw_bf16(_ptr(flat.data), _ptr(g2), _ptr(m), _ptr(v), n_model, _ptr(lr_step), 0.9, 0.95,
+                                             1e-8, 0.01, 1.0 / ws, _ptr(sq), 1.0, _stream()), "adamw")
+
+            base_ms = _timed(lib_step, max(3, args.iters // 4))
+            del m, v, g2
+        report(f"reduce+clip+AdamW+all_gather, {n_model / 1e9:.2f} G params ({label})", fused_ms, base_ms, 0.0, link)
+        del mod, flat, red, opt
+        torch.cuda.empty_cache()
 
     torch.cuda.synchronize()
     raise_on_device_error()

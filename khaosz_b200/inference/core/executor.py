@@ -27,20 +27,61 @@ from .task import Task
 
 
 class _DecodeSlot:
-    """Static buffers (and, from the second use on, the captured graph) of one batch bucket."""
+    """Static buffers (and, from the second use on, the captured graph) of one batch bucket.
+
+    Everything a decode step reads from the host - token ids, positions, lengths, the block table
+    and the sampling parameters - lives in ONE device buffer (``stage``) with a page-locked twin on
+    the host: the host fills the twin with numpy writes and one asynchronous copy moves the step's
+    inputs (the reference builds a handful of small tensors per step, ``astrai/inference/core/
+    executor.py:59-94``).  The named tensors below are views of ``stage``."""
 
     def __init__(self, bucket: int, table_width: int, device):
-        self.bucket = bucket
-        self.ids = torch.zeros(bucket, 1, dtype=torch.long, device=device)
-        self.pos = torch.zeros(bucket, 1, dtype=torch.long, device=device)
-        self.lens = torch.zeros(bucket, dtype=torch.long, device=device)
-        self.table = torch.full((bucket, table_width), -1, dtype=torch.long, device=device)
-        self.temperature = torch.ones(bucket, dtype=torch.float32, device=device)
-        self.top_k = torch.zeros(bucket, dtype=torch.int32, device=device)
-        self.top_p = torch.ones(bucket, dtype=torch.float32, device=device)
+        self.bucket, self.width = bucket, table_width
+        b, w = bucket, table_width
+        tail_words = (3 * b + 1) // 2                      # three 4-byte vectors, packed into 8-byte words
+        self.words = 3 * b + b * w + tail_words
+        self.stage = torch.zeros(self.words, dtype=torch.long, device=device)
+        on_cuda = torch.device(device).type == "cuda"
+        self.host = torch.zeros(self.words, dtype=torch.long, pin_memory=on_cuda)
+
+        def views(buf):
+            tail = buf[3 * b + b * w:]
+            return dict(ids=buf[0:b].view(b, 1), pos=buf[b:2 * b].view(b, 1), lens=buf[2 * b:3 * b],
+                        table=buf[3 * b:3 * b + b * w].view(b, w), temperature=tail.view(torch.float32)[0:b],
+                        top_p=tail.view(torch.float32)[b:2 * b], top_k=tail.view(torch.int32)[2 * b:3 * b])
+
+        for name, t in views(self.stage).items():
+            setattr(self, name, t)
+        self.h = {k: v.numpy() for k, v in views(self.host).items()}
+        self.h["table"][:] = -1
+        self.h["temperature"][:] = 1.0
+        self.h["top_p"][:] = 1.0
+        self.h["top_k"][:] = 1
+        self.stage.copy_(self.host)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.out: Optional[torch.Tensor] = None
         self.uses = 0
+
+    def fill(self, last, pos, table_cpu, temperature, top_k, top_p) -> None:
+        """Write one step's inputs into the host twin and start the (single) copy to the device."""
+        n, h = len(last), self.h
+        h["ids"][:n, 0] = last
+        h["ids"][n:, 0] = 0
+        h["pos"][:n, 0] = pos
+        h["pos"][n:, 0] = 0
+        h["lens"][:n] = pos
+        h["lens"][:n] += 1
+        h["lens"][n:] = 0
+        h["table"][:] = -1
+        if table_cpu.numel():
+            h["table"][:n, : table_cpu.shape[1]] = table_cpu.numpy()
+        h["temperature"][:n] = temperature
+        h["temperature"][n:] = 1.0
+        h["top_k"][:n] = top_k
+        h["top_k"][n:] = 1
+        h["top_p"][:n] = top_p
+        h["top_p"][n:] = 1.0
+        self.stage.copy_(self.host, non_blocking=True)
 
 
 class Executor:
@@ -141,18 +182,12 @@ class Executor:
     def _decode_graphed(self, tasks: List[Task], last: List[int], pos: List[int]) -> List[int]:
         n = len(tasks)
         slot = self._slot(1 << max(0, math.ceil(math.log2(n))))
-        pad = slot.bucket - n
         table = self.page_cache.make_table_tensor([t.task_id for t in tasks], "cpu")
         if table.shape[1] > slot.table.shape[1]:
             raise RuntimeError("block table wider than the decode graph's static table")
-        slot.ids.copy_(torch.tensor(last + [0] * pad, dtype=torch.long).unsqueeze(1), non_blocking=True)
-        slot.pos.copy_(torch.tensor(pos + [0] * pad, dtype=torch.long).unsqueeze(1), non_blocking=True)
-        slot.lens.copy_(torch.tensor([p + 1 for p in pos] + [0] * pad, dtype=torch.long), non_blocking=True)
-        slot.table.fill_(-1)
-        slot.table[:n, : table.shape[1]].copy_(table, non_blocking=True)
-        slot.temperature.copy_(torch.tensor([t.temperature for t in tasks] + [1.0] * pad, dtype=torch.float32))
-        slot.top_k.copy_(torch.tensor([t.top_k for t in tasks] + [1] * pad, dtype=torch.int32))
-        slot.top_p.copy_(torch.tensor([t.top_p for t in tasks] + [1.0] * pad, dtype=torch.float32))
+        # the output of the previous step was read back (tolist) before this point, so the previous
+        # copy out of the host twin has completed and the twin may be rewritten
+        slot.fill(last, pos, table, [t.temperature for t in tasks], [t.top_k for t in tasks], [t.top_p for t in tasks])
         self._announce_slot(slot, n)
         return self._run_slot(slot)[:n].tolist()
 

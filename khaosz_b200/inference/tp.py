@@ -269,7 +269,7 @@ class DistributedExecutor(Executor):
 
     def _announce_slot(self, slot, n) -> None:
         self._header([OP_SLOT, slot.bucket, n])
-        self._send(slot.ids, slot.pos, slot.lens, slot.table)
+        self._send(slot.stage)      # ids, positions, lengths, block table and sampling parameters in one piece
 
     def close(self) -> None:
         if not self._closed and self.info.rank == 0:
@@ -296,8 +296,7 @@ class DistributedExecutor(Executor):
                 self.model(ids, paged_cache=view, position_ids=pos)
             elif op == OP_SLOT:
                 slot = self._slot(a)
-                for t in (slot.ids, slot.pos, slot.lens, slot.table):
-                    dist.broadcast(t, src=0, group=self.info.group)
+                dist.broadcast(slot.stage, src=0, group=self.info.group)
                 self._run_slot(slot)
             else:
                 raise RuntimeError(f"unknown control op {op}")

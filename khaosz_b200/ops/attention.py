@@ -4,8 +4,9 @@
   ``[B,S,H+2Hkv,D]`` projection buffer, then causal flash attention (tcgen05 kernels for
   ``D == 128``) reading q/k/v straight out of that buffer; the backward writes one packed
   gradient buffer and un-rotates it in place.
-* :func:`attention` — generic path for every other configuration (fp32, CPU, masks, other
-  head sizes): fp32 softmax attention with GQA broadcast, also the oracle of the tests.
+* :func:`attention` — same kernels for unpacked ``[B,S,H,D]`` tensors (heads narrower than 128 run
+  zero-padded); every other configuration (fp32, CPU, explicit masks, cross lengths) takes the
+  plain softmax attention with GQA broadcast, which is also the oracle of the tests.
 
 Replaces ``repeat_kv`` + permutes + ``F.scaled_dot_product_attention`` of the reference
 (``astrai/model/components/attention.py:95-103``).
@@ -125,6 +126,15 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     if (mask is None and S == T and q.is_cuda and q.dtype == torch.bfloat16 and D == FLASH_HEAD_DIM
             and v.shape[-1] == D and flash_available()):
         return _FlashFn.apply(q, k, v, bool(causal), scale)
+    if (mask is None and S == T and q.is_cuda and q.dtype == torch.bfloat16 and D < FLASH_HEAD_DIM and D % 8 == 0
+            and v.shape[-1] == D and H % Hkv == 0 and flash_available()):
+        # smaller heads (e.g. 64, the reference's benchmark model) ride the same kernels zero-padded to
+        # 128: the extra columns add nothing to q.k and produce zero output columns, the softmax scale
+        # stays that of the real width; twice the tensor work of a native kernel, but no materialised
+        # K/V repeat and no score matrix
+        pad = FLASH_HEAD_DIM - D
+        out = _FlashFn.apply(F.pad(q, (0, pad)), F.pad(k, (0, pad)), F.pad(v, (0, pad)), bool(causal), scale)
+        return out[..., :D]
     qh, kh, vh = q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3)
     if Hkv != H and kh.shape[1] != 1:
         rep = H // Hkv

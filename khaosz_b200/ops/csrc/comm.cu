@@ -60,8 +60,8 @@ reduce_slice_kernel(Peers grads, const void* grad_mc, Peers ctrl, int rank, int 
   float sq = 0.f;
   // UNROLL chunks per thread per trip: the remote loads of a trip are all issued before the
   // first one is consumed, which is what hides the NVLink / NVSwitch round trip
-  const long long stride = (long long)gridDim.x * THREADS;
-  for (long long c0 = blockIdx.x * (long long)THREADS + threadIdx.x; c0 < nchunks; c0 += stride * UNROLL) {
+  const long long stride = (long long)gridDim.x * blockDim.x;  // launched with THREADS or fewer threads
+  for (long long c0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; c0 < nchunks; c0 += stride * UNROLL) {
     uint4 raw[UNROLL];
     float acc[UNROLL][8];
 #pragma unroll
@@ -110,7 +110,7 @@ reduce_slice_kernel(Peers grads, const void* grad_mc, Peers ctrl, int rank, int 
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
   __syncthreads();
   if (threadIdx.x < 32) {
-    float v = threadIdx.x < THREADS / 32 ? red[threadIdx.x] : 0.f;
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
     v = warp_sum(v);
     if (threadIdx.x == 0) atomicAdd(norm_sq_local, v);
   }
@@ -136,9 +136,9 @@ __global__ void exchange_norm_kernel(Peers norms, Peers ctrl, int rank, int ws, 
 // Phase 3: AdamW on my slice, new parameters to every rank, closing barrier.
 __global__ void __launch_bounds__(THREADS)
 adamw_allgather_kernel(Peers params, void* param_mc, Peers grads, Peers ctrl, int rank, int ws,
-                       long long slice_off, long long slice_n, float* m, float* v, const float* lr_step, float beta1,
-                       float beta2, float eps, float wd, const float* norm_sq_total, float max_norm, uint32_t epoch,
-                       int* err) {
+                       long long bucket_n, long long total_n, long long slice_n, float* m, float* v,
+                       const float* lr_step, float beta1, float beta2, float eps, float wd, const float* norm_sq_total,
+                       float max_norm, uint32_t epoch, int* err) {
   // Never update from gradients that were not reduced or a norm that was not exchanged: with the
   // error word set the moments and the parameters of every rank stay exactly as they were.
   if (*reinterpret_cast<volatile int*>(err) != 0) return;
@@ -147,13 +147,21 @@ adamw_allgather_kernel(Peers params, void* param_mc, Peers grads, Peers ctrl, in
   if (max_norm > 0.f) gs = fminf(1.f, max_norm / (sqrtf(*norm_sq_total) + 1e-6f));
   const float bc1 = 1.f - powf(beta1, step), bc2 = 1.f - powf(beta2, step);
   const float step_size = lr / bc1, inv_sqrt_bc2 = rsqrtf(bc2), decay = 1.f - lr * wd;
-  __nv_bfloat16* p_mine = static_cast<__nv_bfloat16*>(params.p[rank]) + slice_off;
-  const __nv_bfloat16* g_mine = static_cast<const __nv_bfloat16*>(grads.p[rank]) + slice_off;
+  // This rank owns sub-slice `rank` of every bucket of `bucket_n` elements (the last bucket may be
+  // shorter); its moments are stored bucket after bucket.  Local element i -> global element:
+  __nv_bfloat16* p_base = static_cast<__nv_bfloat16*>(params.p[rank]);
+  const __nv_bfloat16* g_base = static_cast<const __nv_bfloat16*>(grads.p[rank]);
+  const long long per = bucket_n / ws;
   const long long nchunks = slice_n >> 3;
   for (long long c = blockIdx.x * (long long)THREADS + threadIdx.x; c < nchunks; c += (long long)gridDim.x * THREADS) {
+    const long long i = c * 8;
+    const long long b = i / per;
+    const long long left = total_n - b * bucket_n;
+    const long long len_b = left < bucket_n ? left : bucket_n;
+    const long long goff = b * bucket_n + rank * (len_b / ws) + (i - b * per);
     float pf[8] = {0}, gf[8] = {0};
-    acc8(pf, *reinterpret_cast<const uint4*>(p_mine + c * 8));
-    acc8(gf, *reinterpret_cast<const uint4*>(g_mine + c * 8));
+    acc8(pf, *reinterpret_cast<const uint4*>(p_base + goff));
+    acc8(gf, *reinterpret_cast<const uint4*>(g_base + goff));
     float4 m0 = *reinterpret_cast<float4*>(m + c * 8), m1 = *reinterpret_cast<float4*>(m + c * 8 + 4);
     float4 v0 = *reinterpret_cast<float4*>(v + c * 8), v1 = *reinterpret_cast<float4*>(v + c * 8 + 4);
     float mf[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
@@ -173,13 +181,13 @@ adamw_allgather_kernel(Peers params, void* param_mc, Peers grads, Peers ctrl, in
     o.x = pack_bf16x2(pf[0], pf[1]); o.y = pack_bf16x2(pf[2], pf[3]);
     o.z = pack_bf16x2(pf[4], pf[5]); o.w = pack_bf16x2(pf[6], pf[7]);
     if (param_mc != nullptr) {
-      multimem_st_bf16x8(static_cast<__nv_bfloat16*>(param_mc) + slice_off + c * 8, o);
+      multimem_st_bf16x8(static_cast<__nv_bfloat16*>(param_mc) + goff, o);
     } else {
 #pragma unroll
       for (int r = 0; r < MAX_RANKS; ++r)
         if (r < ws) {
           const int peer = (rank + r) % ws;
-          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[peer]) + slice_off + c * 8) = o;
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[peer]) + goff) = o;
         }
     }
   }
@@ -244,6 +252,85 @@ allreduce_kernel(Peers bufs, void* mc, Peers ctrl, int rank, int ws, long long n
   cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch + 1, err, KB_WAIT_BUDGET_NS);
 }
 
+// Stand-alone reduce-scatter: out[0, n / ws) = scale * sum over ranks of bufs[r][rank * n / ws ...).
+// `out` is local memory (it may be the rank's own piece of its buffer).  The closing barrier keeps
+// every rank's buffer intact until all pieces have been read.
+__global__ void __launch_bounds__(THREADS)
+reducescatter_kernel(Peers bufs, const void* mc, Peers ctrl, int rank, int ws, long long n, float scale,
+                     __nv_bfloat16* out, uint32_t epoch, int* err) {
+  if (!cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch, err, KB_WAIT_BUDGET_NS)) return;
+  const long long per = n / ws;
+  const long long off = per * rank;
+  const long long nchunks = per >> 3;
+  const long long stride = (long long)gridDim.x * THREADS;
+  for (long long c0 = blockIdx.x * (long long)THREADS + threadIdx.x; c0 < nchunks; c0 += stride * UNROLL) {
+    uint4 raw[UNROLL];
+    float acc[UNROLL][8];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long c = c0 + u * stride;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (mc != nullptr && c < nchunks)
+        raw[u] = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(mc) + off + c * 8);
+    }
+    if (mc != nullptr) {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) acc8(acc[u], raw[u]);
+    } else {
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r)
+        if (r < ws) {
+          const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(bufs.p[(rank + r) % ws]) + off;
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const long long c = c0 + u * stride;
+            raw[u] = c < nchunks ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) acc8(acc[u], raw[u]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long c = c0 + u * stride;
+      if (c >= nchunks) break;
+      uint4 o;
+      o.x = pack_bf16x2(acc[u][0] * scale, acc[u][1] * scale); o.y = pack_bf16x2(acc[u][2] * scale, acc[u][3] * scale);
+      o.z = pack_bf16x2(acc[u][4] * scale, acc[u][5] * scale); o.w = pack_bf16x2(acc[u][6] * scale, acc[u][7] * scale);
+      *reinterpret_cast<uint4*>(out + c * 8) = o;
+    }
+  }
+  cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch + 1, err, KB_WAIT_BUDGET_NS);
+}
+
+// Stand-alone all-gather / broadcast over a symmetric buffer of n elements: rank `src_rank` (all-gather:
+// every rank, its own piece [rank * n / ws ...); broadcast: the root, the whole buffer) stores its data
+// into every peer's buffer (one multimem.st per 16 bytes through the switch, or one store per peer).
+// The opening barrier makes sure that nobody still reads what is overwritten, the closing one that
+// everything has landed.
+__global__ void __launch_bounds__(THREADS)
+push_kernel(Peers bufs, void* mc, Peers ctrl, int rank, int ws, long long off, long long cnt, int active,
+            uint32_t epoch, int* err) {
+  if (!cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch, err, KB_WAIT_BUDGET_NS)) return;
+  if (active) {
+    const __nv_bfloat16* mine = static_cast<const __nv_bfloat16*>(bufs.p[rank]) + off;
+    const long long nchunks = cnt >> 3;
+    for (long long c = blockIdx.x * (long long)THREADS + threadIdx.x; c < nchunks; c += (long long)gridDim.x * THREADS) {
+      const uint4 vv = *reinterpret_cast<const uint4*>(mine + c * 8);
+      if (mc != nullptr) {
+        multimem_st_bf16x8(static_cast<__nv_bfloat16*>(mc) + off + c * 8, vv);
+      } else {
+#pragma unroll
+        for (int r = 1; r < MAX_RANKS; ++r)
+          if (r < ws) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bufs.p[(rank + r) % ws]) + off + c * 8) = vv;
+      }
+    }
+  }
+  cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch + 1, err, KB_WAIT_BUDGET_NS);
+}
+
 __global__ void barrier_kernel(Peers ctrl, int rank, int ws, int slot, uint32_t epoch, int* err,
                                unsigned long long budget_ns) {
   cta_peer_barrier(ctrl, rank, ws, slot, epoch, err, budget_ns);
@@ -296,9 +383,59 @@ int kb_reduce_adamw(const void* const* grad_ptrs, const void* const* param_ptrs,
   reduce_slice_kernel<<<grid, THREADS, 0, st>>>(grads, grad_mc, ctrl, rank, ws, slice_off, slice_n, 1.f / ws, scratch,
                                                 epoch, err);
   exchange_norm_kernel<<<1, 32, 0, st>>>(norms, ctrl, rank, ws, scratch, scratch + 1, grid, epoch + 1, err);
-  adamw_allgather_kernel<<<grid, THREADS, 0, st>>>(params, param_mc, grads, ctrl, rank, ws, slice_off, slice_n, m, v,
-                                                   lr_step, beta1, beta2, eps, weight_decay, scratch + 1, max_norm,
-                                                   epoch + 2, err);
+  // one bucket spanning the whole buffer: rank r owns [r * slice_n, (r + 1) * slice_n)
+  adamw_allgather_kernel<<<grid, THREADS, 0, st>>>(params, param_mc, grads, ctrl, rank, ws, slice_n * ws, slice_n * ws,
+                                                   slice_n, m, v, lr_step, beta1, beta2, eps, weight_decay, scratch + 1,
+                                                   max_norm, epoch + 2, err);
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+// The same step in pieces, for gradient buckets that are reduced while the backward pass is still
+// running.  The flat buffer of `total_n` elements is cut into buckets of `bucket_n` elements
+// (a multiple of 8 * ws; the last one may be shorter, total_n too is a multiple of 8 * ws); rank r
+// owns sub-slice r of every bucket.
+//
+// kb_reduce_bucket: mean of [off, off + n) over the ranks into this rank's gradient buffer, its
+// squared norm added to norm_sq_local[0] (zeroed by the caller once per step).  `grid` CTAs of
+// `threads` threads (a small grid leaves the SMs to the backward pass); every rank must call it for
+// the same buckets in the same order, `epoch` growing by at least 1 per call.
+int kb_reduce_bucket(const void* const* grad_ptrs, const void* const* ctrl_ptrs, const void* grad_mc, int rank, int ws,
+                     long long off, long long n, float* norm_sq_local, unsigned int epoch, int grid, int threads,
+                     void* stream) {
+  using namespace kb::comm;
+  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || (off & 7) || (n & 7) || n < 0) return KB_STATUS_BAD_ARG;
+  if (grid < 1 || grid > grid_size() || threads < 32 || threads > THREADS || (threads & 31)) return KB_STATUS_BAD_ARG;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  reduce_slice_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      load_peers(grad_ptrs, ws), grad_mc, load_peers(ctrl_ptrs, ws), rank, ws, off, n, 1.f / ws, norm_sq_local, epoch,
+      kb::error_word(dev));
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+// kb_adamw_buckets: after every bucket has been reduced: exchange of the squared-norm partials
+// (scratch[0] -> total in scratch[1]), clip factor, AdamW on this rank's sub-slices (moments m / v of
+// total_n / ws elements, stored bucket after bucket) and the updated values stored to every rank.
+// Uses epochs `epoch` and `epoch + 1`.
+int kb_adamw_buckets(const void* const* grad_ptrs, const void* const* param_ptrs, const void* const* ctrl_ptrs,
+                     const void* const* norm_ptrs, void* param_mc, int rank, int ws, long long bucket_n,
+                     long long total_n, float* m, float* v, const float* lr_step, float beta1, float beta2, float eps,
+                     float weight_decay, float max_norm, float* scratch, unsigned int epoch, void* stream) {
+  using namespace kb::comm;
+  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || bucket_n <= 0 || total_n <= 0 ||
+      (bucket_n % (8 * ws)) || (total_n % (8 * ws)))
+    return KB_STATUS_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* err = kb::error_word(dev);
+  const Peers grads = load_peers(grad_ptrs, ws), params = load_peers(param_ptrs, ws);
+  const Peers ctrl = load_peers(ctrl_ptrs, ws), norms = load_peers(norm_ptrs, ws);
+  const int grid = grid_size();
+  exchange_norm_kernel<<<1, 32, 0, st>>>(norms, ctrl, rank, ws, scratch, scratch + 1, grid, epoch, err);
+  adamw_allgather_kernel<<<grid, THREADS, 0, st>>>(params, param_mc, grads, ctrl, rank, ws, bucket_n, total_n,
+                                                   total_n / ws, m, v, lr_step, beta1, beta2, eps, weight_decay,
+                                                   scratch + 1, max_norm, epoch + 1, err);
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 
@@ -310,6 +447,49 @@ int kb_allreduce_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs,
   cudaGetDevice(&dev);
   allreduce_kernel<<<grid_size(), THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       load_peers(buf_ptrs, ws), mc, load_peers(ctrl_ptrs, ws), rank, ws, n, scale, epoch, kb::error_word(dev));
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+// out[n / ws] (local, bf16) = scale * sum over ranks of piece `rank` of the symmetric buffers; n a
+// multiple of 8 * ws.  Uses epochs `epoch` and `epoch + 1`.
+int kb_reducescatter_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, const void* mc, int rank, int ws,
+                          long long n, float scale, void* out, unsigned int epoch, void* stream) {
+  using namespace kb::comm;
+  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || n <= 0 || (n % (8 * ws)) || out == nullptr ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return KB_STATUS_BAD_ARG;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  reducescatter_kernel<<<grid_size(), THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      load_peers(buf_ptrs, ws), mc, load_peers(ctrl_ptrs, ws), rank, ws, n, scale, static_cast<__nv_bfloat16*>(out),
+      epoch, kb::error_word(dev));
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+// All-gather in place: every rank's piece [rank * n / ws, (rank + 1) * n / ws) of its symmetric buffer
+// is stored into all the others.  n a multiple of 8 * ws.  Epochs `epoch`, `epoch + 1`.
+int kb_allgather_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, void* mc, int rank, int ws,
+                      long long n, unsigned int epoch, void* stream) {
+  using namespace kb::comm;
+  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || n <= 0 || (n % (8 * ws))) return KB_STATUS_BAD_ARG;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const long long per = n / ws;
+  push_kernel<<<grid_size(), THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      load_peers(buf_ptrs, ws), mc, load_peers(ctrl_ptrs, ws), rank, ws, per * rank, per, 1, epoch, kb::error_word(dev));
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+// Broadcast: the first n elements (a multiple of 8) of rank `root`'s symmetric buffer go to every rank.
+int kb_broadcast_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, void* mc, int root, int rank, int ws,
+                      long long n, unsigned int epoch, void* stream) {
+  using namespace kb::comm;
+  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || root < 0 || root >= ws || n <= 0 || (n & 7)) return KB_STATUS_BAD_ARG;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  push_kernel<<<grid_size(), THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      load_peers(buf_ptrs, ws), mc, load_peers(ctrl_ptrs, ws), rank, ws, 0, n, rank == root ? 1 : 0, epoch,
+      kb::error_word(dev));
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 

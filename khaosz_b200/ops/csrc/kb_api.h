@@ -151,6 +151,30 @@ int kb_peer_barrier(const void* const* ctrl_ptrs, int rank, int ws, int slot, un
                     int budget_ms, void* stream);
 int kb_allreduce_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, void* mc_ptr, int rank,
                       int ws, long long n, float scale, unsigned int epoch, void* stream);
+// Stand-alone reduce-scatter (into local `out`), all-gather (in place) and broadcast (from `root`) of
+// symmetric bf16 buffers; each uses two epochs.
+int kb_reducescatter_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, const void* mc_ptr, int rank,
+                          int ws, long long n, float scale, void* out, unsigned int epoch, void* stream);
+int kb_allgather_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, void* mc_ptr, int rank, int ws,
+                      long long n, unsigned int epoch, void* stream);
+int kb_broadcast_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, void* mc_ptr, int root, int rank,
+                      int ws, long long n, unsigned int epoch, void* stream);
+// Data-parallel optimizer step over symmetric flat buffers: gradient reduce-scatter (mean) + global
+// clip + sharded AdamW + parameter all-gather.  kb_reduce_adamw does it in one call; the bucket pair
+// lets the reductions run bucket by bucket while the backward pass is still producing gradients
+// (argument meaning at the definitions in comm.cu).
+int kb_reduce_adamw(const void* const* grad_ptrs, const void* const* param_ptrs, const void* const* ctrl_ptrs,
+                    const void* const* norm_ptrs, const void* grad_mc, void* param_mc, int rank, int ws,
+                    long long slice_off, long long slice_n, float* m, float* v, const float* lr_step, float beta1,
+                    float beta2, float eps, float weight_decay, float max_norm, float* scratch, unsigned int epoch,
+                    void* stream);
+int kb_reduce_bucket(const void* const* grad_ptrs, const void* const* ctrl_ptrs, const void* grad_mc, int rank, int ws,
+                     long long off, long long n, float* norm_sq_local, unsigned int epoch, int grid, int threads,
+                     void* stream);
+int kb_adamw_buckets(const void* const* grad_ptrs, const void* const* param_ptrs, const void* const* ctrl_ptrs,
+                     const void* const* norm_ptrs, void* param_mc, int rank, int ws, long long bucket_n,
+                     long long total_n, float* m, float* v, const float* lr_step, float beta1, float beta2, float eps,
+                     float weight_decay, float max_norm, float* scratch, unsigned int epoch, void* stream);
 // GEMM fused with all-gather of an operand and / or reduce-scatter / all-reduce of the result;
 // the argument list is documented at the definition in gemm_comm.cu.
 int kb_gemm_comm(const void* const* a_ptrs, const void* const* b_ptrs, void* c_local,

@@ -68,6 +68,30 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
 _FP8_FORWARD = False
 
+# A data-parallel executor that reduces gradient buckets while the backward pass is still running
+# installs a callback here.  Weight gradients of the linear layers leave through the GEMM epilogue
+# (``main_grad``), not through autograd's accumulation, so the layer functions themselves say when a
+# weight has received its last contribution of the micro-batch: every forward use that will produce
+# a weight gradient is counted, every backward use counts down.
+_GRAD_READY_HOOK = None
+
+
+def set_grad_ready_hook(fn) -> None:
+    global _GRAD_READY_HOOK
+    _GRAD_READY_HOOK = fn
+
+
+def _count_use(w) -> None:
+    if _GRAD_READY_HOOK is not None:
+        w._kb_uses = getattr(w, "_kb_uses", 0) + 1
+
+
+def _use_done(w) -> None:
+    if _GRAD_READY_HOOK is not None:
+        w._kb_done = getattr(w, "_kb_done", 0) + 1
+        if w._kb_done >= getattr(w, "_kb_uses", 0):
+            _GRAD_READY_HOOK(w)
+
 
 def set_fp8_linear(enabled: bool) -> None:
     """Run the forward GEMM of every bf16 linear layer in block-scaled fp8 (e4m3; 1x128
@@ -81,12 +105,36 @@ def fp8_linear_enabled() -> bool:
     return _FP8_FORWARD
 
 
+# fp8 images of the bf16 master weights, valid for one weight generation: the optimizers update the
+# weights in place through raw pointers (no autograd version bump), so they announce every update here
+# and the 128x128-block quantisation of a weight runs once per optimizer step, not once per micro-batch.
+_WEIGHT_GENERATION = 0
+_FP8_WEIGHT_CACHE: dict = {}
+
+
+def bump_weight_generation() -> None:
+    global _WEIGHT_GENERATION
+    _WEIGHT_GENERATION += 1
+
+
+def _fp8_weight(w: torch.Tensor):
+    from .quant import quantize_fp8_128x128
+
+    key = (w.data_ptr(), tuple(w.shape))
+    hit = _FP8_WEIGHT_CACHE.get(key)
+    if hit is not None and hit[0] == _WEIGHT_GENERATION:
+        return hit[1], hit[2]
+    b8, sb = quantize_fp8_128x128(w)
+    _FP8_WEIGHT_CACHE[key] = (_WEIGHT_GENERATION, b8, sb)
+    return b8, sb
+
+
 def _forward_gemm(x2: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     if _FP8_FORWARD and x2.shape[1] % 128 == 0 and w.shape[0] % 8 == 0 and _lib.has("kb_gemm_fp8"):
-        from .quant import gemm_fp8, quantize_fp8_1x128, quantize_fp8_128x128
+        from .quant import gemm_fp8, quantize_fp8_1x128
 
         a8, sa = quantize_fp8_1x128(x2)
-        b8, sb = quantize_fp8_128x128(w)
+        b8, sb = _fp8_weight(w)
         y = gemm_fp8(a8, sa, b8, sb)
         return y if residual is None else y.add_(residual)
     return gemm(x2, w, residual=residual)
@@ -102,6 +150,8 @@ class _LinearFn(torch.autograd.Function):
         y = _forward_gemm(x2, w, res2)
         ctx.save_for_backward(x2, w)
         ctx.w_ref = w
+        if ctx.needs_input_grad[1]:
+            _count_use(w)
         ctx.x_shape = x.shape
         ctx.has_res = residual is not None
         return y.view(*x.shape[:-1], w.shape[0])
@@ -119,6 +169,7 @@ class _LinearFn(torch.autograd.Function):
                 # accumulate straight into the flat gradient buffer (C = A^T B + C)
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=main, residual=main)
                 ctx.w_ref.main_grad_dirty = True
+                _use_done(ctx.w_ref)
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True)
         dres = dy if ctx.has_res else None
@@ -164,6 +215,9 @@ class _MultiLinearFn(torch.autograd.Function):
         ctx.save_for_backward(x2, wcat)
         ctx.ws = ws
         ctx.x_shape = x.shape
+        for i, w in enumerate(ws):
+            if ctx.needs_input_grad[i + 1]:
+                _count_use(w)
         return y.view(*x.shape[:-1], wcat.shape[0])
 
     @staticmethod
@@ -180,6 +234,7 @@ class _MultiLinearFn(torch.autograd.Function):
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=mcat, residual=mcat)
                 for w in ctx.ws:
                     w.main_grad_dirty = True
+                    _use_done(w)
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True)
                 r = 0
@@ -386,6 +441,9 @@ class _LinearSwiGLUFn(torch.autograd.Function):
         ctx.save_for_backward(x2, wcat, gu)
         ctx.ws = (w_gate, w_up)
         ctx.x_shape = x.shape
+        for i, w in enumerate(ctx.ws):
+            if ctx.needs_input_grad[i + 1]:
+                _count_use(w)
         return h.view(*x.shape[:-1], Fh)
 
     @staticmethod
@@ -404,6 +462,7 @@ class _LinearSwiGLUFn(torch.autograd.Function):
                 gemm(dgu, x2, a_mn=True, b_mn=True, out=mcat, residual=mcat)
                 for w in ctx.ws:
                     w.main_grad_dirty = True
+                    _use_done(w)
             else:
                 dw = gemm(dgu, x2, a_mn=True, b_mn=True)
                 Fh = ctx.ws[0].shape[0]

@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import List, Optional
+from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
@@ -95,13 +95,64 @@ def allreduce_(buf: SymmetricBuffer, ctrl: PeerControl, scale: float = 1.0, use_
     return buf.tensor
 
 
+def _mc(buf: SymmetricBuffer, use_multicast: bool):
+    return ctypes.c_void_p(buf.multicast_ptr) if (use_multicast and buf.multicast_ptr) else None
+
+
+def reduce_scatter(buf: SymmetricBuffer, ctrl: PeerControl, out: Optional[torch.Tensor] = None, scale: float = 1.0,
+                   use_multicast: bool = True) -> torch.Tensor:
+    """``out = scale * sum over ranks of piece[rank]`` of a symmetric bf16 buffer (``numel`` a multiple of
+    ``8 * world_size``); ``out`` defaults to a fresh local tensor of ``numel / world_size`` elements."""
+    n = buf.tensor.numel()
+    assert buf.tensor.dtype == torch.bfloat16 and n % (8 * buf.world_size) == 0
+    if out is None:
+        out = torch.empty(n // buf.world_size, dtype=torch.bfloat16, device=buf.tensor.device)
+    check(lib().kb_reducescatter_bf16(buf.ptrs, ctrl.flags.ptrs, _mc(buf, use_multicast), buf.rank, buf.world_size, n,
+                                      float(scale), ptr(out), ctrl.next_epoch(2), stream()), "reducescatter_bf16")
+    return out
+
+
+def all_gather_(buf: SymmetricBuffer, ctrl: PeerControl, use_multicast: bool = True) -> torch.Tensor:
+    """Every rank's piece ``[rank * n / ws, (rank + 1) * n / ws)`` of the symmetric buffer lands in all copies."""
+    n = buf.tensor.numel()
+    assert buf.tensor.dtype == torch.bfloat16 and n % (8 * buf.world_size) == 0
+    check(lib().kb_allgather_bf16(buf.ptrs, ctrl.flags.ptrs, _mc(buf, use_multicast), buf.rank, buf.world_size, n,
+                                  ctrl.next_epoch(2), stream()), "allgather_bf16")
+    return buf.tensor
+
+
+def broadcast_(buf: SymmetricBuffer, ctrl: PeerControl, root: int = 0, numel: Optional[int] = None,
+               use_multicast: bool = True) -> torch.Tensor:
+    """The first ``numel`` elements (default: all; a multiple of 8) of ``root``'s copy land in every copy."""
+    n = buf.tensor.numel() if numel is None else numel
+    assert buf.tensor.dtype == torch.bfloat16 and n % 8 == 0
+    check(lib().kb_broadcast_bf16(buf.ptrs, ctrl.flags.ptrs, _mc(buf, use_multicast), root, buf.rank, buf.world_size, n,
+                                  ctrl.next_epoch(2), stream()), "broadcast_bf16")
+    return buf.tensor
+
+
 class GradReducer:
-    """Owns the symmetric homes of an executor's flat buffers and the fused optimizer step."""
+    """Owns the symmetric homes of an executor's flat buffers and the fused optimizer step.
+
+    The flat gradient buffer is cut into buckets of about ``bucket_cap_mb`` (the reference's
+    ``DDPExecutor(bucket_cap_mb=25)``, ``astrai/parallel/executor.py:146-198``); rank ``r`` owns
+    sub-slice ``r`` of every bucket.  On the micro-batch that ends an accumulation window the buckets
+    are reduced *while the backward pass is still running*: as soon as every parameter of a bucket has
+    received its last gradient contribution (and all later buckets have been handed over), the
+    bucket's reduce-scatter kernel is launched on a side stream behind an event, with a small grid
+    that shares the SMs with the backward kernels.  What is left when the backward pass returns is
+    flushed, then one exchange of the squared-norm partials, the clip factor, the sharded AdamW and
+    the parameter all-gather run as before.  Buckets are always handed over in the same (descending)
+    order on every rank, whatever the timing, because the kernels of the ranks pair up by call order.
+    """
 
     fuses_optimizer = True
     gathers_params = True
+    BUCKET_GRID = 32        # CTAs of a bucket reduction (the same on every rank: per-CTA barriers pair up)
+    BUCKET_THREADS = 256    # light enough to be co-resident with a persistent GEMM CTA
 
-    def __init__(self, flat: FlatParameters, mode: str, group=None):
+    def __init__(self, flat: FlatParameters, mode: str, group=None, bucket_cap_mb: Optional[float] = None,
+                 overlap: Optional[bool] = None):
         dev = flat.data.device
         self.flat, self.mode = flat, mode
         ws = dist.get_world_size(group)
@@ -114,40 +165,199 @@ class GradReducer:
         self.ctrl = PeerControl(dev, group)
         self.rank, self.ws = self.params.rank, ws
         self.slice_n = flat.numel // ws
-        self.slice_off = self.rank * self.slice_n
+        unit = 8 * ws
+        if overlap is None:
+            overlap = os.environ.get("KHAOSZ_B200_DDP_OVERLAP", "1") != "0"
+        bucket_n = flat.numel
+        if overlap and bucket_cap_mb and bucket_cap_mb > 0 and _lib.has("kb_reduce_bucket"):
+            bucket_n = max(unit, int(bucket_cap_mb * 2 ** 20) // flat.data.element_size() // unit * unit)
+        self.bucket_n = min(bucket_n, flat.numel)
+        self.n_buckets = -(-flat.numel // self.bucket_n)
+        self.overlap = bool(overlap) and self.n_buckets > 1
+        self.slice_off = self.rank * self.slice_n if self.n_buckets == 1 else None
         self._m = torch.zeros(self.slice_n, dtype=torch.float32, device=dev)
         self._v = torch.zeros(self.slice_n, dtype=torch.float32, device=dev)
         self._scratch = torch.zeros(2, dtype=torch.float32, device=dev)
         self._lr_dev = torch.zeros(2, dtype=torch.float32, device=dev)
         self.use_multicast = bool(self.params.multicast_ptr and self.grads.multicast_ptr)
+        # bucket bookkeeping for the overlapped hand-over
+        self._comm_stream = torch.cuda.Stream(device=dev) if self.overlap else None
+        self._bucket_params: List[List[int]] = [[] for _ in range(self.n_buckets)]   # indices into flat.params
+        self._param_buckets: Dict[int, List[int]] = {}
+        for i, (p, off) in enumerate(zip(flat.params, flat.offsets)):
+            if not p.requires_grad or p.numel() == 0:
+                continue
+            bs = list(range(off // self.bucket_n, (off + p.numel() - 1) // self.bucket_n + 1))
+            self._param_buckets[id(p)] = bs
+            for b in bs:
+                self._bucket_params[b].append(i)
+        self._armed = False
+        self._remaining: List[int] = []
+        self._next_bucket = -1
+        self._late: set = set()
+        self._used_side_stream = False
+        self.buckets_overlapped = 0   # buckets handed over before the backward pass returned (last window)
 
     @classmethod
-    def create(cls, flat: FlatParameters, mode: str = "allreduce", group=None) -> Optional["GradReducer"]:
+    def create(cls, flat: FlatParameters, mode: str = "allreduce", group=None, bucket_cap_mb: Optional[float] = None,
+               overlap: Optional[bool] = None) -> Optional["GradReducer"]:
         if not (flat.data.is_cuda and flat.data.dtype == torch.bfloat16 and _lib.has("kb_reduce_adamw")):
             return None
         ws = dist.get_world_size(group)
         if ws > 8 or flat.numel % (8 * ws):
             return None
-        return cls(flat, mode, group)
+        return cls(flat, mode, group, bucket_cap_mb, overlap)
+
+    # -- layout ---------------------------------------------------------------------------------
+    def bucket_range(self, b: int):
+        lo = b * self.bucket_n
+        return lo, min(self.bucket_n, self.flat.numel - lo)
+
+    def owned_ranges(self, rank: Optional[int] = None):
+        """``(global_offset, local_offset, n)`` of the pieces of the flat vector whose optimizer state
+        lives on ``rank`` (this rank by default), in the order the moments are stored."""
+        rank = self.rank if rank is None else rank
+        out, local = [], 0
+        for b in range(self.n_buckets):
+            lo, n = self.bucket_range(b)
+            piece = n // self.ws
+            out.append((lo + rank * piece, local, piece))
+            local += piece
+        return out
+
+    # -- hand-over of finished buckets --------------------------------------------------------------
+    def install_hooks(self, model) -> None:
+        """Tell this reducer when a parameter's gradient is final for the micro-batch.  Linear weights
+        report through the layer functions (``ops.functional.set_grad_ready_hook``); every other
+        parameter through autograd's post-accumulation hook, counted against the forward calls of its
+        module.  A parameter that is fed both ways (a tied embedding / output weight) counts as late
+        and goes with the final flush."""
+        if not self.overlap:
+            return
+        from ..models.components.layers import Linear
+        from ..ops import functional
+
+        linear_w = {id(m.weight) for m in model.modules() if isinstance(m, Linear)}
+        for module in model.modules():
+            direct = [p for p in module.parameters(recurse=False) if p.requires_grad and id(p) in self._param_buckets]
+            if not direct:
+                continue
+            if isinstance(module, Linear):
+                continue
+            for p in direct:
+                if id(p) in linear_w:
+                    self._late.add(id(p))
+            others = [p for p in direct if id(p) not in linear_w]
+            if not others:
+                continue
+
+            def count(mod, args, _ps=others):
+                if self._armed and torch.is_grad_enabled():
+                    for p in _ps:
+                        p._kb_uses = getattr(p, "_kb_uses", 0) + 1
+
+            module.register_forward_pre_hook(count)
+            for p in others:
+                def done(param):
+                    if self._armed:
+                        param._kb_done = getattr(param, "_kb_done", 0) + 1
+                        if param._kb_done >= getattr(param, "_kb_uses", 0):
+                            self.notify(param)
+
+                p.register_post_accumulate_grad_hook(done)
+        functional.set_grad_ready_hook(self.notify)
+
+    def begin_window(self, final: bool) -> None:
+        """Called before the forward pass of every micro-batch; ``final``: this one ends the window."""
+        if not self.overlap:
+            return
+        self._armed = bool(final)
+        if not final:
+            return
+        for p in self.flat.params:
+            p._kb_uses = 0
+            p._kb_done = 0
+        self._remaining = [sum(1 for i in idx if id(self.flat.params[i]) not in self._late) +
+                           (10 ** 9 if any(id(self.flat.params[i]) in self._late for i in idx) else 0)
+                           for idx in self._bucket_params]
+        self._next_bucket = self.n_buckets - 1
+        self._used_side_stream = False
+        self.buckets_overlapped = 0
+        self._scratch.zero_()
+
+    def notify(self, p) -> None:
+        if not self._armed:
+            return
+        for b in self._param_buckets.get(id(p), ()):
+            self._remaining[b] -= 1
+        self._hand_over(side=True)
+
+    def _launch_bucket(self, b: int, side: bool) -> None:
+        off, n = self.bucket_range(b)
+        piece = n // self.ws
+        mc_g = ctypes.c_void_p(self.grads.multicast_ptr) if self.use_multicast else None
+        main = torch.cuda.current_stream()
+        if side and self._comm_stream is not None:
+            ev = torch.cuda.Event()
+            ev.record(main)
+            self._comm_stream.wait_event(ev)
+            st = ctypes.c_void_p(self._comm_stream.cuda_stream)
+            self._used_side_stream = True
+            self.buckets_overlapped += 1
+        else:
+            if self._used_side_stream:      # keep the buckets in one order on the device as well
+                ev = torch.cuda.Event()
+                ev.record(self._comm_stream)
+                main.wait_event(ev)
+            st = stream()
+        grid, threads = (self.BUCKET_GRID, self.BUCKET_THREADS) if self.n_buckets > 1 else (lib().kb_comm_slots() - 8, 512)
+        check(lib().kb_reduce_bucket(self.grads.ptrs, self.ctrl.flags.ptrs, mc_g, self.rank, self.ws,
+                                     off + self.rank * piece, piece, ptr(self._scratch), self.ctrl.next_epoch(1), grid,
+                                     threads, st), "reduce_bucket")
+
+    def _hand_over(self, side: bool, flush: bool = False) -> None:
+        while self._next_bucket >= 0 and (flush or self._remaining[self._next_bucket] <= 0):
+            self._launch_bucket(self._next_bucket, side)
+            self._next_bucket -= 1
 
     def reduce(self) -> None:
         """Gradient reduction is part of :meth:`fused_step`; nothing to do at backward time."""
 
     def allreduce_grads(self) -> None:
         """Stand-alone mean all-reduce of the gradient buffer (for optimizers that cannot fuse)."""
+        self._armed = False
         allreduce_(self.grads, self.ctrl, 1.0 / self.ws, self.use_multicast)
 
     def fused_step(self, opt, lr, beta1, beta2, eps, wd, clip, step) -> None:
         _lib.set_device_floats(self._lr_dev, lr, step)   # launch arguments: no staging buffer to overwrite
-        mc_g = ctypes.c_void_p(self.grads.multicast_ptr) if self.use_multicast else None
         mc_p = ctypes.c_void_p(self.params.multicast_ptr) if self.use_multicast else None
-        check(lib().kb_reduce_adamw(self.grads.ptrs, self.params.ptrs, self.ctrl.flags.ptrs, self.ctrl.norms.ptrs,
-                                    mc_g, mc_p, self.rank, self.ws, self.slice_off, self.slice_n, ptr(self._m),
-                                    ptr(self._v), ptr(self._lr_dev), beta1, beta2, eps, wd, float(clip or 0.0),
-                                    ptr(self._scratch), self.ctrl.next_epoch(), stream()), "reduce_adamw")
-        _lib.add_launches(2)
+        if self.n_buckets == 1:
+            mc_g = ctypes.c_void_p(self.grads.multicast_ptr) if self.use_multicast else None
+            check(lib().kb_reduce_adamw(self.grads.ptrs, self.params.ptrs, self.ctrl.flags.ptrs, self.ctrl.norms.ptrs,
+                                        mc_g, mc_p, self.rank, self.ws, self.slice_off, self.slice_n, ptr(self._m),
+                                        ptr(self._v), ptr(self._lr_dev), beta1, beta2, eps, wd, float(clip or 0.0),
+                                        ptr(self._scratch), self.ctrl.next_epoch(), stream()), "reduce_adamw")
+            _lib.add_launches(2)
+        else:
+            if not self._armed:             # nobody announced the window (direct use): everything now
+                self._scratch.zero_()
+                self._next_bucket = self.n_buckets - 1
+                self._used_side_stream = False
+                self.buckets_overlapped = 0
+            self._hand_over(side=False, flush=True)
+            self._armed = False
+            if self._used_side_stream:
+                ev = torch.cuda.Event()
+                ev.record(self._comm_stream)
+                torch.cuda.current_stream().wait_event(ev)
+            check(lib().kb_adamw_buckets(self.grads.ptrs, self.params.ptrs, self.ctrl.flags.ptrs, self.ctrl.norms.ptrs,
+                                         mc_p, self.rank, self.ws, self.bucket_n, self.flat.numel, ptr(self._m),
+                                         ptr(self._v), ptr(self._lr_dev), beta1, beta2, eps, wd, float(clip or 0.0),
+                                         ptr(self._scratch), self.ctrl.next_epoch(2), stream()), "adamw_buckets")
+            _lib.add_launches(1)
         opt.last_grad_norm = self._scratch[1:2].sqrt()
 
     # optimizer-state plumbing used by FusedAdamW.state_dict / load_state_dict
     def moments(self):
-        return self._m, self._v, (self.slice_off, self.slice_n)
+        shard = (self.slice_off, self.slice_n) if self.n_buckets == 1 else (0, self.slice_n)
+        return self._m, self._v, shard

@@ -295,9 +295,16 @@ class BaseExecutor:
     def _no_sync(self, model: nn.Module):
         return contextlib.nullcontext()
 
+    def _begin_micro_step(self, final: bool) -> None:
+        """``final``: this micro-batch ends the accumulation window (its gradients get reduced)."""
+        reducer = getattr(self, "_reducer", None)
+        if reducer is not None and getattr(self, "_fused", False) and hasattr(reducer, "begin_window"):
+            reducer.begin_window(final)
+
     @contextlib.contextmanager
     def accumulate(self, model: nn.Module):
         self.gradient_state._do_sync()
+        self._begin_micro_step(self.gradient_state.sync_gradients)
         ctx = contextlib.nullcontext() if self.gradient_state.sync_gradients else self._no_sync(model)
         with ctx:
             yield
@@ -371,8 +378,9 @@ class DDPExecutor(BaseExecutor):
 
     Works on CPU/gloo as well as CUDA/NCCL (the reference's wrapper cannot wrap a CPU model,
     ``astrai/parallel/executor.py:181-193``).  The torch-DDP keyword arguments of the
-    reference are accepted for compatibility; ``bucket_cap_mb`` sizes the chunks of the
-    NVLink all-reduce kernel.
+    reference are accepted for compatibility; ``bucket_cap_mb`` sizes the gradient buckets that the
+    NVLink reduce kernels take over while the backward pass of the window's last micro-batch is
+    still running (``khaosz_b200.parallel.comm.GradReducer``).
     """
 
     def __init__(self, grad_accum_steps: int = 1, find_unused_parameters: bool = False, bucket_cap_mb: int = 25,
@@ -389,13 +397,22 @@ class DDPExecutor(BaseExecutor):
         same = len({(p.dtype, p.device) for p in params}) == 1
         if same:
             self.flat = FlatParameters(model, with_grad=True, pad_to=8 * max(get_world_size(), 1))
-        if self.init_sync:
-            _broadcast_parameters(model, self.flat)
         self._model = model
         if self.flat is not None and self.flat.data.is_cuda and get_world_size() > 1 and self.comm != "nccl":
             from .comm import GradReducer
 
-            self._reducer = GradReducer.create(self.flat, mode="allreduce")
+            self._reducer = GradReducer.create(self.flat, mode="allreduce", bucket_cap_mb=self.bucket_cap_mb)
+        if self.init_sync:
+            if self._reducer is not None and self.flat.numel % 8 == 0:
+                # rank 0's parameters to everybody through the NVLink broadcast kernel (one pass of
+                # multimem / peer stores over the symmetric parameter buffer)
+                from .comm import broadcast_
+
+                broadcast_(self._reducer.params, self._reducer.ctrl, root=0, use_multicast=self._reducer.use_multicast)
+                for t in model.buffers():
+                    dist.broadcast(t.data, src=0)
+            else:
+                _broadcast_parameters(model, self.flat)
         return model
 
     def _sync_gradients(self) -> None:
@@ -424,6 +441,7 @@ class DDPExecutor(BaseExecutor):
                 if getattr(optimizer, "_flat", None) is not None:
                     optimizer.attach_reducer(self._reducer)
                     self._fused = True
+                    self._reducer.install_hooks(model)   # buckets leave while the backward pass still runs
             elif self.flat is not None and hasattr(optimizer, "attach_flat"):
                 optimizer.attach_flat(self.flat)
             optimizer = AccumOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step)
@@ -444,9 +462,10 @@ class FSDPExecutor(BaseExecutor):
     """
 
     def __init__(self, grad_accum_steps: int = 1, comm: str = "auto", fp8: bool = False, cuda_graph: bool = False,
-                 **_ignored):
+                 bucket_cap_mb: int = 25, **_ignored):
         super().__init__(grad_accum_steps, fp8, cuda_graph)
         self.comm = comm
+        self.bucket_cap_mb = bucket_cap_mb
         self.shard: Optional[Tuple[int, int]] = None
         self._reducer = None
 
@@ -460,7 +479,7 @@ class FSDPExecutor(BaseExecutor):
         if self.flat.data.is_cuda and ws > 1 and self.comm != "nccl":
             from .comm import GradReducer
 
-            self._reducer = GradReducer.create(self.flat, mode="reducescatter")
+            self._reducer = GradReducer.create(self.flat, mode="reducescatter", bucket_cap_mb=self.bucket_cap_mb)
         return model
 
     def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):
@@ -474,6 +493,7 @@ class FSDPExecutor(BaseExecutor):
                 if use_reducer:
                     optimizer.attach_reducer(self._reducer)
                     self._fused = True
+                    self._reducer.install_hooks(model)
             elif get_world_size() > 1:
                 log.warning("fsdp: optimizer %s cannot shard its state; gradients are all-reduced and every "
                             "rank updates the full model", type(optimizer).__name__)

@@ -85,6 +85,9 @@ class FusedAdamW(Optimizer):
         else:
             self._step_per_param()
         self._clip = None
+        from ..ops.functional import bump_weight_generation
+
+        bump_weight_generation()    # cached fp8 images of the weights are stale now
         return loss
 
     def _global_norm_sq(self, g: torch.Tensor) -> torch.Tensor:
@@ -161,6 +164,16 @@ class FusedAdamW(Optimizer):
                                  group["eps"], group["weight_decay"], st["step"])
 
     # -- checkpoint layout: per-parameter ``exp_avg / exp_avg_sq / step`` like torch AdamW ------
+    def _owned_ranges(self, rank: Optional[int] = None):
+        """``(global_offset, local_offset, n)`` pieces of the flat vector whose moments live on ``rank``."""
+        if self._reducer is not None and hasattr(self._reducer, "owned_ranges"):
+            return self._reducer.owned_ranges(rank)
+        if self._shard is None:
+            return [(0, 0, self._flat.numel)]
+        n = self._shard[1]
+        r = dist.get_rank() if rank is None else rank
+        return [(r * n, 0, n)] if rank is not None else [(self._shard[0], 0, n)]
+
     def _full_moments(self) -> Tuple[torch.Tensor, torch.Tensor]:
         if self._shard is None or not dist.is_initialized():
             return self._m, self._v
@@ -169,7 +182,11 @@ class FusedAdamW(Optimizer):
         for t in (self._m, self._v):
             pieces = [torch.empty_like(t) for _ in range(ws)]
             dist.all_gather(pieces, t)
-            out.append(torch.cat(pieces))
+            full = torch.zeros(self._flat.numel, dtype=t.dtype, device=t.device)
+            for r in range(ws):
+                for g, l, n in self._owned_ranges(r):
+                    full[g:g + n] = pieces[r][l:l + n]
+            out.append(full)
         return out[0], out[1]
 
     def state_dict(self) -> Dict[str, Any]:
@@ -203,19 +220,19 @@ class FusedAdamW(Optimizer):
         for k, val in state_dict["param_groups"][0].items():
             if k != "params":
                 self.param_groups[0][k] = val
-        base = self._shard[0] if self._shard is not None else 0
-        n = self._m.numel()
+        owned = self._owned_ranges()
         for i, (p, off) in enumerate(zip(self._flat.params, self._flat.offsets)):
             st = state_dict["state"].get(i) or state_dict["state"].get(str(i))
             if st is None:
                 continue
             self._step_count = int(st["step"])
-            lo, hi = max(off, base), min(off + p.numel(), base + n)
-            if lo >= hi:
-                continue
-            for name, dst in (("exp_avg", self._m), ("exp_avg_sq", self._v)):
-                src = st[name].reshape(-1)[lo - off:hi - off]
-                dst[lo - base:hi - base].copy_(src.to(dst.device, dst.dtype))
+            for g, l, n in owned:
+                lo, hi = max(off, g), min(off + p.numel(), g + n)
+                if lo >= hi:
+                    continue
+                for name, dst in (("exp_avg", self._m), ("exp_avg_sq", self._v)):
+                    src = st[name].reshape(-1)[lo - off:hi - off]
+                    dst[l + lo - g:l + hi - g].copy_(src.to(dst.device, dst.dtype))
 
 
 def newton_schulz_orthogonalize(G: torch.Tensor, steps: int = 5) -> torch.Tensor:

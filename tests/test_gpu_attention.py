@@ -124,3 +124,51 @@ def test_flash_backward_throughput_report():
     flops = 2.5 * 4 * B * H * S * S * 128 / 2
     print(f"flash bwd causal B4 S2048 H16/4: {ms:.3f} ms = {flops / ms / 1e9:.0f} TFLOP/s (5-GEMM count)")
     ops.raise_on_device_error()
+
+
+@pytest.mark.parametrize("B,S,H,Hkv", [(4, 2048, 16, 4), (1, 4096, 16, 4)])
+def test_flash_forward_backward_at_the_training_shapes(B, S, H, Hkv):
+    """The shapes of the 1B configurations (batch 4 x 2048 and a 4096-token sequence, 16 query / 4 KV heads):
+    output, log-sum-exp and all three gradients against fp32 attention on the same inputs."""
+    qkv, q, k, v = _mk(B, S, H, Hkv, seed=5)
+    scale = 1.0 / math.sqrt(128)
+    o, lse = A._flash_fwd(q, k, v, True, scale)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    do = torch.randn(B, S, H, 128, device="cuda", generator=g).to(torch.bfloat16)
+    dqkv = torch.empty_like(qkv)
+    A._flash_bwd(q, k, v, o, do, lse, dqkv[:, :, :H], dqkv[:, :, H:H + Hkv], dqkv[:, :, H + Hkv:], True, scale)
+    torch.cuda.synchronize()
+    ops.raise_on_device_error()
+    # fp32 oracle, one batch entry at a time (the score matrix of a 4096-token sequence is 1 GB per 16 heads)
+    for b in range(B):
+        qf, kf, vf = (t[b:b + 1].float().detach().requires_grad_() for t in (q, k, v))
+        ref = ops.sdpa_reference(qf, kf, vf, True)
+        ref.backward(do[b:b + 1].float())
+        assert (o[b:b + 1].float() - ref).abs().max().item() < 2e-2
+        for name, got, want in (("dq", dqkv[b:b + 1, :, :H], qf.grad), ("dk", dqkv[b:b + 1, :, H:H + Hkv], kf.grad),
+                                ("dv", dqkv[b:b + 1, :, H + Hkv:], vf.grad)):
+            err = (got.float() - want).abs().max().item()
+            assert err <= 2e-2 * want.abs().max().item() + 2e-2, f"{name}[{b}]: {err}"
+
+
+@pytest.mark.parametrize("D,H,Hkv", [(64, 24, 4), (32, 4, 2)])
+def test_narrow_heads_run_on_the_flash_kernels(D, H, Hkv):
+    """Heads narrower than 128 (64 in the reference's benchmark model) take the same kernels zero-padded:
+    values and gradients against fp32 attention, and the kernel library is what runs."""
+    from khaosz_b200.ops import _lib
+
+    B, S = 2, 512
+    g = torch.Generator(device="cuda").manual_seed(7)
+    mk = lambda h: torch.randn(B, S, h, D, device="cuda", generator=g).to(torch.bfloat16).requires_grad_()
+    q, k, v = mk(H), mk(Hkv), mk(Hkv)
+    before = _lib.launch_count()
+    out = ops.attention.attention(q, k, v, causal=True)
+    assert _lib.launch_count() > before and out.shape == (B, S, H, D)
+    do = torch.randn_like(out)
+    out.backward(do)
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = ops.sdpa_reference(qf, kf, vf, True)
+    ref.backward(do.float())
+    assert (out.float() - ref).abs().max().item() < 2e-2
+    for got, want in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 2e-2

@@ -87,6 +87,54 @@ def test_kernel_allreduce_matches_nccl(nvls, port):
     _spawn(_allreduce_case, port, nvls=nvls, expect_multicast=nvls)
 
 
+def _collectives_case(expect_multicast=False):
+    """Stand-alone reduce-scatter, all-gather and broadcast kernels against plain tensor arithmetic."""
+    from khaosz_b200.ops import raise_on_device_error
+    from khaosz_b200.parallel.comm import PeerControl, SymmetricBuffer, all_gather_, broadcast_, reduce_scatter
+
+    rank, ws = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", rank)
+    n = 16 * ws * 4099
+    buf = SymmetricBuffer(n, torch.bfloat16, dev)
+    assert bool(buf.multicast_ptr) == bool(expect_multicast and buf.multicast_ptr)
+    ctrl = PeerControl(dev)
+    srcs = [torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + r)).to(torch.bfloat16)
+            for r in range(ws)]
+    per = n // ws
+    for it in range(2):
+        # reduce-scatter (mean): my piece of the sum
+        buf.tensor.copy_(srcs[rank])
+        torch.cuda.synchronize(); dist.barrier()
+        out = reduce_scatter(buf, ctrl, scale=1.0 / ws)
+        torch.cuda.synchronize()
+        want = sum(s_[rank * per:(rank + 1) * per].float() for s_ in srcs) / ws
+        assert (out.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+        assert torch.equal(buf.tensor, srcs[rank])            # the inputs are left alone
+        dist.barrier()
+        # all-gather: everybody ends with piece r of rank r
+        buf.tensor.zero_()
+        buf.tensor[rank * per:(rank + 1) * per].copy_(srcs[rank][rank * per:(rank + 1) * per])
+        torch.cuda.synchronize(); dist.barrier()
+        all_gather_(buf, ctrl)
+        torch.cuda.synchronize()
+        for r in range(ws):
+            assert torch.equal(buf.tensor[r * per:(r + 1) * per], srcs[r][r * per:(r + 1) * per]), (it, r)
+        dist.barrier()
+        # broadcast from the last rank
+        buf.tensor.copy_(srcs[rank])
+        torch.cuda.synchronize(); dist.barrier()
+        broadcast_(buf, ctrl, root=ws - 1)
+        torch.cuda.synchronize()
+        assert torch.equal(buf.tensor, srcs[ws - 1])
+        dist.barrier()
+    raise_on_device_error()
+
+
+@pytest.mark.parametrize("nvls,port", [(False, 29715), (True, 29716)])
+def test_kernel_reduce_scatter_all_gather_broadcast(nvls, port):
+    _spawn(_collectives_case, port, nvls=nvls, expect_multicast=nvls)
+
+
 def _timeout_case():
     from khaosz_b200.ops import _lib
     from khaosz_b200.parallel.comm import PeerControl

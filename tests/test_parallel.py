@@ -606,3 +606,30 @@ def test_dense_optimizer_state_loads_into_sharded_runs(mode, port, tmp_path):
     torch.save(opt.state_dict(), path)
     spawn_parallel_fn(_dense_state_into_sharded_case, world_size=2, backend="gloo", master_addr="127.0.0.1",
                       master_port=port, path=path, mode=mode)
+
+
+def test_bucketed_ownership_layout_matches_the_kernel_mapping():
+    """Rank r owns sub-slice r of every gradient bucket; the optimizer-state layout that the checkpoint code
+    uses (``owned_ranges``) must be the mapping the update kernel computes (local element -> global element)."""
+    from types import SimpleNamespace
+
+    from khaosz_b200.parallel.comm import GradReducer
+
+    for ws, numel, bucket_n in [(2, 16 * 37, 16 * 10), (8, 64 * 50, 64 * 7), (4, 32 * 9, 32 * 9), (8, 64 * 3, 64 * 100)]:
+        bucket_n = min(bucket_n, numel)
+        covered = torch.zeros(numel, dtype=torch.int32)
+        for rank in range(ws):
+            r = GradReducer.__new__(GradReducer)
+            r.flat = SimpleNamespace(numel=numel)
+            r.ws, r.rank, r.bucket_n = ws, rank, bucket_n
+            r.n_buckets = -(-numel // bucket_n)
+            ranges = r.owned_ranges()
+            assert sum(n for _, _, n in ranges) == numel // ws
+            per = bucket_n // ws
+            for g, l, n in ranges:
+                covered[g:g + n] += 1
+                for i in (l, l + n - 8):          # first and last 8-element chunk of the piece, as the kernel maps them
+                    b = i // per
+                    len_b = min(bucket_n, numel - b * bucket_n)
+                    assert b * bucket_n + rank * (len_b // ws) + (i - b * per) == g + (i - l)
+        assert bool((covered == 1).all())             # the ranks' pieces tile the vector exactly once
