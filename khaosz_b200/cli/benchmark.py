@@ -97,12 +97,14 @@ def bench_decode(model, cfg, batch: int, prompt: int, gen: int, trials: int, pag
 
 
 def bench_serve(model, cfg, requests: int, rate: float, min_prompt: int, max_prompt: int, gen: int, max_batch: int,
-                page_size: int, seed: int, engine_cls=None, stop=None):
+                page_size: int, seed: int, engine_cls=None, stop=None, budget_s: float = 0.0):
     """Replays a Poisson arrival trace through an engine with the reference's public interface
     (``engine.scheduler.add_task(prompt, max_tokens, temperature, top_p, top_k, stream_callback)``).
     ``engine_cls`` / ``stop`` select the engine under test: this package's by default, or the unmodified
     reference's ``InferenceEngine`` and its ``STOP`` sentinel.  Time to first token is taken here, from the
-    stream callbacks, so that both engines are measured by the same clock."""
+    stream callbacks, so that both engines are measured by the same clock.  ``budget_s`` > 0 ends the
+    measurement after that many seconds whatever has finished (the row then says ``cut_at_budget``
+    and the rates cover the tokens produced so far)."""
     from ..inference.core.task import STOP as OWN_STOP
 
     rng = random.Random(seed)
@@ -133,8 +135,12 @@ def bench_serve(model, cfg, requests: int, rate: float, min_prompt: int, max_pro
         submit()
         if rate > 0:
             time.sleep(rng.expovariate(rate))
+    cut = False
     for _ in range(requests):
-        done.acquire()
+        left = None if budget_s <= 0 else max(0.0, budget_s - (time.time() - t_start))
+        if not done.acquire(timeout=left):
+            cut = True
+            break
     wall = time.time() - t_start
     stats = engine.get_stats()
     engine.shutdown()
@@ -143,7 +149,8 @@ def bench_serve(model, cfg, requests: int, rate: float, min_prompt: int, max_pro
     return {"benchmark": "serve", "requests": requests, "arrival_rate_per_s": rate, "generated_per_request": gen,
             "output_tokens_per_s_wall": tokens_out[0] / wall, "decode_tokens_per_s_busy": stats.get("decode_tokens_per_s"),
             "ttft_p50_s": pick(0.50), "ttft_p99_s": pick(0.99), "wall_s": wall,
-            "engine_ttft_p50_s": stats.get("ttft_p50_s"), "decode_graphs": stats.get("decode_graphs", 0)}
+            "engine_ttft_p50_s": stats.get("ttft_p50_s"), "decode_graphs": stats.get("decode_graphs", 0),
+            "cut_at_budget": cut, "tokens_generated": tokens_out[0], "first_tokens_seen": len(ttft)}
 
 
 def reference_serve(a, dtype):
@@ -173,7 +180,8 @@ def reference_serve(a, dtype):
     cfg = RefConfig(**PRESETS[a.preset])
     model = RefLM(cfg).to(device=a.device, dtype=dtype).eval()
     row = bench_serve(model, cfg, a.requests, a.rate, a.min_prompt, a.max_prompt, a.gen_length, a.max_batch_size,
-                      a.page_size if a.page_size != 128 else 16, a.seed, engine_cls=RefEngine, stop=REF_STOP)
+                      a.page_size if a.page_size != 128 else 16, a.seed, engine_cls=RefEngine, stop=REF_STOP,
+                      budget_s=a.budget_s)
     row["impl"] = "reference"
     return row
 
@@ -195,6 +203,8 @@ def parse_args(argv=None):
     p.add_argument("--seed", type=int, default=3407)
     p.add_argument("--device", default="cuda")
     p.add_argument("--int8", action="store_true", help="int8 weight-only linears (per-channel scales)")
+    p.add_argument("--budget_s", type=float, default=0.0,
+                   help="serve mode: stop measuring after this many seconds and report what was produced so far")
     p.add_argument("--impl", choices=["khaosz_b200", "reference"], default="khaosz_b200",
                    help="serve mode: 'reference' drives the unmodified reference engine installed under baseline/_ref")
     return p.parse_args(argv)
@@ -258,7 +268,7 @@ def main(argv=None):
                                 a.device, dtype))
     if a.mode == "serve":
         out.append(bench_serve(model, cfg, a.requests, a.rate, a.min_prompt, a.max_prompt, a.gen_length,
-                               a.max_batch_size, a.page_size if a.page_size != 128 else 16, a.seed))
+                               a.max_batch_size, a.page_size if a.page_size != 128 else 16, a.seed, budget_s=a.budget_s))
     for row in out:
         row["weights"] = "int8" if a.int8 else "bf16"
         print(json.dumps(row))
