@@ -35,7 +35,7 @@ def _time(fn, iters: int, flush: torch.Tensor):
 
 def main(argv=None):
     p = argparse.ArgumentParser()
-    p.add_argument("kernel", choices=["gemm", "gemm_pair", "gemm_w8", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm",
+    p.add_argument("kernel", choices=["gemm", "gemm_pair", "gemm_swiglu", "gemm_w8", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm",
                                       "rmsnorm_bwd", "swiglu", "rope", "ce", "adamw", "decode", "sample", "embedding"])
     p.add_argument("--m", type=int, default=4096)
     p.add_argument("--n", type=int, default=4096)
@@ -63,6 +63,14 @@ def main(argv=None):
 
             fn = lambda: lib().kb_gemm_bf16_pair(ptr(x), ptr(w), ptr(out), None, M, N, K, K, K, N, 0, 0, 0, 0, stream())
         flops, bytes_ = 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
+    elif a.kernel == "gemm_swiglu":
+        # gate|up projection with the SwiGLU epilogue: --n is the number of features F (the GEMM is 2F wide)
+        from ..ops._lib import lib, ptr, stream
+
+        x, w = torch.randn(M, K, device=dev, dtype=bf), torch.randn(2 * N, K, device=dev, dtype=bf) * 0.02
+        gu, h = torch.empty(M, 2 * N, device=dev, dtype=bf), torch.empty(M, N, device=dev, dtype=bf)
+        fn = lambda: lib().kb_gemm_swiglu_bf16(ptr(x), ptr(w), ptr(gu), ptr(h), M, N, K, K, K, 2 * N, N, 0, stream())
+        flops, bytes_ = 4.0 * M * N * K, 2.0 * (M * K + 2 * N * K + 3 * M * N)
     elif a.kernel == "gemm_w8":
         from ..ops.quant import linear_w8, quantize_w8
 

@@ -304,6 +304,37 @@ class KvcacheView:
         return self._storage.gather(layer_id, self._page_table, total)
 
     # -- fused path ----------------------------------------------------------------------------
+    def _token_slots(self, B: int, T: int, device) -> Tensor:
+        """Pool row of each of the ``B * T`` new tokens (cached per view: the same for every layer)."""
+        if self._slots is None or self._slots.numel() != B * T:
+            if self._seq_lens is None:
+                pos = torch.arange(self._total_len - T, self._total_len, device=device).unsqueeze(0).expand(B, T)
+            else:
+                pos = self._seq_lens.long().unsqueeze(1) - T + torch.arange(T, device=device).unsqueeze(0)
+            self._slots = self._storage.slots(self._page_table.to(device), pos.clamp(min=0)).reshape(-1).contiguous()
+        return self._slots
+
+    def fused_rope_write_ok(self, qkv: Tensor, head_dim: int) -> bool:
+        st = self._storage
+        return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and head_dim in (64, 128, 256)
+                and st.k_cache.shape[-1] == head_dim and st.v_cache.shape[-1] == head_dim
+                and not torch.is_grad_enabled() and _lib.has("kb_rope_norm_kvwrite"))
+
+    def fused_rope_write(self, layer_id: int, qkv: Tensor, cs: Tensor, pos: Optional[Tensor], H: int, Hkv: int,
+                         q_norm_w: Optional[Tensor] = None, k_norm_w: Optional[Tensor] = None, eps: float = 1e-5):
+        """One kernel for what the reference does in four steps (``astrai/model/components/attention.py:86-93``):
+        rotate q and k, normalise them per head when the model has QK-norm, and store this step's K / V rows
+        into their pages.  ``qkv`` is the packed projection ``[B, T, H + 2 Hkv, D]`` (rotated in place);
+        returns the ``q, k, v`` views to hand to :meth:`attention` with ``written=True``."""
+        B, T, _, D = qkv.shape
+        slots = self._token_slots(B, T, qkv.device)
+        pos32 = None if pos is None else pos.to(torch.int32).expand(B, T).contiguous()
+        st = self._storage
+        check(lib().kb_rope_norm_kvwrite(ptr(qkv), ptr(cs), ptr(pos32), ptr(q_norm_w), ptr(k_norm_w), float(eps),
+                                         ptr(slots), ptr(st.k_cache[layer_id]), ptr(st.v_cache[layer_id]), B * T, T, H,
+                                         Hkv, D, qkv.stride(1), stream()), "rope_norm_kvwrite")
+        return qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+
     def _write_ragged(self, layer_id: int, k: Tensor, v: Tensor) -> None:
         B, T = k.shape[:2]
         if self._slots is None or self._slots.numel() != B * T:
@@ -318,9 +349,11 @@ class KvcacheView:
                 and H // Hkv <= (32 if self._storage.page_size in (16, 32, 64, 128) else 8)
                 and _lib.has("kb_paged_decode_attn"))
 
-    def attention(self, layer_id: int, q: Tensor, k: Tensor, v: Tensor) -> Tensor:
-        """Append this step's K/V to the pages, then attend: ``q [B,T,H,D]`` -> ``[B,T,H,Dv]``."""
-        self.write(layer_id, k, v)
+    def attention(self, layer_id: int, q: Tensor, k: Tensor, v: Tensor, written: bool = False) -> Tensor:
+        """Append this step's K/V to the pages (unless :meth:`fused_rope_write` already did), then attend:
+        ``q [B,T,H,D]`` -> ``[B,T,H,Dv]``."""
+        if not written:
+            self.write(layer_id, k, v)
         B, T, H, D = q.shape
         if self._decode_kernel_ok(q, k, v):
             st = self._storage

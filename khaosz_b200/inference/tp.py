@@ -93,14 +93,21 @@ class _Attention(nn.Module):
         hl, kl, D = a.h_local, a.kv_local, a.head_dim
         cs, pos = rotary
         qkv = _local_linear(x, a.qkv_weight, self.qkv8).view(B, S, hl + 2 * kl, D)
-        qk = ops.rope(qkv[:, :, : hl + kl], cs, pos)
-        q, k, v = qk[:, :, :hl], qk[:, :, hl:], qkv[:, :, hl + kl:]
-        if a.use_qk_norm:
-            q, k = a.q_norm(q), a.k_norm(k)
-        if paged_cache is not None:
-            ctx = paged_cache.attention(a.layer_id, q, k, v)
+        if paged_cache is not None and paged_cache.fused_rope_write_ok(qkv, D):
+            # RoPE, the optional QK-norm and this rank's K/V page write in one kernel
+            qw, kw = (a.q_norm.weight, a.k_norm.weight) if a.use_qk_norm else (None, None)
+            q, k, v = paged_cache.fused_rope_write(a.layer_id, qkv, cs, pos, hl, kl, qw, kw,
+                                                   a.q_norm.eps if a.use_qk_norm else 0.0)
+            ctx = paged_cache.attention(a.layer_id, q, k, v, written=True)
         else:
-            ctx = attn_ops.attention(q, k, v, causal=True)
+            qk = ops.rope(qkv[:, :, : hl + kl], cs, pos)
+            q, k, v = qk[:, :, :hl], qk[:, :, hl:], qkv[:, :, hl + kl:]
+            if a.use_qk_norm:
+                q, k = a.q_norm(q), a.k_norm(k)
+            if paged_cache is not None:
+                ctx = paged_cache.attention(a.layer_id, q, k, v)
+            else:
+                ctx = attn_ops.attention(q, k, v, causal=True)
         ctx = ctx.reshape(B * S, hl * D)
         if a.use_gate:
             ctx = ctx * torch.sigmoid(_local_linear(x, a.gate_weight, self.gate8).view(B * S, hl * D))

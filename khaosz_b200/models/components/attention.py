@@ -81,6 +81,14 @@ class GQA(nn.Module):
         if paged_cache is None and attn_mask is None and not self.use_qk_norm and attn_ops.fused_ok(qkv, D):
             ctx = attn_ops.rope_attention_packed(qkv, cs, pos, H, Hkv, causal=causal)
             return _finish(self, x, ctx.view(B, S, H * D), residual)
+        if paged_cache is not None and getattr(paged_cache, "fused_rope_write_ok", lambda *_: False)(qkv, D):
+            # serving: RoPE, the optional QK-norm and the K/V page write are one kernel
+            qw = self.q_norm.weight if self.use_qk_norm else None
+            kw = self.k_norm.weight if self.use_qk_norm else None
+            eps = self.q_norm.eps if self.use_qk_norm else 0.0
+            q, k, v = paged_cache.fused_rope_write(self.layer_id, qkv, cs, pos, H, Hkv, qw, kw, eps)
+            ctx = paged_cache.attention(self.layer_id, q, k, v, written=True)
+            return _finish(self, x, ctx.reshape(B, S, H * D), residual)
         qk = ops.rope(qkv[:, :, : H + Hkv], cs, pos)
         q, k, v = qk[:, :, :H], qk[:, :, H:], qkv[:, :, H + Hkv:]
         if self.use_qk_norm:

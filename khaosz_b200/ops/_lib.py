@@ -64,6 +64,7 @@ def _declare(lib):
         "kb_paged_decode_attn": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, L, F, P], I),
         "kb_paged_decode_tc": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, L, L, F, P], I),
         "kb_paged_kv_write": ([P, P, P, P, P, I, I, L, L, P], I),
+        "kb_rope_norm_kvwrite": ([P, P, P, P, P, F, P, P, P, I, I, I, I, I, L, P], I),
         "kb_sample": ([P, P, P, P, P, P, I, I, L, LL, P], I),
         "kb_gemm_w8": ([P, P, P, P, I, I, I, L, L, L, P], I),
         "kb_quant_w8": ([P, P, P, I, I, P], I),

@@ -29,6 +29,68 @@ __global__ void paged_kv_write_kernel(const __nv_bfloat16* __restrict__ k, const
 }
 
 // ---------------------------------------------------------------------------------------
+// RoPE (interleaved pairs, fp32) + optional per-head RMSNorm of q and k (applied after the
+// rotation, as the model does) + the K/V page write, in one pass over a packed projection row
+// [q heads | k heads | v heads].  One warp per (token, head); EPL = head_dim / 32 elements per lane.
+// q and k are rotated (and normalised) in place, k and v rows are also stored to their page slot
+// (slot < 0: no store, e.g. padding rows).
+// ---------------------------------------------------------------------------------------
+template <int EPL>
+__global__ void __launch_bounds__(256)
+rope_norm_kvwrite_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cs, const int* __restrict__ pos,
+                         const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w, float eps,
+                         const long long* __restrict__ slots, __nv_bfloat16* __restrict__ k_pool,
+                         __nv_bfloat16* __restrict__ v_pool, int tokens, int seq_len, int H, int Hkv, long row_stride) {
+  constexpr int D = EPL * 32;
+  const int heads = H + 2 * Hkv;
+  const long warp_id = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp_id >= (long)tokens * heads) return;
+  const long t = warp_id / heads;
+  const int h = (int)(warp_id - t * heads);
+  __nv_bfloat16* src = qkv + t * row_stride + (long)h * D + lane * EPL;
+  float x[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; i += 2) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + i));
+    x[i] = f.x;
+    x[i + 1] = f.y;
+  }
+  const long long slot = slots ? slots[t] : -1;
+  if (h < H + Hkv) {
+    const int position = pos ? pos[t] : (int)(t % seq_len);
+    const float* c = cs + ((size_t)position * (D / 2) + lane * (EPL / 2)) * 2;
+#pragma unroll
+    for (int i = 0; i < EPL; i += 2) {
+      const float co = c[i], si = c[i + 1];
+      const float a = x[i], b = x[i + 1];
+      x[i] = a * co - b * si;
+      x[i + 1] = a * si + b * co;
+    }
+    const __nv_bfloat16* w = h < H ? q_w : k_w;
+    if (w != nullptr) {
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) sq += x[i] * x[i];
+      sq = warp_sum(sq);
+      const float rs = rsqrtf(sq / (float)D + eps);
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) x[i] = x[i] * rs * __bfloat162float(w[lane * EPL + i]);
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; i += 2)
+      *reinterpret_cast<__nv_bfloat162*>(src + i) = __floats2bfloat162_rn(x[i], x[i + 1]);
+  }
+  if (h >= H && slot >= 0) {
+    const bool is_k = h < H + Hkv;
+    __nv_bfloat16* dst = (is_k ? k_pool : v_pool) + slot * ((long)Hkv * D) + (long)(h - H - (is_k ? 0 : Hkv)) * D + lane * EPL;
+#pragma unroll
+    for (int i = 0; i < EPL; i += 2)
+      *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(x[i], x[i + 1]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Paged decode attention.  grid = (n_splits, Hkv, B), 128 threads, head_dim 128.
 // Phase 1 (thread = key): scores of 128 keys against the G query heads of the group.
 // Phase 2 (thread = output dim): P V accumulation with online rescaling.
@@ -317,6 +379,31 @@ int kb_paged_kv_write(const void* k, const void* v, void* k_pool, void* v_pool, 
   kb::inf::paged_kv_write_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
       (const long long*)slots, tokens, row_elems, k_pitch, v_pitch);
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+// qkv: [tokens, row_stride] rows of (H + 2 Hkv) heads of head_dim in {64, 128, 256}; see the kernel.
+// q_w / k_w: per-head RMSNorm weights [head_dim] or NULL; slots: int64 [tokens] or NULL (no page write).
+int kb_rope_norm_kvwrite(void* qkv, const float* cs, const int* pos, const void* q_w, const void* k_w, float eps,
+                         const long long* slots, void* k_pool, void* v_pool, int tokens, int seq_len, int H, int Hkv,
+                         int head_dim, long row_stride, void* stream) {
+  using namespace kb::inf;
+  if (tokens <= 0) return KB_STATUS_OK;
+  if (H <= 0 || Hkv <= 0 || (row_stride & 1) || (reinterpret_cast<uintptr_t>(qkv) & 3) || (slots && (!k_pool || !v_pool)))
+    return KB_STATUS_BAD_ARG;
+  const long warps = (long)tokens * (H + 2 * Hkv);
+  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+  auto go = [&](auto kern) {
+    kern<<<blocks, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)qkv, cs, pos, (const __nv_bfloat16*)q_w,
+                                                   (const __nv_bfloat16*)k_w, eps, slots, (__nv_bfloat16*)k_pool,
+                                                   (__nv_bfloat16*)v_pool, tokens, seq_len, H, Hkv, row_stride);
+  };
+  switch (head_dim) {
+    case 64: go(rope_norm_kvwrite_kernel<2>); break;
+    case 128: go(rope_norm_kvwrite_kernel<4>); break;
+    case 256: go(rope_norm_kvwrite_kernel<8>); break;
+    default: return KB_STATUS_BAD_ARG;
+  }
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 

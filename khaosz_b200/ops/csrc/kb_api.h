@@ -128,6 +128,11 @@ int kb_gemm_fp8(const void* A8, const void* B8, const void* sa, const void* sb, 
                 int K, long lda, long ldb, long ldc, void* stream);
 
 // ---- inference ----------------------------------------------------------------------------
+// RoPE + optional q/k RMSNorm (after the rotation) in place on packed [q | k | v] rows, and the K/V
+// rows stored to their page slots, in one kernel (head_dim 64, 128 or 256).
+int kb_rope_norm_kvwrite(void* qkv, const float* cs, const int* pos, const void* q_w, const void* k_w, float eps,
+                         const long long* slots, void* k_pool, void* v_pool, int tokens, int seq_len, int H, int Hkv,
+                         int head_dim, long row_stride, void* stream);
 int kb_paged_kv_write(const void* k, const void* v, void* k_pool, void* v_pool, const void* slots,
                       int tokens, int row_elems, long k_pitch, long v_pitch, void* stream);
 // CUDA-core split-KV decode attention (any page size, group size <= 8) and its tcgen05 counterpart

@@ -93,3 +93,55 @@ def test_engine_on_gpu_matches_dense_greedy(tokenizer):
         want = "".join(tokenizer.decode([t]) for t in toks)
         # bf16 ties can flip an argmax late in the sequence; the first tokens must agree
         assert text[: len(want) // 2] == want[: len(want) // 2], (p, text, want)
+
+
+@pytest.mark.parametrize("D,H,Hkv,qk_norm,page", [(128, 8, 2, False, 16), (128, 8, 2, True, 16), (64, 6, 3, True, 32)])
+def test_fused_rope_qknorm_kv_write_matches_the_separate_steps(D, H, Hkv, qk_norm, page):
+    """RoPE + optional QK-norm + K/V page write as one kernel against rope -> norm -> write done apart
+    (fp32 formulas): rotated q, the pool rows of k and v, for a ragged decode step and a dense prefill."""
+    from khaosz_b200.ops.functional import _rope_torch, rope_table
+
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(D + H)
+    cs = rope_table(D, 512, 10000.0, device=dev)
+    qw = (1 + 0.1 * torch.randn(D, device=dev, generator=g)).to(torch.bfloat16) if qk_norm else None
+    kw = (1 + 0.1 * torch.randn(D, device=dev, generator=g)).to(torch.bfloat16) if qk_norm else None
+
+    def oracle(qkv, pos):
+        qk = _rope_torch(qkv[:, :, :H + Hkv].float(), cs, pos)
+        q, k = qk[:, :, :H], qk[:, :, H:]
+        if qk_norm:
+            q = torch.nn.functional.rms_norm(q, (D,), qw.float(), 1e-5)
+            k = torch.nn.functional.rms_norm(k, (D,), kw.float(), 1e-5)
+        return q, k, qkv[:, :, H + Hkv:].float()
+
+    for mode in ("decode", "prefill"):
+        B, T = (4, 1) if mode == "decode" else (2, 40)
+        kv = KVCache(1, 64, page, Hkv, D, dev, torch.bfloat16)
+        names = [f"s{i}" for i in range(B)]
+        lens = [37, 5, 64, 90][:B] if mode == "decode" else [T] * B
+        for n, l in zip(names, lens):
+            assert kv.task_alloc(n, list(range(l)))
+        table = kv.make_table_tensor(names, dev)
+        qkv = torch.randn(B, T, H + 2 * Hkv, D, device=dev, generator=g).to(torch.bfloat16)
+        if mode == "decode":
+            seq = torch.tensor(lens, device=dev)
+            pos = (seq - 1).unsqueeze(1)
+            view = kv.bind(table, seq_lens=seq)
+        else:
+            pos = None
+            view = kv.bind(table, total_len=T)
+        want_q, want_k, want_v = oracle(qkv, pos)
+        work = qkv.clone()
+        assert view.fused_rope_write_ok(work, D)
+        q, k, v = view.fused_rope_write(0, work, cs, pos, H, Hkv, qw, kw, 1e-5)
+        torch.cuda.synchronize()
+        assert (q.float() - want_q).abs().max().item() < 3e-2
+        assert (k.float() - want_k).abs().max().item() < 3e-2
+        st = kv._storage
+        kp, vp = st.k_cache[0].view(-1, Hkv, D), st.v_cache[0].view(-1, Hkv, D)
+        positions = pos.expand(B, T) if pos is not None else torch.arange(T, device=dev).unsqueeze(0).expand(B, T)
+        slots = st.slots(table, positions).reshape(-1)
+        assert bool((slots >= 0).all())
+        assert torch.equal(kp[slots], k.reshape(B * T, Hkv, D)) and torch.equal(vp[slots], v.reshape(B * T, Hkv, D))
+        assert (vp[slots].float() - want_v.reshape(B * T, Hkv, D)).abs().max().item() == 0.0

@@ -293,14 +293,21 @@ def test_fused_data_parallel_step_matches_single_gpu(mode, port, tmp_path):
     assert worst < 2e-2, worst
     # the *updates* must agree, not only the weights: four AdamW steps at lr 1e-3 move a weight by a
     # few 1e-3, so a rank that never applied an update would pass the absolute check above
+    moved = 0
     for k, v in sd.items():
         d_ref = v.float().cpu() - init[k]
         d_got = got["sd"][k].float() - init[k]
-        assert d_ref.abs().max().item() > 5e-4, f"{k}: the single-GPU run did not move"
+        if d_ref.abs().max().item() < 5e-4:
+            # bf16 weights without an fp32 master cannot follow every update (a norm weight at 1.0 needs a
+            # step of 2^-9 to move at all): then the parallel run must not have moved either
+            assert d_got.abs().max().item() < 8e-3, k
+            continue
+        moved += 1
         cos = torch.nn.functional.cosine_similarity(d_ref.flatten(), d_got.flatten(), dim=0).item()
         assert cos > 0.9, f"{k}: update direction differs from the single-GPU run (cosine {cos:.3f})"
         ratio = d_got.norm().item() / d_ref.norm().item()
         assert 0.8 < ratio < 1.25, f"{k}: update size differs from the single-GPU run (ratio {ratio:.3f})"
+    assert moved >= len(sd) // 2, f"only {moved} of {len(sd)} tensors moved in the single-GPU run"
     if "m0" in got:
         assert got["m0"].shape == sd["embed_tokens.weight"].shape
 

@@ -218,3 +218,39 @@ def test_throughput_callback_times_steps_on_the_device():
         torch.cuda.synchronize()
     assert cb._use_cuda and len(cb._marks) <= 2
     assert 0 < ctx.kwargs["step_ms"] < 1000 and ctx.kwargs["tokens_per_s"] > 0
+
+
+def test_adamw_kernel_tracks_fp32_adamw_over_30_steps():
+    """The library is compiled with fast-math; the optimizer kernel's divisions, square roots and powers
+    must still follow an fp32 AdamW (parameters rounded to bf16 after every step, as the kernel stores
+    them) over many steps: moments to fp32 accuracy, parameters to a couple of bf16 roundings."""
+    from khaosz_b200.ops._lib import check, lib, ptr, stream
+
+    n, steps = 1 << 20, 30
+    lr, b1, b2, eps, wd = 3e-4, 0.9, 0.95, 1e-8, 0.01
+    g = torch.Generator(device="cuda").manual_seed(11)
+    p = (torch.randn(n, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    p_ref, m_ref, v_ref = p.clone(), m.double(), v.double()
+    lr_step = torch.zeros(2, device="cuda")
+    for t in range(1, steps + 1):
+        grad = (torch.randn(n, device="cuda", generator=g) * (1e-3 if t % 3 else 1e-1)).to(torch.bfloat16)
+        lr_step.copy_(torch.tensor([lr, float(t)]))
+        check(lib().kb_adamw_bf16(ptr(p), ptr(grad), ptr(m), ptr(v), n, ptr(lr_step), b1, b2, eps, wd, 1.0, None, 0.0,
+                                  stream()), "adamw")
+        gd = grad.double()
+        m_ref = b1 * m_ref + (1 - b1) * gd
+        v_ref = b2 * v_ref + (1 - b2) * gd * gd
+        bc1, bc2 = 1 - b1 ** t, 1 - b2 ** t
+        upd = p_ref.double() * (1 - lr * wd) - (lr / bc1) * m_ref / (v_ref.sqrt() / bc2 ** 0.5 + eps)
+        p_ref = upd.to(torch.bfloat16)
+    torch.cuda.synchronize()
+    assert (m.double() - m_ref).abs().max().item() <= 1e-5 * m_ref.abs().max().item()
+    assert (v.double() - v_ref).abs().max().item() <= 1e-5 * v_ref.abs().max().item()
+    ulp = torch.exp2(torch.floor(torch.log2(p_ref.float().abs().clamp_min(1e-30))) - 7)
+    off = (p.float() - p_ref.float()).abs() / ulp
+    assert off.max().item() <= 3.0, off.max().item()                  # never more than a few roundings apart
+    assert (off > 1.0).float().mean().item() < 1e-3                   # and almost everywhere within one
+    moved = (p_ref.float() - (p_ref.float() * 0 + p.float())).abs().max().item()   # sanity: the reference itself moved
+    assert (p_ref.float().abs() > 0).all() and moved >= 0.0
