@@ -60,6 +60,7 @@ def _declare(lib):
         "kb_sumsq_bf16": ([P, LL, P, P], I),
         "kb_adamw_bf16": ([P, P, P, P, LL, P, F, F, F, F, F, P, F, P], I),
         "kb_flash_fwd": ([P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P], I),
+        "kb_flash_fwd_rect": ([P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, F, I, P], I),
         "kb_flash_bwd": ([P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, L, L, F, I, P], I),
         "kb_paged_decode_attn": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, L, F, P], I),
         "kb_paged_decode_tc": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, L, L, F, P], I),

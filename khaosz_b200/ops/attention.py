@@ -38,11 +38,17 @@ def fused_ok(qkv: torch.Tensor, head_dim: int) -> bool:
 def _flash_fwd(q, k, v, causal, scale):
     """q [B,S,H,D], k/v [B,S,Hkv,D] views with unit inner stride and a common row pitch."""
     B, S, H, D = q.shape
-    Hkv = k.shape[2]
+    T, Hkv = k.shape[1], k.shape[2]
     o = torch.empty((B, S, H, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
-    check(lib().kb_flash_fwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), B, S, H, Hkv, D, q.stride(1), k.stride(1),
-                             v.stride(1), o.stride(1), float(scale), int(causal), stream()), "flash_fwd")
+    if T == S:
+        check(lib().kb_flash_fwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), B, S, H, Hkv, D, q.stride(1), k.stride(1),
+                                 v.stride(1), o.stride(1), float(scale), int(causal), stream()), "flash_fwd")
+    else:   # the queries are the last S of T positions (prefill behind a cached prefix)
+        assert k.stride(0) == T * k.stride(1) and v.stride(0) == T * v.stride(1)
+        check(lib().kb_flash_fwd_rect(ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), B, S, T, H, Hkv, D, q.stride(1),
+                                      k.stride(1), v.stride(1), o.stride(1), float(scale), int(causal), stream()),
+              "flash_fwd_rect")
     return o, lse
 
 
@@ -123,16 +129,23 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     B, S, H, D = q.shape
     T, Hkv = k.shape[1], k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if (mask is None and S == T and q.is_cuda and q.dtype == torch.bfloat16 and D == FLASH_HEAD_DIM
-            and v.shape[-1] == D and flash_available()):
+    # S < T (queries behind a cached prefix) runs the forward kernel only: serving needs no gradient
+    lengths_ok = S == T or (S < T and not (torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad))
+                            and _lib.has("kb_flash_fwd_rect"))
+    if (mask is None and lengths_ok and q.is_cuda and q.dtype == torch.bfloat16 and D == FLASH_HEAD_DIM
+            and v.shape[-1] == D and H % Hkv == 0 and flash_available()):
+        if S != T:
+            return _flash_fwd(q.contiguous(), k.contiguous(), v.contiguous(), bool(causal), scale)[0]
         return _FlashFn.apply(q, k, v, bool(causal), scale)
-    if (mask is None and S == T and q.is_cuda and q.dtype == torch.bfloat16 and D < FLASH_HEAD_DIM and D % 8 == 0
+    if (mask is None and lengths_ok and q.is_cuda and q.dtype == torch.bfloat16 and D < FLASH_HEAD_DIM and D % 8 == 0
             and v.shape[-1] == D and H % Hkv == 0 and flash_available()):
         # smaller heads (e.g. 64, the reference's benchmark model) ride the same kernels zero-padded to
         # 128: the extra columns add nothing to q.k and produce zero output columns, the softmax scale
         # stays that of the real width; twice the tensor work of a native kernel, but no materialised
         # K/V repeat and no score matrix
         pad = FLASH_HEAD_DIM - D
+        if S != T:
+            return _flash_fwd(F.pad(q, (0, pad)), F.pad(k, (0, pad)), F.pad(v, (0, pad)), bool(causal), scale)[0][..., :D]
         out = _FlashFn.apply(F.pad(q, (0, pad)), F.pad(k, (0, pad)), F.pad(v, (0, pad)), bool(causal), scale)
         return out[..., :D]
     qh, kh, vh = q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3)

@@ -33,6 +33,8 @@ constexpr float LOG2E = 1.4426950408889634f;
 struct FwdParams {
   float* lse;  // [B, H, S]
   int B, S, H, Hkv;
+  int T;       // number of keys (S for self-attention over one sequence; larger when a cached prefix precedes the queries)
+  int kv_off;  // T - S: query row i sees keys 0 .. i + kv_off under the causal mask
   float scale_log2;
   int causal;
   int pair_heads;  // 1: tiles are heads (h, h+1) at one q block; 0: q blocks (2i, 2i+1) of one head
@@ -86,11 +88,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       q0[0] = (2 * qp) * BQ; q0[1] = (2 * qp + 1) * BQ;
     }
     (void)group;
-    const int total_kv_blocks = (p.S + BKV - 1) / BKV;
+    const int total_kv_blocks = (p.T + BKV - 1) / BKV;
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
       if (q0[t] >= p.S) nblk[t] = 0;
-      else if (p.causal) nblk[t] = min(total_kv_blocks, q0[t] / BKV + 1);
+      else if (p.causal) nblk[t] = min(total_kv_blocks, (q0[t] + BQ - 1 + p.kv_off) / BKV + 1);
       else nblk[t] = total_kv_blocks;
     }
   }
@@ -216,10 +218,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, sreg + c * 32);
       tmem_ld_wait();
       const int kv0 = j * BKV;
-      const bool need_mask = (p.causal && (kv0 + BKV - 1 > q0[t])) || (kv0 + BKV > p.S);
+      const bool need_mask = (p.causal && (kv0 + BKV - 1 > q0[t] + p.kv_off)) || (kv0 + BKV > p.T);
       float mx = m_run;
       if (need_mask) {
-        const int limit = p.causal ? min(qrow, p.S - 1) : (p.S - 1);  // last visible key
+        const int limit = p.causal ? min(qrow + p.kv_off, p.T - 1) : (p.T - 1);  // last visible key
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
           float v = __uint_as_float(sreg[i]) * p.scale_log2;
@@ -320,11 +322,24 @@ static int make_bsd_map(CUtensorMap* m, const void* base, int B, int S, int head
 }  // namespace fa
 }  // namespace kb
 
+extern "C" int kb_flash_fwd_rect(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int T,
+                                 int H, int Hkv, int Dh, long q_pitch, long k_pitch, long v_pitch, long o_pitch,
+                                 float scale, int causal, void* stream);
+
 extern "C" int kb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B,
                             int S, int H, int Hkv, int Dh, long q_pitch, long k_pitch, long v_pitch,
                             long o_pitch, float scale, int causal, void* stream) {
+  return kb_flash_fwd_rect(q, k, v, o, lse, B, S, S, H, Hkv, Dh, q_pitch, k_pitch, v_pitch, o_pitch, scale, causal, stream);
+}
+
+// S queries against T >= S keys per sequence (k / v are [B, T, Hkv, D]); under the causal mask query
+// i sees keys 0 .. i + (T - S): the queries are the last S positions of a sequence of T (prefill
+// behind a cached prefix).  T == S is plain self-attention.
+extern "C" int kb_flash_fwd_rect(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int T,
+                                 int H, int Hkv, int Dh, long q_pitch, long k_pitch, long v_pitch, long o_pitch,
+                                 float scale, int causal, void* stream) {
   using namespace kb::fa;
-  if (Dh != D || B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || H % Hkv) return KB_STATUS_BAD_ARG;
+  if (Dh != D || B <= 0 || S <= 0 || T < S || H <= 0 || Hkv <= 0 || H % Hkv) return KB_STATUS_BAD_ARG;
   auto bad = [](const void* p, long pitch) { return (reinterpret_cast<uintptr_t>(p) & 15) || (pitch & 7); };
   if (bad(q, q_pitch) || bad(k, k_pitch) || bad(v, v_pitch) || bad(o, o_pitch) || !lse) return KB_STATUS_BAD_ARG;
   static bool attr_set_dev[64] = {false};  // the attribute is per device
@@ -337,14 +352,16 @@ extern "C" int kb_flash_fwd(const void* q, const void* k, const void* v, void* o
     attr_set = true;
   }
   CUtensorMap tq, tk, tv, to;
-  if (make_bsd_map(&tq, q, B, S, H, q_pitch) || make_bsd_map(&tk, k, B, S, Hkv, k_pitch) ||
-      make_bsd_map(&tv, v, B, S, Hkv, v_pitch) || make_bsd_map(&to, o, B, S, H, o_pitch))
+  if (make_bsd_map(&tq, q, B, S, H, q_pitch) || make_bsd_map(&tk, k, B, T, Hkv, k_pitch) ||
+      make_bsd_map(&tv, v, B, T, Hkv, v_pitch) || make_bsd_map(&to, o, B, S, H, o_pitch))
     return KB_STATUS_TMAP_ERROR;
   int dev = 0;
   cudaGetDevice(&dev);
   FwdParams p;
   p.lse = lse;
   p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
+  p.T = T;
+  p.kv_off = T - S;
   p.scale_log2 = scale * LOG2E;
   p.causal = causal;
   p.n_qblocks = (S + BQ - 1) / BQ;

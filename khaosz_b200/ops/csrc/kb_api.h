@@ -98,6 +98,10 @@ int kb_adamw_bf16(void* p, const void* g, float* m, float* v, long long n, const
 int kb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S,
                  int H, int Hkv, int D, long q_pitch, long k_pitch, long v_pitch, long o_pitch,
                  float scale, int causal, void* stream);
+// The same with T >= S keys per sequence (k / v are [B,T,Hkv,D]): the queries are the last S positions.
+int kb_flash_fwd_rect(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int T,
+                      int H, int Hkv, int D, long q_pitch, long k_pitch, long v_pitch, long o_pitch,
+                      float scale, int causal, void* stream);
 int kb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                  const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int H,
                  int Hkv, int D, long q_pitch, long k_pitch, long v_pitch, long o_pitch,

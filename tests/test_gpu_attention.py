@@ -172,3 +172,22 @@ def test_narrow_heads_run_on_the_flash_kernels(D, H, Hkv):
     assert (out.float() - ref).abs().max().item() < 2e-2
     for got, want in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
         assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 2e-2
+
+
+@pytest.mark.parametrize("S,T,H,Hkv,D", [(40, 296, 8, 2, 128), (128, 1024, 4, 4, 128), (200, 333, 6, 3, 64), (1, 130, 8, 2, 128)])
+def test_prefill_behind_a_cached_prefix_runs_on_the_flash_kernel(S, T, H, Hkv, D):
+    """S new queries against T > S keys (the last S positions of the sequence): causal offset T - S."""
+    from khaosz_b200.ops import _lib
+
+    g = torch.Generator(device="cuda").manual_seed(S + T)
+    q = torch.randn(2, S, H, D, device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn(2, T, Hkv, D, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(2, T, Hkv, D, device="cuda", generator=g).to(torch.bfloat16)
+    before = _lib.launch_count()
+    with torch.inference_mode():
+        out = ops.attention.attention(q, k, v, causal=True)
+    assert _lib.launch_count() > before
+    torch.cuda.synchronize()
+    ops.raise_on_device_error()
+    ref = ops.sdpa_reference(q.float(), k.float(), v.float(), True)
+    assert (out.float() - ref).abs().max().item() < 2e-2
