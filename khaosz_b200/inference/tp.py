@@ -18,6 +18,8 @@ inputs are announced again, so the workers carry no request state besides their 
 
 from __future__ import annotations
 
+import os
+
 import datetime
 from typing import Dict, Optional
 
@@ -34,7 +36,9 @@ from .core.cache import KVCache
 from .core.executor import Executor
 
 OP_STOP, OP_PREFILL, OP_DECODE, OP_SLOT = 0, 1, 2, 3
-FUSED_ALLREDUCE_MAX_ROWS = 4096  # beyond this the staging buffers of the fused kernel get large
+# The fused GEMM -> all-reduce kernel is a decode kernel: a handful of tiles per rank and three
+# cross-rank waits.  Prefill-sized inputs take a local GEMM followed by a collective instead.
+FUSED_ALLREDUCE_MAX_ROWS = int(os.environ.get("KHAOSZ_B200_TP_FUSED_AR_ROWS", "512"))
 
 
 def _row_all_reduce(x: Tensor, w: Tensor, info: TPInfo) -> Tensor:

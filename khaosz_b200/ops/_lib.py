@@ -75,7 +75,7 @@ def _declare(lib):
         "kb_comm_slots": ([], I),
         "kb_gemm_comm": ([P, P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, I, I, ctypes.c_uint, P, I, P, ctypes.c_uint, P, I, P, P, P], I),
         "kb_reduce_adamw": ([P, P, P, P, P, P, I, I, LL, LL, P, P, P, F, F, F, F, F, P, ctypes.c_uint, P], I),
-        "kb_reduce_bucket": ([P, P, P, I, I, LL, LL, P, ctypes.c_uint, I, I, P], I),
+        "kb_reduce_bucket": ([P, P, P, I, I, LL, LL, I, I, P, ctypes.c_uint, I, I, P], I),
         "kb_adamw_buckets": ([P, P, P, P, P, I, I, LL, LL, P, P, P, F, F, F, F, F, P, ctypes.c_uint, P], I),
         "kb_allreduce_bf16": ([P, P, P, I, I, LL, F, ctypes.c_uint, P], I),
         "kb_reducescatter_bf16": ([P, P, P, I, I, LL, F, P, ctypes.c_uint, P], I),

@@ -50,12 +50,26 @@ __device__ __forceinline__ void multimem_st_bf16x8(void* mc_addr, uint4 v) {
 // Phase 1: reduce my slice of the gradients (mean over ranks), keep it in my own gradient
 // buffer, accumulate its squared norm.
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)   // <= 64 registers: a light CTA fits beside a persistent GEMM CTA
 reduce_slice_kernel(Peers grads, const void* grad_mc, Peers ctrl, int rank, int ws, long long slice_off,
-                    long long slice_n, float scale, float* norm_sq_local, uint32_t epoch, int* err) {
+                    long long slice_n, long long bucket_n, long long total_n, float scale, float* norm_sq_local,
+                    uint32_t epoch, int* err) {
+  // bucket_n == 0: one contiguous slice [slice_off, slice_off + slice_n).  Otherwise slice_off is the
+  // first element of the first bucket of a run of buckets and slice_n the summed length of this rank's
+  // sub-slices in them; local element i of the run lives at bucket_off(i) (see adamw_allgather_kernel).
   __shared__ float red[32];
   if (!cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch, err, KB_WAIT_BUDGET_NS)) return;
-  __nv_bfloat16* mine = static_cast<__nv_bfloat16*>(grads.p[rank]) + slice_off;
+  const long long per = bucket_n > 0 ? bucket_n / ws : 1;
+  auto where = [&](long long c) -> long long {   // global element of local chunk c
+    if (bucket_n == 0) return slice_off + c * 8;
+    const long long i = c * 8;
+    const long long b = i / per;
+    const long long first = slice_off + b * bucket_n;
+    const long long left = total_n - first;
+    const long long len_b = left < bucket_n ? left : bucket_n;
+    return first + rank * (len_b / ws) + (i - b * per);
+  };
+  __nv_bfloat16* mine = static_cast<__nv_bfloat16*>(grads.p[rank]);
   const long long nchunks = slice_n >> 3;
   float sq = 0.f;
   // UNROLL chunks per thread per trip: the remote loads of a trip are all issued before the
@@ -71,22 +85,23 @@ reduce_slice_kernel(Peers grads, const void* grad_mc, Peers ctrl, int rank, int 
       for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
       raw[u] = make_uint4(0u, 0u, 0u, 0u);
       if (grad_mc != nullptr && c < nchunks)
-        raw[u] = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(grad_mc) + slice_off + c * 8);
+        raw[u] = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(grad_mc) + where(c));
     }
     if (grad_mc != nullptr) {
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) acc8(acc[u], raw[u]);
     } else {
+      long long at[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) at[u] = (c0 + u * stride) < nchunks ? where(c0 + u * stride) : -1;
 #pragma unroll
       for (int r = 0; r < MAX_RANKS; ++r) {
         if (r < ws) {
           const int peer = (rank + r) % ws;  // spread the traffic: every rank starts with itself
-          const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(grads.p[peer]) + slice_off;
+          const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(grads.p[peer]);
 #pragma unroll
-          for (int u = 0; u < UNROLL; ++u) {
-            const long long c = c0 + u * stride;
-            raw[u] = c < nchunks ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0u, 0u, 0u, 0u);
-          }
+          for (int u = 0; u < UNROLL; ++u)
+            raw[u] = at[u] >= 0 ? *reinterpret_cast<const uint4*>(src + at[u]) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
           for (int u = 0; u < UNROLL; ++u) acc8(acc[u], raw[u]);
         }
@@ -103,7 +118,7 @@ reduce_slice_kernel(Peers grads, const void* grad_mc, Peers ctrl, int rank, int 
       o.w = pack_bf16x2(acc[u][6] * scale, acc[u][7] * scale);
 #pragma unroll
       for (int e = 0; e < 8; ++e) sq += (acc[u][e] * scale) * (acc[u][e] * scale);
-      *reinterpret_cast<uint4*>(mine + c * 8) = o;
+      *reinterpret_cast<uint4*>(mine + where(c)) = o;
     }
   }
   sq = warp_sum(sq);
@@ -380,8 +395,8 @@ int kb_reduce_adamw(const void* const* grad_ptrs, const void* const* param_ptrs,
   const Peers ctrl = load_peers(ctrl_ptrs, ws), norms = load_peers(norm_ptrs, ws);
   const int grid = grid_size();
   cudaMemsetAsync(scratch, 0, 2 * sizeof(float), st);
-  reduce_slice_kernel<<<grid, THREADS, 0, st>>>(grads, grad_mc, ctrl, rank, ws, slice_off, slice_n, 1.f / ws, scratch,
-                                                epoch, err);
+  reduce_slice_kernel<<<grid, THREADS, 0, st>>>(grads, grad_mc, ctrl, rank, ws, slice_off, slice_n, 0, 0, 1.f / ws,
+                                                scratch, epoch, err);
   exchange_norm_kernel<<<1, 32, 0, st>>>(norms, ctrl, rank, ws, scratch, scratch + 1, grid, epoch + 1, err);
   // one bucket spanning the whole buffer: rank r owns [r * slice_n, (r + 1) * slice_n)
   adamw_allgather_kernel<<<grid, THREADS, 0, st>>>(params, param_mc, grads, ctrl, rank, ws, slice_n * ws, slice_n * ws,
@@ -395,21 +410,28 @@ int kb_reduce_adamw(const void* const* grad_ptrs, const void* const* param_ptrs,
 // (a multiple of 8 * ws; the last one may be shorter, total_n too is a multiple of 8 * ws); rank r
 // owns sub-slice r of every bucket.
 //
-// kb_reduce_bucket: mean of [off, off + n) over the ranks into this rank's gradient buffer, its
-// squared norm added to norm_sq_local[0] (zeroed by the caller once per step).  `grid` CTAs of
-// `threads` threads (a small grid leaves the SMs to the backward pass); every rank must call it for
-// the same buckets in the same order, `epoch` growing by at least 1 per call.
+// kb_reduce_bucket: mean over the ranks of this rank's sub-slices of the buckets b_lo .. b_hi (both
+// inclusive) into its own gradient buffer, their squared norm added to norm_sq_local[0] (zeroed by the
+// caller once per step).  One bucket with a small grid of light CTAs (`grid` x `threads`) shares the
+// SMs with the backward pass; the run of buckets left at the end goes in one launch with the full
+// grid.  Every rank must make the same calls in the same order, `epoch` growing by at least 1 per call.
 int kb_reduce_bucket(const void* const* grad_ptrs, const void* const* ctrl_ptrs, const void* grad_mc, int rank, int ws,
-                     long long off, long long n, float* norm_sq_local, unsigned int epoch, int grid, int threads,
-                     void* stream) {
+                     long long bucket_n, long long total_n, int b_lo, int b_hi, float* norm_sq_local,
+                     unsigned int epoch, int grid, int threads, void* stream) {
   using namespace kb::comm;
-  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || (off & 7) || (n & 7) || n < 0) return KB_STATUS_BAD_ARG;
+  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || bucket_n <= 0 || total_n <= 0 || (bucket_n % (8 * ws)) ||
+      (total_n % (8 * ws)) || b_lo < 0 || b_hi < b_lo || (long long)b_hi * bucket_n >= total_n)
+    return KB_STATUS_BAD_ARG;
   if (grid < 1 || grid > grid_size() || threads < 32 || threads > THREADS || (threads & 31)) return KB_STATUS_BAD_ARG;
   int dev = 0;
   cudaGetDevice(&dev);
+  const long long first = (long long)b_lo * bucket_n;
+  long long last_end = (long long)(b_hi + 1) * bucket_n;
+  if (last_end > total_n) last_end = total_n;
+  const long long mine_n = (last_end - first) / ws;   // summed length of this rank's sub-slices in the run
   reduce_slice_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      load_peers(grad_ptrs, ws), grad_mc, load_peers(ctrl_ptrs, ws), rank, ws, off, n, 1.f / ws, norm_sq_local, epoch,
-      kb::error_word(dev));
+      load_peers(grad_ptrs, ws), grad_mc, load_peers(ctrl_ptrs, ws), rank, ws, first, mine_n, bucket_n, total_n, 1.f / ws,
+      norm_sq_local, epoch, kb::error_word(dev));
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 

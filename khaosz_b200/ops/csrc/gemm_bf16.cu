@@ -23,6 +23,8 @@
 // runs the normal epilogue.  Nobody waits for anybody.  The same mechanism turns skinny
 // problems (decode: M <= 256, a handful of tiles) into split-K over all SMs.
 // All waits are bounded (see common.cuh).
+#include <mutex>
+
 #include "common.cuh"
 #include "kb_api.h"
 
@@ -382,35 +384,52 @@ constexpr int MIN_SLICE_KB = 24;
 constexpr int MIN_SLICE_KB_SKINNY = 8;
 constexpr int MAX_SPLIT = 16;
 
-// Per-device workspace of the tail slices (at most one slice per SM) and the tile counters.
-// Launches that split are expected on one stream per device at a time (they share it).
+// Workspace of the tail slices (at most one slice per SM) and the tile counters: one per (device,
+// stream), because launches on different streams of one device may overlap (a serving thread beside a
+// training loop) and a slice must find its own partials.  A device hands out at most MAX_STREAMS of
+// them (19 MB each); a launch on a further stream simply runs without splitting.
 struct SplitSpace {
   float* ws = nullptr;
   unsigned int* counters = nullptr;
-  bool failed = false;
+  cudaStream_t stream = nullptr;
+  bool used = false;
 };
-static SplitSpace* split_space(int dev, int sms) {
-  static SplitSpace spaces[64];
-  SplitSpace& sp = spaces[dev];
-  if (sp.ws == nullptr && !sp.failed) {
-    static const bool enabled = []() {
-      const char* e = getenv("KHAOSZ_B200_GEMM_SPLIT");
-      return !(e && e[0] == '0');
-    }();
-    void* w = nullptr;
-    void* c = nullptr;
-    if (!enabled || cudaMalloc(&w, (size_t)sms * BM * 256 * sizeof(float)) != cudaSuccess ||
-        cudaMalloc(&c, (size_t)sms * sizeof(unsigned int)) != cudaSuccess ||
-        cudaMemset(c, 0, (size_t)sms * sizeof(unsigned int)) != cudaSuccess) {
-      cudaGetLastError();  // e.g. allocation refused during stream capture: run without splitting
-      if (w) cudaFree(w);
-      sp.failed = !enabled;
-      return nullptr;
-    }
-    sp.ws = static_cast<float*>(w);
-    sp.counters = static_cast<unsigned int*>(c);
+constexpr int MAX_SPLIT_STREAMS = 8;
+static SplitSpace* split_space(int dev, int sms, cudaStream_t stream) {
+  static SplitSpace spaces[64][MAX_SPLIT_STREAMS];
+  static std::mutex mu;
+  static const bool enabled = []() {
+    const char* e = getenv("KHAOSZ_B200_GEMM_SPLIT");
+    return !(e && e[0] == '0');
+  }();
+  if (!enabled || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  SplitSpace* slot = nullptr;
+  for (int i = 0; i < MAX_SPLIT_STREAMS; ++i) {
+    SplitSpace& sp = spaces[dev][i];
+    if (sp.used && sp.stream == stream) return sp.ws ? &sp : nullptr;
+    if (!sp.used && slot == nullptr) slot = &sp;
   }
-  return sp.ws ? &sp : nullptr;
+  if (slot == nullptr) return spaces[dev][0].ws ? &spaces[dev][0] : nullptr;   // table full: share the first
+  void* w = nullptr;
+  void* c = nullptr;
+  if (cudaMalloc(&w, (size_t)sms * BM * 256 * sizeof(float)) != cudaSuccess ||
+      cudaMalloc(&c, (size_t)sms * sizeof(unsigned int)) != cudaSuccess ||
+      cudaMemset(c, 0, (size_t)sms * sizeof(unsigned int)) != cudaSuccess) {
+    // allocation refused, e.g. while this stream records a CUDA graph: the graph's launches share the
+    // workspace that the warm-up launches of this device allocated (they run in stream order with them)
+    cudaGetLastError();
+    if (w) cudaFree(w);
+    if (c) cudaFree(c);
+    for (int i = 0; i < MAX_SPLIT_STREAMS; ++i)
+      if (spaces[dev][i].used && spaces[dev][i].ws) return &spaces[dev][i];
+    return nullptr;
+  }
+  slot->ws = static_cast<float*>(w);
+  slot->counters = static_cast<unsigned int*>(c);
+  slot->stream = stream;
+  slot->used = true;
+  return slot;
 }
 
 template <int BN>
@@ -453,7 +472,7 @@ static int launch(const void* A, const void* B, void* C, const Params& p_in, lon
     if (split > 1) {
       int dev = 0;
       cudaGetDevice(&dev);
-      if (SplitSpace* sp = split_space(dev, grid_cap)) {
+      if (SplitSpace* sp = split_space(dev, grid_cap, stream)) {
         p.full_tiles = total - rem;
         p.split = split;
         p.ws = sp->ws;
@@ -493,9 +512,9 @@ static double tile_cost(int M, int N, int K, int bn, int sms) {
 }  // namespace gemm
 }  // namespace kb
 
-// The split workspace of this device for other GEMM kernels of the library (same stream discipline).
-extern "C" int kb_gemm_split_space(int dev, int sms, float** ws, unsigned int** counters) {
-  kb::gemm::SplitSpace* sp = kb::gemm::split_space(dev, sms);
+// The split workspace of this (device, stream) for the other GEMM kernels of the library.
+extern "C" int kb_gemm_split_space(int dev, int sms, void* stream, float** ws, unsigned int** counters) {
+  kb::gemm::SplitSpace* sp = kb::gemm::split_space(dev, sms, static_cast<cudaStream_t>(stream));
   if (!sp) return KB_STATUS_CUDA_ERROR;
   *ws = sp->ws;
   *counters = sp->counters;

@@ -517,7 +517,7 @@ static double tile_cost(int M, int N, int K, int bn, bool swiglu, int pairs) {
   return (tiles / pairs + tail) * per_tile;
 }
 
-extern "C" int kb_gemm_split_space(int dev, int sms, float** ws, unsigned int** counters);
+extern "C" int kb_gemm_split_space(int dev, int sms, void* stream, float** ws, unsigned int** counters);
 
 template <int BN>
 static int launch(const void* A, const void* B, void* C, void* C2, void* H, Params p, long lda, long ldb, long ldc,
@@ -558,7 +558,7 @@ static int launch(const void* A, const void* B, void* C, void* C2, void* H, Para
       float* ws = nullptr;
       unsigned int* counters = nullptr;
       // the single-CTA kernel's workspace: `sms` slabs of 128 x 256 floats, `sms` counters
-      if (kb_gemm_split_space(dev, sms, &ws, &counters) == KB_STATUS_OK) {
+      if (kb_gemm_split_space(dev, sms, stream, &ws, &counters) == KB_STATUS_OK) {
         p.full_tiles = total - rem;
         p.split = split;
         p.ws = ws;

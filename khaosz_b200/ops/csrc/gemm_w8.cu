@@ -13,7 +13,7 @@
 #include "common.cuh"
 #include "kb_api.h"
 
-extern "C" int kb_gemm_split_space(int dev, int sms, float** ws, unsigned int** counters);
+extern "C" int kb_gemm_split_space(int dev, int sms, void* stream, float** ws, unsigned int** counters);
 
 namespace kb {
 namespace w8 {
@@ -350,7 +350,7 @@ int kb_gemm_w8(const void* X, const void* Wq, const float* scale, void* C, int M
     if (split > 16) split = 16;
     if (split > num_k / 8) split = num_k / 8;
     while (split > 1 && (split - 1) * ((num_k + split - 1) / split) >= num_k) --split;  // no empty slice
-    if (split > 1 && kb_gemm_split_space(dev, sms, &p.ws, &p.counters) == KB_STATUS_OK) p.split = split;
+    if (split > 1 && kb_gemm_split_space(dev, sms, stream, &p.ws, &p.counters) == KB_STATUS_OK) p.split = split;
   }
   const int units = total * p.split;
   gemm_w8_kernel<<<units < sms ? units : sms, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(tx, tw, tc, p);

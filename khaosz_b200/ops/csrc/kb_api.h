@@ -178,8 +178,8 @@ int kb_reduce_adamw(const void* const* grad_ptrs, const void* const* param_ptrs,
                     float beta2, float eps, float weight_decay, float max_norm, float* scratch, unsigned int epoch,
                     void* stream);
 int kb_reduce_bucket(const void* const* grad_ptrs, const void* const* ctrl_ptrs, const void* grad_mc, int rank, int ws,
-                     long long off, long long n, float* norm_sq_local, unsigned int epoch, int grid, int threads,
-                     void* stream);
+                     long long bucket_n, long long total_n, int b_lo, int b_hi, float* norm_sq_local,
+                     unsigned int epoch, int grid, int threads, void* stream);
 int kb_adamw_buckets(const void* const* grad_ptrs, const void* const* param_ptrs, const void* const* ctrl_ptrs,
                      const void* const* norm_ptrs, void* param_mc, int rank, int ws, long long bucket_n,
                      long long total_n, float* m, float* v, const float* lr_step, float beta1, float beta2, float eps,

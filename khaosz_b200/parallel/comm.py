@@ -148,7 +148,7 @@ class GradReducer:
 
     fuses_optimizer = True
     gathers_params = True
-    BUCKET_GRID = 32        # CTAs of a bucket reduction (the same on every rank: per-CTA barriers pair up)
+    BUCKET_GRID = 48        # CTAs of a bucket reduction (the same on every rank: per-CTA barriers pair up)
     BUCKET_THREADS = 256    # light enough to be co-resident with a persistent GEMM CTA
 
     def __init__(self, flat: FlatParameters, mode: str, group=None, bucket_cap_mb: Optional[float] = None,
@@ -237,6 +237,13 @@ class GradReducer:
         from ..models.components.layers import Linear
         from ..ops import functional
 
+        if any(hasattr(m, "n_routed_experts") for m in model.modules()):
+            # data-dependent expert routing: which parameters receive a gradient differs from rank to
+            # rank, and with it the moment a bucket is complete; the ranks' launches must pair up, so
+            # such models reduce everything in one launch after the backward pass
+            self.overlap = False
+            return
+
         linear_w = {id(m.weight) for m in model.modules() if isinstance(m, Linear)}
         for module in model.modules():
             direct = [p for p in module.parameters(recurse=False) if p.requires_grad and id(p) in self._param_buckets]
@@ -292,9 +299,9 @@ class GradReducer:
             self._remaining[b] -= 1
         self._hand_over(side=True)
 
-    def _launch_bucket(self, b: int, side: bool) -> None:
-        off, n = self.bucket_range(b)
-        piece = n // self.ws
+    def _launch_range(self, b_lo: int, b_hi: int, side: bool) -> None:
+        """Reduce-scatter of the buckets ``b_lo .. b_hi``: one finished bucket on the side stream behind
+        an event (small grid of light CTAs), or whatever is left in one launch with the full grid."""
         mc_g = ctypes.c_void_p(self.grads.multicast_ptr) if self.use_multicast else None
         main = torch.cuda.current_stream()
         if side and self._comm_stream is not None:
@@ -303,21 +310,27 @@ class GradReducer:
             self._comm_stream.wait_event(ev)
             st = ctypes.c_void_p(self._comm_stream.cuda_stream)
             self._used_side_stream = True
-            self.buckets_overlapped += 1
+            self.buckets_overlapped += b_hi - b_lo + 1
+            grid, threads = self.BUCKET_GRID, self.BUCKET_THREADS
         else:
             if self._used_side_stream:      # keep the buckets in one order on the device as well
                 ev = torch.cuda.Event()
                 ev.record(self._comm_stream)
                 main.wait_event(ev)
             st = stream()
-        grid, threads = (self.BUCKET_GRID, self.BUCKET_THREADS) if self.n_buckets > 1 else (lib().kb_comm_slots() - 8, 512)
-        check(lib().kb_reduce_bucket(self.grads.ptrs, self.ctrl.flags.ptrs, mc_g, self.rank, self.ws,
-                                     off + self.rank * piece, piece, ptr(self._scratch), self.ctrl.next_epoch(1), grid,
+            grid, threads = lib().kb_comm_slots() - 8, 512
+        check(lib().kb_reduce_bucket(self.grads.ptrs, self.ctrl.flags.ptrs, mc_g, self.rank, self.ws, self.bucket_n,
+                                     self.flat.numel, b_lo, b_hi, ptr(self._scratch), self.ctrl.next_epoch(1), grid,
                                      threads, st), "reduce_bucket")
 
     def _hand_over(self, side: bool, flush: bool = False) -> None:
-        while self._next_bucket >= 0 and (flush or self._remaining[self._next_bucket] <= 0):
-            self._launch_bucket(self._next_bucket, side)
+        if flush:
+            if self._next_bucket >= 0:
+                self._launch_range(0, self._next_bucket, side=False)
+                self._next_bucket = -1
+            return
+        while self._next_bucket >= 0 and self._remaining[self._next_bucket] <= 0:
+            self._launch_range(self._next_bucket, self._next_bucket, side)
             self._next_bucket -= 1
 
     def reduce(self) -> None:
