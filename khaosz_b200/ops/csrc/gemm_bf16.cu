@@ -411,6 +411,16 @@ static SplitSpace* split_space(int dev, int sms, cudaStream_t stream) {
     if (!sp.used && slot == nullptr) slot = &sp;
   }
   if (slot == nullptr) return spaces[dev][0].ws ? &spaces[dev][0] : nullptr;   // table full: share the first
+  // A stream that is recording a CUDA graph must not allocate (the attempt would invalidate the
+  // recording): its launches share the workspace that the warm-up launches of this device allocated,
+  // with which the replayed graph runs in stream order.
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess) cudaGetLastError();
+  if (capturing != cudaStreamCaptureStatusNone) {
+    for (int i = 0; i < MAX_SPLIT_STREAMS; ++i)
+      if (spaces[dev][i].used && spaces[dev][i].ws) return &spaces[dev][i];
+    return nullptr;
+  }
   void* w = nullptr;
   void* c = nullptr;
   if (cudaMalloc(&w, (size_t)sms * BM * 256 * sizeof(float)) != cudaSuccess ||
