@@ -97,7 +97,7 @@ def bench_decode(model, cfg, batch: int, prompt: int, gen: int, trials: int, pag
 
 
 def bench_serve(model, cfg, requests: int, rate: float, min_prompt: int, max_prompt: int, gen: int, max_batch: int,
-                page_size: int, seed: int, engine_cls=None, stop=None, budget_s: float = 0.0):
+                page_size: int, seed: int, engine_cls=None, stop=None, budget_s: float = 0.0, warmup_requests: int = 4):
     """Replays a Poisson arrival trace through an engine with the reference's public interface
     (``engine.scheduler.add_task(prompt, max_tokens, temperature, top_p, top_k, stream_callback)``).
     ``engine_cls`` / ``stop`` select the engine under test: this package's by default, or the unmodified
@@ -114,10 +114,10 @@ def bench_serve(model, cfg, requests: int, rate: float, min_prompt: int, max_pro
                         max_prompt_len=max_prompt, page_size=page_size)
     done = threading.Semaphore(0)
     ttft, tokens_out = [], [0]
-    t_start = time.time()
 
-    def submit():
-        prompt = [rng.randrange(cfg.vocab_size) for _ in range(rng.randint(min_prompt, max_prompt))]
+    def submit(length=None, tokens=None):
+        n = rng.randint(min_prompt, max_prompt) if length is None else length
+        prompt = [rng.randrange(cfg.vocab_size) for _ in range(n)]
         state = {"t0": time.time(), "first": None}
 
         def cb(tok):
@@ -129,7 +129,19 @@ def bench_serve(model, cfg, requests: int, rate: float, min_prompt: int, max_pro
                 state["first"] = time.time() - state["t0"]
                 ttft.append(state["first"])
 
-        engine.scheduler.add_task(prompt, max_tokens=gen, temperature=1.0, top_p=1.0, top_k=1, stream_callback=cb)
+        engine.scheduler.add_task(prompt, max_tokens=gen if tokens is None else tokens, temperature=1.0, top_p=1.0,
+                                  top_k=1, stream_callback=cb)
+
+    # a server is measured warm: a few short requests first (communicator set-up, first-use allocations,
+    # the first recorded decode step), then the counters start again
+    for i in range(max(0, warmup_requests)):
+        submit(length=min_prompt + 16 * i, tokens=8)
+    for _ in range(max(0, warmup_requests)):
+        if not done.acquire(timeout=budget_s if budget_s > 0 else None):
+            break
+    ttft.clear()
+    tokens_out[0] = 0
+    t_start = time.time()
 
     for _ in range(requests):
         submit()
@@ -181,7 +193,7 @@ def reference_serve(a, dtype):
     model = RefLM(cfg).to(device=a.device, dtype=dtype).eval()
     row = bench_serve(model, cfg, a.requests, a.rate, a.min_prompt, a.max_prompt, a.gen_length, a.max_batch_size,
                       a.page_size if a.page_size != 128 else 16, a.seed, engine_cls=RefEngine, stop=REF_STOP,
-                      budget_s=a.budget_s)
+                      budget_s=a.budget_s, warmup_requests=a.warmup_requests)
     row["impl"] = "reference"
     return row
 
@@ -203,6 +215,8 @@ def parse_args(argv=None):
     p.add_argument("--seed", type=int, default=3407)
     p.add_argument("--device", default="cuda")
     p.add_argument("--int8", action="store_true", help="int8 weight-only linears (per-channel scales)")
+    p.add_argument("--warmup_requests", type=int, default=4,
+                   help="serve mode: short requests served before the measured trace starts")
     p.add_argument("--budget_s", type=float, default=0.0,
                    help="serve mode: stop measuring after this many seconds and report what was produced so far")
     p.add_argument("--impl", choices=["khaosz_b200", "reference"], default="khaosz_b200",
@@ -232,7 +246,7 @@ def _tensor_parallel(a, dtype):
                      page_size=page)
     else:
         row = bench_serve(model, cfg, a.requests, a.rate, a.min_prompt, a.max_prompt, a.gen_length, a.max_batch_size,
-                          page, a.seed)
+                          page, a.seed, budget_s=a.budget_s, warmup_requests=a.warmup_requests)
         row.update(weights="int8" if a.int8 else "bf16", tensor_parallel=dist.get_world_size())
         print(json.dumps(row))
     dist.barrier()
@@ -268,7 +282,8 @@ def main(argv=None):
                                 a.device, dtype))
     if a.mode == "serve":
         out.append(bench_serve(model, cfg, a.requests, a.rate, a.min_prompt, a.max_prompt, a.gen_length,
-                               a.max_batch_size, a.page_size if a.page_size != 128 else 16, a.seed, budget_s=a.budget_s))
+                               a.max_batch_size, a.page_size if a.page_size != 128 else 16, a.seed, budget_s=a.budget_s,
+                               warmup_requests=a.warmup_requests))
     for row in out:
         row["weights"] = "int8" if a.int8 else "bf16"
         print(json.dumps(row))
