@@ -17,7 +17,8 @@ FULL_SHARD wrapper against this package's sharded executor), ``--strategy dpo`` 
 plus a frozen copy, 8 chosen/rejected pairs per GPU sharing a 512-token prompt with 512-token
 responses, beta 0.1, one micro-batch per step), ``--serve 1`` (own arm, after the training
 numbers: decode tokens/s and median time to first token of the continuous-batching server on the
-same GPUs, tensor parallel when N > 1, reported under the ``serving`` key).
+same GPUs, tensor parallel when N > 1, reported under the ``serving`` key; on by default for the
+8-GPU headline run, where it gives the TP=8 half of the metric).
 
 Two numbers come out of the own arm: ``value`` — K steps timed on the device with CUDA
 events, inputs already resident; and ``e2e`` — the same K steps through the public
@@ -371,44 +372,52 @@ def run_own(args):
                     "final_loss": final_loss})
     if e2e is not None:
         payload["e2e"] = e2e
-    if args.serve:
-        payload["serving"] = run_serving(args, rank, local_rank, ws)
-    emit(payload)
     if dist.is_initialized():
         dist.destroy_process_group()
+    serve = args.serve if args.serve >= 0 else int(ws == 8 and mode == "ddp" and args.strategy == "seq")
+    if serve and rank == 0:
+        # the other ranks are done and leave; this one frees its memory and runs the serving job as a child
+        torch.cuda.empty_cache()
+        payload["serving"] = run_serving_child(ws)
+    emit(payload)
 
 
-def run_serving(args, rank: int, local_rank: int, ws: int) -> dict:
+def run_serving_child(ws: int) -> dict:
     """Decode tokens/s and median time to first token of the continuous-batching server on the same
-    GPUs (tensor parallel over all ranks when N > 1): 256 Poisson arrivals, prompts uniform in
-    [128, 2048] random ids, 256 greedy tokens each, 16-token KV pages, bf16.  Rank 0 owns the
-    scheduler; the other ranks serve their weight slices."""
-    from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
-    from khaosz_b200.cli.benchmark import PRESETS, _IdTokenizer, bench_serve
+    GPUs (tensor parallel over all of them when N > 1): 256 Poisson arrivals at 64 requests/s, prompts
+    uniform in [128, 2048] random ids, 256 greedy tokens each, 16-token KV pages, bf16.
 
+    Runs as a child job (``khaosz_b200.cli.benchmark serve`` under its own launcher) after the training
+    ranks have released the GPUs, with a hard time limit: whatever happens to it, the training numbers
+    above are already measured and still get printed."""
+    serve = ["-m", "khaosz_b200.cli.benchmark", "serve", "--preset", "1b", "--requests", "256", "--rate", "64",
+             "--gen_length", "256", "--max_batch_size", "256", "--page_size", "16", "--budget_s", "150"]
+    if ws > 1:
+        port = str(int(os.environ.get("MASTER_PORT", "29500")) + 17)
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ws}", "--master-addr",
+               "127.0.0.1", "--master-port", port] + serve
+    else:
+        cmd = [sys.executable] + serve
+    drop = ("RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", "GROUP_WORLD_SIZE", "ROLE_RANK",
+            "ROLE_NAME", "ROLE_WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT")
+    env = {k: v for k, v in os.environ.items() if k not in drop and not k.startswith("TORCHELASTIC")}
     try:
-        device = f"cuda:{local_rank}"
-        torch.manual_seed(SEED)   # identical random weights on every rank
-        cfg = AutoRegressiveLMConfig(**PRESETS["1b"])
-        model = AutoRegressiveLM(cfg).to(device=device, dtype=torch.bfloat16).eval()
-        knobs = dict(requests=256, rate=64.0, min_prompt=128, max_prompt=2048, gen=256, max_batch=256, page_size=16, seed=SEED)
-        if ws > 1:
-            from khaosz_b200.inference.tp import TPInferenceLM, serve_worker
-
-            if not dist.is_initialized():
-                dist.init_process_group("nccl", device_id=torch.device(device))
-            model = TPInferenceLM(model).eval()
-            if rank != 0:
-                serve_worker(model, _IdTokenizer(), max_batch_size=knobs["max_batch"],
-                             max_seq_len=knobs["max_prompt"] + knobs["gen"] + 1, page_size=knobs["page_size"])
-                return {}
-        row = bench_serve(model, cfg, knobs["requests"], knobs["rate"], knobs["min_prompt"], knobs["max_prompt"],
-                          knobs["gen"], knobs["max_batch"], knobs["page_size"], knobs["seed"])
-        return {"decode_tokens_per_s": row["decode_tokens_per_s_busy"], "output_tokens_per_s_wall": row["output_tokens_per_s_wall"],
-                "ttft_p50_s": row["ttft_p50_s"], "ttft_p99_s": row["ttft_p99_s"], "tensor_parallel": ws, "weights": "bf16",
-                "requests": knobs["requests"], "arrival_rate_per_s": knobs["rate"], "generated_per_request": knobs["gen"],
-                "page_size": knobs["page_size"], "clock": "host wall clock around the trace (requests arrive over seconds)"}
-    except Exception as exc:   # the training numbers above stand on their own
+        res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=420)
+        rows = [line for line in res.stdout.splitlines() if line.startswith("{") and '"benchmark"' in line]
+        if not rows:
+            return {"unavailable": ("no result line; " + (res.stderr.strip().splitlines() or ["rc %d" % res.returncode])[-1])[:300]}
+        row = json.loads(rows[-1])
+        return {"decode_tokens_per_s": row.get("decode_tokens_per_s_busy"),
+                "output_tokens_per_s_wall": row.get("output_tokens_per_s_wall"), "ttft_p50_s": row.get("ttft_p50_s"),
+                "ttft_p99_s": row.get("ttft_p99_s"), "tensor_parallel": ws, "weights": "bf16",
+                "requests": row.get("requests"), "arrival_rate_per_s": row.get("arrival_rate_per_s"),
+                "generated_per_request": row.get("generated_per_request"), "page_size": 16,
+                "cut_at_budget": row.get("cut_at_budget"),
+                "clock": "host wall clock around the trace (requests arrive over seconds); decode_tokens_per_s counts the "
+                         "time the decode loop was busy"}
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "the serving job did not finish within its time limit"}
+    except Exception as exc:   # the training numbers stand on their own
         return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
 
@@ -524,8 +533,9 @@ def main():
                          "(tp: every rank reads the same batches, total work is fixed -> strong scaling)")
     ap.add_argument("--strategy", default="seq", choices=["seq", "dpo"],
                     help="seq: next-token pre-training (the headline); dpo: policy + frozen copy on chosen/rejected pairs")
-    ap.add_argument("--serve", type=int, default=0,
-                    help="own arm: 1 appends decode tokens/s and median time to first token of the server on the same GPUs")
+    ap.add_argument("--serve", type=int, default=-1,
+                    help="own arm: 1 appends decode tokens/s and median time to first token of the server on the same "
+                         "GPUs (a child job after the training numbers); default: only for the 8-GPU headline run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     ws = env_rank()[2]
