@@ -53,7 +53,7 @@ SEED = 3407
 class Workload:
     """Shape of one optimizer step for the chosen strategy (per GPU)."""
 
-    def __init__(self, strategy: str):
+    def __init__(self, strategy: str, accum: int = 0):
         self.strategy = strategy
         if strategy == "dpo":
             self.seq, self.bpd, self.accum = DPO_PROMPT + DPO_RESPONSE, DPO_PAIRS, 1
@@ -62,6 +62,8 @@ class Workload:
             self.h2d_per_micro = self.bpd * (2 * self.seq * 8 + 2 * self.seq)   # two id tensors (int64), two masks (bool)
         else:
             self.seq, self.bpd, self.accum = SEQ, BPD, ACCUM
+            if accum > 0:       # off-headline runs (e.g. 1: the gradient collective's share of a step is 8x larger)
+                self.accum = accum
             self.tokens_per_sample = self.seq
             self.extra = {"label_smoothing": SMOOTH}
             self.h2d_per_micro = 2 * self.bpd * self.seq * 8                 # input and target ids (int64)
@@ -270,7 +272,7 @@ def run_own(args):
     from khaosz_b200.trainer import FusedAdamW, SchedulerFactory, StrategyFactory, Trainer
 
     cfg = AutoRegressiveLMConfig(**MODEL)
-    wl = Workload(args.strategy)
+    wl = Workload(args.strategy, args.accum)
     mode = args.parallel if ws > 1 else "none"
     replicas = 1 if mode == "tp" else ws  # data-parallel replicas
     args.cuda_graph = bool(args.cuda_graph) if args.cuda_graph >= 0 else mode == "tp"
@@ -293,7 +295,8 @@ def run_own(args):
 
     # ---- device-timed steps (inputs resident on the device; every step sees data it has not seen) ----
     model = model_fn().to(device)
-    executor = ExecutorFactory.create(mode, grad_accum_steps=accum, cuda_graph=args.cuda_graph)
+    ex_extra = {"overlap_grad_reduce": bool(args.overlap)} if args.overlap >= 0 and mode in ("ddp", "fsdp") else {}
+    executor = ExecutorFactory.create(mode, grad_accum_steps=accum, cuda_graph=args.cuda_graph, **ex_extra)
     opt = optimizer_fn(model)
     model, opt, _, sched = executor.prepare(model, opt, None, scheduler_fn(opt))
     strategy = StrategyFactory.create(wl.strategy, model, device, executor=executor, model_fn=model_fn, **wl.extra)
@@ -352,7 +355,7 @@ def run_own(args):
                          max_grad_norm=CLIP, ckpt_dir=tmp, ckpt_interval=10 ** 9, log_dir=os.path.join(tmp, "logs"),
                          log_interval=accum, random_seed=SEED, num_workers=0, pin_memory=True, nprocs=ws,
                          backend="nccl", parallel_mode=mode, device_type="cuda",
-                         executor_kwargs={"cuda_graph": args.cuda_graph}, extra_kwargs=dict(wl.extra))
+                         executor_kwargs={"cuda_graph": args.cuda_graph, **ex_extra}, extra_kwargs=dict(wl.extra))
 
         trainer = Trainer(tc, callbacks=[timer])
         strip_untimed_callbacks(trainer)
@@ -464,7 +467,7 @@ def run_reference(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     cfg = AutoRegressiveLMConfig(**MODEL)
-    wl = Workload(args.strategy)
+    wl = Workload(args.strategy, args.accum)
     steps_total = args.warmup + args.steps
     if ws > 1 and args.parallel not in ("ddp", "fsdp"):
         if rank == 0:
@@ -533,6 +536,10 @@ def main():
                          "(tp: every rank reads the same batches, total work is fixed -> strong scaling)")
     ap.add_argument("--strategy", default="seq", choices=["seq", "dpo"],
                     help="seq: next-token pre-training (the headline); dpo: policy + frozen copy on chosen/rejected pairs")
+    ap.add_argument("--accum", type=int, default=0,
+                    help="micro-batches per optimizer step of the seq strategy (default: the headline's 8)")
+    ap.add_argument("--overlap", type=int, default=-1,
+                    help="own arm, ddp / fsdp: 1 hands gradient buckets to the reduce kernels during the backward pass")
     ap.add_argument("--serve", type=int, default=-1,
                     help="own arm: 1 appends decode tokens/s and median time to first token of the server on the same "
                          "GPUs (a child job after the training numbers); default: only for the 8-GPU headline run")

@@ -346,6 +346,27 @@ push_kernel(Peers bufs, void* mc, Peers ctrl, int rank, int ws, long long off, l
   cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch + 1, err, KB_WAIT_BUDGET_NS);
 }
 
+// First half of a broadcast from `root`: piece r of the root's buffer goes to rank r (plain peer stores,
+// the pieces spread over the root's CTAs); the all-gather that follows distributes the pieces.  Two
+// passes of n / ws each over every link instead of ws - 1 full copies out of one GPU.
+__global__ void __launch_bounds__(THREADS)
+scatter_kernel(Peers bufs, Peers ctrl, int root, int rank, int ws, long long per, uint32_t epoch, int* err) {
+  if (!cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch, err, KB_WAIT_BUDGET_NS)) return;
+  if (rank == root) {
+    const __nv_bfloat16* mine = static_cast<const __nv_bfloat16*>(bufs.p[rank]);
+    const long long nchunks = per >> 3;
+    const long long total = nchunks * (ws - 1);
+    for (long long c = blockIdx.x * (long long)THREADS + threadIdx.x; c < total; c += (long long)gridDim.x * THREADS) {
+      int dst = (int)(c / nchunks);
+      const long long within = c - dst * nchunks;
+      if (dst >= root) ++dst;   // every rank but the root itself
+      const long long at = dst * per + within * 8;
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bufs.p[dst]) + at) = *reinterpret_cast<const uint4*>(mine + at);
+    }
+  }
+  cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch + 1, err, KB_WAIT_BUDGET_NS);
+}
+
 __global__ void barrier_kernel(Peers ctrl, int rank, int ws, int slot, uint32_t epoch, int* err,
                                unsigned long long budget_ns) {
   cta_peer_barrier(ctrl, rank, ws, slot, epoch, err, budget_ns);
@@ -503,15 +524,24 @@ int kb_allgather_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs,
 }
 
 // Broadcast: the first n elements (a multiple of 8) of rank `root`'s symmetric buffer go to every rank.
+// With n a multiple of 8 * ws: scatter of the pieces, then all-gather (uses
+// epochs epoch .. epoch + 3); otherwise the root stores everything everywhere.
 int kb_broadcast_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, void* mc, int root, int rank, int ws,
                       long long n, unsigned int epoch, void* stream) {
   using namespace kb::comm;
   if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || root < 0 || root >= ws || n <= 0 || (n & 7)) return KB_STATUS_BAD_ARG;
   int dev = 0;
   cudaGetDevice(&dev);
-  push_kernel<<<grid_size(), THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      load_peers(buf_ptrs, ws), mc, load_peers(ctrl_ptrs, ws), rank, ws, 0, n, rank == root ? 1 : 0, epoch,
-      kb::error_word(dev));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const Peers bufs = load_peers(buf_ptrs, ws), ctrl = load_peers(ctrl_ptrs, ws);
+  if (ws >= 2 && n % (8 * ws) == 0) {
+    const long long per = n / ws;
+    scatter_kernel<<<grid_size(), THREADS, 0, st>>>(bufs, ctrl, root, rank, ws, per, epoch, kb::error_word(dev));
+    push_kernel<<<grid_size(), THREADS, 0, st>>>(bufs, mc, ctrl, rank, ws, per * rank, per, 1, epoch + 2, kb::error_word(dev));
+  } else {
+    push_kernel<<<grid_size(), THREADS, 0, st>>>(bufs, mc, ctrl, rank, ws, 0, n, rank == root ? 1 : 0, epoch,
+                                                 kb::error_word(dev));
+  }
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 

@@ -38,6 +38,9 @@ static __device__ bool cta_peer_barrier(const Peers& ctrl, int rank, int ws, int
     uint32_t it = 0;
     // epochs only grow; "at least this epoch" tolerates a peer that already moved on
     while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      // a peer that is far behind (ranks are not in lockstep) is waited for politely: the polls of a long
+      // wait would otherwise compete with the kernels that share the SM and the links
+      if (it > 64u) __nanosleep(it > 4096u ? 512 : 64);
       if ((++it & 255u) == 0u && globaltimer_ns() - t0 > budget_ns) {
         s_ok = 0;
         if (err) atomicCAS(err, 0, KB_ERR_TIMEOUT_PEER);

@@ -127,7 +127,7 @@ def broadcast_(buf: SymmetricBuffer, ctrl: PeerControl, root: int = 0, numel: Op
     n = buf.tensor.numel() if numel is None else numel
     assert buf.tensor.dtype == torch.bfloat16 and n % 8 == 0
     check(lib().kb_broadcast_bf16(buf.ptrs, ctrl.flags.ptrs, _mc(buf, use_multicast), root, buf.rank, buf.world_size, n,
-                                  ctrl.next_epoch(2), stream()), "broadcast_bf16")
+                                  ctrl.next_epoch(4), stream()), "broadcast_bf16")
     return buf.tensor
 
 
@@ -136,7 +136,8 @@ class GradReducer:
 
     The flat gradient buffer is cut into buckets of about ``bucket_cap_mb`` (the reference's
     ``DDPExecutor(bucket_cap_mb=25)``, ``astrai/parallel/executor.py:146-198``); rank ``r`` owns
-    sub-slice ``r`` of every bucket.  On the micro-batch that ends an accumulation window the buckets
+    sub-slice ``r`` of every bucket.  With ``overlap`` (executor keyword ``overlap_grad_reduce=True`` or
+    ``KHAOSZ_B200_DDP_OVERLAP=1``) the buckets of the micro-batch that ends an accumulation window
     are reduced *while the backward pass is still running*: as soon as every parameter of a bucket has
     received its last gradient contribution (and all later buckets have been handed over), the
     bucket's reduce-scatter kernel is launched on a side stream behind an event, with a small grid
@@ -167,7 +168,10 @@ class GradReducer:
         self.slice_n = flat.numel // ws
         unit = 8 * ws
         if overlap is None:
-            overlap = os.environ.get("KHAOSZ_B200_DDP_OVERLAP", "1") != "0"
+            # off unless asked for: with 8 micro-batches per step the reduction is ~1 % of a step and the
+            # bucket kernels that share the SMs with the backward pass cost more than they hide (measured
+            # on 8 GPUs); it pays when there is little accumulation
+            overlap = os.environ.get("KHAOSZ_B200_DDP_OVERLAP", "0") == "1"
         bucket_n = flat.numel
         if overlap and bucket_cap_mb and bucket_cap_mb > 0 and _lib.has("kb_reduce_bucket"):
             bucket_n = max(unit, int(bucket_cap_mb * 2 ** 20) // flat.data.element_size() // unit * unit)

@@ -378,16 +378,19 @@ class DDPExecutor(BaseExecutor):
 
     Works on CPU/gloo as well as CUDA/NCCL (the reference's wrapper cannot wrap a CPU model,
     ``astrai/parallel/executor.py:181-193``).  The torch-DDP keyword arguments of the
-    reference are accepted for compatibility; ``bucket_cap_mb`` sizes the gradient buckets that the
-    NVLink reduce kernels take over while the backward pass of the window's last micro-batch is
-    still running (``khaosz_b200.parallel.comm.GradReducer``).
+    reference are accepted for compatibility.  With ``overlap_grad_reduce=True`` the gradients leave
+    in ``bucket_cap_mb`` buckets while the backward pass of the window's last micro-batch is still
+    running (``khaosz_b200.parallel.comm.GradReducer``); by default they are reduced in one launch
+    after it, which is faster when a step accumulates several micro-batches.
     """
 
     def __init__(self, grad_accum_steps: int = 1, find_unused_parameters: bool = False, bucket_cap_mb: int = 25,
                  gradient_as_bucket_view: bool = True, broadcast_buffers: bool = False, static_graph: bool = False,
-                 init_sync: bool = True, comm: str = "auto", fp8: bool = False, cuda_graph: bool = False, **_ignored):
+                 init_sync: bool = True, comm: str = "auto", fp8: bool = False, cuda_graph: bool = False,
+                 overlap_grad_reduce: Optional[bool] = None, **_ignored):
         super().__init__(grad_accum_steps, fp8, cuda_graph)
         self.bucket_cap_mb = bucket_cap_mb
+        self.overlap_grad_reduce = overlap_grad_reduce   # None: KHAOSZ_B200_DDP_OVERLAP decides (default off)
         self.init_sync = init_sync
         self.comm = comm  # "auto" | "nccl" | "kernel"
         self._reducer = None
@@ -401,7 +404,8 @@ class DDPExecutor(BaseExecutor):
         if self.flat is not None and self.flat.data.is_cuda and get_world_size() > 1 and self.comm != "nccl":
             from .comm import GradReducer
 
-            self._reducer = GradReducer.create(self.flat, mode="allreduce", bucket_cap_mb=self.bucket_cap_mb)
+            self._reducer = GradReducer.create(self.flat, mode="allreduce", bucket_cap_mb=self.bucket_cap_mb,
+                                               overlap=self.overlap_grad_reduce)
         if self.init_sync:
             if self._reducer is not None and self.flat.numel % 8 == 0:
                 # rank 0's parameters to everybody through the NVLink broadcast kernel (one pass of
@@ -462,10 +466,11 @@ class FSDPExecutor(BaseExecutor):
     """
 
     def __init__(self, grad_accum_steps: int = 1, comm: str = "auto", fp8: bool = False, cuda_graph: bool = False,
-                 bucket_cap_mb: int = 25, **_ignored):
+                 bucket_cap_mb: int = 25, overlap_grad_reduce: Optional[bool] = None, **_ignored):
         super().__init__(grad_accum_steps, fp8, cuda_graph)
         self.comm = comm
         self.bucket_cap_mb = bucket_cap_mb
+        self.overlap_grad_reduce = overlap_grad_reduce
         self.shard: Optional[Tuple[int, int]] = None
         self._reducer = None
 
@@ -479,7 +484,8 @@ class FSDPExecutor(BaseExecutor):
         if self.flat.data.is_cuda and ws > 1 and self.comm != "nccl":
             from .comm import GradReducer
 
-            self._reducer = GradReducer.create(self.flat, mode="reducescatter", bucket_cap_mb=self.bucket_cap_mb)
+            self._reducer = GradReducer.create(self.flat, mode="reducescatter", bucket_cap_mb=self.bucket_cap_mb,
+                                               overlap=self.overlap_grad_reduce)
         return model
 
     def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):

@@ -179,7 +179,8 @@ def _train(mode, world, rank, device, steps=4, accum=2, cuda_graph=False, overla
 
     torch.manual_seed(3407)
     model = AutoRegressiveLM(_cfg()).to(device=device, dtype=torch.bfloat16)
-    extra = {"bucket_cap_mb": 1} if overlap else {}   # ~1 MB buckets: several per step on this small model
+    # ~1 MB buckets handed over during the backward pass: several per step on this small model
+    extra = {"bucket_cap_mb": 1, "overlap_grad_reduce": True} if overlap else {}
     ex = ExecutorFactory.create(mode, grad_accum_steps=accum, cuda_graph=cuda_graph, **extra)
     opt = FusedAdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.01)
     model, opt, _, _ = ex.prepare(model, opt, None, None)
