@@ -168,9 +168,9 @@ class GradReducer:
         self.slice_n = flat.numel // ws
         unit = 8 * ws
         if overlap is None:
-            # off unless asked for: with 8 micro-batches per step the reduction is ~1 % of a step and the
-            # bucket kernels that share the SMs with the backward pass cost more than they hide (measured
-            # on 8 GPUs); it pays when there is little accumulation
+            # off unless asked for: in every configuration measured so far (8 and 1 micro-batches per step,
+            # 2 and 8 GPUs) the bucket kernels that share the SMs with the backward pass cost more than
+            # the few milliseconds of reduction they hide
             overlap = os.environ.get("KHAOSZ_B200_DDP_OVERLAP", "0") == "1"
         bucket_n = flat.numel
         if overlap and bucket_cap_mb and bucket_cap_mb > 0 and _lib.has("kb_reduce_bucket"):

@@ -381,7 +381,7 @@ class DDPExecutor(BaseExecutor):
     reference are accepted for compatibility.  With ``overlap_grad_reduce=True`` the gradients leave
     in ``bucket_cap_mb`` buckets while the backward pass of the window's last micro-batch is still
     running (``khaosz_b200.parallel.comm.GradReducer``); by default they are reduced in one launch
-    after it, which is faster when a step accumulates several micro-batches.
+    after it, which measured faster in every configuration tried (the reduction is a few milliseconds).
     """
 
     def __init__(self, grad_accum_steps: int = 1, find_unused_parameters: bool = False, bucket_cap_mb: int = 25,
