@@ -337,6 +337,9 @@ def run_own(args):
     launches = _lib.launch_count() - l0
     clocks = sampler.stop()
     final_loss = float(loss)
+    peak_alloc_gb = round(torch.cuda.max_memory_allocated(device) / 2 ** 30, 2)
+    free_b, total_b = torch.cuda.mem_get_info(device)
+    device_used_gb = round((total_b - free_b) / 2 ** 30, 2)   # allocator cache + symmetric memory + context
     raise_on_device_error()
     tokens = args.steps * wl.tokens_per_step(replicas)
     value = tokens / (ms / 1e3)
@@ -372,7 +375,7 @@ def run_own(args):
         payload["scaling"] = "strong"
         payload["config"]["global_batch"] = wl.bpd * accum
     payload.update({"value": value, "ms_per_step": ms / args.steps, "clocks": clocks, "gpu_launches": launches,
-                    "final_loss": final_loss})
+                    "final_loss": final_loss, "peak_alloc_gb": peak_alloc_gb, "device_used_gb": device_used_gb})
     if e2e is not None:
         payload["e2e"] = e2e
     if dist.is_initialized():
@@ -531,7 +534,7 @@ def main():
     ap.add_argument("--no-e2e", dest="no_e2e", action="store_true")
     ap.add_argument("--cuda-graph", dest="cuda_graph", type=int, default=-1,
                     help="own arm: forward+backward of a micro-batch as a replayed CUDA graph (default: on for tp)")
-    ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp", "fsdp_full", "tp"],
+    ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp", "fsdp_block", "fsdp_full", "tp"],
                     help="own arm, N > 1: data parallel (default), sharded data parallel, or tensor parallel "
                          "(tp: every rank reads the same batches, total work is fixed -> strong scaling)")
     ap.add_argument("--strategy", default="seq", choices=["seq", "dpo"],

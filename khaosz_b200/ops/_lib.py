@@ -41,6 +41,7 @@ def _declare(lib):
         "kb_sm_count": ([], I),
         "kb_error_probe": ([P, P], I),
         "kb_store_f32x2": ([P, F, F, P], I),
+        "kb_copy_async": ([P, P, LL, P], I),
         "kb_last_tmap_error": ([], I),
         "kb_gemm_bf16": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, P], I),
         "kb_gemm_bf16_bn": ([P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P], I),
@@ -81,6 +82,7 @@ def _declare(lib):
         "kb_reducescatter_bf16": ([P, P, P, I, I, LL, F, P, ctypes.c_uint, P], I),
         "kb_allgather_bf16": ([P, P, P, I, I, LL, ctypes.c_uint, P], I),
         "kb_broadcast_bf16": ([P, P, P, I, I, I, LL, ctypes.c_uint, P], I),
+        "kb_unit_reduce_bf16": ([P, P, P, I, I, LL, F, P, I, ctypes.c_uint, I, I, P], I),
         "kb_peer_barrier": ([P, I, I, I, ctypes.c_uint, I, P], I),
         "kb_rmsnorm_bwd_static": ([P, P, P, P, P, P, P, I, I, P], I),
     }

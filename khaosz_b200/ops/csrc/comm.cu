@@ -367,6 +367,73 @@ scatter_kernel(Peers bufs, Peers ctrl, int root, int rank, int ws, long long per
   cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch + 1, err, KB_WAIT_BUDGET_NS);
 }
 
+// Block-granular full sharding, gradients: acc[0, per) += scale * sum over ranks of piece `rank` of the
+// gradient images (acc: this rank's owned gradient piece, local memory).  After the closing barrier (all
+// ranks have read what they own) the rank's own image is cleared for the block that uses it next.
+__global__ void __launch_bounds__(THREADS, 2)   // <= 64 registers: light enough to sit beside a compute CTA
+unit_reduce_kernel(Peers bufs, const void* mc, Peers ctrl, int rank, int ws, long long n, float scale,
+                   __nv_bfloat16* __restrict__ acc_out, int clear, uint32_t epoch, int* err) {
+  if (!cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch, err, KB_WAIT_BUDGET_NS)) return;
+  const long long per = n / ws;
+  const long long off = per * rank;
+  const long long nchunks = per >> 3;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long c0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; c0 < nchunks; c0 += stride * UNROLL) {
+    uint4 raw[UNROLL];
+    float acc[UNROLL][8];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long c = c0 + u * stride;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (mc != nullptr && c < nchunks)
+        raw[u] = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(mc) + off + c * 8);
+    }
+    if (mc != nullptr) {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) acc8(acc[u], raw[u]);
+    } else {
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r)
+        if (r < ws) {
+          const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(bufs.p[(rank + r) % ws]) + off;
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const long long c = c0 + u * stride;
+            raw[u] = c < nchunks ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) acc8(acc[u], raw[u]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long c = c0 + u * stride;
+      if (c >= nchunks) break;
+      float old[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) old[e] = 0.f;
+      acc8(old, *reinterpret_cast<const uint4*>(acc_out + c * 8));
+      uint4 o;
+      o.x = pack_bf16x2(old[0] + acc[u][0] * scale, old[1] + acc[u][1] * scale);
+      o.y = pack_bf16x2(old[2] + acc[u][2] * scale, old[3] + acc[u][3] * scale);
+      o.z = pack_bf16x2(old[4] + acc[u][4] * scale, old[5] + acc[u][5] * scale);
+      o.w = pack_bf16x2(old[6] + acc[u][6] * scale, old[7] + acc[u][7] * scale);
+      *reinterpret_cast<uint4*>(acc_out + c * 8) = o;
+    }
+  }
+  if (!cta_peer_barrier(ctrl, rank, ws, blockIdx.x, epoch + 1, err, KB_WAIT_BUDGET_NS)) return;
+  if (clear) {
+    // the barrier is per CTA slot: CTA b of every rank has read its chunks, CTA b' may not have.  So CTA b
+    // clears, in every rank's piece of its own image, exactly the chunks that CTA b of that rank reads.
+    __nv_bfloat16* mine = static_cast<__nv_bfloat16*>(bufs.p[rank]);
+    for (int r = 0; r < ws; ++r)
+      for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < nchunks; c += stride)
+        *reinterpret_cast<uint4*>(mine + r * per + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 __global__ void barrier_kernel(Peers ctrl, int rank, int ws, int slot, uint32_t epoch, int* err,
                                unsigned long long budget_ns) {
   cta_peer_barrier(ctrl, rank, ws, slot, epoch, err, budget_ns);
@@ -542,6 +609,26 @@ int kb_broadcast_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs,
     push_kernel<<<grid_size(), THREADS, 0, st>>>(bufs, mc, ctrl, rank, ws, 0, n, rank == root ? 1 : 0, epoch,
                                                  kb::error_word(dev));
   }
+  return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
+}
+
+// Unit reduce: acc[0, n / ws) (local bf16) += scale * sum over ranks of piece `rank` of the symmetric images;
+// with `clear` the rank's own image [0, n) is zeroed once every rank has read its piece; `grid` CTAs of
+// `threads` threads (the same on every rank; out of range: one CTA per SM, 512 threads).  Epochs `epoch`, `epoch + 1`.
+int kb_unit_reduce_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, const void* mc, int rank, int ws,
+                        long long n, float scale, void* acc, int clear, unsigned int epoch, int grid, int threads,
+                        void* stream) {
+  using namespace kb::comm;
+  if (ws < 1 || ws > MAX_RANKS || rank < 0 || rank >= ws || n <= 0 || (n % (8 * ws)) || acc == nullptr ||
+      (reinterpret_cast<uintptr_t>(acc) & 15))
+    return KB_STATUS_BAD_ARG;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int g = (grid <= 0 || grid > grid_size()) ? grid_size() : grid;
+  const int t = (threads < 32 || threads > THREADS || (threads & 31)) ? THREADS : threads;
+  unit_reduce_kernel<<<g, t, 0, static_cast<cudaStream_t>(stream)>>>(
+      load_peers(buf_ptrs, ws), mc, load_peers(ctrl_ptrs, ws), rank, ws, n, scale, static_cast<__nv_bfloat16*>(acc),
+      clear, epoch, kb::error_word(dev));
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 

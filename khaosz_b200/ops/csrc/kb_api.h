@@ -22,6 +22,7 @@ enum {
 int kb_last_error(void);  // device-side status of bounded waits since the last call (0 = ok)
 int kb_error_probe(int* pinned_host, void* stream);  // async copy of the error word (no sync)
 int kb_store_f32x2(float* dst, float a, float b, void* stream);  // dst[0..1] = (a, b) on the stream
+int kb_copy_async(void* dst, const void* src, long long bytes, void* stream);  // one device-to-device copy (source may be peer memory)
 int kb_sm_count(void);
 int kb_last_tmap_error(void);  // CUresult of the last failed tensor-map encode
 const char* kb_version(void);
@@ -168,6 +169,12 @@ int kb_allgather_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs,
                       long long n, unsigned int epoch, void* stream);
 int kb_broadcast_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, void* mc_ptr, int root, int rank,
                       int ws, long long n, unsigned int epoch, void* stream);
+// Block-granular full sharding: reduce-scatter of the ranks' symmetric gradient images into local pieces
+// (acc += scale * sum; with `clear` the rank's image is zeroed afterwards) on `grid` CTAs of `threads` threads
+// (<= 0: one CTA per SM / 512; the same on every rank).
+int kb_unit_reduce_bf16(const void* const* buf_ptrs, const void* const* ctrl_ptrs, const void* mc_ptr, int rank, int ws,
+                        long long n, float scale, void* acc, int clear, unsigned int epoch, int grid, int threads,
+                        void* stream);
 // Data-parallel optimizer step over symmetric flat buffers: gradient reduce-scatter (mean) + global
 // clip + sharded AdamW + parameter all-gather.  kb_reduce_adamw does it in one call; the bucket pair
 // lets the reductions run bucket by bucket while the backward pass is still producing gradients

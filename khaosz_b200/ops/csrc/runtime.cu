@@ -160,6 +160,16 @@ int kb_store_f32x2(float* dst, float a, float b, void* stream) {
   return cudaGetLastError() == cudaSuccess ? KB_STATUS_OK : KB_STATUS_CUDA_ERROR;
 }
 
+// One asynchronous device-to-device copy on `stream` (copy engine; the source may be a peer's memory that
+// is mapped into this process).  One call per copy.
+int kb_copy_async(void* dst, const void* src, long long bytes, void* stream) {
+  if (dst == nullptr || src == nullptr || bytes < 0) return KB_STATUS_BAD_ARG;
+  if (bytes == 0) return KB_STATUS_OK;
+  return cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? KB_STATUS_OK
+             : KB_STATUS_CUDA_ERROR;
+}
+
 int kb_sm_count(void) {
   int dev = 0, n = 0;
   cudaGetDevice(&dev);

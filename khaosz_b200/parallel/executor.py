@@ -559,6 +559,67 @@ class FSDPExecutor(BaseExecutor):
         return sq
 
 
+@ExecutorFactory.register("fsdp_block")
+class BlockShardExecutor(BaseExecutor):
+    """Fully sharded data parallel, block by block (``khaosz_b200.parallel.unit_shard``).
+
+    Every decoder block's parameters, gradients and AdamW moments exist as one ``1 / ws`` piece per
+    rank.  A block's weights are all-gathered into one of two reusable images before its forward and
+    again before its backward, by a kernel on a side stream that runs while the previous block
+    computes; its gradients are reduce-scattered the same way while the next block's backward runs.
+    The model's modules, names and kernels are those of the dense model, so a step costs what a
+    data-parallel step costs plus whatever of the transfers does not hide.  Embedding, final norm and
+    an untied output layer stay replicated (one all-reduce of their gradients per optimizer step).
+    ``unwrap_model`` and the optimizer's ``state_dict`` are collective and return the dense layout, as
+    the reference's ``FULL_STATE_DICT`` gather does (``astrai/parallel/executor.py:223-272``).
+    """
+
+    def __init__(self, grad_accum_steps: int = 1, fp8: bool = False, cuda_graph: bool = False, prefetch: bool = True,
+                 **_ignored):
+        # a captured micro-step would freeze the side stream's events into the graph; this executor's
+        # hot loop is not launch-bound, so the micro-step stays eager
+        super().__init__(grad_accum_steps, fp8, cuda_graph=False)
+        self.prefetch = prefetch
+        self.units = None
+
+    def _prepare_model(self, model: nn.Module) -> nn.Module:
+        from .unit_shard import ShardedUnits
+
+        _broadcast_parameters(model, None)
+        self.units = ShardedUnits(model, prefetch=self.prefetch)
+        self.flat = self.units.flat
+        self._model = model
+        return model
+
+    def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):
+        model = self._prepare_model(model)
+        if optimizer is not None:
+            if not hasattr(optimizer, "attach_flat") or len(optimizer.param_groups) != 1:
+                raise NotImplementedError("fsdp_block shards the state of the fused flat AdamW (one parameter group); "
+                                          f"{type(optimizer).__name__} keeps per-parameter state: use ddp or fsdp")
+            optimizer.attach_flat(self.flat, shard=(0, self.units.local_numel))
+            if getattr(optimizer, "_flat", None) is None:
+                raise NotImplementedError("fsdp_block: the optimizer has to cover exactly the model's parameters")
+            optimizer.set_layout(self.units.owned_ranges)
+            optimizer.set_norm_fn(self.units.grad_norm_sq)
+            optimizer = AccumOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step)
+        if scheduler is not None:
+            scheduler = AccumScheduler(scheduler, self.gradient_state)
+        return model, optimizer, dataloader, scheduler
+
+    def _sync_gradients(self) -> None:
+        self.units.finish_backward()
+
+    def _after_optimizer_step(self) -> None:
+        self.units.invalidate()
+
+    def unwrap_model(self, model: nn.Module) -> Dict[str, torch.Tensor]:
+        return self.units.full_state_dict()
+
+    def grad_norm_sq_extra(self) -> Optional[torch.Tensor]:
+        return self.units.grad_norm_sq() if get_world_size() > 1 else None
+
+
 def _hybrid_groups(tp_size: int):
     """Process groups of a ``dp x tp`` layout: tensor-parallel groups are runs of ``tp_size``
     consecutive ranks (same NVLink island), data-parallel groups take one rank of every run.

@@ -39,6 +39,12 @@ class FusedAdamW(Optimizer):
         self._gnorm_sq: Optional[torch.Tensor] = None
         self.last_grad_norm: Optional[torch.Tensor] = None
         self._norm_fn = None
+        self._layout = None
+
+    def set_layout(self, owned_ranges) -> None:
+        """``owned_ranges(rank) -> [(dense offset, local offset, n)]``: which pieces of the dense flat
+        vector the local vectors of ``rank`` hold (executors that shard block by block)."""
+        self._layout = owned_ranges
 
     def set_norm_fn(self, fn) -> None:
         """``fn() -> device scalar`` with the global squared gradient norm; executors whose
@@ -166,6 +172,8 @@ class FusedAdamW(Optimizer):
     # -- checkpoint layout: per-parameter ``exp_avg / exp_avg_sq / step`` like torch AdamW ------
     def _owned_ranges(self, rank: Optional[int] = None):
         """``(global_offset, local_offset, n)`` pieces of the flat vector whose moments live on ``rank``."""
+        if self._layout is not None:
+            return self._layout(rank)
         if self._reducer is not None and hasattr(self._reducer, "owned_ranges"):
             return self._reducer.owned_ranges(rank)
         if self._shard is None:

@@ -55,6 +55,11 @@ def test_cli_trains_fully_sharded_on_two_cpu_ranks(tmp_path):
     assert ck.state_dict["layers.0.attention.k_proj.weight"].shape == (32, 64)
 
 
+def test_cli_trains_block_sharded_on_two_cpu_ranks(tmp_path):
+    ck = _run(tmp_path, "fsdp_block", 2, 29656)
+    assert ck.state_dict["layers.0.attention.k_proj.weight"].shape == (32, 64)
+
+
 def test_cli_trains_single_process(tmp_path):
     ck = _run(tmp_path, "none", 1, 29654)
     assert "lm_head.weight" in ck.state_dict
@@ -229,7 +234,7 @@ def _cosine(opt):
     return SchedulerFactory.create(opt, "cosine", warmup_steps=2, lr_decay_steps=20)
 
 
-@pytest.mark.parametrize("mode", ["ddp", "fsdp"])
+@pytest.mark.parametrize("mode", ["ddp", "fsdp", "fsdp_block"])
 def test_trainer_with_validation_on_two_ranks(tmp_path, mode):
     from khaosz_b200.trainer import Trainer
 
@@ -264,7 +269,7 @@ def test_resuming_a_lora_run_keeps_the_adapters(tmp_path):
         assert torch.equal(resumed[k], v), k
 
 
-@pytest.mark.parametrize("mode,port", [("ddp", 29692), ("fsdp", 29693), ("tp", 29694)])
+@pytest.mark.parametrize("mode,port", [("ddp", 29692), ("fsdp", 29693), ("tp", 29694), ("fsdp_block", 29696)])
 def test_auto_resume_is_exact_on_two_ranks(mode, port, tmp_path):
     """A killed and restarted two-rank run (data parallel, sharded optimizer, tensor parallel) ends with the
     weights of the uninterrupted one."""
@@ -291,7 +296,7 @@ def test_auto_resume_is_exact_on_two_ranks(mode, port, tmp_path):
         assert torch.equal(resumed[k], v), k
 
 
-@pytest.mark.parametrize("mode", ["ddp", "fsdp", "fsdp_full", "tp"])
+@pytest.mark.parametrize("mode", ["ddp", "fsdp", "fsdp_block", "fsdp_full", "tp"])
 def test_parallel_modes_degrade_to_a_single_process(mode, tmp_path):
     ck = _run(tmp_path, mode, 1, 29695)
     assert ck.iteration == 20 and "layers.1.mlp.down.weight" in ck.state_dict

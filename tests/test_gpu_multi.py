@@ -166,19 +166,19 @@ def test_peer_wait_is_bounded_and_context_survives():
     _spawn(_timeout_case, 29702)
 
 
-def _cfg():
+def _cfg(layers=2):
     from khaosz_b200 import AutoRegressiveLMConfig
 
-    return AutoRegressiveLMConfig(vocab_size=4096, dim=512, n_layers=2, norm_eps=1e-5, dim_ffn=1408, tie_weight=True,
+    return AutoRegressiveLMConfig(vocab_size=4096, dim=512, n_layers=layers, norm_eps=1e-5, dim_ffn=1408, tie_weight=True,
                                   max_len=256, rope_theta=1e4, n_heads=4, n_kv_heads=2)
 
 
-def _train(mode, world, rank, device, steps=4, accum=2, cuda_graph=False, overlap=False):
+def _train(mode, world, rank, device, steps=4, accum=2, cuda_graph=False, overlap=False, layers=2):
     from khaosz_b200 import AutoRegressiveLM
     from khaosz_b200.trainer import FusedAdamW, StrategyFactory
 
     torch.manual_seed(3407)
-    model = AutoRegressiveLM(_cfg()).to(device=device, dtype=torch.bfloat16)
+    model = AutoRegressiveLM(_cfg(layers)).to(device=device, dtype=torch.bfloat16)
     # ~1 MB buckets handed over during the backward pass: several per step on this small model
     extra = {"bucket_cap_mb": 1, "overlap_grad_reduce": True} if overlap else {}
     ex = ExecutorFactory.create(mode, grad_accum_steps=accum, cuda_graph=cuda_graph, **extra)
@@ -225,6 +225,26 @@ def _dp_case(mode, out, overlap=False):
                     "m0": osd["state"][0]["exp_avg"]}, out)
 
 
+def _block_case(out):
+    """Block-granular full shard: five blocks through two weight images, gathered and reduced on a side stream."""
+    from khaosz_b200.ops import raise_on_device_error
+
+    rank = dist.get_rank()
+    dev = torch.device("cuda", rank)
+    losses, model, ex, opt = _train("fsdp_block", 2, rank, dev, layers=5)
+    dist.all_reduce(losses)
+    losses /= 2
+    raise_on_device_error()
+    u = ex.units
+    assert u._sym and u.gathers > 0 and u.reductions == 4 * 2 * 5, "the side-stream collectives did not run"
+    assert u.data.numel() == sum(x.numel for x in u.units) // 2 + u.rest_numel
+    sd = ex.unwrap_model(model)
+    osd = opt.state_dict()
+    if rank == 0:
+        torch.save({"losses": losses.cpu(), "sd": {k: v.cpu() for k, v in sd.items()},
+                    "m0": osd["state"][0]["exp_avg"]}, out)
+
+
 def _tp_train_case(out, mode="tp", cuda_graph=False):
     from khaosz_b200.ops import raise_on_device_error
     from khaosz_b200.parallel.tensor_parallel import TPContext
@@ -249,13 +269,17 @@ def _tp_train_case(out, mode="tp", cuda_graph=False):
 
 @pytest.mark.parametrize("mode,port", [("ddp", 29703), ("fsdp", 29704), ("tp", 29707), ("fsdp_full", 29708),
                                        ("tp_graph", 29709), ("ddp_nvls", 29712), ("fsdp_nvls", 29713),
-                                       ("ddp_overlap", 29714)])
+                                       ("ddp_overlap", 29714), ("fsdp_block", 29715), ("fsdp_block_nvls", 29716)])
 def test_fused_data_parallel_step_matches_single_gpu(mode, port, tmp_path):
     out = str(tmp_path / "dp.pt")
     nvls = mode.endswith("_nvls")
     overlap = mode.endswith("_overlap")
     mode = mode.split("_nvls")[0].split("_overlap")[0]
-    if mode == "tp_graph":   # forward+backward of the tensor-parallel micro-step replayed as a CUDA graph
+    layers = 2
+    if mode == "fsdp_block":
+        layers = 5
+        _spawn(_block_case, port, nvls=nvls, out=out)
+    elif mode == "tp_graph":   # forward+backward of the tensor-parallel micro-step replayed as a CUDA graph
         _spawn(_tp_train_case, port, out=out, mode="tp", cuda_graph=True)
     elif mode in ("tp", "fsdp_full"):
         _spawn(_tp_train_case, port, out=out, mode=mode)
@@ -268,7 +292,7 @@ def test_fused_data_parallel_step_matches_single_gpu(mode, port, tmp_path):
 
     torch.manual_seed(3407)
     dev = torch.device("cuda", 0)
-    model = AutoRegressiveLM(_cfg()).to(device=dev, dtype=torch.bfloat16)
+    model = AutoRegressiveLM(_cfg(layers)).to(device=dev, dtype=torch.bfloat16)
     init = {k: v.detach().float().cpu().clone() for k, v in model.state_dict().items()}
     ex = ExecutorFactory.create("none", grad_accum_steps=2)
     opt = FusedAdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.01)

@@ -1,0 +1,130 @@
+"""Block-granular full sharding (``fsdp_block``) on CPU: one process and gloo ranks against the dense /
+data-parallel result, slot reuse over more than two blocks, accumulation, checkpoints, recompute, MoE."""
+import pytest
+import torch
+import torch.distributed as dist
+
+from khaosz_b200.parallel import ExecutorFactory, spawn_parallel_fn
+
+
+def _model(layers=5, moe=False, tie=True, seed=11):
+    from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
+
+    ffn = dict(ffn_type="moe", n_routed_experts=4, n_shared_experts=1, n_activated_experts=2) if moe else {}
+    cfg = AutoRegressiveLMConfig(vocab_size=300, dim=64, n_layers=layers, norm_eps=1e-5, dim_ffn=96, tie_weight=tie,
+                                 max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, **ffn)
+    torch.manual_seed(seed)
+    m = AutoRegressiveLM(cfg)
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            if "norm" in name:
+                p.add_(0.1 * torch.randn_like(p))
+    return m
+
+
+def _train(mode, rank, world, steps=3, accum=2, recompute=False, **model_kw):
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    model = _model(**model_kw)
+    ex = ExecutorFactory.create(mode, grad_accum_steps=accum)
+    opt = FusedAdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.01)
+    model, opt, _, _ = ex.prepare(model, opt, None, None)
+    if recompute:
+        from khaosz_b200.models.components.block import DecoderBlock
+        from khaosz_b200.trainer.callbacks import GradientCheckpointingCallback
+
+        cb = GradientCheckpointingCallback([DecoderBlock])
+        model.apply(cb._enable)
+    strat = StrategyFactory.create("seq", model, "cpu")
+    data = torch.randint(0, 300, (steps * accum, 2 * world, 33), generator=torch.Generator().manual_seed(5))
+    losses = []
+    for i in range(steps * accum):
+        mine = data[i, 2 * rank:2 * rank + 2]
+        with ex.accumulate(model):
+            loss = strat({"input_ids": mine[:, :-1], "target_ids": mine[:, 1:]})
+            ex.backward(loss / accum)
+            if ex.sync_gradients:
+                opt.fused_clip(1.0)
+                opt.step()
+                opt.zero_grad()
+        losses.append(loss.item())
+    return model, ex, opt, losses
+
+
+def test_one_process_equals_the_dense_run():
+    dense, ex0, opt0, l0 = _train("none", 0, 1)
+    model, ex, opt, l1 = _train("fsdp_block", 0, 1)
+    assert l1 == pytest.approx(l0, rel=1e-5, abs=1e-6)
+    sd = ex.unwrap_model(model)
+    for k, v in dense.state_dict().items():
+        assert torch.allclose(sd[k], v, rtol=1e-5, atol=1e-6), k
+    a, b = opt0.state_dict(), opt.state_dict()
+    assert len(a["state"]) == len(b["state"])
+    for i in a["state"]:
+        assert torch.allclose(a["state"][i]["exp_avg"], b["state"][i]["exp_avg"], rtol=1e-5, atol=1e-8), i
+    # five blocks went through two images: every backward re-gathered what the forward had displaced
+    assert ex.units.gathers > 2 * 5 and ex.units.reductions == 3 * 2 * 5
+
+
+def _ranks_case(out, moe=False, recompute=False, tie=True):
+    rank, world = dist.get_rank(), dist.get_world_size()
+    kw = dict(moe=moe, tie=tie)
+    ref_model, ref_ex, ref_opt, ref_losses = _train("ddp", rank, world, **kw)
+    model, ex, opt, losses = _train("fsdp_block", rank, world, recompute=recompute, **kw)
+    assert losses == pytest.approx(ref_losses, rel=1e-4, abs=1e-5)
+    sd = ex.unwrap_model(model)                       # collective, dense names
+    ref_sd = ref_ex.unwrap_model(ref_model)
+    assert list(sd) == list(ref_sd)
+    for k, v in ref_sd.items():
+        assert torch.allclose(sd[k], v, rtol=1e-4, atol=1e-5), k
+    u = ex.units
+    blocks = sum(x.numel for x in u.units)
+    assert u.local_numel == blocks // world + u.rest_numel      # 1 / world of the block weights per rank
+    assert u.data.numel() == u.local_numel and opt.optimizer._m.numel() == u.local_numel
+
+    # optimizer state: dense layout out, this rank's pieces back in
+    state, ref_state = opt.state_dict(), ref_opt.state_dict()
+    for i in ref_state["state"]:
+        assert torch.allclose(state["state"][i]["exp_avg"], ref_state["state"][i]["exp_avg"], rtol=1e-3, atol=1e-7), i
+        assert state["state"][i]["exp_avg"].shape == ref_state["state"][i]["exp_avg"].shape
+    if rank == 0:
+        torch.save({"opt": state, "sd": sd}, out)
+    dist.barrier()
+    saved = torch.load(out, weights_only=False)
+    model2, ex2, opt2, _ = _train("fsdp_block", rank, world, steps=0, **kw)
+    ex2.units.load_full_state_dict(saved["sd"])
+    opt2.load_state_dict(saved["opt"])
+    assert torch.equal(ex2.units.data, u.data)
+    assert torch.equal(opt2.optimizer._m, opt.optimizer._m) and torch.equal(opt2.optimizer._v, opt.optimizer._v)
+    assert opt2.optimizer._step_count == opt.optimizer._step_count
+
+    # a forward without gradients (validation) gathers on demand and sees the updated weights
+    ids = torch.randint(0, 300, (2, 16), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        got = model2(ids)["logits"]
+    dense = _model(**kw)
+    dense.load_state_dict(saved["sd"])
+    with torch.no_grad():
+        want = dense(ids)["logits"]
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-5)
+    dist.barrier()
+
+
+@pytest.mark.parametrize("world,port,kw", [(2, "29741", {}), (4, "29742", {"tie": False}), (2, "29743", {"moe": True}),
+                                           (2, "29744", {"recompute": True})])
+def test_ranks_match_data_parallel(world, port, kw, tmp_path):
+    spawn_parallel_fn(_ranks_case, world_size=world, backend="gloo", master_addr="127.0.0.1", master_port=port,
+                      out=str(tmp_path / "s.pt"), **kw)
+
+
+def test_rejects_what_it_cannot_shard():
+    from khaosz_b200.trainer import FusedAdamW
+
+    model = _model(layers=2)
+    next(model.layers[0].parameters()).requires_grad_(False)
+    with pytest.raises(NotImplementedError):
+        ExecutorFactory.create("fsdp_block").prepare(model, None, None, None)
+    model = _model(layers=2)
+    with pytest.raises(NotImplementedError):
+        ExecutorFactory.create("fsdp_block").prepare(model, torch.optim.SGD(model.parameters(), lr=0.1), None, None)
+    assert FusedAdamW is not None
