@@ -295,7 +295,7 @@ def run_own(args):
 
     # ---- device-timed steps (inputs resident on the device; every step sees data it has not seen) ----
     model = model_fn().to(device)
-    ex_extra = {"overlap_grad_reduce": bool(args.overlap)} if args.overlap >= 0 and mode in ("ddp", "fsdp") else {}
+    ex_extra = {"overlap_grad_reduce": bool(args.overlap)} if args.overlap >= 0 and mode in ("ddp", "fsdp", "fsdp_zero1") else {}
     executor = ExecutorFactory.create(mode, grad_accum_steps=accum, cuda_graph=args.cuda_graph, **ex_extra)
     opt = optimizer_fn(model)
     model, opt, _, sched = executor.prepare(model, opt, None, scheduler_fn(opt))
@@ -534,7 +534,7 @@ def main():
     ap.add_argument("--no-e2e", dest="no_e2e", action="store_true")
     ap.add_argument("--cuda-graph", dest="cuda_graph", type=int, default=-1,
                     help="own arm: forward+backward of a micro-batch as a replayed CUDA graph (default: on for tp)")
-    ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp", "fsdp_block", "fsdp_full", "tp"],
+    ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp", "fsdp_block", "fsdp_zero1", "fsdp_full", "tp"],
                     help="own arm, N > 1: data parallel (default), sharded data parallel, or tensor parallel "
                          "(tp: every rank reads the same batches, total work is fixed -> strong scaling)")
     ap.add_argument("--strategy", default="seq", choices=["seq", "dpo"],

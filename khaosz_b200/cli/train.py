@@ -74,7 +74,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--master_port", type=str, default="29500")
     p.add_argument("--backend", type=str, default="nccl")
     p.add_argument("--nprocs", type=int, default=1)
-    p.add_argument("--parallel_mode", choices=["none", "ddp", "fsdp", "fsdp_block", "fsdp_full", "tp"], default="none")
+    p.add_argument("--parallel_mode", choices=["none", "ddp", "fsdp", "fsdp_block", "fsdp_zero1", "fsdp_full", "tp"], default="none")
     p.add_argument("--tp_size", type=int, default=None)
     p.add_argument("--cuda_graph", action="store_true", default=False,
                    help="replay forward+backward of a micro-batch as a CUDA graph (fixed batch shapes)")
@@ -107,7 +107,7 @@ def train(args: argparse.Namespace) -> None:
     if not os.path.exists(args.param_path):
         raise FileNotFoundError(args.param_path)
     if args.nprocs > 1 and args.parallel_mode == "none":
-        raise ValueError("--nprocs > 1 requires --parallel_mode to be 'ddp', 'fsdp', 'fsdp_block', 'fsdp_full' or 'tp'")
+        raise ValueError("--nprocs > 1 requires --parallel_mode to be 'ddp', 'fsdp', 'fsdp_block', 'fsdp_zero1', 'fsdp_full' or 'tp'")
     config = AutoRegressiveLMConfig.from_file(os.path.join(args.param_path, "config.json"))
     window = args.window_size or config.max_len
     dataset = DatasetFactory.load(train_type=args.train_type, load_path=args.data_root_path, window_size=window,

@@ -59,7 +59,7 @@ class TrainConfig(BaseConfig):
     backend: str = field(default="nccl", metadata=_opt("torch.distributed backend."))
     master_addr: str = field(default="localhost", metadata=_opt("Rendezvous address."))
     master_port: str = field(default="29500", metadata=_opt("Rendezvous port."))
-    parallel_mode: str = field(default="none", metadata=_opt("none, ddp, fsdp, fsdp_block, fsdp_full or tp."))
+    parallel_mode: str = field(default="none", metadata=_opt("none, ddp, fsdp (fsdp_block where it applies, else fsdp_zero1), fsdp_block, fsdp_zero1, fsdp_full or tp."))
     start_method: str = field(default="spawn", metadata=_opt("Multiprocessing start method."))
     # -- misc ---------------------------------------------------------------------------
     device_type: str = field(default="cuda", metadata=_opt("Device type."))

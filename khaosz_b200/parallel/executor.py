@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import contextlib
 import logging
+import os
 from typing import Any, Dict, Optional, Tuple
 
 import torch
@@ -454,25 +455,83 @@ class DDPExecutor(BaseExecutor):
         return model, optimizer, dataloader, scheduler
 
 
+def _why_not_block_sharded(model: nn.Module, optimizer, cuda_graph: bool) -> Optional[str]:
+    """Reason why the block-granular full shard cannot take this model / optimizer (None: it can)."""
+    if not isinstance(getattr(model, "layers", None), (nn.ModuleList, list, tuple)) or len(model.layers) == 0:
+        return f"{type(model).__name__} has no `layers` list to shard by"
+    params = list(model.parameters())
+    if not params or not all(p.requires_grad for p in params):
+        return "the model has frozen parameters (adapters)"
+    if any(p.dtype != params[0].dtype or p.device != params[0].device for p in params):
+        return "the parameters do not share one dtype and device"
+    if optimizer is not None and (not hasattr(optimizer, "attach_flat") or len(optimizer.param_groups) != 1):
+        return f"{type(optimizer).__name__} keeps per-parameter state (only the fused flat AdamW is sharded)"
+    if cuda_graph:
+        return "the micro-step is to be captured as a CUDA graph"
+    if params[0].is_cuda and get_world_size() > 1:
+        from ..ops import _lib
+
+        if params[0].dtype != torch.bfloat16 or not _lib.has("kb_unit_reduce_bf16") or get_world_size() > 8:
+            return "the collective kernels need bf16 parameters and at most 8 ranks"
+    return None
+
+
 @ExecutorFactory.register("fsdp")
 class FSDPExecutor(BaseExecutor):
-    """Fully sharded data parallel over flat buffers.
+    """Fully sharded data parallel.
 
-    Every rank owns the contiguous slice ``[rank * n / ws, (rank + 1) * n / ws)`` of the flat
-    parameter vector: gradients are reduce-scattered to their owner, optimizer state exists
-    for the owned slice only and the owner updates it; updated parameters are all-gathered
-    before the next forward.  ``unwrap_model`` returns the full (unsharded) state dict on every
-    rank, as the reference's ``FULL_STATE_DICT`` gather does (``astrai/parallel/executor.py:263-272``).
+    ``shard_parameters=True`` (mode ``fsdp_block``; the default of ``fsdp`` wherever it applies): every
+    decoder block's parameters, gradients and AdamW moments exist as one ``1 / ws`` piece per rank
+    (``khaosz_b200.parallel.unit_shard``).  A block's weights are gathered into one of two reusable
+    images before its forward and again before its backward, by the copy engine, while the previous
+    block computes; its gradients are reduce-scattered by a kernel on a side stream while the next
+    block's backward runs.  Modules, names and kernels are those of the dense model.  Embedding, final
+    norm and an untied output layer stay replicated (one all-reduce of their gradients per step).  This is
+    the memory behaviour of the reference's ``ShardingStrategy.FULL_SHARD`` wrapper
+    (``astrai/parallel/executor.py:223-272``).
+
+    ``shard_parameters=False`` (mode ``fsdp_zero1``; also what ``fsdp`` falls back to, with a warning, for
+    models with frozen parameters, optimizers other than the fused AdamW or a captured micro-step):
+    whole parameters and gradients stay resident; every rank owns the contiguous slice
+    ``[rank * n / ws, (rank + 1) * n / ws)`` of the flat parameter vector, gradients are
+    reduce-scattered to their owner, optimizer state exists for the owned slice only and the owner
+    updates it; updated parameters are all-gathered before the next forward.
+
+    ``unwrap_model`` returns the full (unsharded) state dict on every rank and the optimizer's
+    ``state_dict`` the dense layout, as the reference's ``FULL_STATE_DICT`` gather does
+    (``astrai/parallel/executor.py:263-272``).
     """
 
+    default_shard_parameters: Optional[bool] = None     # None: where it applies
+
     def __init__(self, grad_accum_steps: int = 1, comm: str = "auto", fp8: bool = False, cuda_graph: bool = False,
-                 bucket_cap_mb: int = 25, overlap_grad_reduce: Optional[bool] = None, **_ignored):
+                 bucket_cap_mb: int = 25, overlap_grad_reduce: Optional[bool] = None,
+                 shard_parameters: Optional[bool] = None, prefetch: bool = True, **_ignored):
         super().__init__(grad_accum_steps, fp8, cuda_graph)
         self.comm = comm
         self.bucket_cap_mb = bucket_cap_mb
         self.overlap_grad_reduce = overlap_grad_reduce
+        self.shard_parameters = self.default_shard_parameters if shard_parameters is None else shard_parameters
+        self.prefetch = prefetch
         self.shard: Optional[Tuple[int, int]] = None
         self._reducer = None
+        self.units = None
+        self._wants_graph = bool(cuda_graph)
+
+    def _block_sharded(self, model: nn.Module, optimizer) -> bool:
+        want = self.shard_parameters
+        if want is None:
+            want = os.environ.get("KHAOSZ_B200_FSDP_SHARD_PARAMS", "1") != "0"
+        if not want:
+            return False
+        why = _why_not_block_sharded(model, optimizer, self._wants_graph)
+        if why is None:
+            return True
+        if self.shard_parameters:
+            raise NotImplementedError(f"fsdp_block: {why}; use fsdp_zero1 or ddp")
+        log.warning("fsdp: %s; whole parameters stay resident on every rank, the optimizer state and the update "
+                    "are sharded (fsdp_zero1)", why)
+        return False
 
     def _prepare_model(self, model: nn.Module) -> nn.Module:
         ws = get_world_size()
@@ -488,7 +547,29 @@ class FSDPExecutor(BaseExecutor):
                                                overlap=self.overlap_grad_reduce)
         return model
 
+    def _prepare_units(self, model: nn.Module, optimizer):
+        from .unit_shard import ShardedUnits
+
+        _broadcast_parameters(model, None)
+        self._graphed = None        # the side streams' events are not captured
+        self.units = ShardedUnits(model, prefetch=self.prefetch)
+        self.flat = self.units.flat
+        self._model = model
+        if optimizer is not None:
+            optimizer.attach_flat(self.flat, shard=(0, self.units.local_numel))
+            if getattr(optimizer, "_flat", None) is None:
+                raise NotImplementedError("fsdp: the optimizer has to cover exactly the model's parameters")
+            optimizer.set_layout(self.units.owned_ranges)
+            optimizer.set_norm_fn(self.units.grad_norm_sq)
+            optimizer = AccumOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step)
+        return model, optimizer
+
     def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):
+        if self._block_sharded(model, optimizer):
+            model, optimizer = self._prepare_units(model, optimizer)
+            if scheduler is not None:
+                scheduler = AccumScheduler(scheduler, self.gradient_state)
+            return model, optimizer, dataloader, scheduler
         model = self._prepare_model(model)
         self._fused = False
         if optimizer is not None:
@@ -510,6 +591,9 @@ class FSDPExecutor(BaseExecutor):
         return model, optimizer, dataloader, scheduler
 
     def _sync_gradients(self) -> None:
+        if self.units is not None:
+            self.units.finish_backward()
+            return
         ws = get_world_size()
         if ws <= 1:
             return
@@ -531,6 +615,9 @@ class FSDPExecutor(BaseExecutor):
         mine.div_(ws)
 
     def _after_optimizer_step(self) -> None:
+        if self.units is not None:
+            self.units.invalidate()
+            return
         ws = get_world_size()
         if ws <= 1 or self.shard is None:
             return
@@ -547,10 +634,14 @@ class FSDPExecutor(BaseExecutor):
             dist.all_gather_into_tensor(data[: n * ws], data[off:off + n].clone())
 
     def unwrap_model(self, model: nn.Module) -> Dict[str, torch.Tensor]:
+        if self.units is not None:
+            return self.units.full_state_dict()
         # parameters are kept whole between steps, so the local state dict is the full one
         return {k: v.detach().clone() for k, v in model.state_dict().items()}
 
     def grad_norm_sq_extra(self) -> Optional[torch.Tensor]:
+        if self.units is not None:
+            return self.units.grad_norm_sq() if get_world_size() > 1 else None
         if get_world_size() <= 1 or self.shard is None:
             return None
         off, n = self.shard
@@ -560,64 +651,18 @@ class FSDPExecutor(BaseExecutor):
 
 
 @ExecutorFactory.register("fsdp_block")
-class BlockShardExecutor(BaseExecutor):
-    """Fully sharded data parallel, block by block (``khaosz_b200.parallel.unit_shard``).
+class BlockShardExecutor(FSDPExecutor):
+    """``fsdp`` that insists on sharding the parameters block by block (raises where it cannot)."""
 
-    Every decoder block's parameters, gradients and AdamW moments exist as one ``1 / ws`` piece per
-    rank.  A block's weights are all-gathered into one of two reusable images before its forward and
-    again before its backward, by a kernel on a side stream that runs while the previous block
-    computes; its gradients are reduce-scattered the same way while the next block's backward runs.
-    The model's modules, names and kernels are those of the dense model, so a step costs what a
-    data-parallel step costs plus whatever of the transfers does not hide.  Embedding, final norm and
-    an untied output layer stay replicated (one all-reduce of their gradients per optimizer step).
-    ``unwrap_model`` and the optimizer's ``state_dict`` are collective and return the dense layout, as
-    the reference's ``FULL_STATE_DICT`` gather does (``astrai/parallel/executor.py:223-272``).
-    """
+    default_shard_parameters = True
 
-    def __init__(self, grad_accum_steps: int = 1, fp8: bool = False, cuda_graph: bool = False, prefetch: bool = True,
-                 **_ignored):
-        # a captured micro-step would freeze the side stream's events into the graph; this executor's
-        # hot loop is not launch-bound, so the micro-step stays eager
-        super().__init__(grad_accum_steps, fp8, cuda_graph=False)
-        self.prefetch = prefetch
-        self.units = None
 
-    def _prepare_model(self, model: nn.Module) -> nn.Module:
-        from .unit_shard import ShardedUnits
+@ExecutorFactory.register("fsdp_zero1")
+class ZeroOneExecutor(FSDPExecutor):
+    """``fsdp`` with whole parameters and gradients resident: only the optimizer state and the update
+    are sharded (works with every model and optimizer, adapters and CUDA-graph capture included)."""
 
-        _broadcast_parameters(model, None)
-        self.units = ShardedUnits(model, prefetch=self.prefetch)
-        self.flat = self.units.flat
-        self._model = model
-        return model
-
-    def prepare(self, model, optimizer=None, dataloader=None, scheduler=None):
-        model = self._prepare_model(model)
-        if optimizer is not None:
-            if not hasattr(optimizer, "attach_flat") or len(optimizer.param_groups) != 1:
-                raise NotImplementedError("fsdp_block shards the state of the fused flat AdamW (one parameter group); "
-                                          f"{type(optimizer).__name__} keeps per-parameter state: use ddp or fsdp")
-            optimizer.attach_flat(self.flat, shard=(0, self.units.local_numel))
-            if getattr(optimizer, "_flat", None) is None:
-                raise NotImplementedError("fsdp_block: the optimizer has to cover exactly the model's parameters")
-            optimizer.set_layout(self.units.owned_ranges)
-            optimizer.set_norm_fn(self.units.grad_norm_sq)
-            optimizer = AccumOptimizer(optimizer, self.gradient_state, self.flat, self._after_optimizer_step)
-        if scheduler is not None:
-            scheduler = AccumScheduler(scheduler, self.gradient_state)
-        return model, optimizer, dataloader, scheduler
-
-    def _sync_gradients(self) -> None:
-        self.units.finish_backward()
-
-    def _after_optimizer_step(self) -> None:
-        self.units.invalidate()
-
-    def unwrap_model(self, model: nn.Module) -> Dict[str, torch.Tensor]:
-        return self.units.full_state_dict()
-
-    def grad_norm_sq_extra(self) -> Optional[torch.Tensor]:
-        return self.units.grad_norm_sq() if get_world_size() > 1 else None
+    default_shard_parameters = False
 
 
 def _hybrid_groups(tp_size: int):

@@ -180,9 +180,10 @@ class ShardedUnits:
             # the gather, nothing waits for the reduction before the image is reused)
             self._side = torch.cuda.Stream(device=dev)
             self._copy = torch.cuda.Stream(device=dev)
-            # CTAs x threads of the reduce kernel (the same on every rank): it is never waited for before two
-            # blocks later, so it runs as a few light CTAs beside the block that is computing
-            self.grid = int(os.environ.get("KHAOSZ_B200_SHARD_GRID", "32"))
+            # CTAs x threads of the reduce kernel (the same on every rank; 0: one CTA per SM).  Measured on the
+            # 1B model: a reduction spread over all SMs and finished quickly costs less than a small grid
+            # that lingers beside the compute kernels (12 / 32 / 96 / 148 CTAs: 674 / 628 / 617 / 608 ms per step)
+            self.grid = int(os.environ.get("KHAOSZ_B200_SHARD_GRID", "0"))
             self.threads = int(os.environ.get("KHAOSZ_B200_SHARD_THREADS", "256"))
         else:
             self.data = torch.zeros(self.local_numel, dtype=dtype, device=dev)

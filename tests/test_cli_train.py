@@ -234,7 +234,7 @@ def _cosine(opt):
     return SchedulerFactory.create(opt, "cosine", warmup_steps=2, lr_decay_steps=20)
 
 
-@pytest.mark.parametrize("mode", ["ddp", "fsdp", "fsdp_block"])
+@pytest.mark.parametrize("mode", ["ddp", "fsdp", "fsdp_zero1"])
 def test_trainer_with_validation_on_two_ranks(tmp_path, mode):
     from khaosz_b200.trainer import Trainer
 
@@ -269,7 +269,7 @@ def test_resuming_a_lora_run_keeps_the_adapters(tmp_path):
         assert torch.equal(resumed[k], v), k
 
 
-@pytest.mark.parametrize("mode,port", [("ddp", 29692), ("fsdp", 29693), ("tp", 29694), ("fsdp_block", 29696)])
+@pytest.mark.parametrize("mode,port", [("ddp", 29692), ("fsdp", 29693), ("tp", 29694), ("fsdp_zero1", 29696)])
 def test_auto_resume_is_exact_on_two_ranks(mode, port, tmp_path):
     """A killed and restarted two-rank run (data parallel, sharded optimizer, tensor parallel) ends with the
     weights of the uninterrupted one."""
@@ -296,7 +296,7 @@ def test_auto_resume_is_exact_on_two_ranks(mode, port, tmp_path):
         assert torch.equal(resumed[k], v), k
 
 
-@pytest.mark.parametrize("mode", ["ddp", "fsdp", "fsdp_block", "fsdp_full", "tp"])
+@pytest.mark.parametrize("mode", ["ddp", "fsdp", "fsdp_zero1", "fsdp_full", "tp"])
 def test_parallel_modes_degrade_to_a_single_process(mode, tmp_path):
     ck = _run(tmp_path, mode, 1, 29695)
     assert ck.iteration == 20 and "layers.1.mlp.down.weight" in ck.state_dict

@@ -267,8 +267,8 @@ def _tp_train_case(out, mode="tp", cuda_graph=False):
         torch.save({"losses": losses.cpu(), "sd": {k: v.cpu() for k, v in sd.items()}}, out)
 
 
-@pytest.mark.parametrize("mode,port", [("ddp", 29703), ("fsdp", 29704), ("tp", 29707), ("fsdp_full", 29708),
-                                       ("tp_graph", 29709), ("ddp_nvls", 29712), ("fsdp_nvls", 29713),
+@pytest.mark.parametrize("mode,port", [("ddp", 29703), ("fsdp_zero1", 29704), ("tp", 29707), ("fsdp_full", 29708),
+                                       ("tp_graph", 29709), ("ddp_nvls", 29712), ("fsdp_zero1_nvls", 29713),
                                        ("ddp_overlap", 29714), ("fsdp_block", 29715), ("fsdp_block_nvls", 29716)])
 def test_fused_data_parallel_step_matches_single_gpu(mode, port, tmp_path):
     out = str(tmp_path / "dp.pt")

@@ -132,7 +132,7 @@ def _single_reference():
 
 @pytest.mark.parametrize("mode,port,world", [("ddp", "29631", 2), ("fsdp", "29632", 2), ("tp", "29633", 2),
                                              ("tp", "29634", 4), ("fsdp_full", "29635", 2),
-                                             ("fsdp_block", "29636", 2)])  # tp on 4 ranks: 2 KV heads shared by rank pairs
+                                             ("fsdp_zero1", "29636", 2)])  # tp on 4 ranks: 2 KV heads shared by rank pairs
 def test_executor_matches_single_process(mode, port, world, tmp_path):
     out = str(tmp_path / "r.pt")
     spawn_parallel_fn(_distributed_case, world_size=world, backend="gloo", master_addr="127.0.0.1", master_port=port,
@@ -591,7 +591,7 @@ def _dense_state_into_sharded_case(path, mode):
     dist.barrier()
 
 
-@pytest.mark.parametrize("mode,port", [("tp", "29686"), ("fsdp_full", "29687"), ("fsdp_block", "29688")])
+@pytest.mark.parametrize("mode,port", [("tp", "29686"), ("fsdp_full", "29687"), ("fsdp", "29688")])
 def test_dense_optimizer_state_loads_into_sharded_runs(mode, port, tmp_path):
     from khaosz_b200.trainer import FusedAdamW, StrategyFactory
 
