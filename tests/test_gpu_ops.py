@@ -222,20 +222,26 @@ def test_throughput_callback_times_steps_on_the_device():
 
 def test_adamw_kernel_tracks_fp32_adamw_over_30_steps():
     """The library is compiled with fast-math; the optimizer kernel's divisions, square roots and powers
-    must still follow an fp32 AdamW (parameters rounded to bf16 after every step, as the kernel stores
-    them) over many steps: moments to fp32 accuracy, parameters to a couple of bf16 roundings."""
+    must still follow an AdamW computed in double precision over many steps.  The moments do not depend
+    on the parameters, so they are compared at the end (fp32 accuracy).  bf16 parameters are compared
+    step by step, each step starting from the kernel's own previous parameters: two trajectories that
+    round one tie differently stay apart for good (a bf16 weight whose update is half an ulp stalls on
+    one side of a binade boundary and keeps moving on the other), which says nothing about the kernel."""
     from khaosz_b200.ops._lib import check, lib, ptr, stream
 
     n, steps = 1 << 20, 30
     lr, b1, b2, eps, wd = 3e-4, 0.9, 0.95, 1e-8, 0.01
     g = torch.Generator(device="cuda").manual_seed(11)
     p = (torch.randn(n, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    start = p.clone()
     m = torch.zeros(n, device="cuda")
     v = torch.zeros(n, device="cuda")
-    p_ref, m_ref, v_ref = p.clone(), m.double(), v.double()
+    m_ref, v_ref = m.double(), v.double()
     lr_step = torch.zeros(2, device="cuda")
+    flips = 0
     for t in range(1, steps + 1):
         grad = (torch.randn(n, device="cuda", generator=g) * (1e-3 if t % 3 else 1e-1)).to(torch.bfloat16)
+        before = p.clone()
         lr_step.copy_(torch.tensor([lr, float(t)]))
         check(lib().kb_adamw_bf16(ptr(p), ptr(grad), ptr(m), ptr(v), n, ptr(lr_step), b1, b2, eps, wd, 1.0, None, 0.0,
                                   stream()), "adamw")
@@ -243,14 +249,29 @@ def test_adamw_kernel_tracks_fp32_adamw_over_30_steps():
         m_ref = b1 * m_ref + (1 - b1) * gd
         v_ref = b2 * v_ref + (1 - b2) * gd * gd
         bc1, bc2 = 1 - b1 ** t, 1 - b2 ** t
-        upd = p_ref.double() * (1 - lr * wd) - (lr / bc1) * m_ref / (v_ref.sqrt() / bc2 ** 0.5 + eps)
-        p_ref = upd.to(torch.bfloat16)
+        exact = before.double() * (1 - lr * wd) - (lr / bc1) * m_ref / (v_ref.sqrt() / bc2 ** 0.5 + eps)
+        want = exact.to(torch.bfloat16).float()
+        # the kernel's fp32 result before rounding is within a few fp32 roundings of `exact`, measured at the
+        # size of the terms (old parameter, update): where the two cancel, the result is tiny and its own bf16
+        # step is smaller than that error, which then shows as several steps of a number near zero
+        fp32_error = 2e-6 * (before.double().abs() + lr)
+        cancelled = (p.double() - exact).abs() <= fp32_error
+        # everywhere else the stored value is the correctly rounded one or, at a tie, its neighbour
+        scale = torch.maximum(want.abs(), p.float().abs()).clamp_min(1e-30)
+        ulp = torch.exp2(torch.floor(torch.log2(scale)) - 7)
+        off = (p.float() - want).abs() / ulp
+        bad = (off > 1.0) & ~cancelled
+        if bad.any():
+            i = int(torch.nonzero(bad)[0])
+            raise AssertionError(f"step {t}: {int(bad.sum())} elements off by more than one bf16 step, e.g. before "
+                                 f"{before[i].item()!r} exact {exact[i].item()!r} kernel {p[i].item()!r} grad {grad[i].item()!r}")
+        differs = (off > 0) & ~cancelled
+        flips += int(differs.sum().item())
+        if differs.any():       # a neighbour is only acceptable when the exact value sat at the tie
+            mid = (p.float().double() + want.double()) / 2
+            assert ((exact - mid).abs()[differs] <= fp32_error[differs]).all(), t
     torch.cuda.synchronize()
     assert (m.double() - m_ref).abs().max().item() <= 1e-5 * m_ref.abs().max().item()
     assert (v.double() - v_ref).abs().max().item() <= 1e-5 * v_ref.abs().max().item()
-    ulp = torch.exp2(torch.floor(torch.log2(p_ref.float().abs().clamp_min(1e-30))) - 7)
-    off = (p.float() - p_ref.float()).abs() / ulp
-    assert off.max().item() <= 3.0, off.max().item()                  # never more than a few roundings apart
-    assert (off > 1.0).float().mean().item() < 1e-3                   # and almost everywhere within one
-    moved = (p_ref.float() - (p_ref.float() * 0 + p.float())).abs().max().item()   # sanity: the reference itself moved
-    assert (p_ref.float().abs() > 0).all() and moved >= 0.0
+    assert flips < 1e-4 * n * steps, flips                 # ties are rare
+    assert (p.float() - start.float()).abs().max().item() > 10 * lr       # the parameters did move
