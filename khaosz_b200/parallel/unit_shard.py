@@ -115,15 +115,19 @@ class _Exit(torch.autograd.Function):
 
 
 class ShardedUnits:
-    def __init__(self, model: nn.Module, group=None, prefetch: bool = True):
+    def __init__(self, model: nn.Module, group=None, prefetch: bool = True, frozen: bool = False):
+        """``frozen``: a model that is only evaluated (the frozen copy of DPO / GRPO): no parameter requires a
+        gradient, and neither gradient vectors nor gradient images exist."""
         if not isinstance(getattr(model, "layers", None), (nn.ModuleList, list, tuple)) or len(model.layers) == 0:
             raise NotImplementedError(f"block-granular sharding needs a model with a `layers` list, not {type(model).__name__}")
-        self.model, self.group, self.prefetch = model, group, prefetch
+        self.model, self.group, self.prefetch, self.frozen = model, group, prefetch, frozen
         on = dist.is_available() and dist.is_initialized()
         self.ws = dist.get_world_size(group) if on else 1
         self.rank = dist.get_rank(group) if on else 0
         all_params = _unique(model.parameters())
-        if not all(p.requires_grad for p in all_params):
+        if frozen and any(p.requires_grad for p in all_params):
+            raise ValueError("a frozen sharded copy must not have trainable parameters")
+        if not frozen and not all(p.requires_grad for p in all_params):
             raise NotImplementedError("block-granular sharding trains every parameter (no frozen weights / adapters)")
         dtype, dev = all_params[0].dtype, all_params[0].device
         if any(p.dtype != dtype or p.device != dev for p in all_params):
@@ -172,9 +176,9 @@ class ShardedUnits:
             # the owned pieces live in symmetric memory: peers' copy engines read them when they gather a unit
             self._dbuf = SymmetricBuffer(self.local_numel, dtype, dev, group)
             self.data = self._dbuf.tensor
-            self._gbuf = [SymmetricBuffer(self.image_numel, dtype, dev, group) for _ in range(2)]
+            self._gbuf = [] if frozen else [SymmetricBuffer(self.image_numel, dtype, dev, group) for _ in range(2)]
             self.g_image = [b.tensor for b in self._gbuf]
-            self._ctrl = PeerControl(dev, group)       # its epochs order the side stream's reductions
+            self._ctrl = None if frozen else PeerControl(dev, group)   # its epochs order the side stream's reductions
             self._sync = PeerControl(dev, group)       # barriers on the main stream around the optimizer step
             # two side streams: a gather must never queue behind a reduction (the block after next waits for
             # the gather, nothing waits for the reduction before the image is reused)
@@ -187,9 +191,9 @@ class ShardedUnits:
             self.threads = int(os.environ.get("KHAOSZ_B200_SHARD_THREADS", "256"))
         else:
             self.data = torch.zeros(self.local_numel, dtype=dtype, device=dev)
-            self.g_image = [torch.zeros(self.image_numel, dtype=dtype, device=dev) for _ in range(2)]
+            self.g_image = [] if frozen else [torch.zeros(self.image_numel, dtype=dtype, device=dev) for _ in range(2)]
             self._side = self._copy = None
-        self.grad = torch.zeros(self.local_numel, dtype=dtype, device=dev)
+        self.grad = None if frozen else torch.zeros(self.local_numel, dtype=dtype, device=dev)
         self.w_image = [torch.zeros(self.image_numel, dtype=dtype, device=dev) for _ in range(2)]
         self._content = [-1, -1]          # which unit each weight image holds
         self._ready = [None, None]        # event: the image's last gather has landed
@@ -204,19 +208,21 @@ class ShardedUnits:
                 for p, o in zip(u.params, u.offsets):
                     full[o:o + p.numel()].copy_(p.data.reshape(-1))
                 self.data[u.local:u.local + u.per].copy_(full[lo:lo + u.per])
-                w, g = self.w_image[i % 2], self.g_image[i % 2]
+                w = self.w_image[i % 2]
                 for p, o in zip(u.params, u.offsets):
                     p.data = w[o:o + p.numel()].view(p.shape)
-                    p.main_grad = g[o:o + p.numel()].view(p.shape)
-                    p.grad = p.main_grad
+                    if not frozen:
+                        p.main_grad = self.g_image[i % 2][o:o + p.numel()].view(p.shape)
+                        p.grad = p.main_grad
                 del full
             for p, o in zip(self.rest, self.rest_offsets):
                 lo = self.rest_local + o
                 view = self.data[lo:lo + p.numel()].view(p.shape)
                 view.copy_(p.data)
                 p.data = view
-                p.main_grad = self.grad[lo:lo + p.numel()].view(p.shape)
-                p.grad = p.main_grad
+                if not frozen:
+                    p.main_grad = self.grad[lo:lo + p.numel()].view(p.shape)
+                    p.grad = p.main_grad
         params, offsets = [], []
         where = {id(p): u.base + o for u in self.units for p, o in zip(u.params, u.offsets)}
         where.update({id(p): self.rest_base + o for p, o in zip(self.rest, self.rest_offsets)})
@@ -237,7 +243,7 @@ class ShardedUnits:
             if not args:
                 raise RuntimeError("a sharded block takes its hidden states as the first positional argument")
             x = args[0]
-            if torch.is_grad_enabled() and not x.requires_grad:
+            if torch.is_grad_enabled() and not x.requires_grad and not self.frozen:
                 x = x.detach().requires_grad_()     # the block's backward must reach its input node
             return (_Enter.apply(x, self, i),) + tuple(args[1:]), kwargs
         return hook
@@ -295,7 +301,7 @@ class ShardedUnits:
             self._gather(i)
         if self._sym and self._ready[s] is not None:
             torch.cuda.current_stream().wait_event(self._ready[s])
-        if not forward:
+        if not forward and not self.frozen:
             u = self.units[i]
             if self._sym and self._reduced[s] is not None:
                 torch.cuda.current_stream().wait_event(self._reduced[s])   # the image's previous user has been reduced
@@ -314,6 +320,8 @@ class ShardedUnits:
     def _reduce(self, i: int) -> None:
         """Block ``i``'s backward is complete: mean of its gradient image over the ranks, added to the
         owned gradient piece."""
+        if self.frozen:         # gradients flow through a frozen copy, none is kept
+            return
         u, s = self.units[i], i % 2
         mine = self.grad[u.local:u.local + u.per]
         lo = self.rank * u.per
@@ -343,6 +351,8 @@ class ShardedUnits:
     def finish_backward(self) -> None:
         """Called once per optimizer step before the update: the side stream's reductions have to be
         complete, and the replicated parameters' gradients are averaged."""
+        if self.frozen:
+            return
         if self._sym:
             for ev in self._reduced:
                 if ev is not None:

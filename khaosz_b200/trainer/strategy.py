@@ -30,10 +30,13 @@ def move_to_device(batch: Dict[str, Tensor], device) -> Dict[str, Tensor]:
     return {k: v.to(device, non_blocking=True) if torch.is_tensor(v) else v for k, v in batch.items()}
 
 
-def create_ref_model(model_fn: Callable[[], nn.Module], state_dict: dict, like: nn.Module = None) -> nn.Module:
+def create_ref_model(model_fn: Callable[[], nn.Module], state_dict: dict, like: nn.Module = None,
+                     shard_like=None) -> nn.Module:
     """Frozen copy of the policy built from ``model_fn`` and a full state dict.  When the policy is
     sliced (tensor parallel) or sharded (fully sharded) the copy is cut the same way, so it costs
-    ``1 / world`` of the memory and runs through the same fused GEMM + collective kernels."""
+    ``1 / world`` of the memory and runs through the same fused GEMM + collective kernels.
+    ``shard_like``: the ``ShardedUnits`` of a policy that is sharded block by block; the copy's blocks are
+    then sharded over the same group and gathered block by block when it is evaluated."""
     ref = model_fn()
     if like is not None:
         p = next(like.parameters())
@@ -49,6 +52,11 @@ def create_ref_model(model_fn: Callable[[], nn.Module], state_dict: dict, like: 
             ref = full_shard(ref, like.info.group)
     ref.requires_grad_(False)
     ref.eval()
+    if shard_like is not None:
+        from ..parallel.unit_shard import ShardedUnits
+
+        ref.sharded_units = ShardedUnits(ref, group=shard_like.group, prefetch=shard_like.prefetch, frozen=True)
+        return ref
     if like is not None and next(ref.parameters()).is_cuda and hasattr(ref, "pack_parameters"):
         ref.pack_parameters(with_grad=False)
     return ref
@@ -98,7 +106,8 @@ class BaseStrategy(ABC):
 
     def _make_ref(self) -> nn.Module:
         state = self.executor.unwrap_model(self.model) if self.executor is not None else self.model.state_dict()
-        return create_ref_model(self.model_fn, state, like=self.model)
+        return create_ref_model(self.model_fn, state, like=self.model,
+                                shard_like=getattr(self.executor, "units", None))
 
 
 class StrategyFactory(BaseFactory[BaseStrategy]):
@@ -179,7 +188,9 @@ class GRPOStrategy(BaseStrategy):
 
     def sync_ref_model(self) -> None:
         state = self.executor.unwrap_model(self.model) if self.executor is not None else self.model.state_dict()
-        if hasattr(self.ref_model, "scatter_named"):     # sliced / sharded copy: every rank takes its own pieces
+        if getattr(self.ref_model, "sharded_units", None) is not None:   # sharded block by block
+            self.ref_model.sharded_units.load_full_state_dict(state)
+        elif hasattr(self.ref_model, "scatter_named"):     # sliced / sharded copy: every rank takes its own pieces
             pieces = self.ref_model.scatter_named(state)
             with torch.no_grad():
                 for p in self.ref_model.parameters():

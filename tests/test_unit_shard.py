@@ -128,3 +128,55 @@ def test_rejects_what_it_cannot_shard():
     with pytest.raises(NotImplementedError):
         ExecutorFactory.create("fsdp_block").prepare(model, torch.optim.SGD(model.parameters(), lr=0.1), None, None)
     assert FusedAdamW is not None
+
+
+# ---- DPO / GRPO: the frozen copy is sharded block by block like the policy ----
+def _preference_case():
+    from khaosz_b200.trainer import FusedAdamW, StrategyFactory
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+
+    def run(mode):
+        model = _model(layers=3)
+        ex = ExecutorFactory.create(mode, grad_accum_steps=1)
+        opt = FusedAdamW(model.parameters(), lr=1e-3)
+        model, opt, _, _ = ex.prepare(model, opt, None, None)
+        dpo = StrategyFactory.create("dpo", model, "cpu", executor=ex, model_fn=lambda: _model(layers=3), beta=0.1)
+        g = torch.Generator().manual_seed(5 + rank)
+        losses = []
+        for _ in range(3):
+            batch = {"chosen": torch.randint(0, 300, (2, 24), generator=g), "rejected": torch.randint(0, 300, (2, 24), generator=g),
+                     "chosen_mask": torch.ones(2, 24, dtype=torch.bool), "rejected_mask": torch.ones(2, 24, dtype=torch.bool)}
+            with ex.accumulate(model):
+                losses.append(ex.micro_step(dpo, batch).item())
+                opt.step()
+                opt.zero_grad()
+        return model, ex, dpo, losses
+
+    _, ref_ex, ref_dpo, ref_losses = run("ddp")
+    model, ex, dpo, losses = run("fsdp_block")
+    assert losses == pytest.approx(ref_losses, rel=1e-4, abs=1e-5)
+    assert losses[0] == pytest.approx(0.6931, abs=2e-3)           # policy == frozen copy before the first update
+    assert getattr(ref_dpo.ref_model, "sharded_units", None) is None
+    units = dpo.ref_model.sharded_units
+    assert units.frozen and units.grad is None and not units.g_image
+    assert units.data.numel() == sum(u.numel for u in units.units) // world + units.rest_numel
+    assert not any(p.requires_grad for p in dpo.ref_model.parameters())
+
+    # GRPO refreshes its old-policy copy from the (sharded) policy: every rank takes its pieces
+    grpo = StrategyFactory.create("grpo", model, "cpu", executor=ex, model_fn=lambda: _model(layers=3), group_size=4,
+                                  sync_interval=1)
+    before = grpo.ref_model.sharded_units.data.clone()
+    with torch.no_grad():
+        ex.units.data.add_(0.01)                                  # the policy moves on
+        ex.units.invalidate()
+    grpo.sync_ref_model()
+    assert torch.allclose(grpo.ref_model.sharded_units.data, before + 0.01, atol=1e-6)
+    ids = torch.randint(0, 300, (2, 12), generator=torch.Generator().manual_seed(2))
+    with torch.no_grad():
+        assert torch.allclose(grpo.ref_model(ids)["logits"], model(ids)["logits"], rtol=1e-4, atol=1e-5)
+    dist.barrier()
+
+
+def test_frozen_copy_of_dpo_and_grpo_is_sharded_like_the_policy():
+    spawn_parallel_fn(_preference_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29745")
