@@ -17,8 +17,8 @@ The model keeps its modules, names and kernels; what changes is where its parame
 * when a block's backward has finished, its gradient image is reduce-scattered by a kernel on the
   side stream (peer loads, or one ``multimem.ld_reduce`` through the switch), scaled by ``1 / ws``
   and added to the owned gradient piece; the same kernel clears the image, which is reused two
-  blocks later.  Nothing waits for it before then, so it runs as a few light CTAs beside the block
-  that is computing;
+  blocks later.  Gathers and reductions have a stream each, so that a gather never queues behind a
+  reduction;
 * parameters outside the blocks (embedding, final norm, an untied output layer) stay replicated;
   their gradients take one all-reduce per optimizer step.
 
@@ -260,7 +260,6 @@ class ShardedUnits:
         """Unit ``i`` into weight image ``i % 2`` (asynchronously on the copy stream on CUDA)."""
         u, s = self.units[i], i % 2
         mine = self.data[u.local:u.local + u.per]
-        lo = self.rank * u.per
         self.gathers += 1
         from ..ops.functional import bump_weight_generation, fp8_linear_enabled
 
