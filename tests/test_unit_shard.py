@@ -180,3 +180,25 @@ def _preference_case():
 
 def test_frozen_copy_of_dpo_and_grpo_is_sharded_like_the_policy():
     spawn_parallel_fn(_preference_case, world_size=2, backend="gloo", master_addr="127.0.0.1", master_port="29745")
+
+
+def test_fsdp_falls_back_to_resident_parameters_where_it_cannot_shard(caplog):
+    from khaosz_b200.trainer import FusedAdamW
+
+    model = _model(layers=2)
+    next(model.layers[0].parameters()).requires_grad_(False)          # e.g. a base weight under LoRA
+    ex = ExecutorFactory.create("fsdp")
+    opt = FusedAdamW([p for p in model.parameters() if p.requires_grad], lr=1e-3)
+    with caplog.at_level("WARNING"):
+        ex.prepare(model, opt, None, None)
+    assert ex.units is None and "frozen parameters" in caplog.text
+    # asked for explicitly: no warning, no sharding
+    model = _model(layers=2)
+    ex = ExecutorFactory.create("fsdp", shard_parameters=False)
+    ex.prepare(model, FusedAdamW(model.parameters(), lr=1e-3), None, None)
+    assert ex.units is None
+    # and the default shards
+    model = _model(layers=2)
+    ex = ExecutorFactory.create("fsdp")
+    ex.prepare(model, FusedAdamW(model.parameters(), lr=1e-3), None, None)
+    assert ex.units is not None and ex.flat is ex.units.flat
