@@ -202,3 +202,26 @@ def test_fsdp_falls_back_to_resident_parameters_where_it_cannot_shard(caplog):
     ex = ExecutorFactory.create("fsdp")
     ex.prepare(model, FusedAdamW(model.parameters(), lr=1e-3), None, None)
     assert ex.units is not None and ex.flat is ex.units.flat
+
+
+@pytest.mark.parametrize("prefetch", [True, False])
+def test_two_forward_passes_before_one_backward(prefetch):
+    """The images are re-gathered on demand in whatever order autograd visits the blocks: two forward
+    passes, then one backward pass through both graphs, give the dense gradients."""
+    from khaosz_b200.parallel.unit_shard import ShardedUnits
+
+    dense, sharded = _model(layers=4), _model(layers=4)
+    units = ShardedUnits(sharded, prefetch=prefetch)
+    g = torch.Generator().manual_seed(9)
+    a, b = torch.randint(0, 300, (2, 20), generator=g), torch.randint(0, 300, (2, 20), generator=g)
+    (dense(a)["logits"].float().pow(2).mean() + dense(b)["logits"].float().pow(2).mean()).backward()
+    (sharded(a)["logits"].float().pow(2).mean() + sharded(b)["logits"].float().pow(2).mean()).backward()
+    units.finish_backward()
+    grads = {}
+    for u in units.units:      # one process owns every piece whole
+        for p, o in zip(u.params, u.offsets):
+            grads[id(p)] = units.grad[u.local + o:u.local + o + p.numel()].view(p.shape)
+    for (name, pd), ps in zip(dense.named_parameters(), sharded.parameters()):
+        got = grads.get(id(ps), ps.grad)
+        assert torch.allclose(got, pd.grad, rtol=1e-4, atol=1e-6), name
+    assert units.reductions == 2 * 4
