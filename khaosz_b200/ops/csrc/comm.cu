@@ -8,6 +8,11 @@
 //                        updates it, and pushes the new values into every peer's parameter
 //                        buffer (peer stores or multimem.st).
 //   kb_allreduce_bf16    stand-alone sum all-reduce (reduce own slice, write it everywhere).
+//   kb_reducescatter_bf16 / kb_allgather_bf16 / kb_broadcast_bf16
+//                        stand-alone collectives over one symmetric buffer.
+//   kb_unit_reduce_bf16  block-granular full sharding: reduce-scatter of the ranks' gradient images
+//                        with the accumulation into the owned piece and the clearing of the image
+//                        in the same kernel (the matching gather is a copy-engine pull, no kernel).
 //   kb_peer_barrier      stand-alone barrier (also the unit test of the bounded wait).
 //
 // Synchronisation: a control buffer of epoch counters, one row of `ws` words per CTA slot.
