@@ -93,12 +93,19 @@ def _use_done(w) -> None:
             _GRAD_READY_HOOK(w)
 
 
-def set_fp8_linear(enabled: bool) -> None:
+_FP8_DGRAD = False
+
+
+def set_fp8_linear(enabled: bool, dgrad: bool = False) -> None:
     """Run the forward GEMM of every bf16 linear layer in block-scaled fp8 (e4m3; 1x128
     activation scales, 128x128 weight scales, quantised on the fly from the bf16 master
-    weights).  Input and weight gradients stay bf16 GEMMs."""
-    global _FP8_FORWARD
+    weights).  With ``dgrad`` the input-gradient GEMM runs in fp8 as well (the output gradient with
+    1x128 scales along the output features, the transposed weight with 128x128 scales, cached per
+    optimizer step like the forward image); weight gradients stay bf16 GEMMs into the fp32-accurate
+    accumulation of the flat gradient buffer."""
+    global _FP8_FORWARD, _FP8_DGRAD
     _FP8_FORWARD = bool(enabled)
+    _FP8_DGRAD = bool(enabled) and bool(dgrad)
 
 
 def fp8_linear_enabled() -> bool:
@@ -127,6 +134,36 @@ def _fp8_weight(w: torch.Tensor):
     b8, sb = quantize_fp8_128x128(w)
     _FP8_WEIGHT_CACHE[key] = (_WEIGHT_GENERATION, b8, sb)
     return b8, sb
+
+
+def _fp8_weight_t(w: torch.Tensor):
+    """fp8 image of ``w.T`` (``[in, out]``, 128x128 scales) for the input-gradient GEMM."""
+    from .quant import quantize_fp8_128x128
+
+    key = (w.data_ptr(), tuple(w.shape), "t")
+    hit = _FP8_WEIGHT_CACHE.get(key)
+    if hit is not None and hit[0] == _WEIGHT_GENERATION:
+        return hit[1], hit[2]
+    b8, sb = quantize_fp8_128x128(w.t().contiguous())
+    _FP8_WEIGHT_CACHE[key] = (_WEIGHT_GENERATION, b8, sb)
+    return b8, sb
+
+
+def dgrad_fp8(dy2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``dy2 [M, out] @ w [out, in]`` in block-scaled fp8 -> bf16 ``[M, in]``."""
+    from .quant import gemm_fp8, quantize_fp8_1x128
+
+    d8, sd = quantize_fp8_1x128(dy2)
+    w8, sw = _fp8_weight_t(w)
+    return gemm_fp8(d8, sd, w8, sw)
+
+
+def _dgrad(dy2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Input gradient ``dy2 @ w`` of a linear layer with weight ``w [out, in]``."""
+    if (_FP8_DGRAD and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0 and dy2.dtype == torch.bfloat16
+            and _lib.has("kb_gemm_fp8")):
+        return dgrad_fp8(dy2, w)
+    return gemm(dy2, w, b_mn=True)
 
 
 def _forward_gemm(x2: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -162,7 +199,7 @@ class _LinearFn(torch.autograd.Function):
         dy2 = _as2d(dy)
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)
+            dx = _dgrad(dy2, w).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             main = getattr(ctx.w_ref, "main_grad", None)
             if main is not None:
@@ -224,7 +261,7 @@ class _MultiLinearFn(torch.autograd.Function):
     def backward(ctx, dy):
         x2, wcat = ctx.saved_tensors
         dy2 = _as2d(dy)
-        dx = gemm(dy2, wcat, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dx = _dgrad(dy2, wcat).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
         mains = [getattr(w, "main_grad", None) for w in ctx.ws]
         need = [ctx.needs_input_grad[i + 1] for i in range(len(ctx.ws))]
         grads = [None] * len(ctx.ws)

@@ -268,10 +268,11 @@ class BaseExecutor:
         self.fp8 = bool(fp8)
         self._graphed = _GraphedMicroStep(self) if cuda_graph and torch.cuda.is_available() else None
         if self.fp8:
-            # forward GEMMs of the local linear layers in block-scaled fp8 (bf16 master weights)
+            # forward GEMMs of the local linear layers in block-scaled fp8 (bf16 master weights); fp8="dgrad"
+            # (or KHAOSZ_B200_FP8_DGRAD=1) runs the input-gradient GEMMs in fp8 as well
             from ..ops.functional import set_fp8_linear
 
-            set_fp8_linear(True)
+            set_fp8_linear(True, dgrad=fp8 == "dgrad" or os.environ.get("KHAOSZ_B200_FP8_DGRAD", "0") == "1")
 
     # -- preparation ------------------------------------------------------------------------
     def prepare(self, model: nn.Module, optimizer=None, dataloader=None, scheduler=None) -> Tuple[Any, Any, Any, Any]:

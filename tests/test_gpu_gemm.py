@@ -226,3 +226,46 @@ def test_fp8_linear_autograd_and_throughput():
     torch.cuda.synchronize()
     print(f"fp8 block-scaled GEMM {M}x{N}x{K}: {2 * M * N * K / (e0.elapsed_time(e1) / 10) / 1e9:.0f} TFLOP/s")
     ops.raise_on_device_error()
+
+
+def test_fp8_input_gradient_of_the_linear_layers():
+    """``set_fp8_linear(True, dgrad=True)``: the input gradient of ``ops.linear`` / ``ops.multi_linear`` runs as a
+    block-scaled fp8 GEMM over the output gradient and the cached transposed weight image; it must agree with
+    the fp32 product to fp8 accuracy, the weight gradient stays the bf16 GEMM, and the cache must follow the
+    optimizer's weight generations."""
+    from khaosz_b200.ops import functional as Fn
+
+    M, K, N = 512, 1024, 768
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    Fn.set_fp8_linear(True, dgrad=True)
+    try:
+        y = ops.linear(x, w)
+        y.backward(dy)
+        dx_ref = dy.float() @ w.detach().float()
+        dw_ref = dy.float().t() @ x.detach().float()
+        assert (x.grad.float() - dx_ref).abs().mean().item() <= 0.06 * dx_ref.abs().mean().item() + 1e-3
+        assert (w.grad.float() - dw_ref).abs().mean().item() <= 0.01 * dw_ref.abs().mean().item() + 1e-3
+        # the kernel product equals the product of the dequantised operands (the GEMM itself is exact to fp32)
+        d8, sd = quant_mod().quantize_fp8_1x128(dy)
+        w8, sw = Fn._fp8_weight_t(w.detach())
+        oracle = quant_mod().dequantize_fp8(d8, sd, False) @ quant_mod().dequantize_fp8(w8, sw, True).t()
+        assert (x.grad.float() - oracle).abs().max().item() <= 2e-2 * oracle.abs().max().item()
+        # a new weight generation re-quantises the transposed image
+        with torch.no_grad():
+            w.mul_(2.0)
+        Fn.bump_weight_generation()
+        x.grad = None
+        ops.linear(x, w).backward(dy)
+        assert (x.grad.float() - 2 * dx_ref).abs().mean().item() <= 0.06 * (2 * dx_ref).abs().mean().item() + 1e-3
+    finally:
+        Fn.set_fp8_linear(False)
+    ops.raise_on_device_error()
+
+
+def quant_mod():
+    from khaosz_b200.ops import quant
+
+    return quant

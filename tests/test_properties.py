@@ -156,3 +156,29 @@ def test_filters_keep_the_argmax_and_only_remove(values, k, p):
     top = TopKStrategy(k).apply(logits.clone())
     if 0 < k < len(values):
         assert int((~torch.isinf(top)).sum()) >= k                        # ties may keep more, never fewer
+
+
+def test_fp8_quantisers_and_input_gradient_oracle_on_cpu():
+    """The CPU forms of the block-scaled fp8 quantisers are the oracles of the GPU kernels: the input gradient
+    built from them (output gradient with 1x128 scales, transposed weight with 128x128 scales) reproduces the
+    fp32 product to fp8 accuracy, and the transposed weight image is cached per weight generation."""
+    import torch
+
+    from khaosz_b200.ops import functional as Fn
+    from khaosz_b200.ops import quant
+
+    torch.manual_seed(0)
+    M, K, N = 256, 512, 384
+    dy = torch.randn(M, N).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    ref = dy.float() @ w.float()
+    dx = Fn.dgrad_fp8(dy, w)
+    assert dx.shape == (M, K) and dx.dtype == torch.bfloat16
+    assert (dx.float() - ref).abs().mean().item() <= 0.06 * ref.abs().mean().item()
+    w8, sw = Fn._fp8_weight_t(w)
+    assert w8.shape == (K, N) and sw.shape == (K // 128, N // 128)
+    assert Fn._fp8_weight_t(w)[0] is w8                       # cached ...
+    Fn.bump_weight_generation()
+    assert Fn._fp8_weight_t(w)[0] is not w8                   # ... for one weight generation
+    back = quant.dequantize_fp8(w8, sw, True)
+    assert (back - w.float().t()).abs().max().item() <= 0.07 * w.float().abs().max().item()
