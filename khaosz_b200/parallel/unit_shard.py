@@ -434,6 +434,8 @@ class ShardedUnits:
         missing = [k for k, p in names.items() if id(p) not in have]     # a tied weight may come under either name
         if strict and missing:
             raise KeyError(f"missing parameters: {missing[:4]}")
+        if self._sym:
+            self._sync.barrier()      # no peer is still gathering the pieces that are about to change
         for k, p in names.items():
             if k not in state:
                 continue
