@@ -7,12 +7,14 @@ import torch.distributed as dist
 from khaosz_b200.parallel import ExecutorFactory, spawn_parallel_fn
 
 
-def _model(layers=5, moe=False, tie=True, seed=11):
+def _model(layers=5, moe=False, tie=True, seed=11, mla=False):
     from khaosz_b200 import AutoRegressiveLM, AutoRegressiveLMConfig
 
     ffn = dict(ffn_type="moe", n_routed_experts=4, n_shared_experts=1, n_activated_experts=2) if moe else {}
+    att = dict(attn_type="mla", kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=8, use_qk_norm=True,
+               use_gated_attention=True) if mla else {}
     cfg = AutoRegressiveLMConfig(vocab_size=300, dim=64, n_layers=layers, norm_eps=1e-5, dim_ffn=96, tie_weight=tie,
-                                 max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, **ffn)
+                                 max_len=64, rope_theta=1e4, n_heads=4, n_kv_heads=2, **ffn, **att)
     torch.manual_seed(seed)
     m = AutoRegressiveLM(cfg)
     with torch.no_grad():
@@ -66,9 +68,9 @@ def test_one_process_equals_the_dense_run():
     assert ex.units.gathers > 2 * 5 and ex.units.reductions == 3 * 2 * 5
 
 
-def _ranks_case(out, moe=False, recompute=False, tie=True):
+def _ranks_case(out, moe=False, recompute=False, tie=True, mla=False):
     rank, world = dist.get_rank(), dist.get_world_size()
-    kw = dict(moe=moe, tie=tie)
+    kw = dict(moe=moe, tie=tie, mla=mla)
     ref_model, ref_ex, ref_opt, ref_losses = _train("ddp", rank, world, **kw)
     model, ex, opt, losses = _train("fsdp_block", rank, world, recompute=recompute, **kw)
     assert losses == pytest.approx(ref_losses, rel=1e-4, abs=1e-5)
@@ -111,7 +113,7 @@ def _ranks_case(out, moe=False, recompute=False, tie=True):
 
 
 @pytest.mark.parametrize("world,port,kw", [(2, "29741", {}), (4, "29742", {"tie": False}), (2, "29743", {"moe": True}),
-                                           (2, "29744", {"recompute": True})])
+                                           (2, "29744", {"recompute": True}), (2, "29746", {"mla": True})])
 def test_ranks_match_data_parallel(world, port, kw, tmp_path):
     spawn_parallel_fn(_ranks_case, world_size=world, backend="gloo", master_addr="127.0.0.1", master_port=port,
                       out=str(tmp_path / "s.pt"), **kw)
