@@ -391,13 +391,24 @@ class KvcacheView:
                 return attn_ops.attention(q, k, v, causal=True)
             kk, vv = self._storage.gather(layer_id, self._page_table, total)
             return attn_ops.attention(q, kk, vv, causal=True)
-        # ragged fallback: dense gather + explicit mask
+        if T > 1:
+            # ragged multi-token step: every sequence attends with its last T positions to its own cached
+            # length.  One rectangular causal attention per sequence over that sequence's pages (the flash
+            # kernel for bf16 on CUDA) instead of one padded batch with an explicit mask
+            if getattr(self, "_lens_host", None) is None:
+                self._lens_host = [int(n) for n in self._seq_lens.tolist()]     # one read per step, not per layer
+            outs = []
+            for b, total in enumerate(self._lens_host):
+                kk, vv = self._storage.gather(layer_id, self._page_table[b:b + 1], total)
+                outs.append(attn_ops.attention(q[b:b + 1], kk, vv, causal=True))
+            return torch.cat(outs, dim=0)
+        # single-token step where the decode kernel does not apply (CPU, fp32, unusual head sizes): one padded
+        # batch with an explicit mask
         lens = self._seq_lens.long()
         total = int(lens.max())
         kk, vv = self._storage.gather(layer_id, self._page_table, total)
-        qpos = lens.unsqueeze(1) - T + torch.arange(T, device=q.device).unsqueeze(0)  # [B,T]
-        keep = torch.arange(total, device=q.device).view(1, 1, total) <= qpos.unsqueeze(-1)
-        mask = torch.zeros(B, 1, T, total, dtype=q.dtype, device=q.device).masked_fill_(
+        keep = torch.arange(total, device=q.device).view(1, 1, total) < lens.view(B, 1, 1)
+        mask = torch.zeros(B, 1, 1, total, dtype=q.dtype, device=q.device).masked_fill_(
             ~keep.unsqueeze(1), -torch.finfo(q.dtype).max / 2)
         return attn_ops.attention(q, kk, vv, causal=False, mask=mask)
 

@@ -102,6 +102,18 @@ def test_paged_forward_matches_dense_forward():
             pos = torch.full((2, 1), t)
             step = model(ids[:, t:t + 1], paged_cache=kv.bind(table, seq_lens=pos.squeeze(1) + 1), position_ids=pos)
             assert torch.allclose(step["logits"][:, 0], dense[:, t], atol=1e-4)
+        # ragged multi-token step: sequence a has 5 cached positions, sequence b has 8; both add 3 tokens
+        kv3 = KVCache(2, 16, 4, 2, 8, "cpu", torch.float32)
+        for name in ("a", "b"):
+            kv3.task_alloc(name, list(range(12)))
+        ta, tb3 = kv3.make_table_tensor(["a"], "cpu"), kv3.make_table_tensor(["b"], "cpu")
+        model(ids[:1, :5], paged_cache=kv3.bind(ta, total_len=5))
+        model(ids[1:, :8], paged_cache=kv3.bind(tb3, total_len=8))
+        both = kv3.make_table_tensor(["a", "b"], "cpu")
+        new_ids = torch.stack([ids[0, 5:8], ids[1, 8:11]])
+        pos = torch.stack([torch.arange(5, 8), torch.arange(8, 11)])
+        rag = model(new_ids, paged_cache=kv3.bind(both, seq_lens=torch.tensor([8, 11])), position_ids=pos)["logits"]
+        assert torch.allclose(rag[0], dense[0, 5:8], atol=1e-4) and torch.allclose(rag[1], dense[1, 8:11], atol=1e-4)
         # chunked prefill with a cached prefix (dense mode, start > 0)
         kv2 = KVCache(2, 16, 4, 2, 8, "cpu", torch.float32)
         kv2.task_alloc("a", list(range(12)))
