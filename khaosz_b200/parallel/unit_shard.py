@@ -211,9 +211,9 @@ class ShardedUnits:
                 w = self.w_image[i % 2]
                 for p, o in zip(u.params, u.offsets):
                     p.data = w[o:o + p.numel()].view(p.shape)
+                    p.grad = None
                     if not frozen:
                         p.main_grad = self.g_image[i % 2][o:o + p.numel()].view(p.shape)
-                        p.grad = p.main_grad
                 del full
             for p, o in zip(self.rest, self.rest_offsets):
                 lo = self.rest_local + o
@@ -346,6 +346,10 @@ class ShardedUnits:
                 if self.ws > 1:
                     dist.all_reduce(g[:u.numel], group=self.group)
                 mine.add_(g[lo:lo + u.per] / self.ws)
+        # the image now belongs to the block after next: outside its own backward pass a block's parameters
+        # carry no ``.grad`` (per-parameter gradient statistics then skip them instead of reading an image)
+        for p in u.params:
+            p.grad = None
 
     def finish_backward(self) -> None:
         """Called once per optimizer step before the update: the side stream's reductions have to be

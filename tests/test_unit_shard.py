@@ -66,6 +66,9 @@ def test_one_process_equals_the_dense_run():
         assert torch.allclose(a["state"][i]["exp_avg"], b["state"][i]["exp_avg"], rtol=1e-5, atol=1e-8), i
     # five blocks went through two images: every backward re-gathered what the forward had displaced
     assert ex.units.gathers > 2 * 5 and ex.units.reductions == 3 * 2 * 5
+    # outside its backward pass a block's parameters carry no gradient tensor; the replicated ones keep theirs
+    assert all(p.grad is None for u in ex.units.units for p in u.params)
+    assert all(p.grad is not None for p in ex.units.rest)
 
 
 def _ranks_case(out, moe=False, recompute=False, tie=True, mla=False):
