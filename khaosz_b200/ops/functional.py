@@ -115,6 +115,8 @@ def fp8_linear_enabled() -> bool:
 # fp8 images of the bf16 master weights, valid for one weight generation: the optimizers update the
 # weights in place through raw pointers (no autograd version bump), so they announce every update here
 # and the 128x128-block quantisation of a weight runs once per optimizer step, not once per micro-batch.
+# An entry is found by the weight's address and shape and keeps the weight alive, so that within one
+# generation the address cannot be handed to another tensor; a new generation drops every entry.
 _WEIGHT_GENERATION = 0
 _FP8_WEIGHT_CACHE: dict = {}
 
@@ -122,17 +124,18 @@ _FP8_WEIGHT_CACHE: dict = {}
 def bump_weight_generation() -> None:
     global _WEIGHT_GENERATION
     _WEIGHT_GENERATION += 1
+    _FP8_WEIGHT_CACHE.clear()
 
 
 def _fp8_weight(w: torch.Tensor):
     from .quant import quantize_fp8_128x128
 
-    key = (w.data_ptr(), tuple(w.shape))
+    key = (w.data_ptr(), tuple(w.shape), tuple(w.stride()))
     hit = _FP8_WEIGHT_CACHE.get(key)
     if hit is not None and hit[0] == _WEIGHT_GENERATION:
         return hit[1], hit[2]
     b8, sb = quantize_fp8_128x128(w)
-    _FP8_WEIGHT_CACHE[key] = (_WEIGHT_GENERATION, b8, sb)
+    _FP8_WEIGHT_CACHE[key] = (_WEIGHT_GENERATION, b8, sb, w)
     return b8, sb
 
 
@@ -140,12 +143,12 @@ def _fp8_weight_t(w: torch.Tensor):
     """fp8 image of ``w.T`` (``[in, out]``, 128x128 scales) for the input-gradient GEMM."""
     from .quant import quantize_fp8_128x128
 
-    key = (w.data_ptr(), tuple(w.shape), "t")
+    key = (w.data_ptr(), tuple(w.shape), tuple(w.stride()), "t")
     hit = _FP8_WEIGHT_CACHE.get(key)
     if hit is not None and hit[0] == _WEIGHT_GENERATION:
         return hit[1], hit[2]
     b8, sb = quantize_fp8_128x128(w.t().contiguous())
-    _FP8_WEIGHT_CACHE[key] = (_WEIGHT_GENERATION, b8, sb)
+    _FP8_WEIGHT_CACHE[key] = (_WEIGHT_GENERATION, b8, sb, w)
     return b8, sb
 
 

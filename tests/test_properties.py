@@ -182,3 +182,22 @@ def test_fp8_quantisers_and_input_gradient_oracle_on_cpu():
     assert Fn._fp8_weight_t(w)[0] is not w8                   # ... for one weight generation
     back = quant.dequantize_fp8(w8, sw, True)
     assert (back - w.float().t()).abs().max().item() <= 0.07 * w.float().abs().max().item()
+
+
+def test_fp8_weight_cache_is_not_fooled_by_a_reused_address():
+    """The fp8 weight images are found by address; an entry keeps its weight alive, so a tensor that is freed
+    within a weight generation cannot hand its address (and its stale image) to the next weight."""
+    import torch
+
+    from khaosz_b200.ops import functional as Fn
+    from khaosz_b200.ops import quant
+
+    torch.manual_seed(1)
+    for _ in range(4):                       # allocate / free the same size repeatedly: the allocator reuses blocks
+        w = (torch.randn(256, 256) * torch.rand(()).item()).to(torch.bfloat16)
+        for cached, fresh in ((Fn._fp8_weight(w), quant.quantize_fp8_128x128(w)),
+                              (Fn._fp8_weight_t(w), quant.quantize_fp8_128x128(w.t().contiguous()))):
+            assert torch.equal(cached[0], fresh[0]) and torch.equal(cached[1], fresh[1])
+        del w
+    Fn.bump_weight_generation()
+    assert not Fn._FP8_WEIGHT_CACHE
