@@ -230,3 +230,25 @@ def test_two_forward_passes_before_one_backward(prefetch):
         got = grads.get(id(ps), ps.grad)
         assert torch.allclose(got, pd.grad, rtol=1e-4, atol=1e-6), name
     assert units.reductions == 2 * 4
+
+
+def test_unit_layout_properties():
+    """Offsets are 16-byte aligned and disjoint, the unit length divides by ``8 * ws`` for every world size, and
+    the pieces of all ranks tile the unit exactly."""
+    import random
+
+    import torch.nn as nn
+
+    from khaosz_b200.parallel.unit_shard import _Unit
+
+    rng = random.Random(0)
+    for _ in range(50):
+        ws = rng.choice([1, 2, 3, 4, 8])
+        params = [nn.Parameter(torch.empty(rng.randint(1, 9), rng.randint(1, 37))) for _ in range(rng.randint(1, 7))]
+        u = _Unit(params, ws)
+        end = 0
+        for p, o in zip(u.params, u.offsets):
+            assert o % 8 == 0 and o >= end
+            end = o + p.numel()
+        assert u.numel >= end and u.numel % (8 * ws) == 0 and u.numel - end < 8 * ws + 8
+        assert u.per * ws == u.numel and u.per % 8 == 0
